@@ -1,0 +1,99 @@
+"""Device memory of the cache and its grouping.
+
+Layers whose mixers ask for the same kind of paged memory (KV head count, head size,
+window) form a group.  A group has pages of its own: one page number addresses the same
+page in every layer of the group, as one block addresses every layer in the reference
+(crates/vipera-backend-cpu/src/model.rs:63-70, crates/vipera-runtime/src/pipeline.rs:128-129).
+Inside a group the memory is [slot in group][k or v][page][position in page][kv head][d],
+the reference's layer-major order lifted to the pool (model.rs:1451-1469), so that each
+layer's keys are one dense [pages * page_size, kv_heads * d] matrix.
+
+Mixers that keep a fixed-size state get one tensor [state slots, *shape] per cache slot.
+The bookkeeping (which request holds which page and which state slot) is the native
+``CacheManager``; this module owns only the memory.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..build import runtime_module
+from ..errors import InvalidArgumentError
+from ..parts.base import FixedState, PagedKV, PagedKVView, StateView
+
+
+@dataclass
+class CacheGroup:
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int]
+    slots: List[int] = field(default_factory=list)  # cache slots (of the schedule) in this group
+
+    def bytes_per_token(self, element_bytes: int) -> int:
+        return 2 * len(self.slots) * self.num_kv_heads * self.head_dim * element_bytes
+
+
+def plan_groups(cache_requests: Dict[int, object]) -> Tuple[List[CacheGroup], Dict[int, FixedState]]:
+    """Sort the cache slots of a model into paged groups and fixed-state slots."""
+    groups: Dict[Tuple[int, int, Optional[int]], CacheGroup] = {}
+    states: Dict[int, FixedState] = {}
+    for slot in sorted(cache_requests):
+        request = cache_requests[slot]
+        if request is None:
+            continue
+        if isinstance(request, PagedKV):
+            key = (request.num_kv_heads, request.head_dim, request.window)
+            if key not in groups:
+                groups[key] = CacheGroup(*key)
+            groups[key].slots.append(slot)
+        elif isinstance(request, FixedState):
+            states[slot] = request
+        else:
+            raise InvalidArgumentError(f"cache slot {slot}: unknown kind of cache request {request!r}")
+    return list(groups.values()), states
+
+
+class CachePools:
+    """Allocates the pools and the native manager for one engine."""
+
+    def __init__(self, cache_requests: Dict[int, object], *, page_size: int, num_pages, num_state_slots: int,
+                 dtype: torch.dtype, device):
+        self.groups, self.states = plan_groups(cache_requests)
+        self.page_size = int(page_size)
+        self.dtype = dtype
+        self.device = device
+        if isinstance(num_pages, int):
+            num_pages = [num_pages] * len(self.groups)
+        if len(num_pages) != len(self.groups):
+            raise InvalidArgumentError("one page count is needed for each group of layers")
+        self.num_pages = [int(n) for n in num_pages]
+        runtime = runtime_module()
+        self.manager = runtime.CacheManager(
+            [(self.page_size, pages, group.window or 0) for group, pages in zip(self.groups, self.num_pages)],
+            int(num_state_slots))
+        self.pool_tensors: List[torch.Tensor] = []
+        self.views: Dict[int, object] = {}
+        for index, (group, pages) in enumerate(zip(self.groups, self.num_pages)):
+            pool = torch.zeros((len(group.slots), 2, pages, self.page_size, group.num_kv_heads, group.head_dim),
+                               dtype=dtype, device=device)
+            self.pool_tensors.append(pool)
+            for position, slot in enumerate(group.slots):
+                self.views[slot] = PagedKVView(index, pool[position, 0], pool[position, 1], self.page_size,
+                                               group.window)
+        for slot, request in self.states.items():
+            data = torch.zeros((int(num_state_slots), *request.shape), dtype=request.dtype, device=device)
+            self.views[slot] = StateView(data)
+
+    def bytes(self) -> int:
+        total = sum(p.numel() * p.element_size() for p in self.pool_tensors)
+        for view in self.views.values():
+            if isinstance(view, StateView):
+                total += view.data.numel() * view.data.element_size()
+        return total
+
+    def poison(self, value: float = float("nan")) -> None:
+        """Fill every page with a value that shows when read (tests use NaN)."""
+        for pool in self.pool_tensors:
+            pool.fill_(value)

@@ -1,0 +1,100 @@
+// Row-wise kernels: embedding lookup into the 32-bit residual stream, and RMSNorm.
+//
+// Embedding: a row lookup without scaling (crates/vipera-backend-cpu/src/model.rs:956-966;
+// the reference's device version dequantises one row, crates/vipera-backend-gpu/src/layer.cu:545-563).
+// RMSNorm: out = x * rsqrt(mean(x^2) + eps) * w with 32-bit statistics
+// (model.rs:4282-4288; device version layer.cu:32-58, one block per row with a tree sum).
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------
+// embedding: out[t, :] = table[tokens[t], :]  (32-bit out, whatever the table's type)
+// ---------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
+                             float* __restrict__ out, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  int token = tokens[t];
+  // The host refuses ids outside the vocabulary before the launch; the clamp only keeps
+  // a stale buffer in a replayed graph from reading outside the table.
+  token = min(max(token, 0), vocab - 1);
+  const TW* row = table + static_cast<size_t>(token) * hidden;
+  float* dst = out + static_cast<size_t>(t) * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float<TW>(row[i]);
+}
+
+VIPERA_API int vipera_embed(const void* table, int table_dtype, const int* tokens, float* out,
+                            int num_tokens, int hidden, int vocab, void* stream) {
+  if (num_tokens <= 0) return VIPERA_OK;
+  if (hidden <= 0 || vocab <= 0) return VIPERA_BAD_SHAPE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (table_dtype == VIPERA_F32)
+    embed_kernel<float><<<num_tokens, threads, 0, s>>>(static_cast<const float*>(table), tokens, out, hidden, vocab);
+  else if (table_dtype == VIPERA_BF16)
+    embed_kernel<__nv_bfloat16><<<num_tokens, threads, 0, s>>>(static_cast<const __nv_bfloat16*>(table), tokens, out, hidden, vocab);
+  else
+    return VIPERA_BAD_DTYPE;
+  return vipera_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm over rows of the 32-bit residual stream.  `rows` (optional) picks which rows of
+// x are normalised: out[r, :] = norm(x[rows[r], :]).  One block per output row; the row
+// stays in registers between the two passes when it is short enough, else it is read twice.
+// ---------------------------------------------------------------------------------------
+constexpr int kNormThreads = 256;
+constexpr int kNormRegs = 8;  // elements per thread kept in registers: rows up to 2048 wide
+
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+                               const int* __restrict__ rows, TO* __restrict__ out, int hidden, float eps) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int src_row = rows ? rows[r] : r;
+  const float* src = x + static_cast<size_t>(src_row) * hidden;
+  TO* dst = out + static_cast<size_t>(r) * hidden;
+  float kept[kNormRegs];
+  float sum = 0.0f;
+  const bool fits = hidden <= kNormThreads * kNormRegs;
+  if (fits) {
+#pragma unroll
+    for (int j = 0; j < kNormRegs; ++j) {
+      const int i = threadIdx.x + j * kNormThreads;
+      kept[j] = i < hidden ? src[i] : 0.0f;
+      sum += kept[j] * kept[j];
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += kNormThreads) {
+      const float v = src[i];
+      sum += v * v;
+    }
+  }
+  const float total = block_sum(sum, scratch);
+  const float inverse = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
+  if (fits) {
+#pragma unroll
+    for (int j = 0; j < kNormRegs; ++j) {
+      const int i = threadIdx.x + j * kNormThreads;
+      if (i < hidden) dst[i] = from_float<TO>(kept[j] * inverse * weight[i]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += kNormThreads)
+      dst[i] = from_float<TO>(src[i] * inverse * weight[i]);
+  }
+}
+
+VIPERA_API int vipera_rmsnorm(const float* x, const float* weight, const int* rows, void* out,
+                              int out_dtype, int num_rows, int hidden, float eps, void* stream) {
+  if (num_rows <= 0) return VIPERA_OK;
+  if (hidden <= 0) return VIPERA_BAD_SHAPE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_dtype == VIPERA_F32)
+    rmsnorm_kernel<float><<<num_rows, kNormThreads, 0, s>>>(x, weight, rows, static_cast<float*>(out), hidden, eps);
+  else if (out_dtype == VIPERA_BF16)
+    rmsnorm_kernel<__nv_bfloat16><<<num_rows, kNormThreads, 0, s>>>(x, weight, rows, static_cast<__nv_bfloat16*>(out), hidden, eps);
+  else
+    return VIPERA_BAD_DTYPE;
+  return vipera_launch_status();
+}
+
+VIPERA_API const char* vipera_rowwise_status_text(int status) { return vipera_status_text(status); }

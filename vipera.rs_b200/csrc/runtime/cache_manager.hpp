@@ -1,0 +1,109 @@
+// Paged cache bookkeeping: which physical page holds which part of which request.
+//
+// The reference keeps one pool of fixed-size blocks, a free stack that hands out the
+// lowest block first, and a block table per sequence; a reservation either succeeds
+// whole or leaves nothing behind (crates/vipera-runtime/src/kv.rs:232-382), and
+// release returns every block of a sequence (kv.rs:539-561).  This manager keeps that
+// behaviour and adds two things the reference does not have: several groups of layers,
+// each with pages of its own and possibly a window after which pages are given back,
+// and a pool of fixed-size state slots, one per live request.
+//
+// Only bookkeeping lives here.  The device memory the page numbers index is owned by
+// the Python side; nothing in this file touches a GPU.
+#pragma once
+
+#include <cstdint>
+#include <map>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace vipera {
+
+struct Infeasible : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+struct InvalidArgument : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
+struct GroupConfig {
+  int page_size = 16;  // tokens per page
+  int num_pages = 0;   // pages in this group's pool
+  int window = 0;      // 0: every key is kept; w > 0: a query at p reads keys p-w+1 .. p
+};
+
+struct GroupStats {
+  int total_pages = 0;
+  int free_pages = 0;
+  int used_pages = 0;
+};
+
+class CacheManager {
+ public:
+  CacheManager(std::vector<GroupConfig> groups, int num_state_slots);
+
+  int num_groups() const { return static_cast<int>(groups_.size()); }
+  const GroupConfig& group(int g) const { return groups_.at(g).config; }
+  int num_state_slots() const { return static_cast<int>(slot_owner_.size()); }
+  int free_state_slots() const { return static_cast<int>(free_slots_.size()); }
+
+  // A request enters: it gets a state slot and empty tables.  Throws Infeasible when no
+  // slot is free, InvalidArgument when the id is already open.
+  int open(int64_t request);
+  bool is_open(int64_t request) const { return requests_.count(request) != 0; }
+
+  // Pages that `reserve(request, new_length)` would have to take, per group.
+  std::vector<int> pages_missing(int64_t request, int new_length) const;
+  // Whether `reserve(request, new_length)` would succeed now.
+  bool fits(int64_t request, int new_length) const;
+  // The longest length <= new_length that fits now (never below the computed length).
+  int longest_fit(int64_t request, int new_length) const;
+  // Make sure every page is held that computing tokens [computed, new_length) reads or
+  // writes.  All groups or nothing: on failure no table changes and Infeasible is thrown.
+  void reserve(int64_t request, int new_length);
+  // Tokens [computed, new_length) are now in the cache.  Pages that no later query can
+  // read (a window has passed them) go back to the free stack.
+  void commit(int64_t request, int new_length);
+  // The request leaves: all its pages and its slot are returned.
+  void close(int64_t request);
+
+  int computed(int64_t request) const;
+  int state_slot(int64_t request) const;
+  // Logical page index -> physical page, -1 where no page is held.
+  const std::vector<int32_t>& table(int64_t request, int g) const;
+  // Whether a request of this many tokens could ever be held, alone, by every group.
+  bool could_ever_fit(int length) const;
+  // Tokens one request can hold at most (the smallest bound over the groups).
+  int64_t capacity_tokens() const;
+
+  GroupStats stats(int g) const;
+  std::vector<int64_t> open_requests() const;
+  // Consistency of the books: every page is either free or held exactly once.  Returns
+  // an empty string when sound, else a description of the first fault found.
+  std::string audit() const;
+
+ private:
+  struct Group {
+    GroupConfig config;
+    std::vector<int32_t> free;  // stack; back() is handed out next
+    std::vector<uint8_t> held;  // per physical page: 1 while in some table
+  };
+  struct Request {
+    int slot = -1;
+    int computed = 0;
+    std::vector<std::vector<int32_t>> tables;  // per group
+  };
+
+  // First and one-past-last logical page that computing [computed, new_length) touches.
+  static void span(const GroupConfig& config, int computed, int new_length, int* first, int* end);
+  const Request& find(int64_t request) const;
+  Request& find(int64_t request);
+
+  std::vector<Group> groups_;
+  std::map<int64_t, Request> requests_;
+  std::vector<int64_t> slot_owner_;  // -1 when free
+  std::vector<int> free_slots_;      // stack; back() is handed out next
+};
+
+}  // namespace vipera

@@ -1,0 +1,149 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+One step runs only the tokens it is given, as one flattened batch, against the cache that
+earlier steps left: portions of prompts beside single decode tokens, cut anywhere.  The
+reference's seam has the same shape — ``logits_batch(BatchContext{kv, entries})`` with an
+entry = (tokens, new_tokens, first_position, block_table) (crates/vipera-runtime/src/
+pipeline.rs:139-152, 219-229) — but its CPU backend runs every entry of a mixed batch alone
+(crates/vipera-backend-cpu/src/model.rs:796-827); here all entries share every product.
+
+Host-side checks before any launch follow model.rs:890-927, 957-964: token ids inside the
+vocabulary, positions inside the model's reach, block tables that cover every position.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..errors import InternalError, InvalidArgumentError
+from ..parts.base import StepContext, Workspace
+
+
+@dataclass
+class StepInput:
+    """One step on the host side.  ``requests[i]`` is open in the cache manager with pages
+    reserved for positions ``pos0[i] .. pos0[i] + counts[i] - 1``."""
+
+    requests: Sequence[int]
+    tokens: np.ndarray          # int32, entry after entry
+    counts: Sequence[int]
+    pos0: Sequence[int]
+    fresh: Sequence[int]
+    logit_rows: np.ndarray      # int32 indices into tokens
+
+
+def _round_up_pow2(value: int, least: int = 8) -> int:
+    out = least
+    while out < value:
+        out *= 2
+    return out
+
+
+class ModelRunner:
+    """Owns the workspace and the staging buffers; turns a StepInput into device tensors,
+    runs the model, and returns the logits tensor (device, float32, [rows, vocab])."""
+
+    def __init__(self, model, pools, *, max_model_len: int):
+        if not torch.cuda.is_available():
+            raise InternalError("no CUDA device: this engine has no CPU path")
+        self.model = model
+        self.pools = pools
+        self.manager = pools.manager
+        self.device = model.device
+        self.max_model_len = int(max_model_len)
+        self.workspace = Workspace(self.device)
+        self._staging_host: Optional[torch.Tensor] = None
+        self._staging_dev: Optional[torch.Tensor] = None
+        self._copy_done = torch.cuda.Event()
+        self._copy_pending = False
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------------------
+    def _staging(self, count: int):
+        if self._staging_host is None or self._staging_host.numel() < count:
+            size = max(count, 1 << 16)
+            self._staging_host = torch.empty(size, dtype=torch.int32, pin_memory=True)
+            self._staging_dev = torch.empty(size, dtype=torch.int32, device=self.device)
+        return self._staging_host, self._staging_dev
+
+    def validate(self, step: StepInput) -> None:
+        tokens = step.tokens
+        total = int(sum(step.counts))
+        if total != tokens.shape[0] or total == 0:
+            raise InvalidArgumentError("a step needs at least one token and counts that add up to its tokens")
+        if len(step.requests) != len(step.counts) or len(step.pos0) != len(step.counts):
+            raise InvalidArgumentError("requests, counts and first positions must have one item per entry")
+        if min(step.counts) < 1:
+            raise InvalidArgumentError("every entry of a step needs at least one token")
+        vocab = self.model.spec.vocab_size
+        if int(tokens.min()) < 0 or int(tokens.max()) >= vocab:
+            raise InvalidArgumentError(f"token id outside the vocabulary of {vocab}")
+        for request, count, first in zip(step.requests, step.counts, step.pos0):
+            if first < 0 or first + count > self.max_model_len:
+                raise InvalidArgumentError(
+                    f"request {request}: positions {first}..{first + count - 1} exceed the limit of "
+                    f"{self.max_model_len}")
+        if step.logit_rows.size and (int(step.logit_rows.min()) < 0 or int(step.logit_rows.max()) >= total):
+            raise InvalidArgumentError("a wanted row lies outside the step's tokens")
+
+    def build_context(self, step: StepInput, dtype: torch.dtype) -> StepContext:
+        self.validate(step)
+        counts = np.asarray(step.counts, dtype=np.int32)
+        pos0 = np.asarray(step.pos0, dtype=np.int32)
+        entries = counts.shape[0]
+        total = int(counts.sum())
+        starts = np.zeros(entries + 1, dtype=np.int32)
+        np.cumsum(counts, out=starts[1:])
+        token_entry = np.repeat(np.arange(entries, dtype=np.int32), counts)
+        positions = np.arange(total, dtype=np.int32) - np.repeat(starts[:-1] - pos0, counts)
+        rows = np.asarray(step.logit_rows, dtype=np.int32)
+        max_len = int((pos0 + counts).max())
+        tables = []
+        for g in range(self.manager.num_groups):
+            page_size = self.manager.group(g)[0]
+            width = _round_up_pow2((max_len + page_size - 1) // page_size)
+            table = self.manager.tables(list(step.requests), g, width)
+            # Every position of the step must have its page.
+            last_page = (pos0 + counts - 1) // page_size
+            if (table[np.arange(entries), last_page] < 0).any():
+                raise InvalidArgumentError("a request of the step has no page reserved for its last position")
+            tables.append(table)
+        slots = np.asarray([self.manager.state_slot(r) for r in step.requests], dtype=np.int32)
+        fresh = np.asarray(step.fresh, dtype=np.int32)
+
+        pieces = [step.tokens.astype(np.int32, copy=False), positions, token_entry, starts, pos0, slots, fresh, rows]
+        pieces += [t.reshape(-1) for t in tables]
+        sizes = [p.shape[0] for p in pieces]
+        host, dev = self._staging(sum(sizes))
+        if self._copy_pending:
+            self._copy_done.synchronize()
+        view = host.numpy()
+        offsets, cursor = [], 0
+        for piece, size in zip(pieces, sizes):
+            view[cursor:cursor + size] = piece
+            offsets.append(cursor)
+            cursor += size
+        dev[:cursor].copy_(host[:cursor], non_blocking=True)
+        self._copy_done.record()
+        self._copy_pending = True
+
+        def part(index):
+            return dev[offsets[index]:offsets[index] + sizes[index]]
+
+        block_tables = [part(8 + g).view(entries, tables[g].shape[1]) for g in range(len(tables))]
+        return StepContext(
+            num_tokens=total, num_entries=entries, tokens=part(0), positions=part(1), token_entry=part(2),
+            entry_starts=part(3), entry_pos0=part(4), state_slots=part(5), fresh=part(6),
+            block_tables=block_tables, logit_rows=part(7) if rows.size else None, num_logit_rows=int(rows.size),
+            host_counts=[int(c) for c in counts], host_pos0=[int(p) for p in pos0],
+            max_count=int(counts.max()), max_kv_len=max_len, all_single=bool((counts == 1).all()),
+            dtype=self.model.dtype, workspace=self.workspace)
+
+    def run(self, step: StepInput) -> Optional[torch.Tensor]:
+        ctx = self.build_context(step, self.model.dtype)
+        logits = self.model.forward(ctx, self.pools.views)
+        self.steps_run += 1
+        return logits

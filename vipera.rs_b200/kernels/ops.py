@@ -1,0 +1,235 @@
+"""Python face of the CUDA kernels: one function per launcher, called through ctypes.
+
+Every function takes torch tensors that already live on the GPU, checks what the kernel
+cannot check for itself (device, dtype, contiguity, extents), and launches on torch's
+current stream.  There is no fallback: a tensor that is not on a CUDA device, a missing
+compiler or a kernel that reports an error raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..build import load_kernel_library
+from ..errors import InternalError, InvalidArgumentError, UnsupportedError
+
+F32, BF16 = 0, 1
+EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+ROPE_NONE, ROPE_NEOX, ROPE_INTERLEAVED = 0, 1, 2
+SAMPLE_OK, SAMPLE_NO_FINITE, SAMPLE_NO_MASS, SAMPLE_NEEDS_HOST = 0, 1, 2, 3
+
+_c_int, _c_float, _c_void = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+_functions = {}
+
+_STATUS_TEXT = {
+    -1: "unsupported element type",
+    -2: "a size this kernel does not take",
+    -3: "bad argument",
+    -4: "the CUDA driver gave no entry point for tensor maps",
+    -5: "a bounded wait inside the kernel ran out",
+}
+
+
+def _function(library: str, name: str, argtypes):
+    key = (library, name)
+    fn = _functions.get(key)
+    if fn is None:
+        fn = getattr(load_kernel_library(library), name)
+        fn.argtypes = argtypes
+        fn.restype = _c_int
+        _functions[key] = fn
+    return fn
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise UnsupportedError(f"kernels take float32 and bfloat16, not {dtype}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status > 0:
+        text = f"CUDA error {status}"
+        try:
+            text = f"CUDA error {status}: " + torch.cuda.cudart().cudaGetErrorString(status)  # type: ignore[attr-defined]
+        except Exception:
+            pass
+    else:
+        text = _STATUS_TEXT.get(status, f"status {status}")
+    raise InternalError(f"{what}: {text}")
+
+
+def _gpu(tensor: torch.Tensor, name: str, dtype=None) -> int:
+    if not tensor.is_cuda:
+        raise InternalError(f"{name} is not on a CUDA device; this engine has no CPU path")
+    if not tensor.is_contiguous():
+        raise InvalidArgumentError(f"{name} must be contiguous")
+    if dtype is not None and tensor.dtype != dtype:
+        raise InvalidArgumentError(f"{name} must be {dtype}, got {tensor.dtype}")
+    return tensor.data_ptr()
+
+
+def _opt(tensor: Optional[torch.Tensor], name: str, dtype=None):
+    return None if tensor is None else _gpu(tensor, name, dtype)
+
+
+# ----------------------------------------------------------------------------------------
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = table[tokens[t], :] as float32."""
+    fn = _function("rowwise", "vipera_embed",
+                   [_c_void, _c_int, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void])
+    count, hidden = out.shape
+    if table.shape[1] != hidden or tokens.numel() != count:
+        raise InvalidArgumentError("embed: shapes of table, tokens and out do not agree")
+    _check(fn(_gpu(table, "table"), dtype_code(table.dtype), _gpu(tokens, "tokens", torch.int32),
+              _gpu(out, "out", torch.float32), count, hidden, table.shape[0], _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r, :] = rmsnorm(x[rows[r], :]) * weight (rows defaults to all rows in order)."""
+    fn = _function("rowwise", "vipera_rmsnorm",
+                   [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_float, _c_void])
+    hidden = x.shape[1]
+    count = out.shape[0]
+    if out.shape[1] != hidden or weight.numel() != hidden:
+        raise InvalidArgumentError("rmsnorm: widths of x, weight and out do not agree")
+    if rows is None and x.shape[0] != count:
+        raise InvalidArgumentError("rmsnorm: x and out have different row counts")
+    if rows is not None and rows.numel() != count:
+        raise InvalidArgumentError("rmsnorm: one row index is needed for each output row")
+    _check(fn(_gpu(x, "x", torch.float32), _gpu(weight, "weight", torch.float32),
+              _opt(rows, "rows", torch.int32), _gpu(out, "out"), dtype_code(out.dtype), count, hidden,
+              float(eps), _stream()), "rmsnorm")
+
+
+def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int,
+               positions: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], style: int,
+               k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+               token_seq: Optional[torch.Tensor], block_table: Optional[torch.Tensor], page_size: int,
+               write_cache: bool) -> None:
+    """Rotate q and k of a float32 [tokens, (heads + 2 kv_heads) * d] product; write q to
+    q_out [tokens, heads * d] and k, v into their cache pages."""
+    fn = _function("rope_cache", "vipera_rope_cache",
+                   [_c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_int,
+                    _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void])
+    count = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise InvalidArgumentError("rope_cache: qkv width does not match the head counts")
+    if q_out.shape[0] != count or q_out.shape[1] != num_heads * head_dim:
+        raise InvalidArgumentError("rope_cache: q_out has the wrong shape")
+    if style != ROPE_NONE:
+        if cos is None or sin is None or cos.shape[1] != head_dim // 2:
+            raise InvalidArgumentError("rope_cache: a cos/sin table of width d/2 is needed")
+    if write_cache:
+        if k_pool is None or v_pool is None or k_pool.dtype != q_out.dtype:
+            raise InvalidArgumentError("rope_cache: cache pools must have the activation dtype")
+        if k_pool.shape[1:] != (page_size, num_kv_heads, head_dim) or v_pool.shape != k_pool.shape:
+            raise InvalidArgumentError("rope_cache: cache pools must be [pages, page_size, kv_heads, d]")
+    width = 0 if block_table is None else block_table.shape[1]
+    _check(fn(_gpu(qkv, "qkv", torch.float32), _gpu(q_out, "q_out"), dtype_code(q_out.dtype), count,
+              num_heads, num_kv_heads, head_dim, _gpu(positions, "positions", torch.int32),
+              _opt(cos, "cos", torch.float32), _opt(sin, "sin", torch.float32), style,
+              _opt(k_pool, "k_pool"), _opt(v_pool, "v_pool"), _opt(token_seq, "token_seq", torch.int32),
+              _opt(block_table, "block_table", torch.int32), width, page_size, 1 if write_cache else 0,
+              _stream()), "rope_cache")
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE,
+              bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+              resid: Optional[torch.Tensor] = None) -> None:
+    """a[M, K] times w[N, K] transposed, on the CUDA cores with float32 accumulation."""
+    fn = _function("gemm_simt", "vipera_gemm_simt",
+                   [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int,
+                    _c_void, _c_void])
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise InvalidArgumentError(f"gemm: inner sizes differ ({k} and {w.shape[1]})")
+    _check_gemm_outputs(m, n, epilogue, bias, out, resid)
+    _check(fn(_gpu(a, "a"), dtype_code(a.dtype), _gpu(w, "w"), dtype_code(w.dtype), m, n, k, epilogue,
+              _opt(bias, "bias", torch.float32), _opt(out, "out"),
+              dtype_code(out.dtype) if out is not None else F32, _opt(resid, "resid", torch.float32),
+              _stream()), "gemm_simt")
+
+
+def _check_gemm_outputs(m, n, epilogue, bias, out, resid) -> None:
+    if epilogue == EPI_STORE:
+        if out is None or tuple(out.shape) != (m, n):
+            raise InvalidArgumentError(f"gemm: out must be [{m}, {n}]")
+        if bias is not None and bias.numel() != n:
+            raise InvalidArgumentError("gemm: bias must have one value per output column")
+    elif epilogue == EPI_RESIDUAL:
+        if resid is None or tuple(resid.shape) != (m, n):
+            raise InvalidArgumentError(f"gemm: resid must be [{m}, {n}]")
+    elif epilogue == EPI_SWIGLU:
+        if n % 32:
+            raise UnsupportedError("gemm: SwiGLU needs an intermediate size that is a multiple of 16")
+        if out is None or tuple(out.shape) != (m, n // 2):
+            raise InvalidArgumentError(f"gemm: out must be [{m}, {n // 2}]")
+    else:
+        raise InvalidArgumentError(f"gemm: unknown epilogue {epilogue}")
+
+
+def attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
+              token_seq: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
+              num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """Causal grouped-query attention of every token of the step over its request's pages."""
+    fn = _function("attention", "vipera_attention",
+                   [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
+                    _c_int, _c_int, _c_int, _c_float, _c_int, _c_void])
+    count = q.shape[0]
+    if head_dim % 16 or head_dim > 256:
+        raise UnsupportedError(f"attention: head size {head_dim} is not a multiple of 16 up to 256")
+    if q.shape[1] != num_heads * head_dim or out.shape != q.shape or out.dtype != q.dtype:
+        raise InvalidArgumentError("attention: q and out must be [tokens, heads * d] of one dtype")
+    if k_pool.dtype != q.dtype or v_pool.shape != k_pool.shape:
+        raise InvalidArgumentError("attention: cache pools must match q's dtype and each other")
+    page_size = k_pool.shape[1]
+    if k_pool.shape[2:] != (num_kv_heads, head_dim):
+        raise InvalidArgumentError("attention: cache pools must be [pages, page_size, kv_heads, d]")
+    _check(fn(_gpu(q, "q"), _gpu(out, "out"), dtype_code(q.dtype), _gpu(k_pool, "k_pool"), _gpu(v_pool, "v_pool"),
+              _gpu(token_seq, "token_seq", torch.int32), _gpu(positions, "positions", torch.int32),
+              _gpu(block_table, "block_table", torch.int32), block_table.shape[1], page_size, count,
+              num_heads, num_kv_heads, head_dim, float(scale), int(window or 0), _stream()), "attention")
+
+
+# ----------------------------------------------------------------------------------------
+def argmax(logits: torch.Tensor, tokens: torch.Tensor, status: Optional[torch.Tensor] = None) -> None:
+    fn = _function("sampling", "vipera_argmax", [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void])
+    rows, vocab = logits.shape
+    _check(fn(_gpu(logits, "logits", torch.float32), rows, vocab, _gpu(tokens, "tokens", torch.int32),
+              _opt(status, "status", torch.int32), _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, *, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, uniform: torch.Tensor, tokens: torch.Tensor, status: torch.Tensor) -> None:
+    fn = _function("sampling", "vipera_sample",
+                   [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void])
+    rows, vocab = logits.shape
+    _check(fn(_gpu(logits, "logits", torch.float32), rows, vocab,
+              _gpu(temperature, "temperature", torch.float32), _gpu(top_k, "top_k", torch.int32),
+              _gpu(top_p, "top_p", torch.float32), _gpu(min_p, "min_p", torch.float32),
+              _gpu(uniform, "uniform", torch.float64), _gpu(tokens, "tokens", torch.int32),
+              _gpu(status, "status", torch.int32), _stream()), "sample")
+
+
+def apply_penalties(logits: torch.Tensor, *, entry_row, entry_id, entry_count, entry_bias,
+                    repetition, presence, frequency) -> None:
+    fn = _function("sampling", "vipera_apply_penalties",
+                   [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void])
+    _check(fn(_gpu(logits, "logits", torch.float32), logits.shape[1], entry_row.numel(),
+              _gpu(entry_row, "entry_row", torch.int32), _gpu(entry_id, "entry_id", torch.int32),
+              _gpu(entry_count, "entry_count", torch.int32), _gpu(entry_bias, "entry_bias", torch.float32),
+              _gpu(repetition, "repetition", torch.float32), _gpu(presence, "presence", torch.float32),
+              _gpu(frequency, "frequency", torch.float32), _stream()), "apply_penalties")

@@ -1,0 +1,112 @@
+"""Grouped-query attention over the paged cache.
+
+In the reference's order (crates/vipera-backend-cpu/src/model.rs:1005-1126): q, k, v products
+from the normalised input, bias added after the product and before the rotation, rotation
+of q and k, keys and values written to their pages, attention of every new token over its
+request's keys, output product added to the residual stream.  Query head h reads KV head
+h // group (model.rs:1813-1826).
+
+Here q, k and v come from one product with the concatenated matrix (the reference keeps
+three products, model.rs:1005-1025); the rotation and the cache write are one kernel; the
+output product adds into the 32-bit residual stream in its own ending.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.registry import MIXERS, POSITION_ENCODINGS
+from ..errors import UnsupportedError
+from ..kernels import ops
+from ..weights import TensorSpec
+from .base import Mixer, PagedKV
+from .linear import Linear
+
+
+class GQAttention(Mixer):
+    """params: hidden_size, num_heads, num_kv_heads, head_dim, qkv_bias, window (None or a
+    count of keys), softmax_scale, position (a PartSpec of a position encoding) and,
+    optionally, ``projection_names`` (defaults q_proj, k_proj, v_proj, o_proj)."""
+
+    kernels = ("rope_cache", "attention")
+
+    @staticmethod
+    def _names(params):
+        return params.get("projection_names", ("q_proj", "k_proj", "v_proj", "o_proj"))
+
+    @classmethod
+    def schema(cls, params, prefix):
+        hidden, d = params["hidden_size"], params["head_dim"]
+        q_width, kv_width = params["num_heads"] * d, params["num_kv_heads"] * d
+        qn, kn, vn, on = cls._names(params)
+        schema = {
+            f"{prefix}.{qn}.weight": TensorSpec((q_width, hidden)),
+            f"{prefix}.{kn}.weight": TensorSpec((kv_width, hidden)),
+            f"{prefix}.{vn}.weight": TensorSpec((kv_width, hidden)),
+            f"{prefix}.{on}.weight": TensorSpec((hidden, q_width)),
+        }
+        if params.get("qkv_bias", False):
+            schema[f"{prefix}.{qn}.bias"] = TensorSpec((q_width,), init="bias")
+            schema[f"{prefix}.{kn}.bias"] = TensorSpec((kv_width,), init="bias")
+            schema[f"{prefix}.{vn}.bias"] = TensorSpec((kv_width,), init="bias")
+        return schema
+
+    def __init__(self, params, prefix, tensors, dtype, device):
+        super().__init__(params, prefix, tensors, dtype, device)
+        self.hidden = int(params["hidden_size"])
+        self.num_heads = int(params["num_heads"])
+        self.num_kv_heads = int(params["num_kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        self.window = params.get("window")
+        self.scale = float(params["softmax_scale"])
+        if self.head_dim % 16 or self.head_dim > 256:
+            raise UnsupportedError(
+                f"head size {self.head_dim}: the attention kernels take multiples of 16 up to 256")
+        if self.num_heads % self.num_kv_heads:
+            raise UnsupportedError("the number of heads must be a multiple of the number of KV heads")
+        qn, kn, vn, on = self._names(params)
+        fused = torch.cat([tensors[f"{prefix}.{n}.weight"] for n in (qn, kn, vn)], dim=0)
+        bias = None
+        if params.get("qkv_bias", False):
+            bias = torch.cat([tensors[f"{prefix}.{n}.bias"].to(torch.float32) for n in (qn, kn, vn)], dim=0)
+        self.qkv = Linear(fused, dtype, device, bias=bias)
+        self.out = Linear(tensors[f"{prefix}.{on}.weight"], dtype, device)
+        position = params["position"]
+        self.position = POSITION_ENCODINGS.find(position.kind)(position.params, prefix, tensors, dtype, device)
+
+    def kernel_families(self):
+        return tuple(dict.fromkeys(self.kernels + self.qkv.kernel_families() + self.out.kernel_families()
+                                   + self.position.kernel_families()))
+
+    def cache_request(self):
+        return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+
+    def forward(self, ctx, h, residual, cache, writes_cache):
+        count = ctx.num_tokens
+        heads, kv_heads, d = self.num_heads, self.num_kv_heads, self.head_dim
+        ws = ctx.workspace
+        qkv = ws.get("attention.qkv", (count, (heads + 2 * kv_heads) * d), torch.float32)
+        self.qkv(ctx, h, epilogue=ops.EPI_STORE, out=qkv)
+        q = ws.get("attention.q", (count, heads * d), ctx.dtype)
+        table = ctx.block_tables[cache.group]
+        style = self.position.style
+        if style is None:
+            # An encoding the fused kernel does not know: the part applies it to the 32-bit
+            # product itself, then the kernel only converts and stores.
+            q_view = qkv[:, : heads * d].unflatten(1, (heads, d))
+            k_view = qkv[:, heads * d : (heads + kv_heads) * d].unflatten(1, (kv_heads, d))
+            self.position.apply(ctx, q_view, k_view)
+            style, cos, sin = ops.ROPE_NONE, None, None
+        else:
+            cos, sin = self.position.tables()
+        ops.rope_cache(qkv, q, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
+                       positions=ctx.positions, cos=cos, sin=sin, style=style,
+                       k_pool=cache.k, v_pool=cache.v, token_seq=ctx.token_entry, block_table=table,
+                       page_size=cache.page_size, write_cache=writes_cache)
+        mixed = ws.get("attention.out", (count, heads * d), ctx.dtype)
+        ops.attention(q, mixed, cache.k, cache.v, token_seq=ctx.token_entry, positions=ctx.positions,
+                      block_table=table, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
+                      scale=self.scale, window=self.window or 0)
+        self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
+
+
+MIXERS.register("gqa_attention", GQAttention)

@@ -1,0 +1,64 @@
+"""Rotary position encoding, NeoX pairing ``(i, i + d/2)``.
+
+Angles as the reference computes them, in 32-bit: ``inv_i = 1 / base^(2i/d)``,
+``angle = position * inv_i`` (crates/vipera-backend-cpu/src/model.rs:4204-4206).  The
+reference builds the table once per position and step and shares it between layers
+(model.rs:970-973); here one table for all positions is built on the host when the model
+is built and shared by every layer with the same head size and base.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.registry import POSITION_ENCODINGS
+from ..kernels import ops
+from .base import PositionEncoding
+
+_TABLES = {}
+
+
+def rotary_tables(head_dim: int, theta: float, max_positions: int, device):
+    """(cos, sin), each float32 [max_positions, head_dim / 2], on ``device``."""
+    key = (head_dim, float(theta), max_positions, str(device))
+    cached = _TABLES.get(key)
+    if cached is not None:
+        return cached
+    half = head_dim // 2
+    index = torch.arange(half, dtype=torch.float32)
+    exponent = 2.0 * index / torch.tensor(float(head_dim), dtype=torch.float32)
+    inverse = 1.0 / torch.pow(torch.tensor(float(theta), dtype=torch.float32), exponent)
+    position = torch.arange(max_positions, dtype=torch.float32)
+    angle = position[:, None] * inverse[None, :]
+    tables = (torch.cos(angle).contiguous().to(device), torch.sin(angle).contiguous().to(device))
+    _TABLES[key] = tables
+    return tables
+
+
+class RopeNeox(PositionEncoding):
+    """params: ``head_dim``, ``theta``, ``max_positions``.  No tensors."""
+
+    style = ops.ROPE_NEOX
+    kernels = ("rope_cache",)
+
+    def __init__(self, params, prefix, tensors, dtype, device):
+        super().__init__(params, prefix, tensors, dtype, device)
+        self.head_dim = int(params["head_dim"])
+        self.theta = float(params["theta"])
+        self.max_positions = int(params["max_positions"])
+        self._tables = rotary_tables(self.head_dim, self.theta, self.max_positions, device)
+
+    def tables(self):
+        return self._tables
+
+
+class NoPositions(PositionEncoding):
+    """Leaves q and k as they are."""
+
+    style = ops.ROPE_NONE
+
+    def tables(self):
+        return (None, None)
+
+
+POSITION_ENCODINGS.register("rope_neox", RopeNeox)
+POSITION_ENCODINGS.register("none", NoPositions)
