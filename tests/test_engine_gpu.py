@@ -1,0 +1,83 @@
+"""Generation through the public entry point on the GPU, held to the plain implementation."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(name, dtype, **kwargs):
+    from vipera_rs_b200 import Engine
+
+    folder = helpers.model_folder(name, dtype)
+    return folder, Engine(folder, dtype=dtype, device="cuda:0", **kwargs)
+
+
+def _check_greedy(folder, prompt, produced, dtype):
+    """Each produced token is the plain implementation's best at its place (or ties it
+    within rounding), given the tokens produced before it."""
+    round_to = torch.bfloat16 if dtype == "bfloat16" else None
+    logits = helpers.plain_logits(folder, list(prompt) + list(produced[:-1]), round_to)
+    limit = 1e-4 if dtype == "float32" else 2e-2
+    for index, token in enumerate(produced):
+        row = logits[len(prompt) - 1 + index]
+        margin = float(row.max() - row[token])
+        assert margin <= limit * float(np.abs(row).max()), (
+            f"token {index}: engine chose {token}, plain prefers {int(row.argmax())} by {margin}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_tiny_a(dtype):
+    from vipera_rs_b200 import SamplingParams
+
+    folder, engine = _engine("A", dtype, page_size=16, ctx=128, max_num_seqs=4)
+    vocab = helpers.CONFIGS["A"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, 500 + n) for n in (1, 7, 33, 64)]
+    results = engine.generate(prompts, SamplingParams(max_new_tokens=16))
+    for prompt, result in zip(prompts, results):
+        assert result.finish == "length" and len(result.tokens) == 16
+        _check_greedy(folder, prompt, result.tokens, dtype)
+    stats = engine.stats()
+    assert stats["kv_used_pages"] == 0 and stats["sequences"] == 0
+    assert engine.pools.manager.audit() == ""
+
+
+def test_batched_equals_alone_and_seed_replays():
+    """A request's tokens do not depend on what else runs beside it, and the same seed gives
+    the same tokens (crates/vipera-runtime/src/engine.rs:1770-1806, 1906-1941)."""
+    from vipera_rs_b200 import SamplingParams
+
+    folder, engine = _engine("B", "float32", page_size=32, ctx=512, max_num_seqs=3, max_tokens_per_step=48)
+    vocab = helpers.CONFIGS["B"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, 600 + n) for n in (5, 100, 257)]
+    params = SamplingParams(max_new_tokens=24, temperature=0.8, seed=1234)
+    together = engine.generate(prompts, params)
+    alone = [engine.generate([prompt], params)[0] for prompt in prompts]
+    for a, b in zip(together, alone):
+        assert a.tokens == b.tokens
+    again = engine.generate(prompts[:1], params)[0]
+    assert again.tokens == together[0].tokens
+    other = engine.generate(prompts[:1], SamplingParams(max_new_tokens=24, temperature=0.8, seed=4321))[0]
+    assert other.tokens != together[0].tokens
+    assert engine.pools.manager.audit() == ""
+
+
+def test_few_pages_preempt_and_recompute():
+    """With too few pages for all requests at once, the one admitted last is put back and
+    computed again; every request still gets the tokens it gets alone."""
+    from vipera_rs_b200 import SamplingParams
+
+    folder, engine = _engine("A", "float32", page_size=16, num_pages=14, max_num_seqs=4, max_tokens_per_step=64)
+    vocab = helpers.CONFIGS["A"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, 700 + n) for n in (40, 50, 60, 30)]
+    params = SamplingParams(max_new_tokens=40)
+    results = engine.generate(prompts, params)
+    assert sum(r.preemptions for r in results) >= 1
+    for prompt, result in zip(prompts, results):
+        assert len(result.tokens) == 40
+        _check_greedy(folder, prompt, result.tokens, "float32")
+    assert engine.pools.manager.audit() == ""
+    assert engine.stats()["kv_used_pages"] == 0

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 PAGE = {"A": 16, "B": 32, "C": 64}
 LENGTHS = {"A": [1, 7, 33, 64, 200], "B": [5, 100, 257], "C": [2, 50, 130]}
 FP32_TOL = 1e-4
-BF16_TOL = 4e-2  # of the request's largest |logit|; bfloat16 keeps 8 bits of mantissa
+BF16_TOL = 1e-2  # of the request's largest |logit|; bfloat16 keeps 8 bits of mantissa
 
 PORTIONS = [48, 17, 5, 3, 2, 2, 31, 64, 2, 7, 19, 2, 90]
 

@@ -1,0 +1,170 @@
+"""The public entry point: requests in, tokens out, by continuous batching.
+
+The surface follows the reference's ``Engine`` (crates/vipera-runtime/src/engine.rs):
+``admit``+``enqueue`` become ``add_request`` (engine.rs:396, 606), ``step`` returns what the
+step produced (engine.rs:671-765), ``generate`` loops ``step`` until its requests end
+(engine.rs:563-591), ``cancel`` frees a request's pages at once (engine.rs:1199-1206) and
+``stats`` reports the cache (engine.rs:94-110, 380-390).  A finished request's record
+carries the reference's ``Generation`` fields (engine.rs:62-82).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from ..build import runtime_module
+from ..cache import CachePools
+from ..errors import InternalError, InvalidArgumentError
+from ..sampling import DeviceSampler, SamplingParams
+from .loader import load_model
+from .runner import ModelRunner, StepInput
+
+
+@dataclass
+class Generation:
+    """How a request ended."""
+
+    request: int
+    tokens: List[int]            # generated tokens, the end token included
+    finish: str                  # "stop" | "length" | "cancelled" | "error"
+    prompt_tokens: int
+    processed_tokens: int        # tokens run through the model, recomputation included
+    preemptions: int
+
+
+@dataclass
+class StepReport:
+    tokens: List[tuple] = field(default_factory=list)        # (request, token) drawn in this step
+    finished: List[Generation] = field(default_factory=list)
+    preempted: List[int] = field(default_factory=list)
+    num_tokens: int = 0                                       # tokens the step ran
+    num_entries: int = 0
+
+
+class Engine:
+    """One model on one GPU, a paged cache and a scheduler.
+
+    ``model`` is a folder (config.json and model.safetensors) or a built ``DecoderModel``.
+    ``ctx`` is the context length each of ``max_num_seqs`` requests can reach with the
+    pages allocated (default: the smaller of the model's limit and 2048, as the reference's
+    ``--ctx``, bins/vipera/src/main.rs:655-663); ``num_pages`` overrides that sizing.
+    """
+
+    def __init__(self, model, dtype="bfloat16", device="cuda:0", *, page_size: int = 16,
+                 num_pages: Optional[int] = None, ctx: Optional[int] = None, max_num_seqs: int = 4,
+                 max_tokens_per_step: int = 2048, max_portion: Optional[int] = None,
+                 max_model_len: Optional[int] = None, decode_graphs: bool = True):
+        if isinstance(model, str):
+            model = load_model(model, dtype, device)
+        self.model = model
+        limit = model.spec.max_position_embeddings
+        self.max_model_len = min(limit, max_model_len) if max_model_len else limit
+        if ctx is None:
+            ctx = min(self.max_model_len, 2048)
+        if num_pages is None:
+            num_pages = max_num_seqs * ((ctx + page_size - 1) // page_size)
+        self.pools = CachePools(model.cache_requests, page_size=page_size, num_pages=num_pages,
+                                num_state_slots=max_num_seqs, dtype=model.dtype, device=model.device)
+        self.runner = ModelRunner(model, self.pools, max_model_len=self.max_model_len)
+        self.runner.decode_graphs = decode_graphs
+        runtime = runtime_module()
+        self.scheduler = runtime.Scheduler(self.pools.manager, int(max_num_seqs), int(max_tokens_per_step),
+                                           int(max_portion or max_tokens_per_step), int(self.max_model_len))
+        self.sampler = DeviceSampler(model.device)
+        self.default_eos = tuple(getattr(getattr(model, "config", None), "eos_token_ids", ()) or ())
+        self._next_id = 0
+        self.generations = 0
+        self.failed = 0
+
+    # ------------------------------------------------------------------------------
+    def add_request(self, prompt_ids: Sequence[int], params: Optional[SamplingParams] = None,
+                    request_id: Optional[int] = None) -> int:
+        params = params or SamplingParams()
+        if request_id is None:
+            request_id = self._next_id
+        self._next_id = max(self._next_id, request_id + 1)
+        prompt = [int(t) for t in prompt_ids]
+        vocab = self.model.spec.vocab_size
+        if any(t < 0 or t >= vocab for t in prompt):
+            raise InvalidArgumentError(f"prompt holds a token id outside the vocabulary of {vocab}")
+        self.scheduler.add(int(request_id), prompt, params.to_native(self.default_eos))
+        return int(request_id)
+
+    def cancel(self, request_id: int) -> None:
+        self.scheduler.cancel(int(request_id))
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def step(self) -> StepReport:
+        plan = self.scheduler.schedule()
+        report = StepReport(preempted=list(plan.preempted), num_tokens=int(plan.num_tokens),
+                            num_entries=int(plan.num_entries))
+        if plan.empty:
+            outcome = self.scheduler.complete(plan, [])
+        else:
+            try:
+                step = StepInput(requests=plan.requests, tokens=plan.tokens, counts=plan.counts.tolist(),
+                                 pos0=plan.starts.tolist(), fresh=plan.fresh.tolist(),
+                                 logit_rows=plan.row_token_index)
+                logits = self.runner.run(step)
+                sampled = self.sampler.draw(logits, plan) if logits is not None else []
+                if logits is None:
+                    torch.cuda.current_stream().synchronize()
+                outcome = self.scheduler.complete(plan, sampled)
+            except InternalError:
+                outcome = self.scheduler.fail(plan)
+                self.failed += len(outcome["finished"])
+                self._collect(report, outcome)
+                raise
+        self._collect(report, outcome)
+        return report
+
+    def _collect(self, report: StepReport, outcome: dict) -> None:
+        report.tokens.extend((int(r), int(t)) for r, t in outcome["tokens"])
+        for item in outcome["finished"]:
+            report.finished.append(Generation(
+                request=int(item["request"]), tokens=[int(t) for t in item["tokens"]], finish=item["reason"],
+                prompt_tokens=int(item["prompt_tokens"]), processed_tokens=int(item["processed_tokens"]),
+                preemptions=int(item["preemptions"])))
+            self.generations += 1
+
+    def generate(self, prompts: Sequence[Sequence[int]], params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 on_token=None) -> List[Generation]:
+        """Run prompts (lists of token ids) to their ends; results in the order given."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        if len(params) != len(prompts):
+            raise InvalidArgumentError("one SamplingParams is needed for each prompt, or one for all")
+        ids = [self.add_request(prompt, p) for prompt, p in zip(prompts, params)]
+        results: Dict[int, Generation] = {}
+        while len(results) < len(ids):
+            if not self.has_work():
+                raise InternalError("the scheduler has no work left but requests are unfinished")
+            report = self.step()
+            if on_token is not None:
+                for request, token in report.tokens:
+                    on_token(request, token)
+            for generation in report.finished:
+                if generation.request in ids:
+                    results[generation.request] = generation
+        return [results[i] for i in ids]
+
+    def stats(self) -> dict:
+        manager = self.pools.manager
+        groups = [manager.stats(g) for g in range(manager.num_groups)]
+        return {
+            "sequences": len(manager.open_requests()),
+            "waiting": self.scheduler.num_waiting,
+            "running": self.scheduler.num_running,
+            "kv_used_pages": sum(g["used_pages"] for g in groups),
+            "kv_free_pages": sum(g["free_pages"] for g in groups),
+            "kv_total_bytes": self.pools.bytes(),
+            "groups": groups,
+            "generations": self.generations,
+            "failed": self.failed,
+        }

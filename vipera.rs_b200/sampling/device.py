@@ -1,0 +1,91 @@
+"""Sampling on the device from the logits of a step, row by row as the scheduler's plan
+says: penalties, then greedy or temperature with top-k, top-p and min-p.  Only the drawn
+token ids (and a status per row) come back to the host."""
+from __future__ import annotations
+
+from typing import List
+
+import numpy as np
+import torch
+
+from ..build import runtime_module
+from ..errors import InternalError
+from ..kernels import ops
+
+
+class DeviceSampler:
+    def __init__(self, device):
+        self.device = device
+        self._tokens = torch.empty(4096, dtype=torch.int32, device=device)
+        self._status = torch.empty(4096, dtype=torch.int32, device=device)
+        self._host = torch.empty(2, 4096, dtype=torch.int32, pin_memory=True)
+
+    def draw(self, logits: torch.Tensor, plan) -> List[int]:
+        rows = logits.shape[0]
+        if rows > self._tokens.numel():
+            raise InternalError(f"{rows} rows to sample exceed the sampler's 4096")
+        if plan.any_penalty:
+            self._penalties(logits, plan)
+        tokens, status = self._tokens[:rows], self._status[:rows]
+        if plan.all_greedy:
+            ops.argmax(logits, tokens, status)
+        else:
+            dev = self.device
+            ops.sample(logits,
+                       temperature=torch.from_numpy(plan.row_temperature).to(dev, non_blocking=True),
+                       top_k=torch.from_numpy(plan.row_top_k).to(dev, non_blocking=True),
+                       top_p=torch.from_numpy(plan.row_top_p).to(dev, non_blocking=True),
+                       min_p=torch.from_numpy(plan.row_min_p).to(dev, non_blocking=True),
+                       uniform=torch.from_numpy(plan.row_uniform).to(dev, non_blocking=True),
+                       tokens=tokens, status=status)
+        self._host[0, :rows].copy_(tokens, non_blocking=True)
+        self._host[1, :rows].copy_(status, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        drawn = self._host[0, :rows].tolist()
+        codes = self._host[1, :rows].tolist()
+        for row, code in enumerate(codes):
+            if code == ops.SAMPLE_OK:
+                continue
+            if code == ops.SAMPLE_NEEDS_HOST:
+                drawn[row] = self._host_draw(logits[row], plan, row)
+            elif code == ops.SAMPLE_NO_FINITE:
+                raise InternalError("no finite logits to sample from")
+            else:
+                raise InternalError("the distribution has no mass")
+        return drawn
+
+    def _host_draw(self, row_logits: torch.Tensor, plan, row: int) -> int:
+        # Penalties were already applied to the row on the device.
+        config = {"temperature": float(plan.row_temperature[row]), "top_k": int(plan.row_top_k[row]),
+                  "top_p": float(plan.row_top_p[row]), "min_p": float(plan.row_min_p[row])}
+        return int(runtime_module().draw_temperature(row_logits.cpu().numpy(), config, [],
+                                                     float(plan.row_uniform[row])))
+
+    def _penalties(self, logits: torch.Tensor, plan) -> None:
+        rows = logits.shape[0]
+        entry_row, entry_id, entry_count, entry_bias = [], [], [], []
+        repetition = np.ones(rows, dtype=np.float32)
+        presence = np.zeros(rows, dtype=np.float32)
+        frequency = np.zeros(rows, dtype=np.float32)
+        for row in range(rows):
+            ids, counts, rep, pres, freq, bias = plan.row_penalty(row)
+            repetition[row], presence[row], frequency[row] = rep, pres, freq
+            merged = {int(i): [int(c), 0.0] for i, c in zip(ids, counts)}
+            for token, value in bias:
+                merged.setdefault(int(token), [0, 0.0])[1] = float(value)
+            for token, (count, value) in merged.items():
+                entry_row.append(row)
+                entry_id.append(token)
+                entry_count.append(count)
+                entry_bias.append(value)
+        if not entry_row:
+            return
+        dev = self.device
+        ops.apply_penalties(
+            logits,
+            entry_row=torch.tensor(entry_row, dtype=torch.int32, device=dev),
+            entry_id=torch.tensor(entry_id, dtype=torch.int32, device=dev),
+            entry_count=torch.tensor(entry_count, dtype=torch.int32, device=dev),
+            entry_bias=torch.tensor(entry_bias, dtype=torch.float32, device=dev),
+            repetition=torch.from_numpy(repetition).to(dev), presence=torch.from_numpy(presence).to(dev),
+            frequency=torch.from_numpy(frequency).to(dev))
