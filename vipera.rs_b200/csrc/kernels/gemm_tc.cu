@@ -1,0 +1,587 @@
+// bfloat16 matrix products on the fifth-generation tensor cores: out[T, N] = A[T, K] . W[N, K]^T
+// with 32-bit accumulation in tensor memory, operands brought to shared memory by TMA.
+//
+// One persistent kernel serves prefill and decode.  Both operands are K-major, so either
+// may sit on the 128-row side of the tcgen05 instruction:
+//   * many tokens (T >= 128): tokens on the 128-row side, 256 (or 128) weight rows on the
+//     other side;
+//   * few tokens (decode, short portions): weight rows on the 128-row side and the tokens,
+//     padded to 16/32/64/128, on the other side.  Each weight byte is read from HBM once and
+//     the K range is cut into splits so that every SM streams a share of the weights; the
+//     last block to finish a tile adds the splits' partial sums in a fixed order.
+// The reference multiplies every weight matrix by all rows of the batch in one pass over the
+// weights (crates/vipera-backend-cpu/src/model.rs:1005-1025, 1154-1198) and has a device
+// kernel that shares one weight read between up to 8 activation sets
+// (crates/vipera-backend-gpu/src/q4k_matvec_q8_batch.cu:40-116); this kernel is that idea on
+// tcgen05.
+//
+// Roles inside a block of 192 threads: warps 0-3 read accumulators from tensor memory and
+// write the ending; one thread of warp 4 issues TMA loads; one thread of warp 5 issues
+// tcgen05.mma.  Two accumulators alternate, so that the ending of one tile overlaps the
+// products of the next.  Every wait on an mbarrier is bounded: when it runs out the block
+// records an error code, stops waiting anywhere, drains and frees its tensor memory, and
+// the launcher's caller finds the code in the status word.
+//
+// Endings (as in gemm_simt.cu): STORE (+bias) as float32 or bfloat16, RESIDUAL (add into
+// the 32-bit residual stream), SWIGLU over gate and up rows interleaved in groups of 16.
+#include <cuda.h>
+
+#include "common.cuh"
+
+enum GemmEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2 };
+enum { GEMM_TC_WAIT_EXPIRED = 1 };
+
+constexpr int kBlockK = 64;        // bf16 elements per k-block: one 128-byte swizzle row
+constexpr int kTileX = 128;        // rows on the 128-row side of the instruction
+constexpr int kThreads = 192;
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+struct GemmParams {
+  int tokens;        // T
+  int features;      // N (for SWIGLU: interleaved gate+up rows)
+  int num_k_blocks;
+  int tiles_x, tiles_y, splits, k_blocks_per_split;
+  int epilogue;
+  int out_dtype;
+  const float* bias;
+  void* out;
+  float* resid;
+  float* scratch;    // split partials: [item][BN][128] floats
+  int* counters;     // one per tile, zero between launches
+  int* status;       // device word: 0, or an error code
+};
+
+// ---------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
+// Bounded wait.  When the limit runs out, or another thread's wait already did, the caller
+// goes on as if the barrier had completed: every role then runs to its end without waiting,
+// so the block drains; what it writes is marked invalid by the status word.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  for (uint32_t spin = 0; spin < kWaitLimit; ++spin) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((spin & 1023u) == 1023u && *abort_flag) return;
+  }
+  *abort_flag = 1;
+  atomicExch(status, GEMM_TC_WAIT_EXPIRED);
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_load_16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
+// bytes, 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);  // start address
+  desc |= static_cast<uint64_t>(1) << 16;                  // leading byte offset (unused with swizzle)
+  desc |= static_cast<uint64_t>(1024 >> 4) << 32;          // stride byte offset
+  desc |= static_cast<uint64_t>(1) << 46;                  // version
+  desc |= static_cast<uint64_t>(2) << 61;                  // SWIZZLE_128B
+  return desc;
+}
+
+__device__ __forceinline__ float silu_mul(float gate, float up) { return up * (gate / (1.0f + __expf(-gate))); }
+
+template <int BN>
+struct TileConfig {
+  static constexpr int kStageBytes = (kTileX + BN) * kBlockK * 2;
+  static constexpr int kStagesRaw = (200 * 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+// ---------------------------------------------------------------------------------------
+// the ending of one tile, by the four epilogue warps
+// ---------------------------------------------------------------------------------------
+// SWAP = false: accumulator rows are tokens, columns are features.
+// SWAP = true : accumulator rows are features, columns are tokens.
+template <int BN, bool SWAP>
+__device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v, int width, int row, int col0) {
+  // `row`: global index on the 128-row side; `col0`: global index of v[0] on the other side.
+  const int N = p.features;
+  if (!SWAP) {
+    const int t = row;
+    if (t >= p.tokens) return;
+    if (p.epilogue == EPI_SWIGLU) {
+      // columns [col0, col0+16) are gate, [col0+16, col0+32) up, of features col0/2 ..
+      const int inter = N >> 1;
+      const int f0 = col0 >> 1;
+      __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(t) * inter + f0;
+      float* dst32 = static_cast<float*>(p.out) + static_cast<size_t>(t) * inter + f0;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        if (col0 + 16 + i >= N) break;
+        const float value = silu_mul(v[i], v[16 + i]);
+        if (p.out_dtype == VIPERA_BF16) dst[i] = __float2bfloat16_rn(value); else dst32[i] = value;
+      }
+      return;
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (i >= width) break;
+      const int n = col0 + i;
+      if (n >= N) break;
+      const size_t at = static_cast<size_t>(t) * N + n;
+      if (p.epilogue == EPI_RESIDUAL) {
+        p.resid[at] += v[i];
+      } else {
+        const float value = v[i] + (p.bias ? p.bias[n] : 0.0f);
+        if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
+        else static_cast<float*>(p.out)[at] = value;
+      }
+    }
+  } else {
+    const int n = row;
+    const int lane = threadIdx.x & 31;
+    if (p.epilogue == EPI_SWIGLU) {
+      // lanes 0-15 of a warp hold gate rows, lanes 16-31 the up rows of the same features
+      const int inter = N >> 1;
+      const int f = ((n - lane) >> 1) + (lane & 15);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (i >= width) break;
+        const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+        const int t = col0 + i;
+        if (lane < 16 && t < p.tokens && n + 16 < N) {
+          const float value = silu_mul(v[i], other);
+          const size_t at = static_cast<size_t>(t) * inter + f;
+          if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
+          else static_cast<float*>(p.out)[at] = value;
+        }
+      }
+      return;
+    }
+    if (n >= N) return;
+    const float bias = (p.epilogue == EPI_STORE && p.bias) ? p.bias[n] : 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (i >= width) break;
+      const int t = col0 + i;
+      if (t >= p.tokens) break;
+      const size_t at = static_cast<size_t>(t) * N + n;
+      if (p.epilogue == EPI_RESIDUAL) {
+        p.resid[at] += v[i];
+      } else {
+        const float value = v[i] + bias;
+        if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
+        else static_cast<float*>(p.out)[at] = value;
+      }
+    }
+  }
+}
+
+template <int BN, bool SWAP>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+               const GemmParams p) {
+  using Config = TileConfig<BN>;
+  constexpr int kStages = Config::kStages;
+  constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                              (static_cast<uint32_t>(kTileX >> 4) << 24);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Config::kStageBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kStages;
+  uint64_t* acc_full = bars + 2 * kStages;
+  uint64_t* acc_empty = bars + 2 * kStages + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Config::kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_items = p.tiles_x * p.tiles_y * p.splits;
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+        const int split = item % p.splits;
+        const int tile = item / p.splits;
+        const int tx = tile % p.tiles_x, ty = tile / p.tiles_x;
+        const int kb_begin = split * p.k_blocks_per_split;
+        const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status);
+          uint8_t* x_tile = tiles + stage * Config::kStageBytes;
+          uint8_t* y_tile = x_tile + kTileX * kBlockK * 2;
+          mbar_expect_tx(&full[stage], Config::kStageBytes);
+          tma_load_2d(x_tile, &map_x, &full[stage], kb * kBlockK, tx * kTileX);
+          tma_load_2d(y_tile, &map_y, &full[stage], kb * kBlockK, ty * BN);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++local) {
+        const int split = item % p.splits;
+        const int kb_begin = split * p.k_blocks_per_split;
+        const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status);
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          mbar_wait(&full[stage], phase, abort_flag, p.status);
+          tcgen05_fence_after();
+          const uint32_t x_addr = smem_u32(tiles + stage * Config::kStageBytes);
+          const uint32_t y_addr = x_addr + kTileX * kBlockK * 2;
+          const uint64_t x_desc = smem_desc_sw128(x_addr);
+          const uint64_t y_desc = smem_desc_sw128(y_addr);
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k) {
+            // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in the address field
+            tcgen05_mma_bf16(d_tmem, x_desc + static_cast<uint64_t>(2 * k), y_desc + static_cast<uint64_t>(2 * k),
+                             kIdesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(&empty[stage]);  // the stage is free once these products have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        tcgen05_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    // ---------------- epilogue warps 0..3 ----------------
+    int local = 0;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++local) {
+      const int tile = item / p.splits;
+      const int tx = tile % p.tiles_x, ty = tile / p.tiles_x;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status);
+      tcgen05_fence_after();
+      const int row_in_tile = warp * 32 + lane;
+      const int row = tx * kTileX + row_in_tile;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      if (p.splits == 1) {
+        if (BN >= 32) {
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 32) {
+            float v[32];
+            tmem_load_32(taddr + c, v);
+            finish_chunk<BN, SWAP>(p, v, 32, row, ty * BN + c);
+          }
+        } else {
+          float v[32];
+          tmem_load_16(taddr, v);
+          finish_chunk<BN, SWAP>(p, v, 16, row, ty * BN);
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      } else {
+        // split partial: scratch[item][column][row_in_tile]
+        float* part = p.scratch + static_cast<size_t>(item) * BN * kTileX;
+        if (BN >= 32) {
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 32) {
+            float v[32];
+            tmem_load_32(taddr + c, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) __stcg(part + static_cast<size_t>(c + i) * kTileX + row_in_tile, v[i]);
+          }
+        } else {
+          float v[32];
+          tmem_load_16(taddr, v);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) __stcg(part + static_cast<size_t>(i) * kTileX + row_in_tile, v[i]);
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        // the last block to finish this tile adds the partials, split 0 first
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 0) {
+          const int seen = atomicAdd(&p.counters[tile], 1);
+          *last_flag = (seen == p.splits - 1) ? 1 : 0;
+          if (seen == p.splits - 1) p.counters[tile] = 0;  // ready for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag) {
+          __threadfence();
+          const float* first = p.scratch + static_cast<size_t>(tile) * p.splits * BN * kTileX;
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 32) {
+            float v[32];
+            const int width = BN - c < 32 ? BN - c : 32;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+            for (int s = 0; s < p.splits; ++s) {
+              const float* src = first + static_cast<size_t>(s) * BN * kTileX;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < width) v[i] += __ldcg(src + static_cast<size_t>(c + i) * kTileX + row_in_tile);
+            }
+            finish_chunk<BN, SWAP>(p, v, width, row, ty * BN + c);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // Loads this block issued may still be landing in its shared memory: give them time.
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 0) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Config::kTmemCols));
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool looked = false;
+  if (!looked) {
+    looked = true;
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(entry);
+  }
+  return fn;
+}
+
+// A [rows, K] bf16 row-major matrix, read in boxes of [box_rows, 64] with 128-byte swizzle;
+// rows and K beyond the matrix read as zero.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (!encode) return VIPERA_NO_DRIVER_ENTRY;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? VIPERA_OK : VIPERA_BAD_ARGUMENT;
+}
+
+struct GemmPlan {
+  bool swap;
+  int bn;
+  int tiles_x, tiles_y, splits, k_blocks_per_split, num_k_blocks;
+  size_t scratch_floats;
+  int counters;
+};
+
+static int sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+    if (count <= 0) count = 148;
+  }
+  return count;
+}
+
+static GemmPlan make_plan(int T, int N, int K, int sms) {
+  GemmPlan plan{};
+  plan.num_k_blocks = (K + kBlockK - 1) / kBlockK;
+  if (T >= 128 + 64) {
+    plan.swap = false;
+    plan.bn = (N >= 256) ? 256 : 128;
+    plan.tiles_x = (T + kTileX - 1) / kTileX;
+    plan.tiles_y = (N + plan.bn - 1) / plan.bn;
+    plan.splits = 1;
+    plan.k_blocks_per_split = plan.num_k_blocks;
+  } else {
+    plan.swap = true;
+    plan.bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    plan.tiles_x = (N + kTileX - 1) / kTileX;
+    plan.tiles_y = (T + plan.bn - 1) / plan.bn;
+    const int tiles = plan.tiles_x * plan.tiles_y;
+    int want = sms / tiles;
+    if (want < 1) want = 1;
+    if (want > plan.num_k_blocks) want = plan.num_k_blocks;
+    plan.k_blocks_per_split = (plan.num_k_blocks + want - 1) / want;
+    plan.splits = (plan.num_k_blocks + plan.k_blocks_per_split - 1) / plan.k_blocks_per_split;
+  }
+  plan.counters = plan.tiles_x * plan.tiles_y;
+  plan.scratch_floats = plan.splits > 1
+      ? static_cast<size_t>(plan.tiles_x) * plan.tiles_y * plan.splits * plan.bn * kTileX : 0;
+  return plan;
+}
+
+// Bytes of scratch and number of counters a product of these sizes needs (0 when it runs
+// without splits).  The counters must be zero before the first launch; every launch leaves
+// them zero.
+VIPERA_API int vipera_gemm_tc_workspace(int T, int N, int K, size_t* scratch_bytes, int* counters) {
+  const GemmPlan plan = make_plan(T, N, K, sm_count());
+  *scratch_bytes = plan.scratch_floats * sizeof(float);
+  *counters = plan.splits > 1 ? plan.counters : 0;
+  return VIPERA_OK;
+}
+
+template <int BN, bool SWAP>
+static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, const GemmParams& p, int grid, cudaStream_t s) {
+  using Config = TileConfig<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, Config::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  gemm_tc_kernel<BN, SWAP><<<grid, kThreads, Config::kSmemBytes, s>>>(map_x, map_y, p);
+  return vipera_launch_status();
+}
+
+// A is [T, K] bfloat16, W is [N, K] bfloat16, both row-major and contiguous with K a
+// multiple of 8 (TMA needs 16-byte row strides).  `status` is a device word that must be 0
+// before the launch; it is non-zero afterwards when a bounded wait inside the kernel ran out.
+VIPERA_API int vipera_gemm_tc(const void* A, const void* W, int T, int N, int K, int epilogue, const float* bias,
+                              void* out, int out_dtype, float* resid, float* scratch, size_t scratch_bytes,
+                              int* counters, int num_counters, int* status, void* stream) {
+  if (T <= 0) return VIPERA_OK;
+  if (N <= 0 || K <= 0 || (K % 8) != 0) return VIPERA_BAD_SHAPE;
+  if (epilogue == EPI_SWIGLU && (N % 32) != 0) return VIPERA_BAD_SHAPE;
+  if (out_dtype != VIPERA_F32 && out_dtype != VIPERA_BF16) return VIPERA_BAD_DTYPE;
+  if ((epilogue == EPI_RESIDUAL && !resid) || (epilogue != EPI_RESIDUAL && !out) || !status) return VIPERA_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return VIPERA_BAD_ARGUMENT;
+  const int sms = sm_count();
+  const GemmPlan plan = make_plan(T, N, K, sms);
+  if (plan.splits > 1) {
+    if (!scratch || !counters || scratch_bytes < plan.scratch_floats * sizeof(float) || num_counters < plan.counters)
+      return VIPERA_BAD_ARGUMENT;
+  }
+  CUtensorMap map_x, map_y;
+  int r;
+  if (plan.swap) {
+    if ((r = make_map(&map_x, W, N, K, kTileX)) != VIPERA_OK) return r;
+    if ((r = make_map(&map_y, A, T, K, plan.bn)) != VIPERA_OK) return r;
+  } else {
+    if ((r = make_map(&map_x, A, T, K, kTileX)) != VIPERA_OK) return r;
+    if ((r = make_map(&map_y, W, N, K, plan.bn)) != VIPERA_OK) return r;
+  }
+  GemmParams p{};
+  p.tokens = T;
+  p.features = N;
+  p.num_k_blocks = plan.num_k_blocks;
+  p.tiles_x = plan.tiles_x;
+  p.tiles_y = plan.tiles_y;
+  p.splits = plan.splits;
+  p.k_blocks_per_split = plan.k_blocks_per_split;
+  p.epilogue = epilogue;
+  p.out_dtype = out_dtype;
+  p.bias = bias;
+  p.out = out;
+  p.resid = resid;
+  p.scratch = scratch;
+  p.counters = counters;
+  p.status = status;
+  const int items = plan.tiles_x * plan.tiles_y * plan.splits;
+  const int grid = items < sms ? items : sms;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!plan.swap) {
+    if (plan.bn == 256) return launch_variant<256, false>(map_x, map_y, p, grid, s);
+    return launch_variant<128, false>(map_x, map_y, p, grid, s);
+  }
+  switch (plan.bn) {
+    case 16: return launch_variant<16, true>(map_x, map_y, p, grid, s);
+    case 32: return launch_variant<32, true>(map_x, map_y, p, grid, s);
+    case 64: return launch_variant<64, true>(map_x, map_y, p, grid, s);
+    case 128: return launch_variant<128, true>(map_x, map_y, p, grid, s);
+    default: return launch_variant<256, true>(map_x, map_y, p, grid, s);
+  }
+}
+
+VIPERA_API const char* vipera_gemm_tc_status_text(int status) { return vipera_status_text(status); }

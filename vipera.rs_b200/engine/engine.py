@@ -19,6 +19,7 @@ import torch
 from ..build import runtime_module
 from ..cache import CachePools
 from ..errors import InternalError, InvalidArgumentError
+from ..kernels import ops
 from ..sampling import DeviceSampler, SamplingParams
 from .loader import load_model
 from .runner import ModelRunner, StepInput
@@ -115,6 +116,7 @@ class Engine:
                 sampled = self.sampler.draw(logits, plan) if logits is not None else []
                 if logits is None:
                     torch.cuda.current_stream().synchronize()
+                ops.check_kernel_status(self.model.device)
                 outcome = self.scheduler.complete(plan, sampled)
             except InternalError:
                 outcome = self.scheduler.fail(plan)

@@ -14,6 +14,7 @@ import torch
 
 from ..cache import CachePools
 from ..errors import InvalidArgumentError
+from ..kernels import ops
 from .loader import load_model
 from .runner import ModelRunner, StepInput
 
@@ -68,6 +69,7 @@ class Replayer:
                 result = logits.cpu().numpy()
             else:
                 torch.cuda.synchronize(self.model.device)
+            ops.check_kernel_status(self.model.device)
             for number, count, first in zip(requests, counts, pos0):
                 manager.commit(number, first + count)
         for name in end:

@@ -14,6 +14,7 @@ import os
 import struct
 from typing import Dict, Iterable, List, Tuple
 
+import numpy as np
 import torch
 
 from ..errors import IoError, ParseError, UnsupportedError
@@ -96,8 +97,8 @@ class SafetensorsFile:
             count *= extent
         if count == 0:
             return torch.empty(shape, dtype=dtype)
-        view = torch.frombuffer(self._map, dtype=dtype, count=count, offset=self._base + begin)
-        return view.reshape(shape).clone()
+        raw = np.frombuffer(self._map, dtype=np.uint8, count=end - begin, offset=self._base + begin).copy()
+        return torch.from_numpy(raw).view(dtype).reshape(shape)
 
     def close(self) -> None:
         try:
