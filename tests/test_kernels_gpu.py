@@ -1,0 +1,391 @@
+"""Each kernel alone against a plain float32/float64 reference of the same operation, at
+sizes other than the engine's configurations."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _ops():
+    import vipera_rs_b200  # noqa: F401
+    from vipera_rs_b200.kernels import ops
+
+    return ops
+
+
+def _rel(got, want):
+    return float((got.double() - want.double()).abs().max() / want.double().abs().max())
+
+
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,hidden", [(1, 16), (5, 250), (33, 1536), (3, 5000)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(rows, hidden, dtype):
+    ops = _ops()
+    torch.manual_seed(rows * 1000 + hidden)
+    x = torch.randn(rows, hidden, device=DEV) * 3
+    w = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    out = torch.empty(rows, hidden, device=DEV, dtype=dtype)
+    ops.rmsnorm(x, w, out, 1e-5)
+    xd = x.double()
+    want = xd * (1.0 / torch.sqrt((xd * xd).mean(-1, keepdim=True) + 1e-5)) * w.double()
+    assert _rel(out, want) < (1e-6 if dtype == torch.float32 else 5e-3)
+    # a choice of rows
+    pick = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, hidden, device=DEV, dtype=dtype)
+    ops.rmsnorm(x, w, out2, 1e-5, rows=pick)
+    assert torch.equal(out2, out[[rows - 1, 0]])
+
+
+@pytest.mark.parametrize("table_dtype", [torch.float32, torch.bfloat16])
+def test_embed(table_dtype):
+    ops = _ops()
+    torch.manual_seed(1)
+    table = torch.randn(777, 120, device=DEV).to(table_dtype)
+    tokens = torch.tensor([0, 776, 5, 5, 300], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 120, device=DEV)
+    ops.embed(table, tokens, out)
+    assert torch.equal(out, table[tokens.long()].float())
+
+
+# ---------------------------------------------------------------------------------------
+def _gemm_reference(a, w, epilogue, bias, resid0):
+    y = a.double() @ w.double().T
+    if epilogue == 0:
+        return y + (bias.double() if bias is not None else 0)
+    if epilogue == 1:
+        return resid0.double() + y
+    m, n = y.shape
+    y = y.view(m, n // 32, 2, 16)
+    gate, up = y[:, :, 0], y[:, :, 1]
+    return (up * (gate / (1 + torch.exp(-gate)))).reshape(m, n // 2)
+
+
+GEMM_SHAPES = [(1, 48, 40), (3, 130, 72), (17, 1003, 384), (70, 96, 1000), (129, 352, 136), (300, 672, 264)]
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+@pytest.mark.parametrize("epilogue", [0, 1, 2])
+@pytest.mark.parametrize("kind", ["simt_f32", "simt_bf16", "tc_bf16"])
+def test_gemm(m, n, k, epilogue, kind):
+    ops = _ops()
+    if epilogue == 2:
+        n = (n + 31) // 32 * 32
+    torch.manual_seed(m * 7 + n * 3 + k)
+    dtype = torch.float32 if kind == "simt_f32" else torch.bfloat16
+    a = (torch.randn(m, k, device=DEV) * 0.5).to(dtype)
+    w = (torch.randn(n, k, device=DEV) * 0.1).to(dtype)
+    bias = torch.randn(n, device=DEV)
+    resid0 = torch.randn(m, n, device=DEV)
+    fn = ops.gemm_tc if kind == "tc_bf16" else ops.gemm_simt
+    if epilogue == 0:
+        out = torch.full((m, n), float("nan"), device=DEV)
+        fn(a, w, epilogue=0, bias=bias, out=out)
+    elif epilogue == 1:
+        out = resid0.clone()
+        fn(a, w, epilogue=1, resid=out)
+    else:
+        out = torch.full((m, n // 2), float("nan"), device=DEV, dtype=dtype)
+        fn(a, w, epilogue=2, out=out)
+    torch.cuda.synchronize()
+    ops.check_kernel_status(a.device)
+    want = _gemm_reference(a, w, epilogue, bias, resid0)
+    limit = 2e-6 if kind == "simt_f32" else (5e-3 if epilogue == 2 else 2e-5)
+    assert _rel(out, want) < limit
+
+
+def test_gemm_tc_repeats_exactly_and_counters_return_to_zero():
+    """Split sums are added in a fixed order: the same product twice gives the same bits."""
+    ops = _ops()
+    torch.manual_seed(5)
+    a = torch.randn(8, 8960, device=DEV).bfloat16()
+    w = (torch.randn(1536, 8960, device=DEV) * 0.05).bfloat16()
+    outs = []
+    for _ in range(3):
+        out = torch.empty(8, 1536, device=DEV)
+        ops.gemm_tc(a, w, out=out)
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    # a row's result does not depend on the rows beside it
+    alone = torch.empty(1, 1536, device=DEV)
+    ops.gemm_tc(a[3:4].contiguous(), w, out=alone)
+    assert _rel(alone, outs[0][3:4]) < 1e-5
+
+
+# ---------------------------------------------------------------------------------------
+def _paged_case(entries, heads, kv_heads, d, page, dtype, seed, window=0, lengths=None, counts=None):
+    """Random q and a paged cache whose pages are handed out in a shuffled order."""
+    g = torch.Generator().manual_seed(seed)
+    lengths = lengths or [int(torch.randint(1, 300, (1,), generator=g)) for _ in range(entries)]
+    counts = counts or [1] * entries
+    total_pages = sum((n + page - 1) // page for n in lengths) + 3
+    order = torch.randperm(total_pages, generator=g).tolist()
+    width = max((n + page - 1) // page for n in lengths)
+    table = torch.full((entries, width), -1, dtype=torch.int32)
+    k_pool = torch.full((total_pages, page, kv_heads, d), float("nan"))
+    v_pool = torch.full((total_pages, page, kv_heads, d), float("nan"))
+    keys, values = [], []
+    for e, n in enumerate(lengths):
+        k = torch.randn(n, kv_heads, d, generator=g)
+        v = torch.randn(n, kv_heads, d, generator=g)
+        keys.append(k.to(dtype).float())
+        values.append(v.to(dtype).float())
+        for p in range((n + page - 1) // page):
+            physical = order.pop()
+            table[e, p] = physical
+            rows = slice(p * page, min(n, (p + 1) * page))
+            k_pool[physical, : rows.stop - rows.start] = keys[e][rows]
+            v_pool[physical, : rows.stop - rows.start] = values[e][rows]
+    total = sum(counts)
+    q = torch.randn(total, heads, d, generator=g).to(dtype).float()
+    return lengths, counts, table, k_pool.to(dtype), v_pool.to(dtype), keys, values, q
+
+
+def _attention_reference(q, keys, values, lengths, counts, heads, kv_heads, scale, window):
+    out = torch.zeros_like(q, dtype=torch.float64)
+    group = heads // kv_heads
+    t = 0
+    for e, (n, c) in enumerate(zip(lengths, counts)):
+        for i in range(c):
+            position = n - c + i
+            first = max(0, position - window + 1) if window else 0
+            for h in range(heads):
+                k = keys[e][first:position + 1, h // group].double()
+                v = values[e][first:position + 1, h // group].double()
+                s = (k @ q[t, h].double()) * scale
+                w = torch.softmax(s, dim=0)
+                out[t, h] = w @ v
+            t += 1
+    return out
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,page", [(4, 2, 64, 16), (3, 1, 128, 32), (5, 5, 48, 8), (8, 2, 80, 64),
+                                                   (12, 2, 128, 16), (16, 1, 64, 16), (20, 1, 64, 32)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 37])
+def test_attention_single_tokens(heads, kv_heads, d, page, dtype, window):
+    """One query per entry (decode): the general kernel and, where built, the split-key
+    tensor-core kernel."""
+    ops = _ops()
+    entries = 5
+    lengths, counts, table, k_pool, v_pool, keys, values, q = _paged_case(
+        entries, heads, kv_heads, d, page, dtype, seed=heads * 100 + d, lengths=[1, 33, 300, 129, 64])
+    scale = 1.0 / math.sqrt(d)
+    want = _attention_reference(q, keys, values, lengths, counts, heads, kv_heads, scale, window)
+    qd = q.to(dtype).reshape(entries, heads * d).to(DEV)
+    kp, vp, tb = k_pool.to(DEV), v_pool.to(DEV), table.to(DEV)
+    positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+    token_seq = torch.arange(entries, dtype=torch.int32, device=DEV)
+    out = torch.full_like(qd, float("nan"))
+    ops.attention(qd, out, kp, vp, token_seq=token_seq, positions=positions, block_table=tb, num_heads=heads,
+                  num_kv_heads=kv_heads, head_dim=d, scale=scale, window=window)
+    limit = 2e-6 if dtype == torch.float32 else 1e-2
+    assert _rel(out.float().cpu().view(entries, heads, d), want) < limit
+    if dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS:
+        for chunk_splits in (ops.decode_splits(entries, kv_heads, max(lengths)), (32, 10), (512, 1)):
+            chunk, splits = chunk_splits
+            scratch = torch.full((ops.attention_decode_scratch_floats(entries, heads, d, splits),), float("nan"),
+                                 device=DEV)
+            out2 = torch.full_like(qd, float("nan"))
+            ops.attention_decode(qd, out2, kp, vp, positions=positions, block_table=tb, num_heads=heads,
+                                 num_kv_heads=kv_heads, head_dim=d, scale=scale, window=window, chunk=chunk,
+                                 num_splits=splits, scratch=scratch)
+            assert _rel(out2.float().cpu().view(entries, heads, d), want) < limit, chunk_splits
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,page", [(4, 2, 64, 16), (3, 1, 128, 32), (5, 5, 48, 8), (12, 2, 128, 64)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 50])
+def test_attention_portions(heads, kv_heads, d, page, dtype, window):
+    """Entries that bring several tokens at the end of what is cached (prefill portions),
+    mixed with a single-token entry."""
+    ops = _ops()
+    lengths = [70, 200, 131, 64, 5]
+    counts = [70, 67, 1, 2, 5]
+    entries = len(lengths)
+    lengths, counts, table, k_pool, v_pool, keys, values, q = _paged_case(
+        entries, heads, kv_heads, d, page, dtype, seed=heads * 10 + d, lengths=lengths, counts=counts)
+    scale = 1.0 / math.sqrt(d)
+    want = _attention_reference(q, keys, values, lengths, counts, heads, kv_heads, scale, window)
+    total = sum(counts)
+    qd = q.to(dtype).reshape(total, heads * d).to(DEV)
+    kp, vp, tb = k_pool.to(DEV), v_pool.to(DEV), table.to(DEV)
+    positions, token_seq = [], []
+    for e, (n, c) in enumerate(zip(lengths, counts)):
+        positions += list(range(n - c, n))
+        token_seq += [e] * c
+    positions = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    token_seq = torch.tensor(token_seq, dtype=torch.int32, device=DEV)
+    out = torch.full_like(qd, float("nan"))
+    ops.attention(qd, out, kp, vp, token_seq=token_seq, positions=positions, block_table=tb, num_heads=heads,
+                  num_kv_heads=kv_heads, head_dim=d, scale=scale, window=window)
+    limit = 2e-6 if dtype == torch.float32 else 1e-2
+    assert _rel(out.float().cpu().view(total, heads, d), want) < limit
+    if dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS:
+        starts = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=DEV)
+        pos0 = torch.tensor([n - c for n, c in zip(lengths, counts)], dtype=torch.int32, device=DEV)
+        out2 = torch.full_like(qd, float("nan"))
+        ops.attention_prefill(qd, out2, kp, vp, entry_starts=starts, entry_pos0=pos0, block_table=tb,
+                              num_entries=entries, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
+                              scale=scale, window=window)
+        assert _rel(out2.float().cpu().view(total, heads, d), want) < limit
+
+
+def test_attention_finds_one_far_key():
+    """Random keys hide a fault at a single position: scale one far key and the query so
+    that its score stands out, in a page of its own, and check that the output is its value."""
+    ops = _ops()
+    heads, kv_heads, d, page = 4, 2, 64, 16
+    for dtype in (torch.float32, torch.bfloat16):
+        for far in (0, 15, 16, 255, 256, 511):
+            n = 600
+            lengths, counts, table, k_pool, v_pool, keys, values, q = _paged_case(
+                1, heads, kv_heads, d, page, dtype, seed=far + 1, lengths=[n])
+            direction = torch.nn.functional.normalize(torch.randn(d), dim=0)
+            q[0, :] = direction * 40
+            physical = int(table[0, far // page])
+            k_pool[physical, far % page, :] = (direction * 40).to(dtype)
+            marker = torch.full((kv_heads, d), 7.0)
+            v_pool[physical, far % page] = marker.to(dtype)
+            qd = q.to(dtype).reshape(1, heads * d).to(DEV)
+            kp, vp, tb = k_pool.to(DEV), v_pool.to(DEV), table.to(DEV)
+            positions = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+            out = torch.empty_like(qd)
+            ops.attention(qd, out, kp, vp, token_seq=torch.zeros(1, dtype=torch.int32, device=DEV),
+                          positions=positions, block_table=tb, num_heads=heads, num_kv_heads=kv_heads,
+                          head_dim=d, scale=1.0, window=0)
+            assert torch.allclose(out.float().cpu(), torch.full((1, heads * d), 7.0), atol=0.05), (dtype, far)
+            if dtype == torch.bfloat16:
+                chunk, splits = 128, 5
+                scratch = torch.empty(ops.attention_decode_scratch_floats(1, heads, d, splits), device=DEV)
+                out2 = torch.empty_like(qd)
+                ops.attention_decode(qd, out2, kp, vp, positions=positions, block_table=tb, num_heads=heads,
+                                     num_kv_heads=kv_heads, head_dim=d, scale=1.0, window=0, chunk=chunk,
+                                     num_splits=splits, scratch=scratch)
+                assert torch.allclose(out2.float().cpu(), torch.full((1, heads * d), 7.0), atol=0.05), far
+
+
+# ---------------------------------------------------------------------------------------
+def test_rope_cache_rotates_and_stores():
+    ops = _ops()
+    heads, kv_heads, d, page = 3, 1, 32, 8
+    tokens = 6
+    torch.manual_seed(3)
+    qkv = torch.randn(tokens, (heads + 2 * kv_heads) * d, device=DEV)
+    positions = torch.tensor([0, 1, 9, 10, 11, 40], dtype=torch.int32, device=DEV)
+    token_seq = torch.tensor([0, 0, 1, 1, 1, 2], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[2, -1, -1, -1, -1, -1], [5, 0, -1, -1, -1, -1], [1, 3, 4, 6, 7, 8]], dtype=torch.int32,
+                         device=DEV)
+    half = d // 2
+    inv = 1.0 / torch.pow(torch.tensor(10000.0), 2.0 * torch.arange(half, dtype=torch.float32) / d)
+    angle = torch.arange(64, dtype=torch.float32)[:, None] * inv[None, :]
+    cos, sin = torch.cos(angle).to(DEV), torch.sin(angle).to(DEV)
+    for dtype in (torch.float32, torch.bfloat16):
+        k_pool = torch.zeros(9, page, kv_heads, d, device=DEV, dtype=dtype)
+        v_pool = torch.zeros_like(k_pool)
+        q_out = torch.empty(tokens, heads * d, device=DEV, dtype=dtype)
+        ops.rope_cache(qkv, q_out, num_heads=heads, num_kv_heads=kv_heads, head_dim=d, positions=positions,
+                       cos=cos, sin=sin, style=ops.ROPE_NEOX, k_pool=k_pool, v_pool=v_pool, token_seq=token_seq,
+                       block_table=table, page_size=page, write_cache=True)
+        x = qkv.view(tokens, heads + 2 * kv_heads, d).cpu().double()
+        c = cos[positions.long()].cpu().double()[:, None, :]
+        s = sin[positions.long()].cpu().double()[:, None, :]
+        low, high = x[..., :half], x[..., half:]
+        rotated = torch.cat([low * c - high * s, low * s + high * c], dim=-1)
+        limit = 1e-6 if dtype == torch.float32 else 5e-3
+        assert _rel(q_out.cpu().view(tokens, heads, d), rotated[:, :heads]) < limit
+        for t in range(tokens):
+            p = int(positions[t])
+            physical = int(table[int(token_seq[t]), p // page])
+            got_k = k_pool[physical, p % page].cpu()
+            got_v = v_pool[physical, p % page].cpu()
+            assert _rel(got_k, rotated[t, heads:heads + kv_heads]) < limit
+            assert _rel(got_v, x[t, heads + kv_heads:]) < limit
+        # position 0 leaves a vector as it is
+        assert _rel(q_out[0].cpu().view(heads, d), x[0, :heads]) < limit
+
+
+# ---------------------------------------------------------------------------------------
+def test_sampler_matches_host():
+    ops = _ops()
+    from vipera_rs_b200.sampling import Rng, draw_greedy, draw_temperature
+
+    torch.manual_seed(9)
+    vocab = 5003
+    rows = 12
+    logits = torch.randn(rows, vocab) * 3
+    logits[1, 17] = float("nan")
+    logits[2, 99] = float("inf")
+    logits[3, :] = 0.25           # all equal: ties go to the lowest id
+    logits[4, 40] = logits[4, 7] = logits[4].max() + 1   # a tie at the top
+    dev = logits.to(DEV).contiguous()
+    tokens = torch.empty(rows, dtype=torch.int32, device=DEV)
+    status = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.argmax(dev, tokens, status)
+    for row in range(rows):
+        assert int(tokens[row]) == draw_greedy(logits[row].numpy())
+    assert int(tokens[3]) == 0 and int(tokens[4]) == 7
+    configs = [
+        dict(temperature=0.8, top_k=40, top_p=0.95, min_p=0.05),
+        dict(temperature=1.5, top_k=5, top_p=1.0, min_p=0.0),
+        dict(temperature=0.3, top_k=1, top_p=0.95, min_p=0.05),
+        dict(temperature=1.0, top_k=200, top_p=0.5, min_p=0.0),
+        dict(temperature=2.0, top_k=4096, top_p=0.9, min_p=0.01),
+        dict(temperature=0.0, top_k=40, top_p=0.95, min_p=0.05),
+    ]
+    rng = Rng(77)
+    for config in configs:
+        uniform = [rng.next_f64() for _ in range(rows)]
+        ops.sample(dev,
+                   temperature=torch.full((rows,), config["temperature"], device=DEV),
+                   top_k=torch.full((rows,), config["top_k"], dtype=torch.int32, device=DEV),
+                   top_p=torch.full((rows,), config["top_p"], device=DEV),
+                   min_p=torch.full((rows,), config["min_p"], device=DEV),
+                   uniform=torch.tensor(uniform, dtype=torch.float64, device=DEV), tokens=tokens, status=status)
+        for row in range(rows):
+            assert int(status[row]) == ops.SAMPLE_OK
+            if config["temperature"] == 0.0:
+                want = draw_greedy(logits[row].numpy())
+            else:
+                want = draw_temperature(logits[row].numpy(), config, [], uniform[row])
+            assert int(tokens[row]) == want, (config, row)
+
+
+def test_sampler_distribution_and_penalties():
+    """Two tokens with weights 3:1 at temperature 1 are drawn about 75 % / 25 % of the time
+    (the reference's check: 0.75 +- 0.05 over 4000 draws, crates/vipera-sampler/src/lib.rs
+    tests), and penalties change the logits as the host sampler does."""
+    ops = _ops()
+    from vipera_rs_b200.sampling import Rng
+
+    vocab, rows = 64, 4000
+    row = torch.full((vocab,), -30.0)
+    row[5] = math.log(3.0)
+    row[9] = 0.0
+    logits = row.repeat(rows, 1).contiguous().to(DEV)
+    rng = Rng(3)
+    uniform = torch.tensor([rng.next_f64() for _ in range(rows)], dtype=torch.float64, device=DEV)
+    tokens = torch.empty(rows, dtype=torch.int32, device=DEV)
+    status = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(logits, temperature=torch.ones(rows, device=DEV),
+               top_k=torch.full((rows,), 40, dtype=torch.int32, device=DEV), top_p=torch.ones(rows, device=DEV),
+               min_p=torch.zeros(rows, device=DEV), uniform=uniform, tokens=tokens, status=status)
+    share = float((tokens == 5).float().mean())
+    assert abs(share - 0.75) < 0.05
+    assert int(((tokens != 5) & (tokens != 9)).sum()) == 0
+
+    logits = torch.tensor([[2.0, -1.0, 0.5, 3.0]], device=DEV)
+    ops.apply_penalties(logits, entry_row=torch.tensor([0, 0, 0], dtype=torch.int32, device=DEV),
+                        entry_id=torch.tensor([0, 1, 3], dtype=torch.int32, device=DEV),
+                        entry_count=torch.tensor([2, 1, 0], dtype=torch.int32, device=DEV),
+                        entry_bias=torch.tensor([0.0, 0.0, -100.0], device=DEV),
+                        repetition=torch.tensor([2.0], device=DEV), presence=torch.tensor([0.5], device=DEV),
+                        frequency=torch.tensor([0.25], device=DEV))
+    want = torch.tensor([[2.0 / 2 - (0.5 + 0.25 * 2), -1.0 * 2 - (0.5 + 0.25), 0.5, 3.0 - 100.0]])
+    assert torch.allclose(logits.cpu(), want)

@@ -1,0 +1,500 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16), with
+// 32-bit scores, softmax and accumulation.  Two kernels share their inner loop:
+//
+//   * prefill / mixed steps: one block per (64 queries of one entry, query head); the four
+//     warps hold 16 queries each and walk the visible keys 64 at a time with a running
+//     (max, sum, output) — the flash form of the reference's online fold
+//     (crates/vipera-backend-cpu/src/model.rs:2752-2857);
+//   * decode (one query per entry): one block per (entry, KV head, split of the keys); the
+//     query heads of the KV head's group are the rows of the tile, so that every key and
+//     value is read once for the whole group (the reference's GQA sharing, model.rs:2221-2244,
+//     crates/vipera-backend-gpu/src/layer.cu:182-292); each warp folds 32-key blocks of the
+//     split into a partial (max, sum, unnormalised output), and a second kernel combines
+//     the partials: m = max m_c, l = sum l_c e^(m_c - m), o = sum o_c e^(m_c - m) / l
+//     (layer.cu:307-467).
+//
+// Definition computed: crates/vipera-backend-cpu/src/model.rs:1804-1859 (see attention.cu).
+// Head sizes 64 and 128 are built; other sizes use the general kernel in attention.cu.
+#include "common.cuh"
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A tile of rows x D bf16 in shared memory; 16-byte chunks are XOR-swizzled by the row so
+// that ldmatrix reads eight rows without bank conflicts.
+template <int D>
+__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
+  return static_cast<uint32_t>(row * D * 2 + ((chunk ^ (row & 7)) << 4));
+}
+
+// Copy `rows` cache rows (keys first_key ..) of one KV head into a tile, through the block
+// table; rows at or beyond `end_key` are filled with zeros.  Executed by `threads` threads.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(uint32_t tile, const __nv_bfloat16* __restrict__ pool,
+                                             const int* __restrict__ table, int page_size, int num_kv_heads,
+                                             int kv_head, int first_key, int end_key, int rows, int thread,
+                                             int threads) {
+  constexpr int kChunks = D / 8;
+  for (int index = thread; index < rows * kChunks; index += threads) {
+    const int row = index / kChunks, chunk = index % kChunks;
+    const int key = first_key + row;
+    const bool valid = key < end_key;
+    const __nv_bfloat16* src = pool;
+    if (valid) {
+      const int page = table[key / page_size];
+      src = pool + ((static_cast<size_t>(page) * page_size + key % page_size) * num_kv_heads + kv_head) * D + chunk * 8;
+    }
+    cp_async_16(tile + tile_offset<D>(row, chunk), src, valid);
+  }
+}
+
+// One warp folds a block of KEYS keys into its running state for its 16 rows.
+//   q_frag: the warp's 16 x D queries as A fragments, one per 16 columns of D
+//   k_tile, v_tile: shared tiles [KEYS][D]
+//   key0: position of the tile's first key; row_limit[2]: the last visible key of the rows
+//   this thread owns (lane/4 and lane/4 + 8); row_first[2]: their first visible key.
+template <int D, int KEYS>
+__device__ __forceinline__ void fold_block(const uint32_t (&q_frag)[D / 16][4], uint32_t k_tile, uint32_t v_tile,
+                                           int key0, const int (&row_first)[2], const int (&row_limit)[2],
+                                           float scale_log2, float (&row_max)[2], float (&row_sum)[2],
+                                           float (&out)[D / 8][4]) {
+  const int lane = threadIdx.x & 31;
+  float s[KEYS / 8][4];
+#pragma unroll
+  for (int n = 0; n < KEYS / 8; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[n][i] = 0.0f;
+  // scores = q . k^T
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+    for (int np = 0; np < KEYS / 16; ++np) {
+      uint32_t b[4];
+      const int row = np * 16 + (lane & 7) + ((lane >> 4) << 3);
+      const int chunk = ks * 2 + ((lane >> 3) & 1);
+      ldmatrix_x4(b, k_tile + tile_offset<D>(row, chunk));
+      mma_16816(s[2 * np], q_frag[ks], b[0], b[1]);
+      mma_16816(s[2 * np + 1], q_frag[ks], b[2], b[3]);
+    }
+  }
+  // mask, running max
+  float block_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int n = 0; n < KEYS / 8; ++n) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int key = key0 + n * 8 + 2 * (lane & 3) + (i & 1);
+      const int r = i >> 1;
+      const bool visible = key >= row_first[r] && key <= row_limit[r];
+      s[n][i] = visible ? s[n][i] * scale_log2 : -INFINITY;
+      block_max[r] = fmaxf(block_max[r], s[n][i]);
+    }
+  }
+  float rescale[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 1));
+    block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 2));
+    const float new_max = fmaxf(row_max[r], block_max[r]);
+    // a row that has seen no visible key yet keeps max = -inf; guard the exponent
+    rescale[r] = new_max == -INFINITY ? 1.0f : exp2f(row_max[r] - new_max);
+    row_max[r] = new_max;
+  }
+  float block_sum[2] = {0.0f, 0.0f};
+#pragma unroll
+  for (int n = 0; n < KEYS / 8; ++n) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = i >> 1;
+      const float p = row_max[r] == -INFINITY ? 0.0f : exp2f(s[n][i] - row_max[r]);
+      s[n][i] = p;
+      block_sum[r] += p;
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) row_sum[r] = row_sum[r] * rescale[r] + block_sum[r];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) {
+    out[n][0] *= rescale[0];
+    out[n][1] *= rescale[0];
+    out[n][2] *= rescale[1];
+    out[n][3] *= rescale[1];
+  }
+  // out += p . v
+#pragma unroll
+  for (int kk = 0; kk < KEYS / 16; ++kk) {
+    uint32_t a[4];
+    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+    for (int np = 0; np < D / 16; ++np) {
+      uint32_t b[4];
+      const int row = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+      const int chunk = np * 2 + (lane >> 4);
+      ldmatrix_x4_trans(b, v_tile + tile_offset<D>(row, chunk));
+      mma_16816(out[2 * np], a, b[0], b[1]);
+      mma_16816(out[2 * np + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// prefill / mixed: block = (tile of 64 queries of one entry, query head)
+// ---------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(128)
+attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                         const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
+                         const int* __restrict__ entry_starts, const int* __restrict__ entry_pos0,
+                         const int* __restrict__ block_table, int table_width, int page_size, int num_entries,
+                         int num_heads, int num_kv_heads, float scale, int window) {
+  constexpr int kQ = 64, kKeys = 64;
+  extern __shared__ __align__(128) uint8_t smem[];
+  // which (entry, tile of that entry) is this block?
+  int entry = -1, tile_in_entry = 0;
+  {
+    int remaining = blockIdx.x;
+    for (int e = 0; e < num_entries; ++e) {
+      const int tiles = (entry_starts[e + 1] - entry_starts[e] + kQ - 1) / kQ;
+      if (remaining < tiles) { entry = e; tile_in_entry = remaining; break; }
+      remaining -= tiles;
+    }
+  }
+  if (entry < 0) return;
+  const int head = blockIdx.y;
+  const int kv_head = head / (num_heads / num_kv_heads);
+  const int token0 = entry_starts[entry] + tile_in_entry * kQ;
+  const int tokens_here = min(kQ, entry_starts[entry + 1] - token0);
+  const int pos0 = entry_pos0[entry] + tile_in_entry * kQ;  // position of the tile's first query
+  const int* table = block_table + static_cast<size_t>(entry) * table_width;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const uint32_t q_tile = smem_addr(smem);
+  const uint32_t k_tiles = q_tile + kQ * D * 2;
+  const uint32_t v_tiles = k_tiles + 2 * kKeys * D * 2;
+
+  // queries into shared memory (rows beyond the entry's tokens are zero)
+  {
+    constexpr int kChunks = D / 8;
+    for (int index = threadIdx.x; index < kQ * kChunks; index += 128) {
+      const int row = index / kChunks, chunk = index % kChunks;
+      const bool valid = row < tokens_here;
+      const __nv_bfloat16* src = q + (static_cast<size_t>(token0 + (valid ? row : 0)) * num_heads + head) * D + chunk * 8;
+      cp_async_16(q_tile + tile_offset<D>(row, chunk), src, valid);
+    }
+  }
+  const int last_pos = pos0 + tokens_here - 1;
+  const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int first_block = first_key / kKeys;
+  const int end_key = last_pos + 1;
+  const int num_blocks = (end_key + kKeys - 1) / kKeys - first_block;
+
+  auto load_block = [&](int block, int buffer) {
+    const int key0 = (first_block + block) * kKeys;
+    load_kv_tile<D>(k_tiles + buffer * kKeys * D * 2, k_pool, table, page_size, num_kv_heads, kv_head, key0,
+                    end_key, kKeys, threadIdx.x, 128);
+    load_kv_tile<D>(v_tiles + buffer * kKeys * D * 2, v_pool, table, page_size, num_kv_heads, kv_head, key0,
+                    end_key, kKeys, threadIdx.x, 128);
+  };
+  load_block(0, 0);
+  cp_async_commit();
+
+  uint32_t q_frag[D / 16][4];
+  float acc[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+  int row_first[2], row_limit[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp * 16 + (lane >> 2) + r * 8;
+    const int position = pos0 + row;
+    row_limit[r] = row < tokens_here ? position : -1;  // rows past the end see nothing
+    row_first[r] = window > 0 ? max(0, position - window + 1) : 0;
+  }
+  const float scale_log2 = scale * kLog2e;
+
+  for (int block = 0; block < num_blocks; ++block) {
+    const int buffer = block & 1;
+    if (block + 1 < num_blocks) load_block(block + 1, buffer ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (block == 0) {
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks)
+        ldmatrix_x4(q_frag[ks], q_tile + tile_offset<D>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+    }
+    const int key0 = (first_block + block) * kKeys;
+    // a warp whose 16 queries all stand before this block has nothing to see in it
+    if (key0 <= pos0 + warp * 16 + 15)
+      fold_block<D, kKeys>(q_frag, k_tiles + buffer * kKeys * D * 2, v_tiles + buffer * kKeys * D * 2, key0,
+                           row_first, row_limit, scale_log2, row_max, row_sum, acc);
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+  // normalise and store
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float sum = row_sum[r];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    const int row = warp * 16 + (lane >> 2) + r * 8;
+    if (row >= tokens_here) continue;
+    const float inverse = 1.0f / sum;
+    __nv_bfloat16* dst = out + (static_cast<size_t>(token0 + row) * num_heads + head) * D;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      const int col = n * 8 + 2 * (lane & 3);
+      *reinterpret_cast<__nv_bfloat162*>(dst + col) =
+          __floats2bfloat162_rn(acc[n][2 * r] * inverse, acc[n][2 * r + 1] * inverse);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// decode: block = (entry, KV head, split); rows of the tile = query heads of the group
+// ---------------------------------------------------------------------------------------
+// partial layout: [token][head][slice] with slice = split * 4 + warp; each holds
+// max (log2 units), sum, and D unnormalised outputs.
+template <int D>
+__global__ void __launch_bounds__(128)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+                        const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
+                        const int* __restrict__ block_table, int table_width, int page_size, int num_heads,
+                        int num_kv_heads, float scale, int window, int chunk, int num_splits,
+                        float* __restrict__ partial_ml, float* __restrict__ partial_out) {
+  constexpr int kKeys = 32;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int entry = blockIdx.x, kv_head = blockIdx.y, split = blockIdx.z;
+  const int group = num_heads / num_kv_heads;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int position = positions[entry];
+  const int* table = block_table + static_cast<size_t>(entry) * table_width;
+  const int first_visible = window > 0 ? max(0, position - window + 1) : 0;
+  const int begin = max(split * chunk, first_visible / kKeys * kKeys);
+  const int end = min((split + 1) * chunk, position + 1);
+
+  const uint32_t q_tile = smem_addr(smem);                       // [16][D], shared by the warps
+  const uint32_t k_tile = q_tile + 16 * D * 2 + warp * 2 * kKeys * D * 2;
+  const uint32_t v_tile = k_tile + kKeys * D * 2;
+
+  for (int m_tile = 0; m_tile * 16 < group; ++m_tile) {
+    __syncthreads();
+    {
+      constexpr int kChunks = D / 8;
+      for (int index = threadIdx.x; index < 16 * kChunks; index += 128) {
+        const int row = index / kChunks, c = index % kChunks;
+        const int head_in_group = m_tile * 16 + row;
+        const bool valid = head_in_group < group;
+        const __nv_bfloat16* src = q + (static_cast<size_t>(entry) * num_heads + kv_head * group + (valid ? head_in_group : 0)) * D + c * 8;
+        cp_async_16(q_tile + tile_offset<D>(row, c), src, valid);
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    uint32_t q_frag[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+      ldmatrix_x4(q_frag[ks], q_tile + tile_offset<D>(lane & 15, ks * 2 + (lane >> 4)));
+
+    float acc[D / 8][4];
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+    const int row_first[2] = {first_visible, first_visible};
+    const int row_limit[2] = {position, position};
+    const float scale_log2 = scale * kLog2e;
+
+    for (int key0 = begin + warp * kKeys; key0 < end; key0 += 4 * kKeys) {
+      load_kv_tile<D>(k_tile, k_pool, table, page_size, num_kv_heads, kv_head, key0, end, kKeys, lane, 32);
+      load_kv_tile<D>(v_tile, v_pool, table, page_size, num_kv_heads, kv_head, key0, end, kKeys, lane, 32);
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncwarp();
+      fold_block<D, kKeys>(q_frag, k_tile, v_tile, key0, row_first, row_limit, scale_log2, row_max, row_sum, acc);
+      __syncwarp();
+    }
+
+    // write this warp's partial for the rows that are real heads
+    const int slices = num_splits * 4;
+    const int slice = split * 4 + warp;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float sum = row_sum[r];
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      const int head_in_group = m_tile * 16 + (lane >> 2) + r * 8;
+      if (head_in_group >= group) continue;
+      const int head = kv_head * group + head_in_group;
+      const size_t at = (static_cast<size_t>(entry) * num_heads + head) * slices + slice;
+      if ((lane & 3) == 0) {
+        partial_ml[2 * at] = row_max[r];
+        partial_ml[2 * at + 1] = sum;
+      }
+      float* dst = partial_out + at * D;
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) {
+        const int col = n * 8 + 2 * (lane & 3);
+        *reinterpret_cast<float2*>(dst + col) = make_float2(acc[n][2 * r], acc[n][2 * r + 1]);
+      }
+    }
+  }
+}
+
+// grid: (tokens, heads); one block of D threads combines the slices of one row.
+template <int D>
+__global__ void attention_combine_kernel(const float* __restrict__ partial_ml, const float* __restrict__ partial_out,
+                                         int slices, __nv_bfloat16* __restrict__ out, int num_heads) {
+  const size_t row = static_cast<size_t>(blockIdx.x) * num_heads + blockIdx.y;
+  const float* ml = partial_ml + 2 * row * slices;
+  float best = -INFINITY;
+  for (int s = 0; s < slices; ++s) best = fmaxf(best, ml[2 * s]);
+  float total = 0.0f, value = 0.0f;
+  const int d = threadIdx.x;
+  for (int s = 0; s < slices; ++s) {
+    const float m = ml[2 * s];
+    if (m == -INFINITY) continue;  // a slice that saw no key
+    const float w = exp2f(m - best);
+    total += ml[2 * s + 1] * w;
+    value += partial_out[(row * slices + s) * D + d] * w;
+  }
+  out[row * D + d] = __float2bfloat16_rn(value / total);
+}
+
+template <int D>
+int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int* entry_starts,
+                   const int* entry_pos0, const int* block_table, int table_width, int page_size, int num_entries,
+                   int num_tokens, int num_heads, int num_kv_heads, float scale, int window, cudaStream_t s) {
+  constexpr int kSmem = (64 + 4 * 64) * D * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  // at most one partly filled tile per entry beyond the full ones
+  dim3 grid((num_tokens + 63) / 64 + num_entries, num_heads);
+  attention_prefill_kernel<D><<<grid, 128, kSmem, s>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(k_pool),
+      static_cast<const __nv_bfloat16*>(v_pool), entry_starts, entry_pos0, block_table, table_width, page_size,
+      num_entries, num_heads, num_kv_heads, scale, window);
+  return vipera_launch_status();
+}
+
+template <int D>
+int launch_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int* positions,
+                  const int* block_table, int table_width, int page_size, int num_entries, int num_heads,
+                  int num_kv_heads, float scale, int window, int chunk, int num_splits, float* partial_ml,
+                  float* partial_out, cudaStream_t s) {
+  constexpr int kSmem = 16 * D * 2 + 4 * 2 * 32 * D * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  dim3 grid(num_entries, num_kv_heads, num_splits);
+  attention_decode_kernel<D><<<grid, 128, kSmem, s>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
+      static_cast<const __nv_bfloat16*>(v_pool), positions, block_table, table_width, page_size, num_heads,
+      num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out);
+  int status = vipera_launch_status();
+  if (status != VIPERA_OK) return status;
+  attention_combine_kernel<D><<<dim3(num_entries, num_heads), D, 0, s>>>(
+      partial_ml, partial_out, num_splits * 4, static_cast<__nv_bfloat16*>(out), num_heads);
+  return vipera_launch_status();
+}
+
+}  // namespace
+
+// Attention of a step with portions of any length.  q and out are bfloat16 [tokens, heads, d];
+// entry_starts [entries + 1] are cumulative token counts and entry_pos0 [entries] the position
+// of each entry's first token.  Head sizes: 64 and 128.
+VIPERA_API int vipera_attention_prefill(const void* q, void* out, const void* k_pool, const void* v_pool,
+                                        const int* entry_starts, const int* entry_pos0, const int* block_table,
+                                        int table_width, int page_size, int num_entries, int num_tokens,
+                                        int num_heads, int num_kv_heads, int head_dim, float scale, int window,
+                                        void* stream) {
+  if (num_tokens <= 0 || num_entries <= 0) return VIPERA_OK;
+  if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads) return VIPERA_BAD_SHAPE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (head_dim == 128)
+    return launch_prefill<128>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width, page_size,
+                               num_entries, num_tokens, num_heads, num_kv_heads, scale, window, s);
+  if (head_dim == 64)
+    return launch_prefill<64>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width, page_size,
+                              num_entries, num_tokens, num_heads, num_kv_heads, scale, window, s);
+  return VIPERA_BAD_SHAPE;
+}
+
+// Floats of scratch a decode launch needs: (2 + d) per (entry, head, slice).
+VIPERA_API size_t vipera_attention_decode_scratch(int num_entries, int num_heads, int head_dim, int num_splits) {
+  return static_cast<size_t>(num_entries) * num_heads * num_splits * 4 * (2 + head_dim);
+}
+
+// Attention of a step in which every entry brings one token (token i belongs to entry i).
+// The keys of an entry are cut into `num_splits` ranges of `chunk` keys (a multiple of 32).
+VIPERA_API int vipera_attention_decode(const void* q, void* out, const void* k_pool, const void* v_pool,
+                                       const int* positions, const int* block_table, int table_width, int page_size,
+                                       int num_entries, int num_heads, int num_kv_heads, int head_dim, float scale,
+                                       int window, int chunk, int num_splits, float* scratch, size_t scratch_floats,
+                                       void* stream) {
+  if (num_entries <= 0) return VIPERA_OK;
+  if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads) return VIPERA_BAD_SHAPE;
+  if (chunk <= 0 || chunk % 32 || num_splits <= 0 || num_splits > 65535) return VIPERA_BAD_ARGUMENT;
+  const size_t need = vipera_attention_decode_scratch(num_entries, num_heads, head_dim, num_splits);
+  if (!scratch || scratch_floats < need) return VIPERA_BAD_ARGUMENT;
+  const size_t rows = static_cast<size_t>(num_entries) * num_heads * num_splits * 4;
+  float* partial_ml = scratch;
+  float* partial_out = scratch + 2 * rows;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (head_dim == 128)
+    return launch_decode<128>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries,
+                              num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, s);
+  if (head_dim == 64)
+    return launch_decode<64>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries,
+                             num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, s);
+  return VIPERA_BAD_SHAPE;
+}
+
+VIPERA_API const char* vipera_attention_mma_status_text(int status) { return vipera_status_text(status); }

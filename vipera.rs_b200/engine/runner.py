@@ -60,6 +60,9 @@ class ModelRunner:
         self._copy_done = torch.cuda.Event()
         self._copy_pending = False
         self.steps_run = 0
+        self.decode_graphs = True
+        self.max_graph_entries = 256
+        self._graphs = {}
 
     # ------------------------------------------------------------------------------
     def _staging(self, count: int):
@@ -143,7 +146,133 @@ class ModelRunner:
             dtype=self.model.dtype, workspace=self.workspace)
 
     def run(self, step: StepInput) -> Optional[torch.Tensor]:
-        ctx = self.build_context(step, self.model.dtype)
-        logits = self.model.forward(ctx, self.pools.views)
+        """Run one step.  A step in which every entry brings one token and wants its logits
+        (a decode step) is replayed from a captured CUDA graph of its size class; every other
+        step is launched kernel by kernel."""
         self.steps_run += 1
-        return logits
+        counts = step.counts
+        if (self.decode_graphs and len(counts) <= self.max_graph_entries and max(counts) == 1
+                and len(step.logit_rows) == len(counts)):
+            return self._run_graph(step)
+        ctx = self.build_context(step, self.model.dtype)
+        return self.model.forward(ctx, self.pools.views)
+
+    # ------------------------------------------------------------------------------
+    # decode steps through CUDA graphs
+    # ------------------------------------------------------------------------------
+    def _run_graph(self, step: StepInput) -> torch.Tensor:
+        self.validate(step)
+        entries = len(step.counts)
+        bucket = _round_up_pow2(entries, 1)
+        pos0 = np.asarray(step.pos0, dtype=np.int32)
+        widths = []
+        for g in range(self.manager.num_groups):
+            page_size = self.manager.group(g)[0]
+            widths.append(_round_up_pow2((int(pos0.max()) + page_size) // page_size))
+        key = (bucket, tuple(widths))
+        graph = self._graphs.get(key)
+        if graph is not None and graph.stale():
+            graph = None
+        if graph is None:
+            graph = _DecodeGraph(self, bucket, widths)
+            self._graphs[key] = graph
+            graph.capture(step)
+        return graph.replay(step)
+
+
+class _DecodeGraph:
+    """One captured decode step for `bucket` entries and block tables of the given widths.
+    Steps with fewer entries are padded with copies of their first entry, which computes and
+    stores the same values twice."""
+
+    def __init__(self, runner: ModelRunner, bucket: int, widths):
+        self.runner = runner
+        self.bucket = bucket
+        self.widths = list(widths)
+        b = bucket
+        self.sizes = [b, b, b, b + 1, b, b, b, b] + [b * w for w in self.widths]
+        self.offsets = np.concatenate([[0], np.cumsum(self.sizes)]).astype(np.int64)
+        total = int(self.offsets[-1])
+        self.host = torch.empty(total, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.empty(total, dtype=torch.int32, device=runner.device)
+        self.copy_done = torch.cuda.Event()
+        self.pending = False
+        self.graph = None
+        self.logits = None
+        self.generations = None
+
+    def stale(self) -> bool:
+        from ..kernels import ops
+
+        return self.generations != (self.runner.workspace.generation, ops.buffer_generation)
+
+    def _part(self, index):
+        return self.dev[int(self.offsets[index]):int(self.offsets[index + 1])]
+
+    def _fill(self, step: StepInput) -> int:
+        runner, b = self.runner, self.bucket
+        n = len(step.counts)
+        if self.pending:
+            self.copy_done.synchronize()
+        view = self.host.numpy()
+        o = self.offsets
+
+        def put(index, values):
+            chunk = view[int(o[index]):int(o[index + 1])]
+            chunk[:n] = values
+            chunk[n:] = values[0]
+
+        put(0, np.asarray(step.tokens, dtype=np.int32))
+        pos0 = np.asarray(step.pos0, dtype=np.int32)
+        put(1, pos0)
+        view[int(o[2]):int(o[3])] = np.arange(b, dtype=np.int32)
+        view[int(o[3]):int(o[4])] = np.arange(b + 1, dtype=np.int32)
+        put(4, pos0)
+        put(5, np.asarray([runner.manager.state_slot(r) for r in step.requests], dtype=np.int32))
+        put(6, np.asarray(step.fresh, dtype=np.int32))
+        view[int(o[7]):int(o[8])] = np.arange(b, dtype=np.int32)
+        requests = list(step.requests)
+        for g, width in enumerate(self.widths):
+            table = runner.manager.tables(requests, g, width)
+            page_size = runner.manager.group(g)[0]
+            if (table[np.arange(n), pos0 // page_size] < 0).any():
+                raise InvalidArgumentError("a request of the step has no page reserved for its position")
+            chunk = view[int(o[8 + g]):int(o[9 + g])].reshape(b, width)
+            chunk[:n] = table
+            chunk[n:] = table[0]
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copy_done.record()
+        self.pending = True
+        return n
+
+    def _context(self) -> StepContext:
+        runner, b = self.runner, self.bucket
+        tables = [self._part(8 + g).view(b, w) for g, w in enumerate(self.widths)]
+        return StepContext(
+            num_tokens=b, num_entries=b, tokens=self._part(0), positions=self._part(1),
+            token_entry=self._part(2), entry_starts=self._part(3), entry_pos0=self._part(4),
+            state_slots=self._part(5), fresh=self._part(6), block_tables=tables, logit_rows=self._part(7),
+            num_logit_rows=b, host_counts=[1] * b, host_pos0=[0] * b, max_count=1,
+            max_kv_len=min(w * runner.manager.group(g)[0] for g, w in enumerate(self.widths)) if self.widths else 0,
+            all_single=True, dtype=runner.model.dtype, workspace=runner.workspace, extras={"graph": True})
+
+    def capture(self, step: StepInput) -> None:
+        from ..kernels import ops
+
+        runner = self.runner
+        self._fill(step)
+        ctx = self._context()
+        # Once outside a graph: buffers get their final sizes, kernels are loaded.  The step's
+        # own keys and values are written here and again, identically, by the replay.
+        runner.model.forward(ctx, runner.pools.views)
+        torch.cuda.current_stream().synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.logits = runner.model.forward(ctx, runner.pools.views)
+        self.graph = graph
+        self.generations = (runner.workspace.generation, ops.buffer_generation)
+
+    def replay(self, step: StepInput) -> torch.Tensor:
+        n = self._fill(step)
+        self.graph.replay()
+        return self.logits[:n]

@@ -239,19 +239,23 @@ def apply_penalties(logits: torch.Tensor, *, entry_row, entry_id, entry_count, e
 # tensor-core products
 # ----------------------------------------------------------------------------------------
 _tc_state = {}
+buffer_generation = 0  # goes up whenever a shared kernel buffer moves; captured graphs are then stale
 
 
 def _tc_buffers(device, scratch_bytes: int, counters: int):
     """Scratch for split partial sums, tile counters (zero between launches) and the status
     word of the tensor-core kernels, per device.  They grow on demand and are shared by all
     products, which run one after another on one stream."""
+    global buffer_generation
     state = _tc_state.setdefault(str(device), {"scratch": None, "counters": None, "status": None})
     if state["status"] is None:
         state["status"] = torch.zeros(1, dtype=torch.int32, device=device)
     if scratch_bytes and (state["scratch"] is None or state["scratch"].numel() * 4 < scratch_bytes):
-        state["scratch"] = torch.empty(max(scratch_bytes // 4, 1 << 20), dtype=torch.float32, device=device)
+        state["scratch"] = torch.empty(max(scratch_bytes // 4, 8 << 20), dtype=torch.float32, device=device)
+        buffer_generation += 1
     if counters and (state["counters"] is None or state["counters"].numel() < counters):
-        state["counters"] = torch.zeros(max(counters, 4096), dtype=torch.int32, device=device)
+        state["counters"] = torch.zeros(max(counters, 16384), dtype=torch.int32, device=device)
+        buffer_generation += 1
     return state
 
 
@@ -299,3 +303,70 @@ def check_kernel_status(device) -> None:
     if code:
         state["status"].zero_()
         raise InternalError(f"a tensor-core kernel gave up waiting (code {code}); the step's results are invalid")
+
+
+# ----------------------------------------------------------------------------------------
+# bfloat16 attention on the tensor cores
+# ----------------------------------------------------------------------------------------
+MMA_HEAD_DIMS = (64, 128)
+
+
+def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
+                      entry_starts: torch.Tensor, entry_pos0: torch.Tensor, block_table: torch.Tensor,
+                      num_entries: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                      window: int = 0) -> None:
+    """Flash-style attention of a step whose entries bring any number of tokens (bfloat16,
+    head sizes 64 and 128)."""
+    fn = _function("attention_mma", "vipera_attention_prefill",
+                   [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
+                    _c_int, _c_int, _c_int, _c_float, _c_int, _c_void])
+    if head_dim not in MMA_HEAD_DIMS:
+        raise UnsupportedError(f"attention_prefill: head size {head_dim} (built: 64, 128)")
+    count = q.shape[0]
+    if q.shape[1] != num_heads * head_dim or out.shape != q.shape:
+        raise InvalidArgumentError("attention_prefill: q and out must be [tokens, heads * d]")
+    if k_pool.shape[2:] != (num_kv_heads, head_dim) or v_pool.shape != k_pool.shape:
+        raise InvalidArgumentError("attention_prefill: cache pools must be [pages, page_size, kv_heads, d]")
+    _check(fn(_gpu(q, "q", torch.bfloat16), _gpu(out, "out", torch.bfloat16), _gpu(k_pool, "k_pool", torch.bfloat16),
+              _gpu(v_pool, "v_pool", torch.bfloat16), _gpu(entry_starts, "entry_starts", torch.int32),
+              _gpu(entry_pos0, "entry_pos0", torch.int32), _gpu(block_table, "block_table", torch.int32),
+              block_table.shape[1], k_pool.shape[1], num_entries, count, num_heads, num_kv_heads, head_dim,
+              float(scale), int(window or 0), _stream()), "attention_prefill")
+
+
+def decode_splits(num_entries: int, num_kv_heads: int, max_keys: int, sm_count: int = 148):
+    """How a decode step's keys are cut: (keys per split, splits), so that about two blocks
+    per SM run and no split is shorter than 128 keys (32 for each of a block's four warps)."""
+    want = max(1, (2 * sm_count) // max(1, num_entries * num_kv_heads))
+    chunk = max(128, -(-max_keys // want))
+    chunk = -(-chunk // 32) * 32
+    return chunk, max(1, -(-max_keys // chunk))
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
+                     positions: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int,
+                     head_dim: int, scale: float, window: int, chunk: int, num_splits: int,
+                     scratch: torch.Tensor) -> None:
+    """Split-key attention of a step in which every entry brings one token (bfloat16, head
+    sizes 64 and 128); the partial results of the splits are combined by a second kernel."""
+    fn = _function("attention_mma", "vipera_attention_decode",
+                   [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
+                    _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, ctypes.c_size_t, _c_void])
+    if head_dim not in MMA_HEAD_DIMS:
+        raise UnsupportedError(f"attention_decode: head size {head_dim} (built: 64, 128)")
+    count = q.shape[0]
+    if q.shape[1] != num_heads * head_dim or out.shape != q.shape:
+        raise InvalidArgumentError("attention_decode: q and out must be [entries, heads * d]")
+    if k_pool.shape[2:] != (num_kv_heads, head_dim) or v_pool.shape != k_pool.shape:
+        raise InvalidArgumentError("attention_decode: cache pools must be [pages, page_size, kv_heads, d]")
+    if block_table.shape[0] != count or positions.numel() != count:
+        raise InvalidArgumentError("attention_decode: one position and one block table row per entry")
+    _check(fn(_gpu(q, "q", torch.bfloat16), _gpu(out, "out", torch.bfloat16), _gpu(k_pool, "k_pool", torch.bfloat16),
+              _gpu(v_pool, "v_pool", torch.bfloat16), _gpu(positions, "positions", torch.int32),
+              _gpu(block_table, "block_table", torch.int32), block_table.shape[1], k_pool.shape[1], count,
+              num_heads, num_kv_heads, head_dim, float(scale), int(window or 0), int(chunk), int(num_splits),
+              _gpu(scratch, "scratch", torch.float32), scratch.numel(), _stream()), "attention_decode")
+
+
+def attention_decode_scratch_floats(num_entries: int, num_heads: int, head_dim: int, num_splits: int) -> int:
+    return num_entries * num_heads * num_splits * 4 * (2 + head_dim)

@@ -27,7 +27,7 @@ class GQAttention(Mixer):
     count of keys), softmax_scale, position (a PartSpec of a position encoding) and,
     optionally, ``projection_names`` (defaults q_proj, k_proj, v_proj, o_proj)."""
 
-    kernels = ("rope_cache", "attention")
+    kernels = ("rope_cache", "attention", "attention_mma")
 
     @staticmethod
     def _names(params):
@@ -103,10 +103,33 @@ class GQAttention(Mixer):
                        k_pool=cache.k, v_pool=cache.v, token_seq=ctx.token_entry, block_table=table,
                        page_size=cache.page_size, write_cache=writes_cache)
         mixed = ws.get("attention.out", (count, heads * d), ctx.dtype)
+        self._attend(ctx, q, mixed, cache, table)
+        self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
+
+    def _attend(self, ctx, q, mixed, cache, table):
+        """Choose the attention kernel: on the bfloat16 path with a head size the tensor-core
+        kernels are built for, the split-key kernel for steps of single tokens and the flash
+        kernel otherwise; in every other case the general kernel."""
+        heads, kv_heads, d = self.num_heads, self.num_kv_heads, self.head_dim
+        window = self.window or 0
+        if ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS:
+            if ctx.all_single:
+                chunk, splits = ops.decode_splits(ctx.num_entries, kv_heads, max(ctx.max_kv_len, 1))
+                scratch = ctx.workspace.get(
+                    "attention.partials",
+                    (ops.attention_decode_scratch_floats(ctx.num_entries, heads, d, splits),), torch.float32)
+                ops.attention_decode(q, mixed, cache.k, cache.v, positions=ctx.positions, block_table=table,
+                                     num_heads=heads, num_kv_heads=kv_heads, head_dim=d, scale=self.scale,
+                                     window=window, chunk=chunk, num_splits=splits, scratch=scratch)
+            else:
+                ops.attention_prefill(q, mixed, cache.k, cache.v, entry_starts=ctx.entry_starts,
+                                      entry_pos0=ctx.entry_pos0, block_table=table, num_entries=ctx.num_entries,
+                                      num_heads=heads, num_kv_heads=kv_heads, head_dim=d, scale=self.scale,
+                                      window=window)
+            return
         ops.attention(q, mixed, cache.k, cache.v, token_seq=ctx.token_entry, positions=ctx.positions,
                       block_table=table, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
-                      scale=self.scale, window=self.window or 0)
-        self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
+                      scale=self.scale, window=window)
 
 
 MIXERS.register("gqa_attention", GQAttention)

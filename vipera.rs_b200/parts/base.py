@@ -74,6 +74,7 @@ class Workspace:
         self.device = device
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self.frozen = False
+        self.generation = 0  # goes up whenever a buffer moves; captured graphs are then stale
 
     def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         count = 1
@@ -86,6 +87,7 @@ class Workspace:
                 raise RuntimeError(f"workspace buffer {name!r} would grow while frozen")
             buffer = torch.empty(max(count, 1), dtype=dtype, device=self.device)
             self._buffers[key] = buffer
+            self.generation += 1
         return buffer[:count].view(*shape)
 
     def bytes(self) -> int:
