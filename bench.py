@@ -1,0 +1,371 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine on one B200: decode tokens per second and prefill tokens per
+second on the Qwen2.5-1.5B shape with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  The default run decodes a batch of 8
+requests, each with 2,048 tokens of history, and reports on ONE JSON line:
+
+  value      decoded tokens per second, timed on the device (CUDA events around K steps of
+             the engine's step function and its device sampler; token ids come from pinned
+             host buffers, nothing is read back)
+  e2e        the same through the public entry point ``Engine.step()``: scheduling, the
+             host-to-device copy of the step's inputs and the device-to-host read of the
+             sampled tokens included
+  prefill    one prompt of 2,048 tokens: tokens per second, milliseconds, and the fraction
+             of the bfloat16 tensor-core peak that its flops amount to
+  roofline   bytes the decode step has to read (every weight once, the cache of the live
+             requests) over its time, against the measured HBM copy bandwidth
+  points     decode tokens per second at batch 1 and batch 64
+
+Peaks come from MEASURED_PEAKS.json beside this file when it exists, else from the
+figures measured earlier on the same pool (6.65 TB/s, 1.59 PFLOP/s).  Data are synthetic:
+seeded random weights of the architecture's shapes and uniform random token ids.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN25_1P5B = {
+    "architectures": ["Qwen2ForCausalLM"], "num_hidden_layers": 28, "hidden_size": 1536,
+    "num_attention_heads": 12, "num_key_value_heads": 2, "intermediate_size": 8960, "vocab_size": 151936,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+    "max_position_embeddings": 32768, "use_sliding_window": False, "sliding_window": 32768,
+    "max_window_layers": 21,
+}
+FULL_LAYERS = 28
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as handle:
+                data = json.load(handle)
+            peaks = dict(FALLBACK_PEAKS)
+            for key in peaks:
+                if isinstance(data.get(key), (int, float)) and data[key] > 0:
+                    peaks[key] = float(data[key])
+            return peaks, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed work runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples = []
+        self.process = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.process = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.process.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        clocks, maxima, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for parts in self.samples:
+            try:
+                clocks.append(float(parts[0]))
+                maxima.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[2:6]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None,
+                "sm_max_mhz": max(maxima) if maxima else None, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+def decode_bytes(config, layers, batch, history, element=2):
+    """Bytes one decode step has to read: every weight it uses once, and the cache of the
+    live requests at the mean history of the timed steps."""
+    h, d = config["hidden_size"], config["hidden_size"] // config["num_attention_heads"]
+    q, kv = config["num_attention_heads"] * d, config["num_key_value_heads"] * d
+    per_layer = h * (q + 2 * kv) + q * h + 3 * h * config["intermediate_size"]
+    weights = (layers * per_layer + config["vocab_size"] * h) * element
+    cache = batch * history * 2 * layers * kv * element
+    return weights + cache
+
+
+def prefill_flops(config, layers, tokens):
+    h, d = config["hidden_size"], config["hidden_size"] // config["num_attention_heads"]
+    q, kv = config["num_attention_heads"] * d, config["num_key_value_heads"] * d
+    per_layer = h * (q + 2 * kv) + q * h + 3 * h * config["intermediate_size"]
+    gemm = 2.0 * tokens * layers * per_layer + 2.0 * config["vocab_size"] * h
+    attention = 2.0 * tokens * tokens * d * config["num_attention_heads"] * layers  # causal half of 4*T^2*d*heads
+    return gemm + attention
+
+
+class DecodeHarness:
+    """`batch` requests with `history` tokens already in the cache (random keys and values,
+    placed without running a prefill), decoded one token per step through the engine's
+    runner and device sampler."""
+
+    def __init__(self, model, batch, history, steps, page_size=16):
+        import numpy as np
+        import torch
+
+        from vipera_rs_b200.cache import CachePools
+        from vipera_rs_b200.engine import ModelRunner
+        from vipera_rs_b200.sampling import DeviceSampler
+
+        self.np, self.torch = np, torch
+        self.model, self.batch, self.history = model, batch, history
+        per_request = -(-(history + steps + 2) // page_size)
+        self.pools = CachePools(model.cache_requests, page_size=page_size, num_pages=batch * per_request + 1,
+                                num_state_slots=batch, dtype=model.dtype, device=model.device)
+        for pool in self.pools.pool_tensors:
+            pool.normal_(0.0, 0.5)
+        self.runner = ModelRunner(model, self.pools, max_model_len=model.spec.max_position_embeddings)
+        self.sampler_tokens = torch.empty(batch, dtype=torch.int32, device=model.device)
+        self.manager = self.pools.manager
+        self.requests = list(range(batch))
+        for r in self.requests:
+            self.manager.open(r)
+            self.manager.reserve(r, history)
+            self.manager.commit(r, history)
+        self.position = history
+        rng = np.random.default_rng(batch)
+        self.token_stream = rng.integers(0, model.spec.vocab_size, size=(4096, batch), dtype=np.int32)
+        self.cursor = 0
+
+    def step(self):
+        from vipera_rs_b200.engine import StepInput
+        from vipera_rs_b200.kernels import ops
+
+        np = self.np
+        for r in self.requests:
+            self.manager.reserve(r, self.position + 1)
+        tokens = self.token_stream[self.cursor % 4096]
+        self.cursor += 1
+        step = StepInput(requests=self.requests, tokens=tokens, counts=[1] * self.batch,
+                         pos0=[self.position] * self.batch, fresh=[0] * self.batch,
+                         logit_rows=np.arange(self.batch, dtype=np.int32))
+        logits = self.runner.run(step)
+        ops.argmax(logits, self.sampler_tokens)
+        for r in self.requests:
+            self.manager.commit(r, self.position + 1)
+        self.position += 1
+
+    def timed(self, steps, warmup):
+        torch = self.torch
+        for _ in range(warmup):
+            self.step()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        first_position = self.position
+        start.record()
+        for _ in range(steps):
+            self.step()
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop) / steps
+        mean_history = (first_position + self.position - 1) / 2.0 + 1
+        return ms, mean_history
+
+    def close(self):
+        for r in self.requests:
+            self.manager.close(r)
+
+
+def measure_prefill(model, tokens, repeats, warmup, page_size=16):
+    import numpy as np
+    import torch
+
+    from vipera_rs_b200.cache import CachePools
+    from vipera_rs_b200.engine import ModelRunner, StepInput
+
+    pools = CachePools(model.cache_requests, page_size=page_size, num_pages=-(-tokens // page_size) + 1,
+                       num_state_slots=1, dtype=model.dtype, device=model.device)
+    runner = ModelRunner(model, pools, max_model_len=model.spec.max_position_embeddings)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, model.spec.vocab_size, size=tokens, dtype=np.int32)
+    times = []
+    for index in range(warmup + repeats):
+        pools.manager.open(0)
+        pools.manager.reserve(0, tokens)
+        step = StepInput(requests=[0], tokens=prompt, counts=[tokens], pos0=[0], fresh=[1],
+                         logit_rows=np.asarray([tokens - 1], dtype=np.int32))
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.run(step)
+        stop.record()
+        torch.cuda.synchronize()
+        pools.manager.close(0)
+        if index >= warmup:
+            times.append(start.elapsed_time(stop))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def measure_e2e(model, batch, history, steps, warmup, page_size=16):
+    """Through the public entry point: requests with `history`-token prompts are added and
+    prefilled by the engine itself; then decode steps are timed on the host clock, each one
+    scheduling, copying its inputs from pinned host memory, running, sampling and reading
+    the sampled tokens back."""
+    import numpy as np
+    import torch
+
+    from vipera_rs_b200 import Engine, SamplingParams
+
+    per_request = -(-(history + steps + warmup + 8) // page_size)
+    engine = Engine(model, page_size=page_size, num_pages=batch * per_request + 1, max_num_seqs=batch,
+                    max_tokens_per_step=4096, max_portion=2048)
+    rng = np.random.default_rng(1)
+    params = SamplingParams(max_new_tokens=steps + warmup + 4, eos_ids=[])
+    for _ in range(batch):
+        engine.add_request(rng.integers(0, model.spec.vocab_size, size=history).tolist(), params)
+    while True:  # prefill until every request decodes
+        report = engine.step()
+        if report.num_entries == batch and report.num_tokens == batch:
+            break
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    produced = 0
+    for _ in range(steps):
+        produced += len(engine.step().tokens)
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - started
+    h2d = 4 * (8 * batch + 1 + batch * 256)  # packed int32 inputs of a decode step (tables 256 wide at most)
+    d2h = 8 * batch                           # token ids and status words
+    return produced / elapsed, h2d, d2h
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--history", type=int, default=2048)
+    parser.add_argument("--layers", type=int, default=FULL_LAYERS)
+    parser.add_argument("--skip-points", action="store_true")
+    args = parser.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust workspace that loads GGUF files; no cargo/rustc and no "
+                          "GGUF model exist here, and pip cannot install it"}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"error": "this engine runs on one GPU; bench.py measures --gpus 1 only",
+                          "n_gpus": args.gpus}))
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+
+    import vipera_rs_b200  # noqa: F401
+    from vipera_rs_b200.engine import random_model
+
+    peaks, peak_source = read_peaks()
+    config = dict(QWEN25_1P5B)
+    config["num_hidden_layers"] = args.layers
+    from vipera_rs_b200.kernels import ops
+
+    model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
+    sampler = ClockSampler()
+    sampler.start()
+
+    harness = DecodeHarness(model, args.batch, args.history, args.steps + warmup)
+    harness.timed(2, warmup)  # graphs captured, buffers sized
+    launches_before = ops.launches
+    ms_per_step, mean_history = harness.timed(args.steps, warmup)
+    timed_launches = ops.launches - launches_before
+    harness.close()
+    value = args.batch * 1000.0 / ms_per_step
+    step_bytes = decode_bytes(config, args.layers, args.batch, mean_history)
+    achieved_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    points = {}
+    if not args.skip_points:
+        for batch in (1, 64):
+            other = DecodeHarness(model, batch, args.history, 32 + warmup)
+            ms, _ = other.timed(32, warmup)
+            other.close()
+            points[f"decode_b{batch}"] = round(batch * 1000.0 / ms, 1)
+            del other
+            torch.cuda.empty_cache()
+
+    prefill_tokens = 2048
+    prefill_ms = measure_prefill(model, prefill_tokens, repeats=5, warmup=3)
+    flops = prefill_flops(config, args.layers, prefill_tokens)
+    prefill_frac = flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)
+
+    e2e_value, h2d, d2h = measure_e2e(model, args.batch, args.history, args.steps, warmup)
+    clocks = sampler.stop()
+
+    line = {
+        "metric": "decode tok/s at batch 8, 2048 tokens of history (Qwen2.5-1.5B shape); prefill tok/s at 2,048 tokens",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random token ids",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen2.5-1.5B shape", "layers": args.layers, "layers_full": FULL_LAYERS,
+            "hidden": config["hidden_size"], "heads": config["num_attention_heads"],
+            "kv_heads": config["num_key_value_heads"], "head_dim": 128,
+            "intermediate": config["intermediate_size"], "vocab": config["vocab_size"],
+            "tied_head": True, "global_batch": args.batch, "seq_len": args.history,
+            "new_tokens": args.steps, "page_size": 16, "parallelism": "single GPU",
+            "l2": "inputs larger than L2: 3.1 GB of weights per step against 126 MB",
+            "peaks": peak_source,
+        },
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": timed_launches,
+        "prefill": {"value": round(prefill_tokens * 1000.0 / prefill_ms, 1), "tokens": prefill_tokens,
+                    "ms": round(prefill_ms, 3), "frac": round(prefill_frac, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved_gbs / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

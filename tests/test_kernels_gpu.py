@@ -147,6 +147,21 @@ def _paged_case(entries, heads, kv_heads, d, page, dtype, seed, window=0, length
     return lengths, counts, table, k_pool.to(dtype), v_pool.to(dtype), keys, values, q
 
 
+def _give_back_passed_pages(table, k_pool, v_pool, lengths, counts, page, window):
+    """What the cache manager does for a windowed group: pages wholly before the first key
+    the entry's first query can see are no longer held (-1), and their memory may hold
+    anything (NaN here)."""
+    if not window:
+        return
+    for e, (n, c) in enumerate(zip(lengths, counts)):
+        first_visible = max(0, (n - c) - window + 1)
+        for p in range(first_visible // page):
+            physical = int(table[e, p])
+            k_pool[physical] = float("nan")
+            v_pool[physical] = float("nan")
+            table[e, p] = -1
+
+
 def _attention_reference(q, keys, values, lengths, counts, heads, kv_heads, scale, window):
     out = torch.zeros_like(q, dtype=torch.float64)
     group = heads // kv_heads
@@ -178,6 +193,7 @@ def test_attention_single_tokens(heads, kv_heads, d, page, dtype, window):
         entries, heads, kv_heads, d, page, dtype, seed=heads * 100 + d, lengths=[1, 33, 300, 129, 64])
     scale = 1.0 / math.sqrt(d)
     want = _attention_reference(q, keys, values, lengths, counts, heads, kv_heads, scale, window)
+    _give_back_passed_pages(table, k_pool, v_pool, lengths, counts, page, window)
     qd = q.to(dtype).reshape(entries, heads * d).to(DEV)
     kp, vp, tb = k_pool.to(DEV), v_pool.to(DEV), table.to(DEV)
     positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
@@ -213,6 +229,7 @@ def test_attention_portions(heads, kv_heads, d, page, dtype, window):
         entries, heads, kv_heads, d, page, dtype, seed=heads * 10 + d, lengths=lengths, counts=counts)
     scale = 1.0 / math.sqrt(d)
     want = _attention_reference(q, keys, values, lengths, counts, heads, kv_heads, scale, window)
+    _give_back_passed_pages(table, k_pool, v_pool, lengths, counts, page, window)
     total = sum(counts)
     qd = q.to(dtype).reshape(total, heads * d).to(DEV)
     kp, vp, tb = k_pool.to(DEV), v_pool.to(DEV), table.to(DEV)

@@ -58,22 +58,27 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
   return static_cast<uint32_t>(row * D * 2 + ((chunk ^ (row & 7)) << 4));
 }
 
-// Copy `rows` cache rows (keys first_key ..) of one KV head into a tile, through the block
-// table; rows at or beyond `end_key` are filled with zeros.  Executed by `threads` threads.
+// Copy `rows` cache rows (keys tile_key0 ..) of one KV head into a tile, through the block
+// table.  Only keys in [visible_key, end_key) are read; every other row of the tile is
+// filled with zeros: keys before `visible_key` may lie in pages the request has given back
+// (a window has passed them), keys from `end_key` on are not written yet, and a masked
+// value still enters the value product with weight zero, where 0 * NaN would be NaN.
 template <int D>
 __device__ __forceinline__ void load_kv_tile(uint32_t tile, const __nv_bfloat16* __restrict__ pool,
                                              const int* __restrict__ table, int page_size, int num_kv_heads,
-                                             int kv_head, int first_key, int end_key, int rows, int thread,
-                                             int threads) {
+                                             int kv_head, int tile_key0, int visible_key, int end_key, int rows,
+                                             int thread, int threads) {
   constexpr int kChunks = D / 8;
   for (int index = thread; index < rows * kChunks; index += threads) {
     const int row = index / kChunks, chunk = index % kChunks;
-    const int key = first_key + row;
-    const bool valid = key < end_key;
+    const int key = tile_key0 + row;
+    bool valid = key >= visible_key && key < end_key;
     const __nv_bfloat16* src = pool;
     if (valid) {
       const int page = table[key / page_size];
-      src = pool + ((static_cast<size_t>(page) * page_size + key % page_size) * num_kv_heads + kv_head) * D + chunk * 8;
+      valid = page >= 0;
+      if (valid)
+        src = pool + ((static_cast<size_t>(page) * page_size + key % page_size) * num_kv_heads + kv_head) * D + chunk * 8;
     }
     cp_async_16(tile + tile_offset<D>(row, chunk), src, valid);
   }
@@ -225,9 +230,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   auto load_block = [&](int block, int buffer) {
     const int key0 = (first_block + block) * kKeys;
     load_kv_tile<D>(k_tiles + buffer * kKeys * D * 2, k_pool, table, page_size, num_kv_heads, kv_head, key0,
-                    end_key, kKeys, threadIdx.x, 128);
+                    first_key, end_key, kKeys, threadIdx.x, 128);
     load_kv_tile<D>(v_tiles + buffer * kKeys * D * 2, v_pool, table, page_size, num_kv_heads, kv_head, key0,
-                    end_key, kKeys, threadIdx.x, 128);
+                    first_key, end_key, kKeys, threadIdx.x, 128);
   };
   load_block(0, 0);
   cp_async_commit();
@@ -346,8 +351,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const float scale_log2 = scale * kLog2e;
 
     for (int key0 = begin + warp * kKeys; key0 < end; key0 += 4 * kKeys) {
-      load_kv_tile<D>(k_tile, k_pool, table, page_size, num_kv_heads, kv_head, key0, end, kKeys, lane, 32);
-      load_kv_tile<D>(v_tile, v_pool, table, page_size, num_kv_heads, kv_head, key0, end, kKeys, lane, 32);
+      load_kv_tile<D>(k_tile, k_pool, table, page_size, num_kv_heads, kv_head, key0, first_visible, end, kKeys, lane, 32);
+      load_kv_tile<D>(v_tile, v_pool, table, page_size, num_kv_heads, kv_head, key0, first_visible, end, kKeys, lane, 32);
       cp_async_commit();
       cp_async_wait<0>();
       __syncwarp();

@@ -267,12 +267,18 @@ class _DecodeGraph:
         runner.model.forward(ctx, runner.pools.views)
         torch.cuda.current_stream().synchronize()
         graph = torch.cuda.CUDAGraph()
+        before = ops.launches
         with torch.cuda.graph(graph):
             self.logits = runner.model.forward(ctx, runner.pools.views)
+        self.kernels = ops.launches - before
+        ops.launches = before
         self.graph = graph
         self.generations = (runner.workspace.generation, ops.buffer_generation)
 
     def replay(self, step: StepInput) -> torch.Tensor:
+        from ..kernels import ops
+
         n = self._fill(step)
         self.graph.replay()
+        ops.launches += self.kernels
         return self.logits[:n]

@@ -55,8 +55,13 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _check(status: int, what: str) -> None:
+launches = 0  # kernels launched through this module (replayed graphs add what they captured)
+
+
+def _check(status: int, what: str, kernels: int = 1) -> None:
+    global launches
     if status == 0:
+        launches += kernels
         return
     if status > 0:
         text = f"CUDA error {status}"
@@ -263,7 +268,7 @@ def gemm_tc_workspace(m: int, n: int, k: int):
     fn = _function("gemm_tc", "vipera_gemm_tc_workspace",
                    [_c_int, _c_int, _c_int, ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(_c_int)])
     scratch, counters = ctypes.c_size_t(0), _c_int(0)
-    _check(fn(m, n, k, ctypes.byref(scratch), ctypes.byref(counters)), "gemm_tc_workspace")
+    _check(fn(m, n, k, ctypes.byref(scratch), ctypes.byref(counters)), "gemm_tc_workspace", kernels=0)
     return scratch.value, counters.value
 
 
@@ -365,7 +370,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v
               _gpu(v_pool, "v_pool", torch.bfloat16), _gpu(positions, "positions", torch.int32),
               _gpu(block_table, "block_table", torch.int32), block_table.shape[1], k_pool.shape[1], count,
               num_heads, num_kv_heads, head_dim, float(scale), int(window or 0), int(chunk), int(num_splits),
-              _gpu(scratch, "scratch", torch.float32), scratch.numel(), _stream()), "attention_decode")
+              _gpu(scratch, "scratch", torch.float32), scratch.numel(), _stream()), "attention_decode", kernels=2)
 
 
 def attention_decode_scratch_floats(num_entries: int, num_heads: int, head_dim: int, num_splits: int) -> int:
