@@ -282,6 +282,8 @@ def main():
     parser.add_argument("--history", type=int, default=2048)
     parser.add_argument("--layers", type=int, default=FULL_LAYERS)
     parser.add_argument("--skip-points", action="store_true")
+    parser.add_argument("--only", choices=["decode", "prefill"], default=None,
+                        help="run one part only and print a short line (for profiling a small case)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -306,6 +308,15 @@ def main():
     from vipera_rs_b200.kernels import ops
 
     model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
+    if args.only == "prefill":
+        ms = measure_prefill(model, 2048, repeats=2, warmup=warmup)
+        print(json.dumps({"only": "prefill", "layers": args.layers, "ms": round(ms, 3)}))
+        return 0
+    if args.only == "decode":
+        harness = DecodeHarness(model, args.batch, args.history, args.steps + 2 * warmup + 2)
+        ms, _ = harness.timed(args.steps, warmup)
+        print(json.dumps({"only": "decode", "layers": args.layers, "batch": args.batch, "ms_per_step": round(ms, 4)}))
+        return 0
     sampler = ClockSampler()
     sampler.start()
 
