@@ -50,8 +50,19 @@ def _say(message: str) -> None:
     print(f"[vipera build] {message}", file=sys.stderr, flush=True)
 
 
+_build_dir = None
+
+
 def build_dir() -> str:
     """Where built libraries go: in-tree when writable, else a per-user temporary folder."""
+    global _build_dir
+    with _lock:
+        if _build_dir is None:
+            _build_dir = _find_build_dir()
+        return _build_dir
+
+
+def _find_build_dir() -> str:
     override = os.environ.get("VIPERA_BUILD_DIR")
     candidates = [override] if override else []
     candidates.append(os.path.join(_HERE, "_build"))
@@ -59,7 +70,7 @@ def build_dir() -> str:
     for path in candidates:
         try:
             os.makedirs(path, exist_ok=True)
-            probe = os.path.join(path, f".write_probe_{os.getpid()}")
+            probe = os.path.join(path, f".write_probe_{os.getpid()}_{threading.get_ident()}")
             with open(probe, "w"):
                 pass
             os.remove(probe)

@@ -9,8 +9,8 @@
 //     query heads of the KV head's group are the rows of the tile, so that every key and
 //     value is read once for the whole group (the reference's GQA sharing, model.rs:2221-2244,
 //     crates/vipera-backend-gpu/src/layer.cu:182-292); each warp folds 32-key blocks of the
-//     split into a partial (max, sum, unnormalised output), and a second kernel combines
-//     the partials: m = max m_c, l = sum l_c e^(m_c - m), o = sum o_c e^(m_c - m) / l
+//     split, the block's four warps merge into one partial (max, sum, unnormalised output),
+//     and a second kernel combines the splits' partials: m = max m_c, l = sum l_c e^(m_c - m), o = sum o_c e^(m_c - m) / l
 //     (layer.cu:307-467).
 //
 // Definition computed: crates/vipera-backend-cpu/src/model.rs:1804-1859 (see attention.cu).
@@ -296,16 +296,44 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 // ---------------------------------------------------------------------------------------
 // decode: block = (entry, KV head, split); rows of the tile = query heads of the group
 // ---------------------------------------------------------------------------------------
-// partial layout: [token][head][slice] with slice = split * 4 + warp; each holds
-// max (log2 units), sum, and D unnormalised outputs.
+// One warp's copy of 32 cache rows into its tile: in every pass the warp reads two whole
+// rows (16 lanes x 16 bytes each), so global reads are contiguous.
+template <int D>
+__device__ __forceinline__ void load_kv_rows32(uint32_t tile, const __nv_bfloat16* __restrict__ pool,
+                                               const int* __restrict__ table, int page_size, int page_shift,
+                                               int num_kv_heads, int kv_head, int tile_key0, int visible_key,
+                                               int end_key, int lane) {
+  constexpr int kChunks = D / 8;            // 16-byte chunks in a row
+  constexpr int kRowsPerPass = 32 / kChunks;  // 2 for d = 128, 4 for d = 64
+  const int chunk = lane % kChunks;
+#pragma unroll
+  for (int pass = 0; pass < 32 / kRowsPerPass; ++pass) {
+    const int row = pass * kRowsPerPass + lane / kChunks;
+    const int key = tile_key0 + row;
+    bool valid = key >= visible_key && key < end_key;
+    const __nv_bfloat16* src = pool;
+    if (valid) {
+      const int page = page_shift >= 0 ? table[key >> page_shift] : table[key / page_size];
+      const int slot = page_shift >= 0 ? (key & (page_size - 1)) : key % page_size;
+      valid = page >= 0;
+      if (valid)
+        src = pool + ((static_cast<size_t>(page) * page_size + slot) * num_kv_heads + kv_head) * D + chunk * 8;
+    }
+    cp_async_16(tile + tile_offset<D>(row, chunk), src, valid);
+  }
+}
+
+// partial layout: [token][head][split]: max (log2 units), sum, and D unnormalised outputs.
 template <int D>
 __global__ void __launch_bounds__(128)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
-                        const int* __restrict__ block_table, int table_width, int page_size, int num_heads,
-                        int num_kv_heads, float scale, int window, int chunk, int num_splits,
+                        const int* __restrict__ block_table, int table_width, int page_size, int page_shift,
+                        int num_heads, int num_kv_heads, float scale, int window, int chunk, int num_splits,
                         float* __restrict__ partial_ml, float* __restrict__ partial_out) {
   constexpr int kKeys = 32;
+  constexpr int kWarpTile = 2 * kKeys * D * 2;  // bytes of one warp's key and value tiles
+  static_assert(16 * (D + 4) * 4 <= kWarpTile, "a warp's partial must fit in its tiles");
   extern __shared__ __align__(128) uint8_t smem[];
   const int entry = blockIdx.x, kv_head = blockIdx.y, split = blockIdx.z;
   const int group = num_heads / num_kv_heads;
@@ -316,12 +344,20 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int begin = max(split * chunk, first_visible / kKeys * kKeys);
   const int end = min((split + 1) * chunk, position + 1);
 
-  const uint32_t q_tile = smem_addr(smem);                       // [16][D], shared by the warps
-  const uint32_t k_tile = q_tile + 16 * D * 2 + warp * 2 * kKeys * D * 2;
+  uint8_t* q_bytes = smem;                                        // [16][D] bf16, shared by the warps
+  uint8_t* warp_bytes = smem + 16 * D * 2 + warp * kWarpTile;
+  const uint32_t q_tile = smem_addr(q_bytes);
+  const uint32_t k_tile = smem_addr(warp_bytes);
   const uint32_t v_tile = k_tile + kKeys * D * 2;
 
   for (int m_tile = 0; m_tile * 16 < group; ++m_tile) {
     __syncthreads();
+    // this warp's first block of keys goes on its way before anything else
+    int key0 = begin + warp * kKeys;
+    if (key0 < end) {
+      load_kv_rows32<D>(k_tile, k_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0, first_visible, end, lane);
+      load_kv_rows32<D>(v_tile, v_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0, first_visible, end, lane);
+    }
     {
       constexpr int kChunks = D / 8;
       for (int index = threadIdx.x; index < 16 * kChunks; index += 128) {
@@ -331,9 +367,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         const __nv_bfloat16* src = q + (static_cast<size_t>(entry) * num_heads + kv_head * group + (valid ? head_in_group : 0)) * D + c * 8;
         cp_async_16(q_tile + tile_offset<D>(row, c), src, valid);
       }
-      cp_async_commit();
-      cp_async_wait<0>();
     }
+    cp_async_commit();
+    cp_async_wait<0>();
     __syncthreads();
     uint32_t q_frag[D / 16][4];
 #pragma unroll
@@ -350,60 +386,101 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int row_limit[2] = {position, position};
     const float scale_log2 = scale * kLog2e;
 
-    for (int key0 = begin + warp * kKeys; key0 < end; key0 += 4 * kKeys) {
-      load_kv_tile<D>(k_tile, k_pool, table, page_size, num_kv_heads, kv_head, key0, first_visible, end, kKeys, lane, 32);
-      load_kv_tile<D>(v_tile, v_pool, table, page_size, num_kv_heads, kv_head, key0, first_visible, end, kKeys, lane, 32);
-      cp_async_commit();
-      cp_async_wait<0>();
-      __syncwarp();
+    for (; key0 < end; key0 += 4 * kKeys) {
+      if (key0 != begin + warp * kKeys) {
+        load_kv_rows32<D>(k_tile, k_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0, first_visible, end, lane);
+        load_kv_rows32<D>(v_tile, v_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0, first_visible, end, lane);
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncwarp();
+      }
       fold_block<D, kKeys>(q_frag, k_tile, v_tile, key0, row_first, row_limit, scale_log2, row_max, row_sum, acc);
       __syncwarp();
     }
 
-    // write this warp's partial for the rows that are real heads
-    const int slices = num_splits * 4;
-    const int slice = split * 4 + warp;
+    // each warp leaves its partial in its own tiles: [16 rows][D + 4] floats
+    float* mine = reinterpret_cast<float*>(warp_bytes);
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       float sum = row_sum[r];
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      const int head_in_group = m_tile * 16 + (lane >> 2) + r * 8;
-      if (head_in_group >= group) continue;
-      const int head = kv_head * group + head_in_group;
-      const size_t at = (static_cast<size_t>(entry) * num_heads + head) * slices + slice;
+      const int row = (lane >> 2) + r * 8;
+      float* dst = mine + row * (D + 4);
       if ((lane & 3) == 0) {
-        partial_ml[2 * at] = row_max[r];
-        partial_ml[2 * at + 1] = sum;
+        dst[D] = row_max[r];
+        dst[D + 1] = sum;
       }
-      float* dst = partial_out + at * D;
 #pragma unroll
       for (int n = 0; n < D / 8; ++n) {
         const int col = n * 8 + 2 * (lane & 3);
-        *reinterpret_cast<float2*>(dst + col) = make_float2(acc[n][2 * r], acc[n][2 * r + 1]);
+        dst[col] = acc[n][2 * r];
+        dst[col + 1] = acc[n][2 * r + 1];
+      }
+    }
+    __syncthreads();
+    // merge the four warps' partials: thread = (row, eighth of the columns)
+    {
+      const int row = threadIdx.x >> 3, part = threadIdx.x & 7;
+      const int head_in_group = m_tile * 16 + row;
+      if (head_in_group < group) {
+        float m[4], best = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          m[w] = reinterpret_cast<const float*>(smem + 16 * D * 2 + w * kWarpTile)[row * (D + 4) + D];
+          best = fmaxf(best, m[w]);
+        }
+        float weight[4], total = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          weight[w] = m[w] == -INFINITY ? 0.0f : exp2f(m[w] - best);
+          total += weight[w] * reinterpret_cast<const float*>(smem + 16 * D * 2 + w * kWarpTile)[row * (D + 4) + D + 1];
+        }
+        const int head = kv_head * group + head_in_group;
+        const size_t at = (static_cast<size_t>(entry) * num_heads + head) * num_splits + split;
+        if (part == 0) {
+          partial_ml[2 * at] = best;
+          partial_ml[2 * at + 1] = total;
+        }
+        float* dst = partial_out + at * D;
+#pragma unroll
+        for (int c = 0; c < D / 8; c += 4) {
+          const int col = part * (D / 8) + c;
+          float4 value = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const float4 v = *reinterpret_cast<const float4*>(
+                reinterpret_cast<const float*>(smem + 16 * D * 2 + w * kWarpTile) + row * (D + 4) + col);
+            value.x += weight[w] * v.x;
+            value.y += weight[w] * v.y;
+            value.z += weight[w] * v.z;
+            value.w += weight[w] * v.w;
+          }
+          *reinterpret_cast<float4*>(dst + col) = value;
+        }
       }
     }
   }
 }
 
-// grid: (tokens, heads); one block of D threads combines the slices of one row.
+// grid: (tokens, heads); one block of D threads combines the splits of one row.
 template <int D>
 __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, const float* __restrict__ partial_out,
                                          int slices, __nv_bfloat16* __restrict__ out, int num_heads) {
   const size_t row = static_cast<size_t>(blockIdx.x) * num_heads + blockIdx.y;
   const float* ml = partial_ml + 2 * row * slices;
+  const float* values = partial_out + row * slices * D + threadIdx.x;
   float best = -INFINITY;
   for (int s = 0; s < slices; ++s) best = fmaxf(best, ml[2 * s]);
   float total = 0.0f, value = 0.0f;
-  const int d = threadIdx.x;
+#pragma unroll 8
   for (int s = 0; s < slices; ++s) {
     const float m = ml[2 * s];
-    if (m == -INFINITY) continue;  // a slice that saw no key
-    const float w = exp2f(m - best);
+    const float w = m == -INFINITY ? 0.0f : exp2f(m - best);  // a split that saw no key
     total += ml[2 * s + 1] * w;
-    value += partial_out[(row * slices + s) * D + d] * w;
+    value += values[static_cast<size_t>(s) * D] * w;
   }
-  out[row * D + d] = __float2bfloat16_rn(value / total);
+  out[row * D + threadIdx.x] = __float2bfloat16_rn(value / total);
 }
 
 template <int D>
@@ -432,6 +509,11 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
                   int num_kv_heads, float scale, int window, int chunk, int num_splits, float* partial_ml,
                   float* partial_out, cudaStream_t s) {
   constexpr int kSmem = 16 * D * 2 + 4 * 2 * 32 * D * 2;
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0) {
+    page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
@@ -441,12 +523,12 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
   dim3 grid(num_entries, num_kv_heads, num_splits);
   attention_decode_kernel<D><<<grid, 128, kSmem, s>>>(
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
-      static_cast<const __nv_bfloat16*>(v_pool), positions, block_table, table_width, page_size, num_heads,
-      num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out);
+      static_cast<const __nv_bfloat16*>(v_pool), positions, block_table, table_width, page_size, page_shift,
+      num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out);
   int status = vipera_launch_status();
   if (status != VIPERA_OK) return status;
   attention_combine_kernel<D><<<dim3(num_entries, num_heads), D, 0, s>>>(
-      partial_ml, partial_out, num_splits * 4, static_cast<__nv_bfloat16*>(out), num_heads);
+      partial_ml, partial_out, num_splits, static_cast<__nv_bfloat16*>(out), num_heads);
   return vipera_launch_status();
 }
 
@@ -474,7 +556,9 @@ VIPERA_API int vipera_attention_prefill(const void* q, void* out, const void* k_
 
 // Floats of scratch a decode launch needs: (2 + d) per (entry, head, slice).
 VIPERA_API size_t vipera_attention_decode_scratch(int num_entries, int num_heads, int head_dim, int num_splits) {
-  return static_cast<size_t>(num_entries) * num_heads * num_splits * 4 * (2 + head_dim);
+  // (max, sum) pairs first, padded so that the outputs after them start on 16 bytes
+  const size_t rows = static_cast<size_t>(num_entries) * num_heads * num_splits;
+  return ((2 * rows + 3) / 4) * 4 + rows * head_dim;
 }
 
 // Attention of a step in which every entry brings one token (token i belongs to entry i).
@@ -489,9 +573,10 @@ VIPERA_API int vipera_attention_decode(const void* q, void* out, const void* k_p
   if (chunk <= 0 || chunk % 32 || num_splits <= 0 || num_splits > 65535) return VIPERA_BAD_ARGUMENT;
   const size_t need = vipera_attention_decode_scratch(num_entries, num_heads, head_dim, num_splits);
   if (!scratch || scratch_floats < need) return VIPERA_BAD_ARGUMENT;
-  const size_t rows = static_cast<size_t>(num_entries) * num_heads * num_splits * 4;
+  const size_t rows = static_cast<size_t>(num_entries) * num_heads * num_splits;
   float* partial_ml = scratch;
-  float* partial_out = scratch + 2 * rows;
+  float* partial_out = scratch + ((2 * rows + 3) / 4) * 4;
+  if (reinterpret_cast<uintptr_t>(scratch) & 15) return VIPERA_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (head_dim == 128)
     return launch_decode<128>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries,

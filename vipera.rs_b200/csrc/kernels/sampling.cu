@@ -108,20 +108,89 @@ __device__ Best block_argmax(const float* __restrict__ row, int vocab, Best* scr
   return best;
 }
 
-__global__ void __launch_bounds__(kSampleThreads)
-argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ tokens, int* __restrict__ status) {
+// Greedy over a wide vocabulary in two stages, so that many blocks read each row at once:
+// every block finds the best of its slice of the row (eight independent loads in flight per
+// thread), then one warp per row picks the best of the slices.  Ties still go to the lowest id.
+constexpr int kArgmaxSlices = 32;
+constexpr int kArgmaxThreads = 256;
+
+__global__ void __launch_bounds__(kArgmaxThreads)
+argmax_slice_kernel(const float* __restrict__ logits, int vocab, float* __restrict__ slice_value,
+                    int* __restrict__ slice_id) {
   __shared__ Best scratch[32];
-  const Best best = block_argmax(logits + static_cast<size_t>(blockIdx.x) * vocab, vocab, scratch);
-  if (threadIdx.x == 0) {
-    tokens[blockIdx.x] = best.id < 0 ? 0 : best.id;
-    if (status) status[blockIdx.x] = best.id < 0 ? SAMPLE_NO_FINITE : SAMPLE_OK;
+  const int row = blockIdx.x, slice = blockIdx.y;
+  const int per = (vocab + kArgmaxSlices - 1) / kArgmaxSlices;
+  const int begin = slice * per, end = min(vocab, begin + per);
+  const float* src = logits + static_cast<size_t>(row) * vocab;
+  Best best{0.0f, -1};
+  for (int base = begin + threadIdx.x; base < end; base += 8 * kArgmaxThreads) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + u * kArgmaxThreads;
+      v[u] = i < end ? src[i] : NAN;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (finite(v[u])) best = better_of(best, Best{v[u], base + u * kArgmaxThreads});
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    Best other;
+    other.value = __shfl_xor_sync(0xffffffffu, best.value, offset);
+    other.id = __shfl_xor_sync(0xffffffffu, best.id, offset);
+    best = better_of(best, other);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) scratch[warp] = best;
+  __syncthreads();
+  if (warp == 0) {
+    best = lane < kArgmaxThreads / 32 ? scratch[lane] : Best{0.0f, -1};
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      Best other;
+      other.value = __shfl_xor_sync(0xffffffffu, best.value, offset);
+      other.id = __shfl_xor_sync(0xffffffffu, best.id, offset);
+      best = better_of(best, other);
+    }
+    if (lane == 0) {
+      slice_value[row * kArgmaxSlices + slice] = best.value;
+      slice_id[row * kArgmaxSlices + slice] = best.id;
+    }
   }
 }
 
-VIPERA_API int vipera_argmax(const float* logits, int rows, int vocab, int* tokens, int* status, void* stream) {
+__global__ void argmax_final_kernel(const float* __restrict__ slice_value, const int* __restrict__ slice_id,
+                                    int* __restrict__ tokens, int* __restrict__ status) {
+  const int row = blockIdx.x, lane = threadIdx.x;
+  Best best{slice_value[row * kArgmaxSlices + lane], slice_id[row * kArgmaxSlices + lane]};
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    Best other;
+    other.value = __shfl_xor_sync(0xffffffffu, best.value, offset);
+    other.id = __shfl_xor_sync(0xffffffffu, best.id, offset);
+    best = better_of(best, other);
+  }
+  if (lane == 0) {
+    tokens[row] = best.id < 0 ? 0 : best.id;
+    if (status) status[row] = best.id < 0 ? SAMPLE_NO_FINITE : SAMPLE_OK;
+  }
+}
+
+// `scratch` holds 64 * rows 32-bit words (a value and an id for each of 32 slices of a row).
+VIPERA_API int vipera_argmax(const float* logits, int rows, int vocab, int* tokens, int* status, void* scratch,
+                             void* stream) {
   if (rows <= 0) return VIPERA_OK;
   if (vocab <= 0) return VIPERA_BAD_SHAPE;
-  argmax_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(logits, vocab, tokens, status);
+  if (!scratch) return VIPERA_BAD_ARGUMENT;
+  static_assert(kArgmaxSlices == 32, "the final stage is one warp");
+  float* slice_value = static_cast<float*>(scratch);
+  int* slice_id = reinterpret_cast<int*>(slice_value + static_cast<size_t>(rows) * kArgmaxSlices);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  argmax_slice_kernel<<<dim3(rows, kArgmaxSlices), kArgmaxThreads, 0, s>>>(logits, vocab, slice_value, slice_id);
+  int launched = vipera_launch_status();
+  if (launched != VIPERA_OK) return launched;
+  argmax_final_kernel<<<rows, 32, 0, s>>>(slice_value, slice_id, tokens, status);
   return vipera_launch_status();
 }
 

@@ -210,11 +210,19 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: 
 
 
 # ----------------------------------------------------------------------------------------
+_argmax_scratch = {}
+
+
 def argmax(logits: torch.Tensor, tokens: torch.Tensor, status: Optional[torch.Tensor] = None) -> None:
-    fn = _function("sampling", "vipera_argmax", [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void])
+    """tokens[r] = index of the best finite logit of row r, ties to the lowest index."""
+    fn = _function("sampling", "vipera_argmax", [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void])
     rows, vocab = logits.shape
+    scratch = _argmax_scratch.get(str(logits.device))
+    if scratch is None or scratch.numel() < 64 * rows:
+        scratch = torch.empty(64 * max(rows, 256), dtype=torch.int32, device=logits.device)
+        _argmax_scratch[str(logits.device)] = scratch
     _check(fn(_gpu(logits, "logits", torch.float32), rows, vocab, _gpu(tokens, "tokens", torch.int32),
-              _opt(status, "status", torch.int32), _stream()), "argmax")
+              _opt(status, "status", torch.int32), scratch.data_ptr(), _stream()), "argmax", kernels=2)
 
 
 def sample(logits: torch.Tensor, *, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
@@ -340,11 +348,14 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
 
 
 def decode_splits(num_entries: int, num_kv_heads: int, max_keys: int, sm_count: int = 148):
-    """How a decode step's keys are cut: (keys per split, splits), so that about two blocks
-    per SM run and no split is shorter than 128 keys (32 for each of a block's four warps)."""
-    want = max(1, (2 * sm_count) // max(1, num_entries * num_kv_heads))
-    chunk = max(128, -(-max_keys // want))
-    chunk = -(-chunk // 32) * 32
+    """How a decode step's keys are cut: (keys per split, splits).  A split is 128 keys (32
+    for each of a block's four warps), so that every block asks for all its keys at once and
+    the whole cache of the step is in flight together; only when that would make more than
+    64 splits, or more than sixteen blocks per SM, do splits grow."""
+    blocks = max(1, num_entries * num_kv_heads)
+    most = max(1, min(64, (16 * sm_count) // blocks))
+    chunk = max(128, -(-max_keys // most))
+    chunk = -(-chunk // 128) * 128
     return chunk, max(1, -(-max_keys // chunk))
 
 
@@ -374,4 +385,5 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v
 
 
 def attention_decode_scratch_floats(num_entries: int, num_heads: int, head_dim: int, num_splits: int) -> int:
-    return num_entries * num_heads * num_splits * 4 * (2 + head_dim)
+    rows = num_entries * num_heads * num_splits
+    return (2 * rows + 3) // 4 * 4 + rows * head_dim
