@@ -63,24 +63,32 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
 // filled with zeros: keys before `visible_key` may lie in pages the request has given back
 // (a window has passed them), keys from `end_key` on are not written yet, and a masked
 // value still enters the value product with weight zero, where 0 * NaN would be NaN.
-template <int D>
+template <int D, int ROWS, int THREADS>
 __device__ __forceinline__ void load_kv_tile(uint32_t tile, const __nv_bfloat16* __restrict__ pool,
                                              const int* __restrict__ table, int page_size, int num_kv_heads,
-                                             int kv_head, int tile_key0, int visible_key, int end_key, int rows,
-                                             int thread, int threads) {
+                                             int kv_head, int tile_key0, int visible_key, int end_key, int thread) {
   constexpr int kChunks = D / 8;
-  for (int index = thread; index < rows * kChunks; index += threads) {
+  constexpr int kPasses = ROWS * kChunks / THREADS;
+  static_assert(ROWS * kChunks % THREADS == 0, "the tile must divide among the threads");
+  // first every source address (the block table reads are independent and overlap), then the copies
+  const __nv_bfloat16* src[kPasses];
+#pragma unroll
+  for (int pass = 0; pass < kPasses; ++pass) {
+    const int index = thread + pass * THREADS;
     const int row = index / kChunks, chunk = index % kChunks;
     const int key = tile_key0 + row;
-    bool valid = key >= visible_key && key < end_key;
-    const __nv_bfloat16* src = pool;
-    if (valid) {
+    src[pass] = nullptr;
+    if (key >= visible_key && key < end_key) {
       const int page = table[key / page_size];
-      valid = page >= 0;
-      if (valid)
-        src = pool + ((static_cast<size_t>(page) * page_size + key % page_size) * num_kv_heads + kv_head) * D + chunk * 8;
+      if (page >= 0)
+        src[pass] = pool + ((static_cast<size_t>(page) * page_size + key % page_size) * num_kv_heads + kv_head) * D + chunk * 8;
     }
-    cp_async_16(tile + tile_offset<D>(row, chunk), src, valid);
+  }
+#pragma unroll
+  for (int pass = 0; pass < kPasses; ++pass) {
+    const int index = thread + pass * THREADS;
+    const int row = index / kChunks, chunk = index % kChunks;
+    cp_async_16(tile + tile_offset<D>(row, chunk), src[pass] ? src[pass] : pool, src[pass] != nullptr);
   }
 }
 
@@ -188,6 +196,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
                          int num_heads, int num_kv_heads, float scale, int window) {
   constexpr int kQ = 64, kKeys = 64;
   extern __shared__ __align__(128) uint8_t smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   // which (entry, tile of that entry) is this block?
   int entry = -1, tile_in_entry = 0;
   {
@@ -229,10 +239,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 
   auto load_block = [&](int block, int buffer) {
     const int key0 = (first_block + block) * kKeys;
-    load_kv_tile<D>(k_tiles + buffer * kKeys * D * 2, k_pool, table, page_size, num_kv_heads, kv_head, key0,
-                    first_key, end_key, kKeys, threadIdx.x, 128);
-    load_kv_tile<D>(v_tiles + buffer * kKeys * D * 2, v_pool, table, page_size, num_kv_heads, kv_head, key0,
-                    first_key, end_key, kKeys, threadIdx.x, 128);
+    load_kv_tile<D, kKeys, 128>(k_tiles + buffer * kKeys * D * 2, k_pool, table, page_size, num_kv_heads, kv_head,
+                                key0, first_key, end_key, threadIdx.x);
+    load_kv_tile<D, kKeys, 128>(v_tiles + buffer * kKeys * D * 2, v_pool, table, page_size, num_kv_heads, kv_head,
+                                key0, first_key, end_key, threadIdx.x);
   };
   load_block(0, 0);
   cp_async_commit();
@@ -299,27 +309,33 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 // One warp's copy of 32 cache rows into its tile: in every pass the warp reads two whole
 // rows (16 lanes x 16 bytes each), so global reads are contiguous.
 template <int D>
-__device__ __forceinline__ void load_kv_rows32(uint32_t tile, const __nv_bfloat16* __restrict__ pool,
-                                               const int* __restrict__ table, int page_size, int page_shift,
-                                               int num_kv_heads, int kv_head, int tile_key0, int visible_key,
-                                               int end_key, int lane) {
+__device__ __forceinline__ void load_kv_rows32(uint32_t k_tile, uint32_t v_tile, const __nv_bfloat16* __restrict__ k_pool,
+                                               const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table,
+                                               int page_size, int page_shift, int num_kv_heads, int kv_head,
+                                               int tile_key0, int visible_key, int end_key, int lane) {
   constexpr int kChunks = D / 8;            // 16-byte chunks in a row
   constexpr int kRowsPerPass = 32 / kChunks;  // 2 for d = 128, 4 for d = 64
   const int chunk = lane % kChunks;
+  // Lane l finds where key tile_key0 + l lives (one block table read per lane, all at once);
+  // the rows' offsets then travel by shuffle.  -1 marks a row that is not read.
+  long long my_offset = -1;
+  {
+    const int key = tile_key0 + lane;
+    if (key >= visible_key && key < end_key) {
+      const int page = page_shift >= 0 ? table[key >> page_shift] : table[key / page_size];
+      const int slot = page_shift >= 0 ? (key & (page_size - 1)) : key % page_size;
+      if (page >= 0)
+        my_offset = ((static_cast<long long>(page) * page_size + slot) * num_kv_heads + kv_head) * D;
+    }
+  }
 #pragma unroll
   for (int pass = 0; pass < 32 / kRowsPerPass; ++pass) {
     const int row = pass * kRowsPerPass + lane / kChunks;
-    const int key = tile_key0 + row;
-    bool valid = key >= visible_key && key < end_key;
-    const __nv_bfloat16* src = pool;
-    if (valid) {
-      const int page = page_shift >= 0 ? table[key >> page_shift] : table[key / page_size];
-      const int slot = page_shift >= 0 ? (key & (page_size - 1)) : key % page_size;
-      valid = page >= 0;
-      if (valid)
-        src = pool + ((static_cast<size_t>(page) * page_size + slot) * num_kv_heads + kv_head) * D + chunk * 8;
-    }
-    cp_async_16(tile + tile_offset<D>(row, chunk), src, valid);
+    const long long offset = __shfl_sync(0xffffffffu, my_offset, row);
+    const bool valid = offset >= 0;
+    const long long at = valid ? offset + chunk * 8 : 0;
+    cp_async_16(k_tile + tile_offset<D>(row, chunk), k_pool + at, valid);
+    cp_async_16(v_tile + tile_offset<D>(row, chunk), v_pool + at, valid);
   }
 }
 
@@ -335,6 +351,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   constexpr int kWarpTile = 2 * kKeys * D * 2;  // bytes of one warp's key and value tiles
   static_assert(16 * (D + 4) * 4 <= kWarpTile, "a warp's partial must fit in its tiles");
   extern __shared__ __align__(128) uint8_t smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int entry = blockIdx.x, kv_head = blockIdx.y, split = blockIdx.z;
   const int group = num_heads / num_kv_heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -355,8 +373,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     // this warp's first block of keys goes on its way before anything else
     int key0 = begin + warp * kKeys;
     if (key0 < end) {
-      load_kv_rows32<D>(k_tile, k_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0, first_visible, end, lane);
-      load_kv_rows32<D>(v_tile, v_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0, first_visible, end, lane);
+      load_kv_rows32<D>(k_tile, v_tile, k_pool, v_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0,
+                        first_visible, end, lane);
     }
     {
       constexpr int kChunks = D / 8;
@@ -388,8 +406,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 
     for (; key0 < end; key0 += 4 * kKeys) {
       if (key0 != begin + warp * kKeys) {
-        load_kv_rows32<D>(k_tile, k_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0, first_visible, end, lane);
-        load_kv_rows32<D>(v_tile, v_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0, first_visible, end, lane);
+        load_kv_rows32<D>(k_tile, v_tile, k_pool, v_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0,
+                          first_visible, end, lane);
         cp_async_commit();
         cp_async_wait<0>();
         __syncwarp();
@@ -467,17 +485,27 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 template <int D>
 __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, const float* __restrict__ partial_out,
                                          int slices, __nv_bfloat16* __restrict__ out, int num_heads) {
+  __shared__ float maxima[128];
+  __shared__ float sums[128];
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = static_cast<size_t>(blockIdx.x) * num_heads + blockIdx.y;
   const float* ml = partial_ml + 2 * row * slices;
   const float* values = partial_out + row * slices * D + threadIdx.x;
-  float best = -INFINITY;
-  for (int s = 0; s < slices; ++s) best = fmaxf(best, ml[2 * s]);
+  // all (max, sum) pairs at once, then the weights of the splits (at most 128 splits)
+  float mine = -INFINITY;
+  for (int s = threadIdx.x; s < slices; s += D) {
+    maxima[s] = ml[2 * s];
+    sums[s] = ml[2 * s + 1];
+  }
+  __syncthreads();
+  for (int s = 0; s < slices; ++s) mine = fmaxf(mine, maxima[s]);
   float total = 0.0f, value = 0.0f;
 #pragma unroll 8
   for (int s = 0; s < slices; ++s) {
-    const float m = ml[2 * s];
-    const float w = m == -INFINITY ? 0.0f : exp2f(m - best);  // a split that saw no key
-    total += ml[2 * s + 1] * w;
+    const float m = maxima[s];
+    const float w = m == -INFINITY ? 0.0f : exp2f(m - mine);  // a split that saw no key
+    total += sums[s] * w;
     value += values[static_cast<size_t>(s) * D] * w;
   }
   out[row * D + threadIdx.x] = __float2bfloat16_rn(value / total);
@@ -496,11 +524,10 @@ int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_p
   }
   // at most one partly filled tile per entry beyond the full ones
   dim3 grid((num_tokens + 63) / 64 + num_entries, num_heads);
-  attention_prefill_kernel<D><<<grid, 128, kSmem, s>>>(
+  return vipera_launch(attention_prefill_kernel<D>, grid, 128, kSmem, s,
       static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(k_pool),
       static_cast<const __nv_bfloat16*>(v_pool), entry_starts, entry_pos0, block_table, table_width, page_size,
       num_entries, num_heads, num_kv_heads, scale, window);
-  return vipera_launch_status();
 }
 
 template <int D>
@@ -521,15 +548,14 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
     configured = true;
   }
   dim3 grid(num_entries, num_kv_heads, num_splits);
-  attention_decode_kernel<D><<<grid, 128, kSmem, s>>>(
+  int status = vipera_launch(attention_decode_kernel<D>, grid, 128, kSmem, s,
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
       static_cast<const __nv_bfloat16*>(v_pool), positions, block_table, table_width, page_size, page_shift,
       num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out);
-  int status = vipera_launch_status();
   if (status != VIPERA_OK) return status;
-  attention_combine_kernel<D><<<dim3(num_entries, num_heads), D, 0, s>>>(
-      partial_ml, partial_out, num_splits, static_cast<__nv_bfloat16*>(out), num_heads);
-  return vipera_launch_status();
+  return vipera_launch(attention_combine_kernel<D>, dim3(num_entries, num_heads), D, 0, s,
+      static_cast<const float*>(partial_ml), static_cast<const float*>(partial_out), num_splits,
+      static_cast<__nv_bfloat16*>(out), num_heads);
 }
 
 }  // namespace
@@ -570,7 +596,7 @@ VIPERA_API int vipera_attention_decode(const void* q, void* out, const void* k_p
                                        void* stream) {
   if (num_entries <= 0) return VIPERA_OK;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads) return VIPERA_BAD_SHAPE;
-  if (chunk <= 0 || chunk % 32 || num_splits <= 0 || num_splits > 65535) return VIPERA_BAD_ARGUMENT;
+  if (chunk <= 0 || chunk % 32 || num_splits <= 0 || num_splits > 128) return VIPERA_BAD_ARGUMENT;
   const size_t need = vipera_attention_decode_scratch(num_entries, num_heads, head_dim, num_splits);
   if (!scratch || scratch_floats < need) return VIPERA_BAD_ARGUMENT;
   const size_t rows = static_cast<size_t>(num_entries) * num_heads * num_splits;

@@ -5,6 +5,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+#include <utility>
+
 #define VIPERA_API extern "C" __attribute__((visibility("default")))
 
 // Element type codes of the C interface.
@@ -67,6 +70,46 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   const int warps = (blockDim.x + 31) >> 5;
   float total = lane < warps ? scratch[lane] : -INFINITY;
   return warp_max(total);
+}
+
+// ---------------------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel may be started while the kernel before it on the
+// stream is still running.  It then runs its own set-up (and reads of memory no earlier
+// kernel writes, such as weights) at once, and calls pdl_wait() before it touches anything
+// an earlier kernel produced; pdl_wait() returns when the earlier kernels have finished and
+// their writes are visible.  pdl_launch_dependents() lets the kernel after this one start
+// in the same way.  Every kernel of this package calls both, so a chain of them overlaps
+// each launch and prologue with the tail of the kernel before.  VIPERA_PDL=0 in the
+// environment turns the launch attribute off; the calls are then no-ops.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool vipera_pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* value = std::getenv("VIPERA_PDL");
+    enabled = (value && value[0] == '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+// Launch `kernel` on `stream`, allowed to start before the kernel ahead of it has finished.
+template <typename... KernelArgs, typename... Args>
+static inline int vipera_launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t shared_bytes,
+                                cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared_bytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = vipera_pdl_enabled() ? 1 : 0;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  cudaError_t error = cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(std::forward<Args>(args))...);
+  return error == cudaSuccess ? 0 : static_cast<int>(error);
 }
 
 static inline int vipera_launch_status() {

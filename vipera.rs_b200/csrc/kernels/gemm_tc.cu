@@ -144,8 +144,11 @@ __device__ __forceinline__ float silu_mul(float gate, float up) { return up * (g
 template <int BN>
 struct TileConfig {
   static constexpr int kStageBytes = (kTileX + BN) * kBlockK * 2;
-  static constexpr int kStagesRaw = (200 * 1024) / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  // Wide tiles take all the shared memory of an SM; narrow ones (few tokens) take less
+  // than half, so that two blocks share an SM and the next product's block can set up and
+  // prefetch weights while this one finishes.
+  static constexpr int kBudget = BN >= 128 ? 200 * 1024 : 100 * 1024;
+  static constexpr int kStages = kBudget / kStageBytes;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
 };
@@ -231,7 +234,7 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
 }
 
 template <int BN, bool SWAP>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, (BN >= 128 ? 1 : 2))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                const GemmParams p) {
   using Config = TileConfig<BN>;
@@ -251,6 +254,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
@@ -271,7 +275,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   if (warp == 4) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      int stage = 0;
+      // The weight operand depends on no earlier kernel: its tiles for the first stages are
+      // on their way before this kernel waits for the kernels ahead of it.
+      int prefetched = 0;
+      if (static_cast<int>(blockIdx.x) < total_items) {
+        const int item = blockIdx.x;
+        const int split = item % p.splits;
+        const int tile = item / p.splits;
+        const int tx = tile % p.tiles_x, ty = tile / p.tiles_x;
+        const int kb_begin = split * p.k_blocks_per_split;
+        const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
+        prefetched = min(kStages, kb_end - kb_begin);
+        for (int i = 0; i < prefetched; ++i) {
+          uint8_t* x_tile = tiles + i * Config::kStageBytes;
+          uint8_t* y_tile = x_tile + kTileX * kBlockK * 2;
+          mbar_expect_tx(&full[i], Config::kStageBytes);
+          if (SWAP) tma_load_2d(x_tile, &map_x, &full[i], (kb_begin + i) * kBlockK, tx * kTileX);
+          else tma_load_2d(y_tile, &map_y, &full[i], (kb_begin + i) * kBlockK, ty * BN);
+        }
+      }
+      pdl_wait();
+      int stage = 0, issued = 0;
       uint32_t phase = 0;
       for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
         const int split = item % p.splits;
@@ -279,13 +303,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const int tx = tile % p.tiles_x, ty = tile / p.tiles_x;
         const int kb_begin = split * p.k_blocks_per_split;
         const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
-          mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status);
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++issued) {
           uint8_t* x_tile = tiles + stage * Config::kStageBytes;
           uint8_t* y_tile = x_tile + kTileX * kBlockK * 2;
-          mbar_expect_tx(&full[stage], Config::kStageBytes);
-          tma_load_2d(x_tile, &map_x, &full[stage], kb * kBlockK, tx * kTileX);
-          tma_load_2d(y_tile, &map_y, &full[stage], kb * kBlockK, ty * BN);
+          if (issued < prefetched) {
+            // the weight half of this stage is already in flight: add the activation half
+            if (SWAP) tma_load_2d(y_tile, &map_y, &full[stage], kb * kBlockK, ty * BN);
+            else tma_load_2d(x_tile, &map_x, &full[stage], kb * kBlockK, tx * kTileX);
+          } else {
+            mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status);
+            mbar_expect_tx(&full[stage], Config::kStageBytes);
+            tma_load_2d(x_tile, &map_x, &full[stage], kb * kBlockK, tx * kTileX);
+            tma_load_2d(y_tile, &map_y, &full[stage], kb * kBlockK, ty * BN);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -326,6 +356,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
   } else {
     // ---------------- epilogue warps 0..3 ----------------
+    pdl_wait();  // outputs, the residual stream, scratch and counters belong to earlier kernels until now
     int local = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++local) {
       const int tile = item / p.splits;
@@ -521,8 +552,7 @@ static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, co
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  gemm_tc_kernel<BN, SWAP><<<grid, kThreads, Config::kSmemBytes, s>>>(map_x, map_y, p);
-  return vipera_launch_status();
+  return vipera_launch(gemm_tc_kernel<BN, SWAP>, grid, kThreads, Config::kSmemBytes, s, map_x, map_y, p);
 }
 
 // A is [T, K] bfloat16, W is [N, K] bfloat16, both row-major and contiguous with K a

@@ -23,6 +23,8 @@ __global__ void rope_cache_kernel(const float* __restrict__ qkv, T* __restrict__
                                   int style, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                   const int* __restrict__ token_seq, const int* __restrict__ block_table,
                                   int table_width, int page_size, int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int h = blockIdx.y;
   const int half = head_dim >> 1;
@@ -77,16 +79,14 @@ VIPERA_API int vipera_rope_cache(const float* qkv, void* q_out, int dtype, int n
   dim3 grid(num_tokens, num_heads + 2 * num_kv_heads);
   const int threads = head_dim >= 128 ? 64 : 32;
   if (dtype == VIPERA_F32)
-    rope_cache_kernel<float><<<grid, threads, 0, s>>>(qkv, static_cast<float*>(q_out), num_heads, num_kv_heads, head_dim,
+    return vipera_launch(rope_cache_kernel<float>, grid, threads, 0, s, qkv, static_cast<float*>(q_out), num_heads, num_kv_heads, head_dim,
         positions, cos_table, sin_table, style, static_cast<float*>(k_pool), static_cast<float*>(v_pool),
         token_seq, block_table, table_width, page_size, write_cache);
-  else if (dtype == VIPERA_BF16)
-    rope_cache_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(qkv, static_cast<__nv_bfloat16*>(q_out), num_heads, num_kv_heads, head_dim,
+  if (dtype == VIPERA_BF16)
+    return vipera_launch(rope_cache_kernel<__nv_bfloat16>, grid, threads, 0, s, qkv, static_cast<__nv_bfloat16*>(q_out), num_heads, num_kv_heads, head_dim,
         positions, cos_table, sin_table, style, static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool),
         token_seq, block_table, table_width, page_size, write_cache);
-  else
-    return VIPERA_BAD_DTYPE;
-  return vipera_launch_status();
+  return VIPERA_BAD_DTYPE;
 }
 
 VIPERA_API const char* vipera_rope_cache_status_text(int status) { return vipera_status_text(status); }

@@ -12,6 +12,8 @@
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int hidden, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int token = tokens[t];
   // The host refuses ids outside the vocabulary before the launch; the clamp only keeps
@@ -29,12 +31,10 @@ VIPERA_API int vipera_embed(const void* table, int table_dtype, const int* token
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == VIPERA_F32)
-    embed_kernel<float><<<num_tokens, threads, 0, s>>>(static_cast<const float*>(table), tokens, out, hidden, vocab);
-  else if (table_dtype == VIPERA_BF16)
-    embed_kernel<__nv_bfloat16><<<num_tokens, threads, 0, s>>>(static_cast<const __nv_bfloat16*>(table), tokens, out, hidden, vocab);
-  else
-    return VIPERA_BAD_DTYPE;
-  return vipera_launch_status();
+    return vipera_launch(embed_kernel<float>, num_tokens, threads, 0, s, static_cast<const float*>(table), tokens, out, hidden, vocab);
+  if (table_dtype == VIPERA_BF16)
+    return vipera_launch(embed_kernel<__nv_bfloat16>, num_tokens, threads, 0, s, static_cast<const __nv_bfloat16*>(table), tokens, out, hidden, vocab);
+  return VIPERA_BAD_DTYPE;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -49,6 +49,8 @@ template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ weight,
                                const int* __restrict__ rows, TO* __restrict__ out, int hidden, float eps) {
   __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src_row = rows ? rows[r] : r;
   const float* src = x + static_cast<size_t>(src_row) * hidden;
@@ -89,12 +91,10 @@ VIPERA_API int vipera_rmsnorm(const float* x, const float* weight, const int* ro
   if (hidden <= 0) return VIPERA_BAD_SHAPE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (out_dtype == VIPERA_F32)
-    rmsnorm_kernel<float><<<num_rows, kNormThreads, 0, s>>>(x, weight, rows, static_cast<float*>(out), hidden, eps);
-  else if (out_dtype == VIPERA_BF16)
-    rmsnorm_kernel<__nv_bfloat16><<<num_rows, kNormThreads, 0, s>>>(x, weight, rows, static_cast<__nv_bfloat16*>(out), hidden, eps);
-  else
-    return VIPERA_BAD_DTYPE;
-  return vipera_launch_status();
+    return vipera_launch(rmsnorm_kernel<float>, num_rows, kNormThreads, 0, s, x, weight, rows, static_cast<float*>(out), hidden, eps);
+  if (out_dtype == VIPERA_BF16)
+    return vipera_launch(rmsnorm_kernel<__nv_bfloat16>, num_rows, kNormThreads, 0, s, x, weight, rows, static_cast<__nv_bfloat16*>(out), hidden, eps);
+  return VIPERA_BAD_DTYPE;
 }
 
 VIPERA_API const char* vipera_rowwise_status_text(int status) { return vipera_status_text(status); }
