@@ -406,3 +406,83 @@ def test_sampler_distribution_and_penalties():
                         frequency=torch.tensor([0.25], device=DEV))
     want = torch.tensor([[2.0 / 2 - (0.5 + 0.25 * 2), -1.0 * 2 - (0.5 + 0.25), 0.5, 3.0 - 100.0]])
     assert torch.allclose(logits.cpu(), want)
+
+
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("tokens", [1, 3, 8, 17, 32])
+@pytest.mark.parametrize("n,k", [(96, 64), (1003, 384), (2048, 1536), (130, 8960), (64, 40)])
+@pytest.mark.parametrize("epilogue", [0, 1, 2])
+@pytest.mark.parametrize("normed", [False, True])
+def test_gemv_small(tokens, n, k, epilogue, normed):
+    ops = _ops()
+    if not ops.gemv_small_takes(tokens, k):
+        pytest.skip(f"{tokens} tokens of width {k} do not fit one block's shared memory: the kernel refuses them")
+    if epilogue == 2:
+        n = (n + 31) // 32 * 32
+    torch.manual_seed(tokens * 31 + n + k)
+    w = (torch.randn(n, k, device=DEV) * 0.1).bfloat16()
+    bias = torch.randn(n, device=DEV)
+    resid0 = torch.randn(tokens, n, device=DEV)
+    if normed:
+        x = torch.randn(tokens + 2, k, device=DEV) * 2
+        g = 1 + 0.1 * torch.randn(k, device=DEV)
+        rows = torch.tensor(list(range(tokens + 1, 1, -1)), dtype=torch.int32, device=DEV)
+        xd = x[rows.long()].double()
+        act = xd * (1.0 / torch.sqrt((xd * xd).mean(-1, keepdim=True) + 1e-5)) * g.double()
+        act = act.float().bfloat16().double()  # the kernel stages the normalised rows in bfloat16
+        source = dict(x=x, norm_weight=g, eps=1e-5, rows=rows)
+    else:
+        a = (torch.randn(tokens, k, device=DEV) * 0.5).bfloat16()
+        act = a.double()
+        source = dict(a=a)
+    if epilogue == 0:
+        out = torch.full((tokens, n), float("nan"), device=DEV)
+        ops.gemv_small(w, epilogue=0, bias=bias, out=out, **source)
+    elif epilogue == 1:
+        out = resid0.clone()
+        ops.gemv_small(w, epilogue=1, resid=out, **source)
+    else:
+        out = torch.full((tokens, n // 2), float("nan"), device=DEV, dtype=torch.bfloat16)
+        ops.gemv_small(w, epilogue=2, out=out, **source)
+    want = _gemm_reference(act, w, epilogue, bias, resid0)
+    # a normalised value that lies next to a bfloat16 rounding boundary may round the other
+    # way in the kernel's 32-bit norm than in this 64-bit one: one unit in the last place
+    assert _rel(out, want) < (5e-3 if epilogue == 2 else (1e-3 if normed else 2e-5))
+
+
+def test_gemv_small_rope_cache():
+    """The q/k/v ending: bias, rotation of q and k pairs, q to its buffer, k and v to their pages."""
+    ops = _ops()
+    heads, kv_heads, d, page, hidden = 3, 1, 32, 8, 64
+    tokens = 4
+    torch.manual_seed(4)
+    n = (heads + 2 * kv_heads) * d
+    w = (torch.randn(n, hidden, device=DEV) * 0.2).bfloat16()
+    bias = torch.randn(n, device=DEV)
+    a = torch.randn(tokens, hidden, device=DEV).bfloat16()
+    positions = torch.tensor([0, 9, 10, 40], dtype=torch.int32, device=DEV)
+    token_entry = torch.tensor([0, 1, 1, 2], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[2, -1, -1, -1, -1, -1], [5, 0, -1, -1, -1, -1], [1, 3, 4, 6, 7, 8]], dtype=torch.int32,
+                         device=DEV)
+    half = d // 2
+    inv = 1.0 / torch.pow(torch.tensor(10000.0), 2.0 * torch.arange(half, dtype=torch.float32) / d)
+    angle = torch.arange(64, dtype=torch.float32)[:, None] * inv[None, :]
+    cos, sin = torch.cos(angle).to(DEV), torch.sin(angle).to(DEV)
+    k_pool = torch.zeros(9, page, kv_heads, d, device=DEV, dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    q_out = torch.empty(tokens, heads * d, device=DEV, dtype=torch.bfloat16)
+    rope = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=d, style=ops.ROPE_NEOX, positions=positions,
+                cos=cos, sin=sin, q_out=q_out, write_cache=True, k_pool=k_pool, v_pool=v_pool,
+                token_entry=token_entry, block_table=table, page_size=page)
+    ops.gemv_small(w, a=a, epilogue=ops.GEMV_ROPE_CACHE, bias=bias, rope=rope)
+    x = (a.double() @ w.double().T + bias.double()).view(tokens, heads + 2 * kv_heads, d).cpu()
+    c = cos[positions.long()].cpu().double()[:, None, :]
+    s = sin[positions.long()].cpu().double()[:, None, :]
+    low, high = x[..., :half], x[..., half:]
+    rotated = torch.cat([low * c - high * s, low * s + high * c], dim=-1)
+    assert _rel(q_out.cpu().view(tokens, heads, d), rotated[:, :heads]) < 5e-3
+    for t in range(tokens):
+        p = int(positions[t])
+        physical = int(table[int(token_entry[t]), p // page])
+        assert _rel(k_pool[physical, p % page].cpu(), rotated[t, heads:heads + kv_heads]) < 5e-3
+        assert _rel(v_pool[physical, p % page].cpu(), x[t, heads + kv_heads:]) < 5e-3

@@ -387,3 +387,92 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v
 def attention_decode_scratch_floats(num_entries: int, num_heads: int, head_dim: int, num_splits: int) -> int:
     rows = num_entries * num_heads * num_splits
     return (2 * rows + 3) // 4 * 4 + rows * head_dim
+
+
+# ----------------------------------------------------------------------------------------
+# products for at most 8 tokens, with the norm in front and the ending behind fused in
+# ----------------------------------------------------------------------------------------
+GEMV_MAX_TOKENS = 32
+GEMV_STORE, GEMV_RESIDUAL, GEMV_SWIGLU, GEMV_ROPE_CACHE = 0, 1, 2, 3
+
+
+def gemv_small_takes(tokens: int, k: int) -> bool:
+    """Whether the small-token kernel takes `tokens` tokens against an inner size `k` (the
+    step's activations must fit in one block's shared memory)."""
+    fn = getattr(load_kernel_library("gemv_small"), "vipera_gemv_small_takes")
+    fn.argtypes, fn.restype = [_c_int, _c_int], _c_int
+    return bool(fn(int(tokens), int(k)))
+
+
+class _GemvParams(ctypes.Structure):
+    _fields_ = [
+        ("weight", _c_void), ("N", _c_int), ("K", _c_int), ("T", _c_int),
+        ("x32", _c_void), ("norm_weight", _c_void), ("eps", _c_float), ("rows", _c_void), ("a16", _c_void),
+        ("epilogue", _c_int), ("bias", _c_void), ("out", _c_void), ("out_dtype", _c_int), ("resid", _c_void),
+        ("num_heads", _c_int), ("num_kv_heads", _c_int), ("head_dim", _c_int), ("rope_style", _c_int),
+        ("positions", _c_void), ("cos_table", _c_void), ("sin_table", _c_void), ("q_out", _c_void),
+        ("k_pool", _c_void), ("v_pool", _c_void), ("token_entry", _c_void), ("block_table", _c_void),
+        ("table_width", _c_int), ("page_size", _c_int), ("write_cache", _c_int),
+    ]
+
+
+_gemv_checked = False
+
+
+def gemv_small(w: torch.Tensor, *, a: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None,
+               norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, rows: Optional[torch.Tensor] = None,
+               tokens: Optional[int] = None, epilogue: int = GEMV_STORE, bias: Optional[torch.Tensor] = None,
+               out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None, rope: Optional[dict] = None) -> None:
+    """w[N, K] (bfloat16) times at most 32 tokens.  The input is either ``a`` (bfloat16 [T, K])
+    or the float32 residual stream ``x`` with an RMSNorm (``norm_weight``, ``eps``, optional
+    ``rows`` choosing which rows of x are the tokens) computed on the way.  ``rope`` holds
+    the arguments of the rotary/cache ending (see GQAttention)."""
+    global _gemv_checked
+    fn = _function("gemv_small", "vipera_gemv_small", [ctypes.POINTER(_GemvParams), _c_void])
+    if not _gemv_checked:
+        size = _function("gemv_small", "vipera_gemv_params_size", [])()
+        if size != ctypes.sizeof(_GemvParams):
+            raise InternalError(f"gemv_small: parameter block is {ctypes.sizeof(_GemvParams)} bytes here, {size} in the kernel")
+        _gemv_checked = True
+    n, k = w.shape
+    p = _GemvParams()
+    p.weight, p.N, p.K = _gpu(w, "w", torch.bfloat16), n, k
+    if (a is None) == (x is None):
+        raise InvalidArgumentError("gemv_small: give either a or x")
+    if a is not None:
+        if a.shape[1] != k:
+            raise InvalidArgumentError("gemv_small: inner sizes differ")
+        p.a16, p.T = _gpu(a, "a", torch.bfloat16), a.shape[0]
+    else:
+        if x.shape[1] != k or norm_weight is None or norm_weight.numel() != k:
+            raise InvalidArgumentError("gemv_small: x and norm_weight must have the weight's inner size")
+        p.x32, p.norm_weight, p.eps = _gpu(x, "x", torch.float32), _gpu(norm_weight, "norm_weight", torch.float32), float(eps)
+        p.rows = _opt(rows, "rows", torch.int32)
+        p.T = int(tokens if tokens is not None else (rows.numel() if rows is not None else x.shape[0]))
+    t = p.T
+    if not gemv_small_takes(t, k):
+        raise UnsupportedError(f"gemv_small does not take {t} tokens against an inner size of {k}")
+    p.epilogue = epilogue
+    if epilogue == GEMV_ROPE_CACHE:
+        r = rope
+        p.bias = _opt(bias, "bias", torch.float32)
+        p.num_heads, p.num_kv_heads, p.head_dim, p.rope_style = r["num_heads"], r["num_kv_heads"], r["head_dim"], r["style"]
+        p.positions = _gpu(r["positions"], "positions", torch.int32)
+        p.cos_table, p.sin_table = _opt(r["cos"], "cos", torch.float32), _opt(r["sin"], "sin", torch.float32)
+        q_out = r["q_out"]
+        if tuple(q_out.shape) != (t, r["num_heads"] * r["head_dim"]):
+            raise InvalidArgumentError("gemv_small: q_out has the wrong shape")
+        p.q_out = _gpu(q_out, "q_out", torch.bfloat16)
+        p.write_cache = 1 if r["write_cache"] else 0
+        if r["write_cache"]:
+            p.k_pool, p.v_pool = _gpu(r["k_pool"], "k_pool", torch.bfloat16), _gpu(r["v_pool"], "v_pool", torch.bfloat16)
+            p.token_entry = _gpu(r["token_entry"], "token_entry", torch.int32)
+            p.block_table = _gpu(r["block_table"], "block_table", torch.int32)
+            p.table_width, p.page_size = r["block_table"].shape[1], r["page_size"]
+    else:
+        _check_gemm_outputs(t, n, epilogue, bias, out, resid)
+        p.bias = _opt(bias, "bias", torch.float32) if epilogue == GEMV_STORE else None
+        p.out = _opt(out, "out")
+        p.out_dtype = dtype_code(out.dtype) if out is not None else F32
+        p.resid = _opt(resid, "resid", torch.float32)
+    _check(fn(ctypes.byref(p), _stream()), "gemv_small")

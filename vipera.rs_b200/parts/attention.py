@@ -19,7 +19,7 @@ from ..errors import UnsupportedError
 from ..kernels import ops
 from ..weights import TensorSpec
 from .base import Mixer, PagedKV
-from .linear import Linear
+from .linear import Linear, NormedInput
 
 
 class GQAttention(Mixer):
@@ -28,6 +28,7 @@ class GQAttention(Mixer):
     optionally, ``projection_names`` (defaults q_proj, k_proj, v_proj, o_proj)."""
 
     kernels = ("rope_cache", "attention", "attention_mma")
+    takes_lazy_input = True
 
     @staticmethod
     def _names(params):
@@ -84,11 +85,27 @@ class GQAttention(Mixer):
         count = ctx.num_tokens
         heads, kv_heads, d = self.num_heads, self.num_kv_heads, self.head_dim
         ws = ctx.workspace
-        qkv = ws.get("attention.qkv", (count, (heads + 2 * kv_heads) * d), torch.float32)
-        self.qkv(ctx, h, epilogue=ops.EPI_STORE, out=qkv)
         q = ws.get("attention.q", (count, heads * d), ctx.dtype)
         table = ctx.block_tables[cache.group]
         style = self.position.style
+        if self.qkv.takes_small(count) and style in (ops.ROPE_NONE, ops.ROPE_NEOX):
+            # few tokens: one kernel for norm, q/k/v product, bias, rotation and cache write
+            cos, sin = self.position.tables()
+            rope = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=d, style=style, positions=ctx.positions,
+                        cos=cos, sin=sin, q_out=q, write_cache=writes_cache, k_pool=cache.k, v_pool=cache.v,
+                        token_entry=ctx.token_entry, block_table=table, page_size=cache.page_size)
+            if isinstance(h, NormedInput) and h.fusable:
+                ops.gemv_small(self.qkv.weight, x=h.residual, norm_weight=h.norm.weight, eps=h.norm.eps,
+                               tokens=count, epilogue=ops.GEMV_ROPE_CACHE, bias=self.qkv.bias, rope=rope)
+            else:
+                ops.gemv_small(self.qkv.weight, a=h.tensor() if isinstance(h, NormedInput) else h,
+                               epilogue=ops.GEMV_ROPE_CACHE, bias=self.qkv.bias, rope=rope)
+            mixed = ws.get("attention.out", (count, heads * d), ctx.dtype)
+            self._attend(ctx, q, mixed, cache, table)
+            self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
+            return
+        qkv = ws.get("attention.qkv", (count, (heads + 2 * kv_heads) * d), torch.float32)
+        self.qkv(ctx, h, epilogue=ops.EPI_STORE, out=qkv)
         if style is None:
             # An encoding the fused kernel does not know: the part applies it to the 32-bit
             # product itself, then the kernel only converts and stores.

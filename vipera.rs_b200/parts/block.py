@@ -8,6 +8,7 @@ last product.
 from __future__ import annotations
 
 from ..config.registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS
+from .linear import NormedInput
 
 
 class PreNormBlock:
@@ -37,12 +38,13 @@ class PreNormBlock:
         return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
 
     def forward(self, ctx, residual, cache, writes_cache):
-        hidden = residual.shape[1]
-        h = ctx.workspace.get("block.h", (ctx.num_tokens, hidden), ctx.dtype)
-        self.mixer_norm.forward(ctx, residual, h)
-        self.mixer.forward(ctx, h, residual, cache, writes_cache)
-        self.ffn_norm.forward(ctx, residual, h)
-        self.ffn.forward(ctx, h, residual)
+        # A part that sets ``takes_lazy_input`` receives the normalised input as a NormedInput
+        # and may fuse the norm into its first product; any other part receives a tensor.
+        h = NormedInput(ctx, self.mixer_norm, residual)
+        self.mixer.forward(ctx, h if getattr(self.mixer, "takes_lazy_input", False) else h.tensor(),
+                           residual, cache, writes_cache)
+        h = NormedInput(ctx, self.ffn_norm, residual)
+        self.ffn.forward(ctx, h if getattr(self.ffn, "takes_lazy_input", False) else h.tensor(), residual)
 
 
 BLOCKS.register("prenorm", PreNormBlock)

@@ -8,6 +8,7 @@ and the CUDA-core kernel elsewhere.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -16,6 +17,7 @@ from ..errors import UnsupportedError
 from ..kernels import ops
 
 SWIGLU_GROUP = 16  # gate rows and up rows alternate in groups of this many
+SMALL_KERNEL_MAX_ROWS = int(os.environ.get("VIPERA_GEMV_MAX_ROWS", 4096))
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -34,6 +36,34 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return stacked.reshape(2 * inter, hidden).contiguous()
 
 
+class NormedInput:
+    """The normalised residual stream as an input that may not have been computed yet.
+
+    A product that can take the norm with it (the small-token kernel) reads ``residual``,
+    ``norm.weight`` and ``norm.eps`` itself; everything else calls ``tensor()``, which runs
+    the norm once and keeps the result for the other products of the same part."""
+
+    def __init__(self, ctx, norm, residual: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                 num_rows: Optional[int] = None, name: str = "block.h"):
+        self.ctx, self.norm, self.residual, self.rows = ctx, norm, residual, rows
+        self.num_rows = int(num_rows if num_rows is not None else residual.shape[0])
+        self.name = name
+        self._tensor = None
+
+    @property
+    def fusable(self) -> bool:
+        weight = getattr(self.norm, "weight", None)
+        return (getattr(self.norm, "fused_kind", None) == "rmsnorm" and weight is not None
+                and weight.dtype == torch.float32)
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            out = self.ctx.workspace.get(self.name, (self.num_rows, self.residual.shape[1]), self.ctx.dtype)
+            self.norm.forward(self.ctx, self.residual, out, rows=self.rows)
+            self._tensor = out
+        return self._tensor
+
+
 class Linear:
     """``weight`` is [N, K] in the run dtype on the device; ``bias`` float32 [N] or None."""
 
@@ -44,6 +74,7 @@ class Linear:
         self.bias = None if bias is None else bias.to(device=device, dtype=torch.float32).contiguous()
         self.out_features, self.in_features = self.weight.shape
         self._tensor_core = None
+        self._small_ok = {}
         if dtype == torch.bfloat16:
             from . import tensor_core
 
@@ -51,12 +82,39 @@ class Linear:
 
     def kernel_families(self):
         if self._tensor_core is not None:
-            return ("gemm_simt", "gemm_tc")
+            return ("gemm_simt", "gemm_tc", "gemv_small")
         return ("gemm_simt",)
 
-    def __call__(self, ctx, a: torch.Tensor, *, epilogue: int = ops.EPI_STORE,
+    def takes_small(self, tokens: int) -> bool:
+        """Whether the small-token kernel runs this product for `tokens` tokens."""
+        # The small-token kernel wins where a product has few output rows (its fixed cost is
+        # low and it fuses the norm in front); wide products stream better through TMA.
+        if self._tensor_core is None or self.out_features > SMALL_KERNEL_MAX_ROWS:
+            return False
+        most = min(int(os.environ.get("VIPERA_GEMV_MAX_TOKENS", ops.GEMV_MAX_TOKENS)), ops.GEMV_MAX_TOKENS)
+        if tokens > most:
+            return False
+        known = self._small_ok.get(tokens)
+        if known is None:
+            known = self._small_ok[tokens] = ops.gemv_small_takes(tokens, self.in_features)
+        return known
+
+    def __call__(self, ctx, a, *, epilogue: int = ops.EPI_STORE,
                  out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None) -> None:
+        """``a`` is a tensor [tokens, K] in the run dtype, or a NormedInput."""
         bias = self.bias if epilogue == ops.EPI_STORE else None
+        lazy = a if isinstance(a, NormedInput) else None
+        tokens = lazy.num_rows if lazy is not None else a.shape[0]
+        if self.takes_small(tokens):
+            if lazy is not None and lazy.fusable and lazy._tensor is None:
+                ops.gemv_small(self.weight, x=lazy.residual, norm_weight=lazy.norm.weight, eps=lazy.norm.eps,
+                               rows=lazy.rows, tokens=tokens, epilogue=epilogue, bias=bias, out=out, resid=resid)
+            else:
+                ops.gemv_small(self.weight, a=lazy.tensor() if lazy is not None else a, epilogue=epilogue,
+                               bias=bias, out=out, resid=resid)
+            return
+        if lazy is not None:
+            a = lazy.tensor()
         if self._tensor_core is not None and self._tensor_core.takes(a, epilogue, out):
             self._tensor_core.run(ctx, a, epilogue=epilogue, bias=bias, out=out, resid=resid)
             return

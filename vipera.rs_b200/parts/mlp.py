@@ -21,6 +21,8 @@ class SwiGLU(FeedForward):
     """params: hidden_size, intermediate_size and, optionally, ``projection_names``
     (defaults gate_proj, up_proj, down_proj)."""
 
+    takes_lazy_input = True
+
     @staticmethod
     def _names(params):
         return params.get("projection_names", ("gate_proj", "up_proj", "down_proj"))

@@ -17,7 +17,7 @@ from ..errors import InvalidArgumentError
 from ..kernels import ops
 from ..weights import Schema, TensorSpec, WeightSource, check_source, to_run_dtype
 from .base import StepContext
-from .linear import Linear
+from .linear import Linear, NormedInput
 
 
 def model_schema(spec: ModelSpec) -> Schema:
@@ -98,8 +98,8 @@ class DecoderModel:
             self.blocks[entry.layer].forward(ctx, residual, caches.get(entry.cache), entry.writes_cache)
         if ctx.num_logit_rows == 0:
             return None
-        h = ws.get("model.final", (ctx.num_logit_rows, self.spec.hidden_size), ctx.dtype)
-        self.final_norm.forward(ctx, residual, h, rows=ctx.logit_rows)
+        h = NormedInput(ctx, self.final_norm, residual, rows=ctx.logit_rows, num_rows=ctx.num_logit_rows,
+                        name="model.final")
         logits = ws.get("model.logits", (ctx.num_logit_rows, self.spec.vocab_size), torch.float32)
         self.head(ctx, h, epilogue=ops.EPI_STORE, out=logits)
         if self.spec.logit_scale != 1.0:

@@ -14,6 +14,7 @@ class RMSNorm(Norm):
     """params: ``size`` (width of a row), ``eps``.  Tensor: ``<prefix>.weight`` [size]."""
 
     kernels = ("rowwise",)
+    fused_kind = "rmsnorm"  # products that can compute a norm on the way recognise it by this
 
     @classmethod
     def schema(cls, params, prefix):
