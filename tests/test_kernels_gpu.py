@@ -99,7 +99,7 @@ def test_gemm(m, n, k, epilogue, kind):
     assert _rel(out, want) < limit
 
 
-def test_gemm_tc_repeats_exactly_and_counters_return_to_zero():
+def test_gemm_tc_repeats_exactly():
     """Split sums are added in a fixed order: the same product twice gives the same bits."""
     ops = _ops()
     torch.manual_seed(5)

@@ -341,7 +341,7 @@ __device__ __forceinline__ void load_kv_rows32(uint32_t k_tile, uint32_t v_tile,
 
 // partial layout: [token][head][split]: max (log2 units), sum, and D unnormalised outputs.
 template <int D>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 3)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
                         const int* __restrict__ block_table, int table_width, int page_size, int page_shift,
@@ -361,6 +361,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const int first_visible = window > 0 ? max(0, position - window + 1) : 0;
   const int begin = max(split * chunk, first_visible / kKeys * kKeys);
   const int end = min((split + 1) * chunk, position + 1);
+  if (begin >= end) return;  // a split without visible keys: the combine kernel skips it too
 
   uint8_t* q_bytes = smem;                                        // [16][D] bf16, shared by the warps
   uint8_t* warp_bytes = smem + 16 * D * 2 + warp * kWarpTile;
@@ -484,7 +485,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 // grid: (tokens, heads); one block of D threads combines the splits of one row.
 template <int D>
 __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, const float* __restrict__ partial_out,
-                                         int slices, __nv_bfloat16* __restrict__ out, int num_heads) {
+                                         int slices, __nv_bfloat16* __restrict__ out, int num_heads,
+                                         const int* __restrict__ positions, int window, int chunk) {
   __shared__ float maxima[128];
   __shared__ float sums[128];
   pdl_launch_dependents();
@@ -492,17 +494,22 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
   const size_t row = static_cast<size_t>(blockIdx.x) * num_heads + blockIdx.y;
   const float* ml = partial_ml + 2 * row * slices;
   const float* values = partial_out + row * slices * D + threadIdx.x;
+  // only the splits that hold visible keys were written by the decode kernel
+  const int position = positions[blockIdx.x];
+  const int first_visible = window > 0 ? max(0, position - window + 1) : 0;
+  const int first = (first_visible / 32 * 32) / chunk;
+  const int last = min(slices - 1, position / chunk);
   // all (max, sum) pairs at once, then the weights of the splits (at most 128 splits)
   float mine = -INFINITY;
-  for (int s = threadIdx.x; s < slices; s += D) {
+  for (int s = first + threadIdx.x; s <= last; s += D) {
     maxima[s] = ml[2 * s];
     sums[s] = ml[2 * s + 1];
   }
   __syncthreads();
-  for (int s = 0; s < slices; ++s) mine = fmaxf(mine, maxima[s]);
+  for (int s = first; s <= last; ++s) mine = fmaxf(mine, maxima[s]);
   float total = 0.0f, value = 0.0f;
 #pragma unroll 8
-  for (int s = 0; s < slices; ++s) {
+  for (int s = first; s <= last; ++s) {
     const float m = maxima[s];
     const float w = m == -INFINITY ? 0.0f : exp2f(m - mine);  // a split that saw no key
     total += sums[s] * w;
@@ -555,7 +562,7 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
   if (status != VIPERA_OK) return status;
   return vipera_launch(attention_combine_kernel<D>, dim3(num_entries, num_heads), D, 0, s,
       static_cast<const float*>(partial_ml), static_cast<const float*>(partial_out), num_splits,
-      static_cast<__nv_bfloat16*>(out), num_heads);
+      static_cast<__nv_bfloat16*>(out), num_heads, positions, window, chunk);
 }
 
 }  // namespace

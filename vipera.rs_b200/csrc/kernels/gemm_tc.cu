@@ -7,8 +7,8 @@
 //     other side;
 //   * few tokens (decode, short portions): weight rows on the 128-row side and the tokens,
 //     padded to 16/32/64/128, on the other side.  Each weight byte is read from HBM once and
-//     the K range is cut into splits so that every SM streams a share of the weights; the
-//     last block to finish a tile adds the splits' partial sums in a fixed order.
+//     the K range is cut into splits so that every SM streams a share of the weights; a
+//     second small kernel adds the splits' partial sums in a fixed order and writes the ending.
 // The reference multiplies every weight matrix by all rows of the batch in one pass over the
 // weights (crates/vipera-backend-cpu/src/model.rs:1005-1025, 1154-1198) and has a device
 // kernel that shares one weight read between up to 8 activation sets
@@ -47,7 +47,6 @@ struct GemmParams {
   void* out;
   float* resid;
   float* scratch;    // split partials: [item][BN][128] floats
-  int* counters;     // one per tile, zero between launches
   int* status;       // device word: 0, or an error code
 };
 
@@ -251,7 +250,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   uint64_t* acc_empty = bars + 2 * kStages + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
@@ -356,7 +354,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
   } else {
     // ---------------- epilogue warps 0..3 ----------------
-    pdl_wait();  // outputs, the residual stream, scratch and counters belong to earlier kernels until now
+    pdl_wait();  // outputs, the residual stream, and the scratch belong to earlier kernels until now
     int local = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++local) {
       const int tile = item / p.splits;
@@ -404,34 +402,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
-        // the last block to finish this tile adds the partials, split 0 first
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (threadIdx.x == 0) {
-          const int seen = atomicAdd(&p.counters[tile], 1);
-          *last_flag = (seen == p.splits - 1) ? 1 : 0;
-          if (seen == p.splits - 1) p.counters[tile] = 0;  // ready for the next launch
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*last_flag) {
-          __threadfence();
-          const float* first = p.scratch + static_cast<size_t>(tile) * p.splits * BN * kTileX;
-#pragma unroll 1
-          for (int c = 0; c < BN; c += 32) {
-            float v[32];
-            const int width = BN - c < 32 ? BN - c : 32;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0.0f;
-            for (int s = 0; s < p.splits; ++s) {
-              const float* src = first + static_cast<size_t>(s) * BN * kTileX;
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (i < width) v[i] += __ldcg(src + static_cast<size_t>(c + i) * kTileX + row_in_tile);
-            }
-            finish_chunk<BN, SWAP>(p, v, width, row, ty * BN + c);
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
       }
     }
   }
@@ -448,6 +418,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Config::kTmemCols));
   }
+}
+
+// The second kernel of a product that was cut along K: adds the splits' partial sums, split
+// 0 first, and writes the ending.  grid = (tiles, BN / 16): a block takes 16 columns of a tile.
+template <int BN>
+__global__ void __launch_bounds__(kTileX)
+splitk_finish_kernel(const GemmParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tile = blockIdx.x;
+  const int tx = tile % p.tiles_x, ty = tile / p.tiles_x;
+  const int c0 = blockIdx.y * 16;
+  const int row_in_tile = threadIdx.x;
+  const float* first = p.scratch + static_cast<size_t>(tile) * p.splits * BN * kTileX;
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+  for (int s = 0; s < p.splits; ++s) {
+    const float* src = first + static_cast<size_t>(s) * BN * kTileX + static_cast<size_t>(c0) * kTileX + row_in_tile;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] += __ldcg(src + static_cast<size_t>(i) * kTileX);
+  }
+  finish_chunk<BN, true>(p, v, 16, tx * kTileX + row_in_tile, ty * BN + c0);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -491,7 +484,6 @@ struct GemmPlan {
   int bn;
   int tiles_x, tiles_y, splits, k_blocks_per_split, num_k_blocks;
   size_t scratch_floats;
-  int counters;
 };
 
 static int sm_count() {
@@ -527,19 +519,16 @@ static GemmPlan make_plan(int T, int N, int K, int sms) {
     plan.k_blocks_per_split = (plan.num_k_blocks + want - 1) / want;
     plan.splits = (plan.num_k_blocks + plan.k_blocks_per_split - 1) / plan.k_blocks_per_split;
   }
-  plan.counters = plan.tiles_x * plan.tiles_y;
   plan.scratch_floats = plan.splits > 1
       ? static_cast<size_t>(plan.tiles_x) * plan.tiles_y * plan.splits * plan.bn * kTileX : 0;
   return plan;
 }
 
-// Bytes of scratch and number of counters a product of these sizes needs (0 when it runs
-// without splits).  The counters must be zero before the first launch; every launch leaves
-// them zero.
-VIPERA_API int vipera_gemm_tc_workspace(int T, int N, int K, size_t* scratch_bytes, int* counters) {
+// Bytes of scratch a product of these sizes needs for the partial sums of its splits (0 when
+// it runs without splits).
+VIPERA_API int vipera_gemm_tc_workspace(int T, int N, int K, size_t* scratch_bytes) {
   const GemmPlan plan = make_plan(T, N, K, sm_count());
   *scratch_bytes = plan.scratch_floats * sizeof(float);
-  *counters = plan.splits > 1 ? plan.counters : 0;
   return VIPERA_OK;
 }
 
@@ -552,7 +541,9 @@ static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, co
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  return vipera_launch(gemm_tc_kernel<BN, SWAP>, grid, kThreads, Config::kSmemBytes, s, map_x, map_y, p);
+  int status = vipera_launch(gemm_tc_kernel<BN, SWAP>, grid, kThreads, Config::kSmemBytes, s, map_x, map_y, p);
+  if (status != VIPERA_OK || p.splits == 1) return status;
+  return vipera_launch(splitk_finish_kernel<BN>, dim3(p.tiles_x * p.tiles_y, BN / 16), dim3(kTileX), 0, s, p);
 }
 
 // A is [T, K] bfloat16, W is [N, K] bfloat16, both row-major and contiguous with K a
@@ -560,7 +551,7 @@ static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, co
 // before the launch; it is non-zero afterwards when a bounded wait inside the kernel ran out.
 VIPERA_API int vipera_gemm_tc(const void* A, const void* W, int T, int N, int K, int epilogue, const float* bias,
                               void* out, int out_dtype, float* resid, float* scratch, size_t scratch_bytes,
-                              int* counters, int num_counters, int* status, void* stream) {
+                              int* status, void* stream) {
   if (T <= 0) return VIPERA_OK;
   if (N <= 0 || K <= 0 || (K % 8) != 0) return VIPERA_BAD_SHAPE;
   if (epilogue == EPI_SWIGLU && (N % 32) != 0) return VIPERA_BAD_SHAPE;
@@ -570,8 +561,7 @@ VIPERA_API int vipera_gemm_tc(const void* A, const void* W, int T, int N, int K,
   const int sms = sm_count();
   const GemmPlan plan = make_plan(T, N, K, sms);
   if (plan.splits > 1) {
-    if (!scratch || !counters || scratch_bytes < plan.scratch_floats * sizeof(float) || num_counters < plan.counters)
-      return VIPERA_BAD_ARGUMENT;
+    if (!scratch || scratch_bytes < plan.scratch_floats * sizeof(float)) return VIPERA_BAD_ARGUMENT;
   }
   CUtensorMap map_x, map_y;
   int r;
@@ -596,7 +586,6 @@ VIPERA_API int vipera_gemm_tc(const void* A, const void* W, int T, int N, int K,
   p.out = out;
   p.resid = resid;
   p.scratch = scratch;
-  p.counters = counters;
   p.status = status;
   const int items = plan.tiles_x * plan.tiles_y * plan.splits;
   const int grid = items < sms ? items : sms;

@@ -255,29 +255,26 @@ _tc_state = {}
 buffer_generation = 0  # goes up whenever a shared kernel buffer moves; captured graphs are then stale
 
 
-def _tc_buffers(device, scratch_bytes: int, counters: int):
-    """Scratch for split partial sums, tile counters (zero between launches) and the status
-    word of the tensor-core kernels, per device.  They grow on demand and are shared by all
-    products, which run one after another on one stream."""
+def _tc_buffers(device, scratch_bytes: int):
+    """Scratch for the partial sums of split products and the status word of the tensor-core
+    kernels, per device.  The scratch grows on demand and is shared by all products, which
+    run one after another on one stream."""
     global buffer_generation
-    state = _tc_state.setdefault(str(device), {"scratch": None, "counters": None, "status": None})
+    state = _tc_state.setdefault(str(device), {"scratch": None, "status": None})
     if state["status"] is None:
         state["status"] = torch.zeros(1, dtype=torch.int32, device=device)
     if scratch_bytes and (state["scratch"] is None or state["scratch"].numel() * 4 < scratch_bytes):
         state["scratch"] = torch.empty(max(scratch_bytes // 4, 8 << 20), dtype=torch.float32, device=device)
-        buffer_generation += 1
-    if counters and (state["counters"] is None or state["counters"].numel() < counters):
-        state["counters"] = torch.zeros(max(counters, 16384), dtype=torch.int32, device=device)
         buffer_generation += 1
     return state
 
 
 def gemm_tc_workspace(m: int, n: int, k: int):
     fn = _function("gemm_tc", "vipera_gemm_tc_workspace",
-                   [_c_int, _c_int, _c_int, ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(_c_int)])
-    scratch, counters = ctypes.c_size_t(0), _c_int(0)
-    _check(fn(m, n, k, ctypes.byref(scratch), ctypes.byref(counters)), "gemm_tc_workspace", kernels=0)
-    return scratch.value, counters.value
+                   [_c_int, _c_int, _c_int, ctypes.POINTER(ctypes.c_size_t)])
+    scratch = ctypes.c_size_t(0)
+    _check(fn(m, n, k, ctypes.byref(scratch)), "gemm_tc_workspace", kernels=0)
+    return scratch.value
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE,
@@ -286,7 +283,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE,
     """a[M, K] times w[N, K] transposed in bfloat16 on the tensor cores (tcgen05, TMA)."""
     fn = _function("gemm_tc", "vipera_gemm_tc",
                    [_c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void,
-                    ctypes.c_size_t, _c_void, _c_int, _c_void, _c_void])
+                    ctypes.c_size_t, _c_void, _c_void])
     m, k = a.shape
     n = w.shape[0]
     if w.shape[1] != k:
@@ -294,17 +291,15 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE,
     if k % 8:
         raise UnsupportedError(f"gemm_tc: inner size {k} is not a multiple of 8")
     _check_gemm_outputs(m, n, epilogue, bias, out, resid)
-    scratch_bytes, counters = gemm_tc_workspace(m, n, k)
-    state = _tc_buffers(a.device, scratch_bytes, counters)
-    scratch, counter_tensor = state["scratch"], state["counters"]
+    scratch_bytes = gemm_tc_workspace(m, n, k)
+    state = _tc_buffers(a.device, scratch_bytes)
+    scratch = state["scratch"]
     _check(fn(_gpu(a, "a", torch.bfloat16), _gpu(w, "w", torch.bfloat16), m, n, k, epilogue,
               _opt(bias, "bias", torch.float32), _opt(out, "out"),
               dtype_code(out.dtype) if out is not None else F32, _opt(resid, "resid", torch.float32),
               None if scratch is None else scratch.data_ptr(),
               0 if scratch is None else scratch.numel() * 4,
-              None if counter_tensor is None else counter_tensor.data_ptr(),
-              0 if counter_tensor is None else counter_tensor.numel(),
-              state["status"].data_ptr(), _stream()), "gemm_tc")
+              state["status"].data_ptr(), _stream()), "gemm_tc", kernels=2 if scratch_bytes else 1)
 
 
 def check_kernel_status(device) -> None:
