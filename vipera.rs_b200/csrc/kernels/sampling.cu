@@ -396,3 +396,44 @@ VIPERA_API int vipera_sample(const float* logits, int rows, int vocab, const flo
 }
 
 VIPERA_API const char* vipera_sampling_status_text(int status) { return vipera_status_text(status); }
+
+// ---------------------------------------------------------------------------------------
+// greedy argmax for callers that cannot allocate (see no_alloc.h)
+// ---------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// The scratch of the two argmax stages, inside the library image itself.  In host code this
+// name is only a handle for the symbol, not a device address: the address comes from
+// cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned int argmax_static_scratch[64 * VIPERA_ARGMAX_STATIC_MAX_ROWS];
+
+// Device address of the array on each device, looked up on the first call there.
+static void* argmax_static_address[64] = {nullptr};
+
+extern "C" __attribute__((visibility("default")))
+int vipera_argmax_static(const float* logits, int rows, int vocab, int* tokens, int* status, void* stream) {
+  if (rows <= 0) return VIPERA_OK;
+  if (rows > VIPERA_ARGMAX_STATIC_MAX_ROWS || vocab <= 0) return VIPERA_BAD_SHAPE;
+  if (!logits || !tokens) return VIPERA_BAD_ARGUMENT;
+  int device = 0;
+  cudaError_t error = cudaGetDevice(&device);
+  if (error != cudaSuccess) return static_cast<int>(error);
+  if (device < 0 || device >= 64) return VIPERA_BAD_ARGUMENT;
+  if (argmax_static_address[device] == nullptr) {
+    // set-up, once per device, with that device current
+    void* address = nullptr;
+    error = cudaGetSymbolAddress(&address, argmax_static_scratch);
+    if (error != cudaSuccess) return static_cast<int>(error);
+    argmax_static_address[device] = address;
+  }
+  float* slice_value = static_cast<float*>(argmax_static_address[device]);
+  int* slice_id = reinterpret_cast<int*>(slice_value + static_cast<size_t>(rows) * kArgmaxSlices);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // Every (row, slice) word is written by the first kernel before the second reads it, so
+  // nothing left by an earlier call is ever read and nothing needs clearing.
+  argmax_slice_kernel<<<dim3(rows, kArgmaxSlices), kArgmaxThreads, 0, s>>>(logits, vocab, slice_value, slice_id);
+  int launched = vipera_launch_status();
+  if (launched != VIPERA_OK) return launched;
+  argmax_final_kernel<<<rows, 32, 0, s>>>(slice_value, slice_id, tokens, status);
+  return vipera_launch_status();
+}
