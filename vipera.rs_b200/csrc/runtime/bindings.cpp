@@ -123,6 +123,7 @@ PYBIND11_MODULE(_vipera_runtime, m) {
       .def("is_open", &CacheManager::is_open)
       .def("pages_missing", &CacheManager::pages_missing)
       .def("fits", &CacheManager::fits)
+      .def("admits", &CacheManager::admits)
       .def("longest_fit", &CacheManager::longest_fit)
       .def("reserve", &CacheManager::reserve)
       .def("commit", &CacheManager::commit)

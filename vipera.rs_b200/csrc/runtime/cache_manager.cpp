@@ -2,7 +2,7 @@
 
 #include <algorithm>
 #include <limits>
-#include <sstream>
+#include <string>
 
 namespace vipera {
 
@@ -81,6 +81,17 @@ bool CacheManager::fits(int64_t request, int new_length) const {
   return true;
 }
 
+bool CacheManager::admits(int length, int portion) const {
+  for (const Group& group : groups_) {
+    const int ps = group.config.page_size;
+    int tokens = length;
+    if (group.config.window > 0) tokens = std::min(length, group.config.window + portion + ps);
+    const int pages = (tokens + ps - 1) / ps;
+    if (pages > static_cast<int>(group.free.size())) return false;
+  }
+  return true;
+}
+
 int CacheManager::longest_fit(int64_t request, int new_length) const {
   const Request& entry = find(request);
   int low = entry.computed, high = new_length;  // `low` always fits: it needs nothing new
@@ -96,10 +107,11 @@ void CacheManager::reserve(int64_t request, int new_length) {
   std::vector<int> missing = pages_missing(request, new_length);
   for (size_t g = 0; g < groups_.size(); ++g) {
     if (missing[g] > static_cast<int>(groups_[g].free.size())) {
-      std::ostringstream message;
-      message << "cache is full: " << missing[g] << " pages needed for request " << request
-              << " in group " << g << ", " << groups_[g].free.size() << " free";
-      throw Infeasible(message.str());
+      // (plain string building: stream formatting has crashed inside processes that load
+      // several C++ runtimes)
+      throw Infeasible("cache is full: " + std::to_string(missing[g]) + " pages needed for request " +
+                       std::to_string(request) + " in group " + std::to_string(g) + ", " +
+                       std::to_string(groups_[g].free.size()) + " free");
     }
   }
   Request& entry = find(request);
@@ -209,46 +221,37 @@ std::vector<int64_t> CacheManager::open_requests() const {
 }
 
 std::string CacheManager::audit() const {
-  std::ostringstream fault;
   for (size_t g = 0; g < groups_.size(); ++g) {
     const Group& group = groups_[g];
     std::vector<int> seen(group.config.num_pages, 0);
     for (int32_t page : group.free) {
       if (page < 0 || page >= group.config.num_pages) {
-        fault << "group " << g << ": free stack holds page " << page << " outside the pool";
-        return fault.str();
+        return std::string("group ") + std::to_string(g) + std::string(": free stack holds page ") + std::to_string(page) + std::string(" outside the pool");
       }
       if (++seen[page] > 1) {
-        fault << "group " << g << ": page " << page << " is on the free stack twice";
-        return fault.str();
+        return std::string("group ") + std::to_string(g) + std::string(": page ") + std::to_string(page) + std::string(" is on the free stack twice");
       }
       if (group.held[page]) {
-        fault << "group " << g << ": page " << page << " is free and marked held";
-        return fault.str();
+        return std::string("group ") + std::to_string(g) + std::string(": page ") + std::to_string(page) + std::string(" is free and marked held");
       }
     }
     for (const auto& item : requests_) {
       for (int32_t page : item.second.tables[g]) {
         if (page < 0) continue;
         if (page >= group.config.num_pages) {
-          fault << "group " << g << ": request " << item.first << " holds page " << page
-                << " outside the pool";
-          return fault.str();
+          return std::string("group ") + std::to_string(g) + std::string(": request ") + std::to_string(item.first) + std::string(" holds page ") + std::to_string(page) + std::string(" outside the pool");
         }
         if (++seen[page] > 1) {
-          fault << "group " << g << ": page " << page << " is held twice or held and free";
-          return fault.str();
+          return std::string("group ") + std::to_string(g) + std::string(": page ") + std::to_string(page) + std::string(" is held twice or held and free");
         }
         if (!group.held[page]) {
-          fault << "group " << g << ": page " << page << " is in a table but not marked held";
-          return fault.str();
+          return std::string("group ") + std::to_string(g) + std::string(": page ") + std::to_string(page) + std::string(" is in a table but not marked held");
         }
       }
     }
     for (int page = 0; page < group.config.num_pages; ++page) {
       if (seen[page] == 0) {
-        fault << "group " << g << ": page " << page << " is lost (neither free nor held)";
-        return fault.str();
+        return std::string("group ") + std::to_string(g) + std::string(": page ") + std::to_string(page) + std::string(" is lost (neither free nor held)");
       }
     }
   }

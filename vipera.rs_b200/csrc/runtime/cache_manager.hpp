@@ -57,6 +57,10 @@ class CacheManager {
   std::vector<int> pages_missing(int64_t request, int new_length) const;
   // Whether `reserve(request, new_length)` would succeed now.
   bool fits(int64_t request, int new_length) const;
+  // Whether a request of `length` tokens, computed in portions of at most `portion` tokens,
+  // can be taken in now: groups that keep every key need pages for all of it, windowed
+  // groups for the window and one portion.
+  bool admits(int length, int portion) const;
   // The longest length <= new_length that fits now (never below the computed length).
   int longest_fit(int64_t request, int new_length) const;
   // Make sure every page is held that computing tokens [computed, new_length) reads or

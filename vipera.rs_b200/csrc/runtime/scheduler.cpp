@@ -186,7 +186,7 @@ StepPlan Scheduler::schedule() {
     Request& head = waiting_.front();
     int length = static_cast<int>(head.tokens.size());
     cache_->open(head.id);
-    if (!cache_->fits(head.id, length)) {
+    if (!cache_->admits(length, config_.max_portion)) {
       cache_->close(head.id);
       if (running_.empty()) {
         // Nothing runs and it still does not fit: it never will.
@@ -198,6 +198,11 @@ StepPlan Scheduler::schedule() {
       break;
     }
     int want = std::min({length, config_.max_portion, config_.max_tokens_per_step - used});
+    want = cache_->longest_fit(head.id, want);
+    if (want <= 0) {
+      cache_->close(head.id);
+      break;
+    }
     cache_->reserve(head.id, want);
     Request request = std::move(waiting_.front());
     waiting_.pop_front();
