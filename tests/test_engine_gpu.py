@@ -81,3 +81,45 @@ def test_few_pages_preempt_and_recompute():
         _check_greedy(folder, prompt, result.tokens, "float32")
     assert engine.pools.manager.audit() == ""
     assert engine.stats()["kv_used_pages"] == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_the_first_tokens(dtype):
+    """A one-token prompt decoded for 300 steps (over many pages, through the decode graphs of
+    growing table widths): the first tokens and every later one are the plain implementation's
+    choices."""
+    from vipera_rs_b200 import SamplingParams
+
+    folder, engine = _engine("A", dtype, page_size=16, ctx=512, max_num_seqs=2)
+    prompt = [7]
+    result = engine.generate([prompt], SamplingParams(max_new_tokens=300))[0]
+    assert len(result.tokens) == 300 and result.finish == "length"
+    _check_greedy(folder, prompt, result.tokens, dtype)
+    # the same through steps without graphs gives the same tokens
+    _, eager = _engine("A", dtype, page_size=16, ctx=512, max_num_seqs=2, decode_graphs=False)
+    again = eager.generate([prompt], SamplingParams(max_new_tokens=60))[0]
+    if dtype == "float32":
+        assert again.tokens == result.tokens[:60]
+
+
+def test_sampling_options_through_the_entry_point():
+    """Temperature with penalties and a bias on the device gives what the host sampler gives on
+    the same logits (checked through determinism and the ban of one token)."""
+    from vipera_rs_b200 import SamplingParams
+
+    folder, engine = _engine("C", "float32", page_size=64, ctx=256, max_num_seqs=2)
+    vocab = helpers.CONFIGS["C"]["vocab_size"]
+    prompt = helpers.random_tokens(vocab, 20, 3)
+    greedy = engine.generate([prompt], SamplingParams(max_new_tokens=8))[0].tokens
+    banned = greedy[0]
+    params = SamplingParams(max_new_tokens=8, temperature=0.0, logit_bias=[(banned, -100.0)])
+    other = engine.generate([prompt], params)[0].tokens
+    assert other[0] != banned and banned not in other
+    sampled = SamplingParams(max_new_tokens=12, temperature=0.9, top_k=0, top_p=0.9, min_p=0.0, seed=5,
+                             repetition_penalty=1.2, frequency_penalty=0.3)
+    a = engine.generate([prompt], sampled)[0].tokens       # top_k = 0: rows the device hands to the host sampler
+    b = engine.generate([prompt], sampled)[0].tokens
+    assert a == b and len(a) == 12
+    stop = SamplingParams(max_new_tokens=8, eos_ids=[greedy[2]])
+    ended = engine.generate([prompt], stop)[0]
+    assert ended.finish == "stop" and ended.tokens == greedy[:greedy.index(greedy[2]) + 1]   # the end token is kept

@@ -1,0 +1,94 @@
+"""Toy parts and toy architectures for the tests: a mixer with state of its own, another
+position encoding, an architecture that mixes both kinds of layer, and one whose execution
+order names a layer twice and lets a layer read another layer's cache.  They are defined and
+registered here, outside the package; ``register()`` is called by the tests, and by a process
+that lists this file in VIPERA_PLUGINS (bin/trace_run in the replay tests)."""
+import torch
+
+
+def register():
+    import vipera_rs_b200  # noqa: F401
+    from vipera_rs_b200 import parts  # noqa: F401
+    from vipera_rs_b200.config import (ARCHITECTURES, MIXERS, POSITION_ENCODINGS, LayerSpec, ModelSpec, PartSpec,
+                                       Qwen2Config, ScheduleEntry, qwen2_model_spec, register_architecture)
+    from vipera_rs_b200.parts import FixedState, Mixer, PositionEncoding
+    from vipera_rs_b200.weights import TensorSpec
+
+    if "toy_running_mean" in MIXERS:
+        return
+
+    class RunningMean(Mixer):
+        """A mixer with state of its own: out_t = W . mean(h_0 .. h_t).  It keeps, per request,
+        the running sum of h and the count: one float32 row of hidden + 1 numbers, whatever
+        the length.  Written with torch operations; it talks to the host, so it is not captured."""
+
+        graph_safe = False
+
+        @classmethod
+        def schema(cls, params, prefix):
+            return {f"{prefix}.mix.weight": TensorSpec((params["hidden_size"], params["hidden_size"]))}
+
+        def __init__(self, params, prefix, tensors, dtype, device):
+            super().__init__(params, prefix, tensors, dtype, device)
+            self.hidden = params["hidden_size"]
+            self.weight = tensors[f"{prefix}.mix.weight"].to(device=device, dtype=torch.float32)
+
+        def cache_request(self):
+            return FixedState((self.hidden + 1,), torch.float32)
+
+        def forward(self, ctx, h, residual, cache, writes_cache):
+            slots, fresh = ctx.state_slots.tolist(), ctx.fresh.tolist()
+            offset = 0
+            for entry, count in enumerate(ctx.host_counts):
+                state = cache.data[slots[entry]]
+                if fresh[entry]:
+                    state.zero_()
+                rows = h[offset:offset + count].float()
+                sums = state[: self.hidden] + torch.cumsum(rows, dim=0)
+                counts = state[self.hidden] + torch.arange(1, count + 1, device=h.device, dtype=torch.float32)
+                residual[offset:offset + count] += (sums / counts[:, None]) @ self.weight.T
+                state[: self.hidden] = sums[-1]
+                state[self.hidden] = counts[-1]
+                offset += count
+
+    class LearnedShift(PositionEncoding):
+        """Another position encoding: a learned vector per position added to q and k.  The fused
+        kernels do not know it (style None), so the attention part calls apply()."""
+
+        style = None
+
+        @classmethod
+        def schema(cls, params, prefix):
+            return {f"{prefix}.shift.weight": TensorSpec((params["max_positions"], params["head_dim"]))}
+
+        def __init__(self, params, prefix, tensors, dtype, device):
+            super().__init__(params, prefix, tensors, dtype, device)
+            self.table = tensors[f"{prefix}.shift.weight"].to(device=device, dtype=torch.float32)
+
+        def apply(self, ctx, q, k):
+            shift = self.table[ctx.positions.long()][:, None, :]
+            q += shift
+            k += shift
+
+    MIXERS.register("toy_running_mean", RunningMean)
+    POSITION_ENCODINGS.register("toy_learned_shift", LearnedShift)
+
+    def toy_state_spec(config):
+        """Layer 0 mixes with the running mean, layer 1 with attention."""
+        base = qwen2_model_spec(config)
+        first = base.layers[0]
+        toy = LayerSpec(block="prenorm", prefix=first.prefix, mixer_norm=first.mixer_norm, ffn_norm=first.ffn_norm,
+                        mixer=PartSpec("toy_running_mean", {"hidden_size": config.hidden_size}), ffn=first.ffn,
+                        names=first.names)
+        return ModelSpec(**{**base.__dict__, "layers": [toy] + base.layers[1:], "architecture": "ToyStateLM"})
+
+    def toy_shared_spec(config):
+        """Layer 0 runs twice (cache slots 0 and 1), then layer 1 reads slot 0 without writing."""
+        base = qwen2_model_spec(config)
+        return ModelSpec(**{**base.__dict__, "architecture": "ToySharedLM",
+                            "schedule": [ScheduleEntry(0, 0), ScheduleEntry(0, 1), ScheduleEntry(1, 0, False)]})
+
+    register_architecture("ToyStateLM", Qwen2Config.from_dict, toy_state_spec)
+    register_architecture("ToySharedLM", Qwen2Config.from_dict, toy_shared_spec)
+
+

@@ -151,8 +151,9 @@ class ModelRunner:
         step is launched kernel by kernel."""
         self.steps_run += 1
         counts = step.counts
-        if (self.decode_graphs and len(counts) <= self.max_graph_entries and max(counts) == 1
-                and len(step.logit_rows) == len(counts)):
+        if (self.decode_graphs and self.model.graph_safe and len(counts) <= self.max_graph_entries
+                and max(counts) == 1 and len(step.logit_rows) == len(counts)
+                and np.array_equal(step.logit_rows, np.arange(len(counts)))):
             return self._run_graph(step)
         ctx = self.build_context(step, self.model.dtype)
         return self.model.forward(ctx, self.pools.views)

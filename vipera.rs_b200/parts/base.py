@@ -125,6 +125,7 @@ class Part:
     """Base of all parts."""
 
     kernels: Tuple[str, ...] = ()  # kernel families this part launches
+    graph_safe: bool = True         # False: forward() talks to the host, so it cannot be captured in a CUDA graph
 
     @classmethod
     def schema(cls, params: Dict[str, Any], prefix: str) -> Schema:

@@ -66,6 +66,19 @@ class DecoderModel:
             if entry.writes_cache:
                 self.cache_requests[entry.cache] = self.blocks[entry.layer].mixer.cache_request()
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether decode steps of this model may be captured in CUDA graphs: every part must
+        launch device work only, and no mixer may keep per-request state (padding a graph's
+        batch with copies of an entry would update such a state twice)."""
+        from .base import FixedState
+
+        for block in self.blocks:
+            for part in block.parts():
+                if not getattr(part, "graph_safe", True):
+                    return False
+        return not any(isinstance(request, FixedState) for request in self.cache_requests.values())
+
     def kernel_families(self) -> List[str]:
         names = ["rowwise", *self.head.kernel_families()]
         for block in self.blocks:
