@@ -1,8 +1,9 @@
 // bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16), with
 // 32-bit scores, softmax and accumulation.  Two kernels share their inner loop:
 //
-//   * prefill / mixed steps: one block per (64 queries of one entry, query head); the four
-//     warps hold 16 queries each and walk the visible keys 64 at a time with a running
+//   * prefill / mixed steps: one block per (64 queries of one entry, one or two query heads
+//     of a KV group); four warps per head hold 16 queries each and walk the visible keys 64
+//     at a time (every tile loaded once for both heads) with a running
 //     (max, sum, output) — the flash form of the reference's online fold
 //     (crates/vipera-backend-cpu/src/model.rs:2752-2857);
 //   * decode (one query per entry): one block per (entry, KV head, split of the keys); the
@@ -187,21 +188,24 @@ __device__ __forceinline__ void fold_block(const uint32_t (&q_frag)[D / 16][4], 
 // ---------------------------------------------------------------------------------------
 // prefill / mixed: block = (tile of 64 queries of one entry, query head)
 // ---------------------------------------------------------------------------------------
-template <int D>
-__global__ void __launch_bounds__(128)
+// HPC: query heads per block (1 or 2).  Two heads of the same KV group share every key and
+// value tile the block loads; the block then has eight warps, four per head.
+template <int D, int HPC>
+__global__ void __launch_bounds__(128 * HPC)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                          const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                          const int* __restrict__ entry_starts, const int* __restrict__ entry_pos0,
                          const int* __restrict__ block_table, int table_width, int page_size, int num_entries,
                          int num_heads, int num_kv_heads, float scale, int window) {
-  constexpr int kQ = 64, kKeys = 64;
+  constexpr int kQ = 64, kKeys = 64, kThreads = 128 * HPC;
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_launch_dependents();
   pdl_wait();
-  // which (entry, tile of that entry) is this block?
+  // Which (entry, tile of that entry) is this block?  Blocks are numbered from the back, so
+  // that the tiles with the longest history (the last of each entry) start first.
   int entry = -1, tile_in_entry = 0;
   {
-    int remaining = blockIdx.x;
+    int remaining = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
     for (int e = 0; e < num_entries; ++e) {
       const int tiles = (entry_starts[e + 1] - entry_starts[e] + kQ - 1) / kQ;
       if (remaining < tiles) { entry = e; tile_in_entry = remaining; break; }
@@ -209,26 +213,28 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     }
   }
   if (entry < 0) return;
-  const int head = blockIdx.y;
-  const int kv_head = head / (num_heads / num_kv_heads);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * HPC + (warp >> 2);  // this warp's query head
+  const int q_warp = warp & 3;                       // which 16 of the 64 queries
+  const int kv_head = (blockIdx.y * HPC) / (num_heads / num_kv_heads);
   const int token0 = entry_starts[entry] + tile_in_entry * kQ;
   const int tokens_here = min(kQ, entry_starts[entry + 1] - token0);
   const int pos0 = entry_pos0[entry] + tile_in_entry * kQ;  // position of the tile's first query
   const int* table = block_table + static_cast<size_t>(entry) * table_width;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const uint32_t q_tile = smem_addr(smem);
-  const uint32_t k_tiles = q_tile + kQ * D * 2;
+  const uint32_t q_tiles = smem_addr(smem);                   // [HPC][64][D]
+  const uint32_t k_tiles = q_tiles + HPC * kQ * D * 2;        // two buffers of [64][D]
   const uint32_t v_tiles = k_tiles + 2 * kKeys * D * 2;
 
   // queries into shared memory (rows beyond the entry's tokens are zero)
   {
     constexpr int kChunks = D / 8;
-    for (int index = threadIdx.x; index < kQ * kChunks; index += 128) {
-      const int row = index / kChunks, chunk = index % kChunks;
+    for (int index = threadIdx.x; index < HPC * kQ * kChunks; index += kThreads) {
+      const int which = index / (kQ * kChunks);
+      const int row = (index / kChunks) % kQ, chunk = index % kChunks;
       const bool valid = row < tokens_here;
-      const __nv_bfloat16* src = q + (static_cast<size_t>(token0 + (valid ? row : 0)) * num_heads + head) * D + chunk * 8;
-      cp_async_16(q_tile + tile_offset<D>(row, chunk), src, valid);
+      const __nv_bfloat16* src = q + (static_cast<size_t>(token0 + (valid ? row : 0)) * num_heads + blockIdx.y * HPC + which) * D + chunk * 8;
+      cp_async_16(q_tiles + which * kQ * D * 2 + tile_offset<D>(row, chunk), src, valid);
     }
   }
   const int last_pos = pos0 + tokens_here - 1;
@@ -239,10 +245,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 
   auto load_block = [&](int block, int buffer) {
     const int key0 = (first_block + block) * kKeys;
-    load_kv_tile<D, kKeys, 128>(k_tiles + buffer * kKeys * D * 2, k_pool, table, page_size, num_kv_heads, kv_head,
-                                key0, first_key, end_key, threadIdx.x);
-    load_kv_tile<D, kKeys, 128>(v_tiles + buffer * kKeys * D * 2, v_pool, table, page_size, num_kv_heads, kv_head,
-                                key0, first_key, end_key, threadIdx.x);
+    load_kv_tile<D, kKeys, kThreads>(k_tiles + buffer * kKeys * D * 2, k_pool, table, page_size, num_kv_heads, kv_head,
+                                     key0, first_key, end_key, threadIdx.x);
+    load_kv_tile<D, kKeys, kThreads>(v_tiles + buffer * kKeys * D * 2, v_pool, table, page_size, num_kv_heads, kv_head,
+                                     key0, first_key, end_key, threadIdx.x);
   };
   load_block(0, 0);
   cp_async_commit();
@@ -257,7 +263,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   int row_first[2], row_limit[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    const int row = warp * 16 + (lane >> 2) + r * 8;
+    const int row = q_warp * 16 + (lane >> 2) + r * 8;
     const int position = pos0 + row;
     row_limit[r] = row < tokens_here ? position : -1;  // rows past the end see nothing
     row_first[r] = window > 0 ? max(0, position - window + 1) : 0;
@@ -273,11 +279,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     if (block == 0) {
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks)
-        ldmatrix_x4(q_frag[ks], q_tile + tile_offset<D>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+        ldmatrix_x4(q_frag[ks], q_tiles + (warp >> 2) * kQ * D * 2 +
+                                    tile_offset<D>(q_warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
     }
     const int key0 = (first_block + block) * kKeys;
     // a warp whose 16 queries all stand before this block has nothing to see in it
-    if (key0 <= pos0 + warp * 16 + 15)
+    if (key0 <= pos0 + q_warp * 16 + 15)
       fold_block<D, kKeys>(q_frag, k_tiles + buffer * kKeys * D * 2, v_tiles + buffer * kKeys * D * 2, key0,
                            row_first, row_limit, scale_log2, row_max, row_sum, acc);
     __syncthreads();
@@ -290,7 +297,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     float sum = row_sum[r];
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    const int row = warp * 16 + (lane >> 2) + r * 8;
+    const int row = q_warp * 16 + (lane >> 2) + r * 8;
     if (row >= tokens_here) continue;
     const float inverse = 1.0f / sum;
     __nv_bfloat16* dst = out + (static_cast<size_t>(token0 + row) * num_heads + head) * D;
@@ -518,23 +525,36 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
   out[row * D + threadIdx.x] = __float2bfloat16_rn(value / total);
 }
 
-template <int D>
-int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int* entry_starts,
-                   const int* entry_pos0, const int* block_table, int table_width, int page_size, int num_entries,
-                   int num_tokens, int num_heads, int num_kv_heads, float scale, int window, cudaStream_t s) {
-  constexpr int kSmem = (64 + 4 * 64) * D * 2;
+template <int D, int HPC>
+int launch_prefill_variant(const void* q, void* out, const void* k_pool, const void* v_pool, const int* entry_starts,
+                           const int* entry_pos0, const int* block_table, int table_width, int page_size,
+                           int num_entries, int num_tokens, int num_heads, int num_kv_heads, float scale, int window,
+                           cudaStream_t s) {
+  constexpr int kSmem = (HPC * 64 + 4 * 64) * D * 2;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
   // at most one partly filled tile per entry beyond the full ones
-  dim3 grid((num_tokens + 63) / 64 + num_entries, num_heads);
-  return vipera_launch(attention_prefill_kernel<D>, grid, 128, kSmem, s,
+  dim3 grid((num_tokens + 63) / 64 + num_entries, num_heads / HPC);
+  return vipera_launch(attention_prefill_kernel<D, HPC>, grid, dim3(128 * HPC), kSmem, s,
       static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(k_pool),
       static_cast<const __nv_bfloat16*>(v_pool), entry_starts, entry_pos0, block_table, table_width, page_size,
       num_entries, num_heads, num_kv_heads, scale, window);
+}
+
+template <int D>
+int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int* entry_starts,
+                   const int* entry_pos0, const int* block_table, int table_width, int page_size, int num_entries,
+                   int num_tokens, int num_heads, int num_kv_heads, float scale, int window, cudaStream_t s) {
+  // two heads per block where the heads of a KV group pair up
+  if ((num_heads / num_kv_heads) % 2 == 0)
+    return launch_prefill_variant<D, 2>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width,
+                                        page_size, num_entries, num_tokens, num_heads, num_kv_heads, scale, window, s);
+  return launch_prefill_variant<D, 1>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width,
+                                      page_size, num_entries, num_tokens, num_heads, num_kv_heads, scale, window, s);
 }
 
 template <int D>

@@ -28,7 +28,8 @@
 
 #include "common.cuh"
 
-enum GemmEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2 };
+// EPI_DISCARD drops the result: it exists to time the products without their ending.
+enum GemmEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_DISCARD = 3 };
 enum { GEMM_TC_WAIT_EXPIRED = 1 };
 
 constexpr int kBlockK = 64;        // bf16 elements per k-block: one 128-byte swizzle row
@@ -46,6 +47,7 @@ struct GemmParams {
   const float* bias;
   void* out;
   float* resid;
+  int tma_ending;    // 1: the ending goes through shared memory and TMA stores (map_out)
   float* scratch;    // split partials: [item][BN][128] floats
   int* status;       // device word: 0, or an error code
 };
@@ -88,6 +90,19 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
@@ -138,6 +153,10 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   return desc;
 }
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
 __device__ __forceinline__ float silu_mul(float gate, float up) { return up * (gate / (1.0f + __expf(-gate))); }
 
 template <int BN>
@@ -146,10 +165,11 @@ struct TileConfig {
   // Wide tiles take all the shared memory of an SM; narrow ones (few tokens) take less
   // than half, so that two blocks share an SM and the next product's block can set up and
   // prefetch weights while this one finishes.
-  static constexpr int kBudget = BN >= 128 ? 200 * 1024 : 100 * 1024;
+  static constexpr int kStagingBytes = BN >= 128 ? 4 * 2 * 4096 : 0;  // 2 buffers of 32 rows x 128 B per epilogue warp
+  static constexpr int kBudget = BN >= 128 ? 196 * 1024 - kStagingBytes + 32 * 1024 : 100 * 1024;
   static constexpr int kStages = kBudget / kStageBytes;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
 // ---------------------------------------------------------------------------------------
@@ -161,6 +181,7 @@ template <int BN, bool SWAP>
 __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v, int width, int row, int col0) {
   // `row`: global index on the 128-row side; `col0`: global index of v[0] on the other side.
   const int N = p.features;
+  if (p.epilogue == EPI_DISCARD) return;
   if (!SWAP) {
     const int t = row;
     if (t >= p.tokens) return;
@@ -235,7 +256,7 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
 template <int BN, bool SWAP>
 __global__ void __launch_bounds__(kThreads, (BN >= 128 ? 1 : 2))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
   using Config = TileConfig<BN>;
   constexpr int kStages = Config::kStages;
   constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
@@ -243,7 +264,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* tiles = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Config::kStageBytes);
+  uint8_t* staging = smem + kStages * Config::kStageBytes;  // 1024-byte aligned: stage sizes are multiples of 1024
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + Config::kStagingBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + kStages;
   uint64_t* acc_full = bars + 2 * kStages;
@@ -367,7 +389,81 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const int row = tx * kTileX + row_in_tile;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(acc * BN);
       if (p.splits == 1) {
-        if (BN >= 32) {
+        if (!SWAP && BN >= 128 && p.tma_ending) {
+          // The ending through shared memory: each warp lays 32 rows x 128 bytes into a
+          // swizzled buffer (no bank conflicts), and one lane hands the box to TMA, which
+          // writes whole lines, clips at the matrix's edges and, for the residual stream,
+          // does the addition in memory.  Two buffers per warp: one is filled while the
+          // other is read.
+          uint8_t* mine = staging + warp * 2 * 4096;
+          int use = 0;
+          const int row0 = tx * kTileX + warp * 32;
+          if (p.epilogue == EPI_SWIGLU) {
+            // 128 accumulator columns make 64 outputs = one 128-byte row of bfloat16
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 128) {
+              // a box that lies wholly outside the matrix is skipped altogether (were it only
+              // not handed over, the next box would overwrite a buffer TMA may still be reading)
+              if (row0 >= p.tokens || ty * BN + c >= p.features) continue;
+              uint8_t* buffer = mine + use * 4096;
+              if (lane == 0) tma_store_wait_read<1>();
+              __syncwarp();
+#pragma unroll 1
+              for (int q4 = 0; q4 < 4; ++q4) {
+                float v[32];
+                tmem_load_32(taddr + c + q4 * 32, v);
+                uint32_t packed[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  packed[i] = pack_bf16x2(silu_mul(v[2 * i], v[16 + 2 * i]), silu_mul(v[2 * i + 1], v[16 + 2 * i + 1]));
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  const int chunk = (q4 * 2 + h) ^ (lane & 7);
+                  *reinterpret_cast<uint4*>(buffer + lane * 128 + chunk * 16) =
+                      make_uint4(packed[4 * h], packed[4 * h + 1], packed[4 * h + 2], packed[4 * h + 3]);
+                }
+              }
+              fence_async_shared();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&map_out, buffer, (ty * BN + c) >> 1, row0);
+                tma_store_commit();
+              }
+              use ^= 1;
+            }
+          } else {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+              if (row0 >= p.tokens || ty * BN + c >= p.features) continue;
+              uint8_t* buffer = mine + use * 4096;
+              float v[32];
+              tmem_load_32(taddr + c, v);
+              if (p.epilogue == EPI_STORE && p.bias) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  const int n = ty * BN + c + i;
+                  v[i] += n < p.features ? p.bias[n] : 0.0f;
+                }
+              }
+              if (lane == 0) tma_store_wait_read<1>();
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int chunk = j ^ (lane & 7);
+                *reinterpret_cast<float4*>(buffer + lane * 128 + chunk * 16) =
+                    make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              }
+              fence_async_shared();
+              __syncwarp();
+              if (lane == 0) {
+                if (p.epilogue == EPI_RESIDUAL) tma_reduce_add_2d(&map_out, buffer, ty * BN + c, row0);
+                else tma_store_2d(&map_out, buffer, ty * BN + c, row0);
+                tma_store_commit();
+              }
+              use ^= 1;
+            }
+          }
+        } else if (BN >= 32) {
 #pragma unroll 1
           for (int c = 0; c < BN; c += 32) {
             float v[32];
@@ -405,6 +501,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       }
     }
   }
+
+  // stores handed to TMA must have landed before the block leaves
+  if (warp < 4 && lane == 0) tma_store_wait_all();
 
   // ---------------- teardown ----------------
   tcgen05_fence_before();
@@ -479,6 +578,21 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
   return r == CUDA_SUCCESS ? VIPERA_OK : VIPERA_BAD_ARGUMENT;
 }
 
+// The output as TMA sees it: [rows, cols] of float32 or bfloat16, in boxes of 32 rows x 128 bytes.
+static int make_out_map(CUtensorMap* map, void* base, int rows, int cols, bool bf16) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (!encode) return VIPERA_NO_DRIVER_ENTRY;
+  const int element = bf16 ? 2 : 4;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * element};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / element), 32};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims,
+                      strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? VIPERA_OK : VIPERA_BAD_ARGUMENT;
+}
+
 struct GemmPlan {
   bool swap;
   int bn;
@@ -533,7 +647,8 @@ VIPERA_API int vipera_gemm_tc_workspace(int T, int N, int K, size_t* scratch_byt
 }
 
 template <int BN, bool SWAP>
-static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, const GemmParams& p, int grid, cudaStream_t s) {
+static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, const CUtensorMap& map_out,
+                          const GemmParams& p, int grid, cudaStream_t s) {
   using Config = TileConfig<BN>;
   static bool configured = false;
   if (!configured) {
@@ -541,7 +656,7 @@ static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, co
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  int status = vipera_launch(gemm_tc_kernel<BN, SWAP>, grid, kThreads, Config::kSmemBytes, s, map_x, map_y, p);
+  int status = vipera_launch(gemm_tc_kernel<BN, SWAP>, grid, kThreads, Config::kSmemBytes, s, map_x, map_y, map_out, p);
   if (status != VIPERA_OK || p.splits == 1) return status;
   return vipera_launch(splitk_finish_kernel<BN>, dim3(p.tiles_x * p.tiles_y, BN / 16), dim3(kTileX), 0, s, p);
 }
@@ -590,16 +705,34 @@ VIPERA_API int vipera_gemm_tc(const void* A, const void* W, int T, int N, int K,
   const int items = plan.tiles_x * plan.tiles_y * plan.splits;
   const int grid = items < sms ? items : sms;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The ending goes through TMA stores where the output's rows are whole multiples of 16
+  // bytes: float32 [T, N] for STORE and RESIDUAL, bfloat16 [T, N / 2] for SWIGLU.
+  CUtensorMap map_out = map_x;  // a valid map where the ending does not use one
+  p.tma_ending = 0;
+  if (!plan.swap && std::getenv("VIPERA_GEMM_DIRECT_STORE") == nullptr) {
+    if (epilogue == EPI_SWIGLU && out_dtype == VIPERA_BF16 && (N / 2) % 8 == 0 &&
+        (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+      if ((r = make_out_map(&map_out, out, T, N / 2, true)) != VIPERA_OK) return r;
+      p.tma_ending = 1;
+    } else if (epilogue == EPI_STORE && out_dtype == VIPERA_F32 && N % 4 == 0 &&
+               (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+      if ((r = make_out_map(&map_out, out, T, N, false)) != VIPERA_OK) return r;
+      p.tma_ending = 1;
+    } else if (epilogue == EPI_RESIDUAL && N % 4 == 0 && (reinterpret_cast<uintptr_t>(resid) & 15) == 0) {
+      if ((r = make_out_map(&map_out, resid, T, N, false)) != VIPERA_OK) return r;
+      p.tma_ending = 1;
+    }
+  }
   if (!plan.swap) {
-    if (plan.bn == 256) return launch_variant<256, false>(map_x, map_y, p, grid, s);
-    return launch_variant<128, false>(map_x, map_y, p, grid, s);
+    if (plan.bn == 256) return launch_variant<256, false>(map_x, map_y, map_out, p, grid, s);
+    return launch_variant<128, false>(map_x, map_y, map_out, p, grid, s);
   }
   switch (plan.bn) {
-    case 16: return launch_variant<16, true>(map_x, map_y, p, grid, s);
-    case 32: return launch_variant<32, true>(map_x, map_y, p, grid, s);
-    case 64: return launch_variant<64, true>(map_x, map_y, p, grid, s);
-    case 128: return launch_variant<128, true>(map_x, map_y, p, grid, s);
-    default: return launch_variant<256, true>(map_x, map_y, p, grid, s);
+    case 16: return launch_variant<16, true>(map_x, map_y, map_out, p, grid, s);
+    case 32: return launch_variant<32, true>(map_x, map_y, map_out, p, grid, s);
+    case 64: return launch_variant<64, true>(map_x, map_y, map_out, p, grid, s);
+    case 128: return launch_variant<128, true>(map_x, map_y, map_out, p, grid, s);
+    default: return launch_variant<256, true>(map_x, map_y, map_out, p, grid, s);
   }
 }
 
