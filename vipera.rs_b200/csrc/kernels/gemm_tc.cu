@@ -168,7 +168,8 @@ struct TileConfig {
   static constexpr int kStagingBytes = BN >= 128 ? 4 * 2 * 4096 : 0;  // 2 buffers of 32 rows x 128 B per epilogue warp
   static constexpr int kBudget = BN >= 128 ? 196 * 1024 - kStagingBytes + 32 * 1024 : 100 * 1024;
   static constexpr int kStages = kBudget / kStageBytes;
-  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  // two accumulators; tensor memory is handed out in powers of two of at least 32 columns
+  static constexpr int kTmemCols = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
@@ -611,13 +612,26 @@ static int sm_count() {
   return count;
 }
 
-static GemmPlan make_plan(int T, int N, int K, int sms) {
+static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE) {
   GemmPlan plan{};
   plan.num_k_blocks = (K + kBlockK - 1) / kBlockK;
   if (T >= 128 + 64) {
     plan.swap = false;
-    plan.bn = (N >= 256) ? 256 : 128;
     plan.tiles_x = (T + kTileX - 1) / kTileX;
+    // The widest tile that keeps the SMs busy: a tile of 256 columns reads the least per
+    // flop, but when the tiles do not fill the last wave a narrower tile wastes less.
+    const int candidates[3] = {256, 192, 128};
+    double best = -1.0;
+    plan.bn = 128;
+    for (int bn : candidates) {
+      if (bn > 128 && N < bn) continue;
+      if (bn == 192 && epilogue == EPI_SWIGLU) continue;  // the SwiGLU ending works in 128-column steps
+      const long items = static_cast<long>(plan.tiles_x) * ((N + bn - 1) / bn);
+      const long waves = (items + sms - 1) / sms;
+      double efficiency = static_cast<double>(plan.tiles_x) * N / (static_cast<double>(waves) * sms * bn);
+      efficiency *= bn == 256 ? 1.0 : bn == 192 ? 0.95 : 0.85;  // narrower tiles run below the wide tile's rate
+      if (efficiency > best) { best = efficiency; plan.bn = bn; }
+    }
     plan.tiles_y = (N + plan.bn - 1) / plan.bn;
     plan.splits = 1;
     plan.k_blocks_per_split = plan.num_k_blocks;
@@ -674,7 +688,7 @@ VIPERA_API int vipera_gemm_tc(const void* A, const void* W, int T, int N, int K,
   if ((epilogue == EPI_RESIDUAL && !resid) || (epilogue != EPI_RESIDUAL && !out) || !status) return VIPERA_BAD_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return VIPERA_BAD_ARGUMENT;
   const int sms = sm_count();
-  const GemmPlan plan = make_plan(T, N, K, sms);
+  const GemmPlan plan = make_plan(T, N, K, sms, epilogue);
   if (plan.splits > 1) {
     if (!scratch || scratch_bytes < plan.scratch_floats * sizeof(float)) return VIPERA_BAD_ARGUMENT;
   }
@@ -725,6 +739,7 @@ VIPERA_API int vipera_gemm_tc(const void* A, const void* W, int T, int N, int K,
   }
   if (!plan.swap) {
     if (plan.bn == 256) return launch_variant<256, false>(map_x, map_y, map_out, p, grid, s);
+    if (plan.bn == 192) return launch_variant<192, false>(map_x, map_y, map_out, p, grid, s);
     return launch_variant<128, false>(map_x, map_y, map_out, p, grid, s);
   }
   switch (plan.bn) {
