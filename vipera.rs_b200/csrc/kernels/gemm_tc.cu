@@ -520,27 +520,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   }
 }
 
-// The second kernel of a product that was cut along K: adds the splits' partial sums, split
-// 0 first, and writes the ending.  grid = (tiles, BN / 16): a block takes 16 columns of a tile.
+// The second kernel of a product that was cut along K (few tokens: rows of the partial tiles
+// are features, columns are tokens): one thread per output element adds the splits' partial
+// sums, split 0 first, and writes the ending.  Neighbouring threads take neighbouring
+// features, so the partial sums and the outputs are both read and written in whole lines.
 template <int BN>
-__global__ void __launch_bounds__(kTileX)
+__global__ void __launch_bounds__(256)
 splitk_finish_kernel(const GemmParams p) {
   pdl_launch_dependents();
   pdl_wait();
-  const int tile = blockIdx.x;
-  const int tx = tile % p.tiles_x, ty = tile / p.tiles_x;
-  const int c0 = blockIdx.y * 16;
-  const int row_in_tile = threadIdx.x;
-  const float* first = p.scratch + static_cast<size_t>(tile) * p.splits * BN * kTileX;
-  float v[32];
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = 0.0f;
-  for (int s = 0; s < p.splits; ++s) {
-    const float* src = first + static_cast<size_t>(s) * BN * kTileX + static_cast<size_t>(c0) * kTileX + row_in_tile;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] += __ldcg(src + static_cast<size_t>(i) * kTileX);
+  const int N = p.features;
+  const bool swiglu = p.epilogue == EPI_SWIGLU;
+  const int width = swiglu ? N >> 1 : N;            // outputs per token
+  const long id = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (id >= static_cast<long>(p.tokens) * width) return;
+  const int t = static_cast<int>(id / width), o = static_cast<int>(id % width);
+  const int ty = t / BN, col = t % BN;
+  // feature rows this output needs: itself, or the gate and up rows of feature o
+  const int n0 = swiglu ? (o >> 4) * 32 + (o & 15) : o;
+  const int n1 = n0 + 16;
+  auto total = [&](int n) {
+    const int tx = n / kTileX, row = n % kTileX;
+    const size_t tile = static_cast<size_t>(ty) * p.tiles_x + tx;
+    const float* src = p.scratch + ((tile * p.splits) * BN + col) * kTileX + row;
+    const size_t step = static_cast<size_t>(BN) * kTileX;
+    float sum = 0.0f;
+    int s = 0;
+    for (; s + 4 <= p.splits; s += 4) {
+      const float a = __ldcg(src + (s + 0) * step), b = __ldcg(src + (s + 1) * step);
+      const float c = __ldcg(src + (s + 2) * step), d = __ldcg(src + (s + 3) * step);
+      sum += a;
+      sum += b;
+      sum += c;
+      sum += d;
+    }
+    for (; s < p.splits; ++s) sum += __ldcg(src + s * step);
+    return sum;
+  };
+  if (swiglu) {
+    const float value = silu_mul(total(n0), total(n1));
+    const size_t at = static_cast<size_t>(t) * width + o;
+    if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
+    else static_cast<float*>(p.out)[at] = value;
+    return;
   }
-  finish_chunk<BN, true>(p, v, 16, tx * kTileX + row_in_tile, ty * BN + c0);
+  const float value = total(n0);
+  const size_t at = static_cast<size_t>(t) * N + o;
+  if (p.epilogue == EPI_RESIDUAL) {
+    p.resid[at] += value;
+  } else {
+    const float biased = value + (p.bias ? p.bias[o] : 0.0f);
+    if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(biased);
+    else static_cast<float*>(p.out)[at] = biased;
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -672,7 +704,8 @@ static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, co
   }
   int status = vipera_launch(gemm_tc_kernel<BN, SWAP>, grid, kThreads, Config::kSmemBytes, s, map_x, map_y, map_out, p);
   if (status != VIPERA_OK || p.splits == 1) return status;
-  return vipera_launch(splitk_finish_kernel<BN>, dim3(p.tiles_x * p.tiles_y, BN / 16), dim3(kTileX), 0, s, p);
+  const long outputs = static_cast<long>(p.tokens) * (p.epilogue == EPI_SWIGLU ? p.features / 2 : p.features);
+  return vipera_launch(splitk_finish_kernel<BN>, dim3(static_cast<unsigned>((outputs + 255) / 256)), dim3(256), 0, s, p);
 }
 
 // A is [T, K] bfloat16, W is [N, K] bfloat16, both row-major and contiguous with K a
