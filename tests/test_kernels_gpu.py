@@ -415,7 +415,7 @@ def test_sampler_distribution_and_penalties():
 @pytest.mark.parametrize("normed", [False, True])
 def test_gemv_small(tokens, n, k, epilogue, normed):
     ops = _ops()
-    if not ops.gemv_small_takes(tokens, k):
+    if not ops.gemv_small_takes(tokens, k, n):
         pytest.skip(f"{tokens} tokens of width {k} do not fit one block's shared memory: the kernel refuses them")
     if epilogue == 2:
         n = (n + 31) // 32 * 32

@@ -335,10 +335,10 @@ static size_t gemv_shared_bytes(int tokens, int K, int warps) {
 
 static int gemv_warps(int K) { return K >= 4096 ? 16 : 8; }
 
-// Whether vipera_gemv_small takes `tokens` tokens against an inner size K (the activations of
-// the step must fit in one block's shared memory).
-VIPERA_API int vipera_gemv_small_takes(int tokens, int K) {
-  if (tokens <= 0 || tokens > 32 || K <= 0 || (K % 8) != 0) return 0;
+// Whether vipera_gemv_small takes `tokens` tokens against a matrix of N rows and inner size K
+// (the activations of the step must fit in one block's shared memory).
+VIPERA_API int vipera_gemv_small_takes(int tokens, int K, int N) {
+  if (tokens <= 0 || tokens > 32 || K <= 0 || (K % 8) != 0 || N <= 0) return 0;
   return gemv_shared_bytes(tokens, K, gemv_warps(K)) <= kGemvMaxShared ? 1 : 0;
 }
 
@@ -349,7 +349,7 @@ VIPERA_API int vipera_gemv_small_takes(int tokens, int K) {
 VIPERA_API int vipera_gemv_small(const GemvParams* params, void* stream) {
   const GemvParams& p = *params;
   if (p.T <= 0) return VIPERA_OK;
-  if (p.N <= 0 || !vipera_gemv_small_takes(p.T, p.K)) return VIPERA_BAD_SHAPE;
+  if (p.N <= 0 || !vipera_gemv_small_takes(p.T, p.K, p.N)) return VIPERA_BAD_SHAPE;
   if ((p.x32 == nullptr) == (p.a16 == nullptr)) return VIPERA_BAD_ARGUMENT;
   if (p.x32 && !p.norm_weight) return VIPERA_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(p.weight) & 15) return VIPERA_BAD_ARGUMENT;

@@ -391,12 +391,12 @@ GEMV_MAX_TOKENS = 32
 GEMV_STORE, GEMV_RESIDUAL, GEMV_SWIGLU, GEMV_ROPE_CACHE = 0, 1, 2, 3
 
 
-def gemv_small_takes(tokens: int, k: int) -> bool:
-    """Whether the small-token kernel takes `tokens` tokens against an inner size `k` (the
-    step's activations must fit in one block's shared memory)."""
+def gemv_small_takes(tokens: int, k: int, n: int) -> bool:
+    """Whether the small-token kernel takes `tokens` tokens against a matrix of `n` rows and
+    inner size `k` (the activations a block stages must fit in its shared memory)."""
     fn = getattr(load_kernel_library("gemv_small"), "vipera_gemv_small_takes")
-    fn.argtypes, fn.restype = [_c_int, _c_int], _c_int
-    return bool(fn(int(tokens), int(k)))
+    fn.argtypes, fn.restype = [_c_int, _c_int, _c_int], _c_int
+    return bool(fn(int(tokens), int(k), int(n)))
 
 
 class _GemvParams(ctypes.Structure):
@@ -445,7 +445,7 @@ def gemv_small(w: torch.Tensor, *, a: Optional[torch.Tensor] = None, x: Optional
         p.rows = _opt(rows, "rows", torch.int32)
         p.T = int(tokens if tokens is not None else (rows.numel() if rows is not None else x.shape[0]))
     t = p.T
-    if not gemv_small_takes(t, k):
+    if not gemv_small_takes(t, k, n):
         raise UnsupportedError(f"gemv_small does not take {t} tokens against an inner size of {k}")
     p.epilogue = epilogue
     if epilogue == GEMV_ROPE_CACHE:

@@ -18,6 +18,7 @@ from ..kernels import ops
 
 SWIGLU_GROUP = 16  # gate rows and up rows alternate in groups of this many
 SMALL_KERNEL_MAX_ROWS = int(os.environ.get("VIPERA_GEMV_MAX_ROWS", 4096))
+SMALL_KERNEL_MAX_INNER = int(os.environ.get("VIPERA_GEMV_MAX_INNER", 4096))
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -87,16 +88,17 @@ class Linear:
 
     def takes_small(self, tokens: int) -> bool:
         """Whether the small-token kernel runs this product for `tokens` tokens."""
-        # The small-token kernel wins where a product has few output rows (its fixed cost is
-        # low and it fuses the norm in front); wide products stream better through TMA.
-        if self._tensor_core is None or self.out_features > SMALL_KERNEL_MAX_ROWS:
+        # The small-token kernel wins where a product is small (its fixed cost is low and it
+        # fuses the norm in front); wide or deep products stream better through TMA.
+        if (self._tensor_core is None or self.out_features > SMALL_KERNEL_MAX_ROWS
+                or self.in_features > SMALL_KERNEL_MAX_INNER):
             return False
         most = min(int(os.environ.get("VIPERA_GEMV_MAX_TOKENS", ops.GEMV_MAX_TOKENS)), ops.GEMV_MAX_TOKENS)
         if tokens > most:
             return False
         known = self._small_ok.get(tokens)
         if known is None:
-            known = self._small_ok[tokens] = ops.gemv_small_takes(tokens, self.in_features)
+            known = self._small_ok[tokens] = ops.gemv_small_takes(tokens, self.in_features, self.out_features)
         return known
 
     def __call__(self, ctx, a, *, epilogue: int = ops.EPI_STORE,
