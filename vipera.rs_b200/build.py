@@ -39,6 +39,9 @@ NVCC_FLAGS = [
     "-O3", "-lineinfo", "-std=c++17", "--expt-relaxed-constexpr",
     "-shared", "-Xcompiler", "-fPIC",
 ]
+# Further compiler flags from the environment (for instance -D switches of a kernel file);
+# they are part of a library's name, so builds with different flags live side by side.
+NVCC_FLAGS += os.environ.get("VIPERA_NVCC_FLAGS", "").split()
 CXX_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
 
 _lock = threading.Lock()

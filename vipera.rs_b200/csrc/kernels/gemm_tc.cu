@@ -159,6 +159,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 __device__ __forceinline__ float silu_mul(float gate, float up) { return up * (gate / (1.0f + __expf(-gate))); }
 
+#ifndef VIPERA_SMALL_BUDGET
+#define VIPERA_SMALL_BUDGET 100
+#endif
 template <int BN>
 struct TileConfig {
   static constexpr int kStageBytes = (kTileX + BN) * kBlockK * 2;
@@ -166,7 +169,7 @@ struct TileConfig {
   // than half, so that two blocks share an SM and the next product's block can set up and
   // prefetch weights while this one finishes.
   static constexpr int kStagingBytes = BN >= 128 ? 4 * 2 * 4096 : 0;  // 2 buffers of 32 rows x 128 B per epilogue warp
-  static constexpr int kBudget = BN >= 128 ? 196 * 1024 - kStagingBytes + 32 * 1024 : 100 * 1024;
+  static constexpr int kBudget = BN >= 128 ? 196 * 1024 - kStagingBytes + 32 * 1024 : VIPERA_SMALL_BUDGET * 1024;
   static constexpr int kStages = kBudget / kStageBytes;
   // two accumulators; tensor memory is handed out in powers of two of at least 32 columns
   static constexpr int kTmemCols = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
@@ -255,7 +258,7 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
 }
 
 template <int BN, bool SWAP>
-__global__ void __launch_bounds__(kThreads, (BN >= 128 ? 1 : 2))
+__global__ void __launch_bounds__(kThreads, (BN >= 128 || VIPERA_SMALL_BUDGET > 110 ? 1 : 2))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
   using Config = TileConfig<BN>;

@@ -13,6 +13,17 @@ from ..errors import InvalidArgumentError
 from ..parts.model import DecoderModel, model_schema
 from ..weights import RandomSource, SafetensorsSource, write_model_folder
 
+
+def _kernel_families(model) -> list:
+    """The kernel families the model's parts name, and the fused decode step where the model
+    qualifies for it."""
+    from .fused_decode import FusedDecode
+
+    names = list(model.kernel_families())
+    if FusedDecode.qualifies(model):
+        names.append("decode_fused")
+    return names
+
 _DTYPES = {
     "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
     "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32,
@@ -35,7 +46,7 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0") -> DecoderMode
     spec = arch.model_spec(config)
     model = DecoderModel(spec, SafetensorsSource(model_dir), parse_dtype(dtype), device)
     model.config = config
-    build_kernels(model.kernel_families())
+    build_kernels(_kernel_families(model))
     return model
 
 
@@ -50,7 +61,7 @@ def random_model(config_dict: dict, seed: int, dtype="bfloat16", device="cuda:0"
     source = RandomSource(model_schema(spec), seed, run_dtype, device=str(device))
     model = DecoderModel(spec, source, run_dtype, device)
     model.config = config
-    build_kernels(model.kernel_families())
+    build_kernels(_kernel_families(model))
     return model
 
 

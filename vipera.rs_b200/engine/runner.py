@@ -63,6 +63,10 @@ class ModelRunner:
         self.decode_graphs = True
         self.max_graph_entries = 256
         self._graphs = {}
+        # Decode steps of few tokens run as one persistent kernel where the model qualifies.
+        from .fused_decode import FusedDecode
+
+        self.fused = FusedDecode.plan_for(model)
 
     # ------------------------------------------------------------------------------
     def _staging(self, count: int):
@@ -143,7 +147,16 @@ class ModelRunner:
             block_tables=block_tables, logit_rows=part(7) if rows.size else None, num_logit_rows=int(rows.size),
             host_counts=[int(c) for c in counts], host_pos0=[int(p) for p in pos0],
             max_count=int(counts.max()), max_kv_len=max_len, all_single=bool((counts == 1).all()),
-            dtype=self.model.dtype, workspace=self.workspace)
+            dtype=self.model.dtype, workspace=self.workspace,
+            logits_all_rows=bool(rows.size == total and np.array_equal(rows, np.arange(total))))
+
+    def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        """The model's forward pass for a prepared step, through the fused decode kernel
+        where the step and the model qualify."""
+        views = self.pools.views
+        if self.fused is not None and self.fused.takes(ctx, views):
+            return self.fused.run(ctx, views)
+        return self.model.forward(ctx, views)
 
     def run(self, step: StepInput) -> Optional[torch.Tensor]:
         """Run one step.  A step in which every entry brings one token and wants its logits
@@ -156,7 +169,7 @@ class ModelRunner:
                 and np.array_equal(step.logit_rows, np.arange(len(counts)))):
             return self._run_graph(step)
         ctx = self.build_context(step, self.model.dtype)
-        return self.model.forward(ctx, self.pools.views)
+        return self.forward(ctx)
 
     # ------------------------------------------------------------------------------
     # decode steps through CUDA graphs
@@ -255,7 +268,8 @@ class _DecodeGraph:
             state_slots=self._part(5), fresh=self._part(6), block_tables=tables, logit_rows=self._part(7),
             num_logit_rows=b, host_counts=[1] * b, host_pos0=[0] * b, max_count=1,
             max_kv_len=min(w * runner.manager.group(g)[0] for g, w in enumerate(self.widths)) if self.widths else 0,
-            all_single=True, dtype=runner.model.dtype, workspace=runner.workspace, extras={"graph": True})
+            all_single=True, dtype=runner.model.dtype, workspace=runner.workspace, logits_all_rows=True,
+            extras={"graph": True})
 
     def capture(self, step: StepInput) -> None:
         from ..kernels import ops
@@ -265,12 +279,12 @@ class _DecodeGraph:
         ctx = self._context()
         # Once outside a graph: buffers get their final sizes, kernels are loaded.  The step's
         # own keys and values are written here and again, identically, by the replay.
-        runner.model.forward(ctx, runner.pools.views)
+        runner.forward(ctx)
         torch.cuda.current_stream().synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launches
         with torch.cuda.graph(graph):
-            self.logits = runner.model.forward(ctx, runner.pools.views)
+            self.logits = runner.forward(ctx)
         self.kernels = ops.launches - before
         ops.launches = before
         self.graph = graph

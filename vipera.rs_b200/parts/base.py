@@ -118,6 +118,7 @@ class StepContext:
     all_single: bool            # every entry brings exactly one token
     dtype: torch.dtype          # activation dtype of the run
     workspace: Workspace
+    logits_all_rows: bool = False  # the wanted rows are all the step's tokens, in order
     extras: Dict[str, Any] = field(default_factory=dict)
 
 
