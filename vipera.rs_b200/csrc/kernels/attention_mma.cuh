@@ -173,8 +173,10 @@ __device__ __forceinline__ void fold_block(const uint32_t (&q_frag)[D / 16][4], 
 }
 
 // One warp's copy of ROWS (16 or 32) cache rows into its tile: in every pass the warp reads
-// two whole rows (16 lanes x 16 bytes each), so global reads are contiguous.
-template <int D, int ROWS>
+// two whole rows (16 lanes x 16 bytes each), so global reads are contiguous.  Rows whose keys
+// lie outside [visible_key, end_key) are filled with zeros, or left as they are when
+// ZERO_FILL is false (a second copy that adds rows to a tile filled before).
+template <int D, int ROWS, bool ZERO_FILL = true>
 __device__ __forceinline__ void load_kv_rows(uint32_t k_tile, uint32_t v_tile, const __nv_bfloat16* __restrict__ k_pool,
                                              const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table,
                                              int page_size, int page_shift, int num_kv_heads, int kv_head,
@@ -201,8 +203,10 @@ __device__ __forceinline__ void load_kv_rows(uint32_t k_tile, uint32_t v_tile, c
     const long long offset = __shfl_sync(0xffffffffu, my_offset, row);
     const bool valid = offset >= 0;
     const long long at = valid ? offset + chunk * 8 : 0;
-    cp_async_16(k_tile + tile_offset<D>(row, chunk), k_pool + at, valid);
-    cp_async_16(v_tile + tile_offset<D>(row, chunk), v_pool + at, valid);
+    if (ZERO_FILL || valid) {
+      cp_async_16(k_tile + tile_offset<D>(row, chunk), k_pool + at, valid);
+      cp_async_16(v_tile + tile_offset<D>(row, chunk), v_pool + at, valid);
+    }
   }
 }
 

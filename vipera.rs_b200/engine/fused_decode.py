@@ -26,7 +26,7 @@ from ..parts.norm import RMSNorm
 
 
 def _enabled() -> bool:
-    return os.environ.get("VIPERA_FUSED_DECODE", "1") != "0"
+    return os.environ.get("VIPERA_FUSED_DECODE", "0") == "1"
 
 
 class FusedDecode:
@@ -35,10 +35,9 @@ class FusedDecode:
     def __init__(self, model):
         self.model = model
         self._kept: Dict[tuple, tuple] = {}
-        self._counters = None
         self._barrier = None
         self._maps = None
-        self.trace = None  # profiling: an int64 tensor [blocks, 2 + 10 * layers] that receives timestamps
+        self.trace = None  # profiling: an int64 tensor [blocks, 2 + 12 * layers] that receives timestamps
         layers = [model.blocks[entry.layer] for entry in model.spec.schedule]
         self.head_dim = layers[0].mixer.head_dim
         self.max_heads = max(block.mixer.num_heads for block in layers)
@@ -92,7 +91,7 @@ class FusedDecode:
     def takes(self, ctx, caches) -> bool:
         if not (ctx.all_single and ctx.dtype == torch.bfloat16 and ctx.logits_all_rows):
             return False
-        if ctx.num_tokens > ops.FUSED_MAX_TOKENS:
+        if ctx.num_tokens > ops.FUSED_MAX_TOKENS or ctx.max_kv_len > ops.decode_fused_max_keys():
             return False
         model = self.model
         if not ops.decode_fused_takes(ctx.num_tokens, model.spec.hidden_size, self.head_dim, self.max_inter,
@@ -118,8 +117,7 @@ class FusedDecode:
         rows = tokens * self.max_heads * max_chunks
         partial_ml = ws.get("fused.partial_ml", (rows, 2), torch.float32)
         partial_out = ws.get("fused.partial_out", (rows, d), torch.float32)
-        if self._counters is None:
-            self._counters = torch.zeros(ops.FUSED_MAX_TOKENS * self.max_kv_heads, dtype=torch.int32, device=device)
+        if self._barrier is None:
             self._barrier = torch.zeros(1, dtype=torch.int32, device=device)
         key = (tokens, max_chunks, ctx.tokens.data_ptr(), ctx.positions.data_ptr(), ws.generation,
                tuple((t.data_ptr(), t.shape[1]) for t in ctx.block_tables))
@@ -170,7 +168,7 @@ class FusedDecode:
         m.embedding = model.embedding.data_ptr()
         m.x, m.q, m.attn, m.act = x.data_ptr(), q.data_ptr(), attn.data_ptr(), act.data_ptr()
         m.partial_ml, m.partial_out = partial_ml.data_ptr(), partial_out.data_ptr()
-        m.counters, m.barrier = self._counters.data_ptr(), self._barrier.data_ptr()
+        m.barrier = self._barrier.data_ptr()
         m.final_norm, m.final_eps = model.final_norm.weight.data_ptr(), model.final_norm.eps
         m.head = model.head.weight.data_ptr()
         m.logits = logits.data_ptr()

@@ -499,7 +499,7 @@ class FusedModel(ctypes.Structure):
     _fields_ = [
         ("layers", _c_void), ("maps", _c_void), ("tokens", _c_void), ("positions", _c_void), ("embedding", _c_void),
         ("x", _c_void), ("q", _c_void), ("attn", _c_void), ("act", _c_void),
-        ("partial_ml", _c_void), ("partial_out", _c_void), ("counters", _c_void),
+        ("partial_ml", _c_void), ("partial_out", _c_void),
         ("final_norm", _c_void), ("head", _c_void), ("logits", _c_void),
         ("barrier", _c_void), ("status", _c_void), ("trace", _c_void),
         ("final_eps", _c_float), ("logit_scale", _c_float),
@@ -520,6 +520,11 @@ def _fused_sizes_checked() -> None:
 
 def decode_fused_chunk_keys() -> int:
     return _function("decode_fused", "vipera_decode_fused_chunk_keys", [])()
+
+
+def decode_fused_max_keys() -> int:
+    """The longest history (in keys) the fused step takes."""
+    return decode_fused_chunk_keys() * _function("decode_fused", "vipera_decode_fused_max_chunks", [])()
 
 
 def decode_fused_takes(tokens: int, hidden: int, head_dim: int, max_inter: int, max_q_dim: int) -> bool:
