@@ -32,15 +32,15 @@ def test_fused_decode_is_used_and_agrees_with_the_parts():
 
     folder = helpers.model_folder("A", "bfloat16")
     prompts = [helpers.random_tokens(helpers.CONFIGS["A"]["vocab_size"], n, 70 + n) for n in (5, 40, 90)]
-    results = []
+    results, launched = [], []
     for fused in (False, True):
         engine = Engine(folder, dtype="bfloat16", page_size=16, num_pages=64)
         engine.runner.fused = FusedDecode(engine.model) if fused else None
         before = ops.launches
         outs = engine.generate(prompts, SamplingParams(max_new_tokens=24, temperature=0.0))
         results.append([list(o.tokens) for o in outs])
-        if fused:
-            assert ops.launches - before < 40 * 3, "the decode steps did not run as single kernels"
+        launched.append(ops.launches - before)
+    assert launched[1] < launched[0] / 2, f"the decode steps did not run as single kernels: {launched}"
     same = sum(a == b for a, b in zip(*results))
     # bfloat16 rounding differs between the two paths; greedy choices may part at a near tie
     assert same >= 2, results

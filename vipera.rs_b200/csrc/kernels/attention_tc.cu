@@ -1,0 +1,752 @@
+// bfloat16 attention of prompt portions over the paged cache on the fifth-generation tensor
+// cores (tcgen05, accumulators in tensor memory), head size 128.
+//
+// One block serves 128 queries of one entry and one query head and walks the visible keys
+// 128 at a time, in the flash form of the reference's online fold
+// (crates/vipera-backend-cpu/src/model.rs:2752-2857; definition model.rs:1804-1859):
+//
+//   scores  S = Q . K^T        tcgen05.mma, 128 x 128 x 128, into tensor memory
+//   softmax                    four warps, one query row per thread: running max and sum in
+//                              32-bit, p = 2^(s * scale * log2 e - max), rounded to bfloat16
+//                              into shared memory
+//   output  O += P . V         tcgen05.mma, 128 x 128 x 128, accumulated in tensor memory;
+//                              when a row's max grows, its accumulator is scaled first
+//
+// Roles: warps 0-7 softmax and ending, warp 8 issues the MMAs, warps 9-12 bring keys and values
+// through the block table into shared memory, two tiles in flight: with TMA, one box per page
+// and half of the head (pages of 8, 16, 32, 64 or multiples of 128 keys; the copies of four
+// warps' 16-byte cp.async cannot keep enough bytes in flight), else with cp.async.  Two score
+// accumulators alternate, so the scores of the next 128 keys are computed while the softmax
+// of the current ones runs.  Keys and values share one shared-memory image, 128-byte rows
+// with 16-byte chunks XOR-swizzled by the row: for the scores it is read K-major (the
+// contraction runs along the head dimension), for the output MN-major (the contraction runs
+// along the keys), so no transposed copy of V is made.
+//
+// Rows of a tile that hold no visible key (before a window, after the causal limit, past the
+// written part of the cache) are zero-filled, never read: they may lie in pages the request
+// gave back.  Every wait on an mbarrier is bounded; a wait that runs out records an error
+// code in the status word and lets every role run to its end.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+enum { ATTENTION_TC_WAIT_EXPIRED = 3 };
+
+#ifdef VIPERA_ATTN_TIMING
+#include <cstdio>
+#define ATT_T(var) const long long var = clock64()
+#define ATT_ADD(acc, a, b) acc += (b) - (a)
+#else
+#define ATT_T(var)
+#define ATT_ADD(acc, a, b)
+#endif
+
+namespace {
+
+constexpr int kD = 128;                 // head size
+constexpr int kQ = 128;                 // queries per block
+constexpr int kKeys = 128;              // keys per tile
+constexpr int kTileBytes = 128 * 256;   // a [128][128] bfloat16 tile: two halves of [128 rows][128 bytes]
+constexpr int kHalfBytes = 128 * 128;
+constexpr int kSoftmaxWarps = 8, kLoaderWarps = 4;
+constexpr int kHalfCols = 64;            // columns of a row one softmax thread takes
+constexpr int kMmaWarp = kSoftmaxWarps;
+constexpr int kThreads = (kSoftmaxWarps + 1 + kLoaderWarps) * 32;
+constexpr int kLoaderThreads = kLoaderWarps * 32;
+constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kMaxSlack = 8.0f;       // in powers of two
+// tensor memory columns: two score accumulators and the output accumulator
+constexpr uint32_t kColsS0 = 0, kColsS1 = 128, kColsO = 256, kTmemCols = 512;
+
+struct Params {
+  const __nv_bfloat16* q;      // [tokens, heads, 128]
+  __nv_bfloat16* out;          // [tokens, heads, 128]
+  const __nv_bfloat16* k_pool; // [pages, page_size, kv_heads, 128]
+  const __nv_bfloat16* v_pool;
+  const int* entry_starts;     // [entries + 1]
+  const int* entry_pos0;       // [entries]
+  const int* block_table;      // [entries, table_width]
+  int table_width, page_size, num_entries, num_heads, num_kv_heads, window;
+  float scale;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  for (uint32_t spin = 0; spin < kWaitLimit; ++spin) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (spin > 8) __nanosleep(64);  // a waiting role leaves the issue slots to the working ones
+    if ((spin & 1023u) == 1023u && *abort_flag) return;
+  }
+  *abort_flag = 1;
+  atomicExch(status, ATTENTION_TC_WAIT_EXPIRED);
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// one box [1 page][rows][1 KV head][64 values] of a cache pool
+__device__ __forceinline__ void tma_load_box(void* dst, const CUtensorMap* map, uint64_t* bar, int d0, int kv_head, int slot, int page) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(d0), "r"(kv_head), "r"(slot), "r"(page)
+      : "memory");
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_load_32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 2^x with the hardware's approximation (exact enough for weights that are rounded to bfloat16);
+// 2^(-inf) = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// A tile in shared memory: two halves (columns 0-63 and 64-127) of [128 rows][128 bytes], the
+// 16-byte chunks of a row XOR-swizzled by the row (the 128-byte swizzle of the tensor cores).
+__device__ __forceinline__ uint32_t tile_offset(int row, int chunk /* 0..15 */) {
+  return static_cast<uint32_t>((chunk >> 3) * kHalfBytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
+// Descriptor of a tile read K-major: rows are the M or N side, the contraction runs along the
+// 128-byte rows.  Groups of 8 rows are 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  desc |= static_cast<uint64_t>(1) << 16;                 // leading byte offset: unused with this swizzle
+  desc |= static_cast<uint64_t>(1024 >> 4) << 32;         // stride byte offset: between groups of 8 rows
+  desc |= static_cast<uint64_t>(1) << 46;                 // descriptor version
+  desc |= static_cast<uint64_t>(2) << 61;                 // 128-byte swizzle
+  return desc;
+}
+// Descriptor of the same image read MN-major: the 128-byte rows run along the N side (64
+// values each, the second 64 in the other half), the contraction runs down the rows.
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  desc |= static_cast<uint64_t>(kHalfBytes >> 4) << 16;   // leading byte offset: between the halves (64 values of N)
+  desc |= static_cast<uint64_t>(1024 >> 4) << 32;         // stride byte offset: between groups of 8 rows (of the contraction)
+  desc |= static_cast<uint64_t>(1) << 46;
+  desc |= static_cast<uint64_t>(2) << 61;
+  return desc;
+}
+
+struct Barriers {
+  uint64_t q_full;
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t v_landed[2];  // TMA path: the boxes of a value tile have arrived (rows outside the visible keys are zeroed after that)
+  uint64_t s_full[2], s_empty[2];
+  uint64_t p_full, pv_done;
+  uint32_t tmem_base;
+  int abort_flag;
+  float half_max[2][2][128];  // [score buffer][half of the columns][row]: what the two halves of a row tell each other
+  float half_sum[2][128];
+};
+
+template <bool TMA_KV>
+__global__ void __launch_bounds__(kThreads, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* q_tile = smem;
+  uint8_t* k_tiles = smem + kTileBytes;       // two tiles
+  uint8_t* v_tiles = smem + 3 * kTileBytes;   // two tiles
+  uint8_t* p_tile = smem + 5 * kTileBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + 6 * kTileBytes);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, kLoaderThreads);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->k_full[i], TMA_KV ? 1 : kLoaderThreads);
+      mbar_init(&bars->v_full[i], kLoaderThreads);
+      mbar_init(&bars->v_landed[i], 1);
+      mbar_init(&bars->k_empty[i], 1);
+      mbar_init(&bars->v_empty[i], 1);
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->s_empty[i], kSoftmaxWarps * 32);
+    }
+    mbar_init(&bars->p_full, kSoftmaxWarps * 32);
+    mbar_init(&bars->pv_done, 1);
+    bars->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)), "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  pdl_wait();
+
+  // Which (entry, tile of that entry) is this block?  Blocks are numbered from the back, so
+  // that the tiles with the longest history (the last of each entry) start first.
+  int entry = -1, tile_in_entry = 0;
+  {
+    int remaining = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+    for (int e = 0; e < p.num_entries; ++e) {
+      const int tiles = (p.entry_starts[e + 1] - p.entry_starts[e] + kQ - 1) / kQ;
+      if (remaining < tiles) { entry = e; tile_in_entry = remaining; break; }
+      remaining -= tiles;
+    }
+  }
+  int num_tiles = 0, first_tile = 0, token0 = 0, tokens_here = 0, pos0 = 0, first_key = 0, end_key = 0;
+  const int head = blockIdx.y;
+  const int kv_head = head / (p.num_heads / p.num_kv_heads);
+  if (entry >= 0) {
+    token0 = p.entry_starts[entry] + tile_in_entry * kQ;
+    tokens_here = min(kQ, p.entry_starts[entry + 1] - token0);
+    pos0 = p.entry_pos0[entry] + tile_in_entry * kQ;  // position of the tile's first query
+    first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    end_key = pos0 + tokens_here;                     // one past the last visible key
+    first_tile = first_key / kKeys;
+    num_tiles = (end_key + kKeys - 1) / kKeys - first_tile;
+  }
+
+  if (warp < kSoftmaxWarps) {
+    // ---------------- softmax and ending: thread = (query row, half of the columns) ----------------
+    // Warps w and w + 4 share the rows 32 (w % 4) .. + 31 (a warp reaches only its quarter of
+    // the tensor memory's lanes) and take 64 columns each; two warps per scheduler hide each
+    // other's latencies.  The two halves of a row agree on the row's max through shared memory.
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = quarter * 32 + lane;
+    const int col0 = half * kHalfCols;
+    const int position = pos0 + row;
+    const int row_limit = row < tokens_here ? position : -1;  // rows past the entry's end see nothing
+    const int row_first = p.window > 0 ? max(0, position - p.window + 1) : 0;
+    const float scale_log2 = p.scale * kLog2e;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    float row_max = -INFINITY, row_sum = 0.0f;
+#ifdef VIPERA_ATTN_TIMING
+    long long w_s = 0, w_pv = 0, c_p1 = 0, c_rs = 0, c_p2 = 0;
+#endif
+    for (int j = 0; j < num_tiles; ++j) {
+      const int buffer = j & 1;
+      const uint32_t s_addr = lane_base + (buffer ? kColsS1 : kColsS0) + col0;
+      const int key0 = (first_tile + j) * kKeys + col0;
+      ATT_T(t0);
+      mbar_wait(&bars->s_full[buffer], static_cast<uint32_t>(j >> 1) & 1u, abort_flag, p.status);
+      tcgen05_fence_after();
+      ATT_T(t1);
+      ATT_ADD(w_s, t0, t1);
+      // does any row of this block need a mask in this tile?
+      const bool edge = (first_tile + j) * kKeys + kKeys - 1 > pos0 ||
+                        (p.window > 0 && (first_tile + j) * kKeys < pos0 + tokens_here - p.window + 1) || tokens_here < kQ;
+      // the thread's 64 scores into registers; the accumulator is then free for the next tile but one
+      uint32_t sv[kHalfCols];
+#pragma unroll
+      for (int c = 0; c < kHalfCols; c += 32) tmem_load_32_nowait(s_addr + c, *reinterpret_cast<uint32_t(*)[32]>(&sv[c]));
+      tmem_load_wait();
+      tcgen05_fence_before();
+      mbar_arrive(&bars->s_empty[buffer]);
+      // the row's largest visible score
+      float tile_max = -INFINITY;
+      if (edge) {
+#pragma unroll
+        for (int i = 0; i < kHalfCols; ++i) {
+          const int key = key0 + i;
+          if (key < row_first || key > row_limit) sv[i] = __float_as_uint(-INFINITY);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kHalfCols; ++i) tile_max = fmaxf(tile_max, __uint_as_float(sv[i]));
+      bars->half_max[buffer][half][row] = tile_max;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      tile_max = fmaxf(tile_max, bars->half_max[buffer][half ^ 1][row]);
+      tile_max *= scale_log2;
+      // The running max only has to keep the exponentials in range: it follows the row's true
+      // max when that has grown by more than kMaxSlack (weights then stay below 2^kMaxSlack,
+      // and the final division by the sum cancels the common factor).  Most tiles thus leave the
+      // output accumulator as it is.
+      float new_max = row_max;
+      if (tile_max > row_max + kMaxSlack || row_max == -INFINITY) new_max = fmaxf(row_max, tile_max);
+      const float alpha = new_max == row_max ? 1.0f : fast_exp2(row_max - new_max);
+      row_max = new_max;
+      row_sum *= alpha;
+      // the output accumulator and the P tile are free once the products of the tile before are done
+      ATT_T(t2);
+      ATT_ADD(c_p1, t1, t2);
+      if (j > 0) mbar_wait(&bars->pv_done, static_cast<uint32_t>(j - 1) & 1u, abort_flag, p.status);
+      tcgen05_fence_after();
+      ATT_T(t3);
+      ATT_ADD(w_pv, t2, t3);
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+        for (int c = 0; c < kHalfCols; c += 32) {
+          uint32_t v[32];
+          tmem_load_32(lane_base + kColsO + col0 + c, v);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_store_32(lane_base + kColsO + col0 + c, v);
+        }
+        tmem_store_wait();
+      }
+      // p = 2^(s * scale * log2 e - max), summed in 32-bit, rounded to bfloat16 into the P tile
+      ATT_T(t4);
+      ATT_ADD(c_rs, t3, t4);
+      float tile_sum = 0.0f;
+      const float shift = row_max == -INFINITY ? 0.0f : row_max;  // a row without visible keys: 2^(-inf) = 0 everywhere
+#pragma unroll
+      for (int c = 0; c < kHalfCols; c += 8) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c + i]), scale_log2, -shift));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c + i + 1]), scale_log2, -shift));
+          tile_sum += p0 + p1;
+          __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+        }
+        *reinterpret_cast<uint4*>(p_tile + tile_offset(row, (col0 + c) >> 3)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+      row_sum += tile_sum;
+      // P is written: hand it over to the MMA warp
+      tcgen05_fence_before();
+      fence_async_shared();
+      mbar_arrive(&bars->p_full);
+      ATT_T(t5);
+      ATT_ADD(c_p2, t4, t5);
+    }
+#ifdef VIPERA_ATTN_TIMING
+    if (blockIdx.x == 1 && blockIdx.y == 0 && threadIdx.x == 0 && num_tiles > 0)
+      printf("softmax: tiles %d wait_s %lld pass1 %lld wait_pv %lld rescale %lld pass2 %lld (cycles per tile)\n", num_tiles,
+             w_s / num_tiles, c_p1 / num_tiles, w_pv / num_tiles, c_rs / num_tiles, c_p2 / num_tiles);
+#endif
+    // ---------------- ending: out = O / sum ----------------
+    if (num_tiles > 0) {
+      // the row's sum is the sum of its two halves
+      bars->half_sum[half][row] = row_sum;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      row_sum += bars->half_sum[half ^ 1][row];
+      mbar_wait(&bars->pv_done, static_cast<uint32_t>(num_tiles - 1) & 1u, abort_flag, p.status);
+      tcgen05_fence_after();
+      const float inverse = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
+      __nv_bfloat16* dst = p.out + (static_cast<size_t>(token0 + row) * p.num_heads + head) * kD + col0;
+#pragma unroll 1
+      for (int c = 0; c < kHalfCols; c += 32) {
+        uint32_t v[32];
+        tmem_load_32(lane_base + kColsO + col0 + c, v);
+        if (row < tokens_here && !*abort_flag) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 packed;
+            __nv_bfloat162* halves = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int h = 0; h < 4; ++h)
+              halves[h] = __floats2bfloat162_rn(__uint_as_float(v[i + 2 * h]) * inverse, __uint_as_float(v[i + 2 * h + 1]) * inverse);
+            *reinterpret_cast<uint4*>(dst + c + i) = packed;
+          }
+        }
+      }
+    }
+    tcgen05_fence_before();
+  } else if (warp == kMmaWarp) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0 && num_tiles > 0) {
+      // instruction descriptors: bf16 x bf16 -> f32, M = 128, N = 128; B K-major for the scores, MN-major for the output
+      constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) | (static_cast<uint32_t>(kQ >> 4) << 24);
+      constexpr uint32_t kIdescO = kIdescS | (1u << 16);
+      const uint32_t q_addr = smem_u32(q_tile), p_addr = smem_u32(p_tile);
+#ifdef VIPERA_ATTN_TIMING
+      long long m_k = 0, m_s = 0, m_v = 0, m_p = 0;
+#endif
+      auto issue_scores = [&](int j) {
+        const int buffer = j & 1;
+        ATT_T(a0);
+        mbar_wait(&bars->k_full[buffer], static_cast<uint32_t>(j >> 1) & 1u, abort_flag, p.status);
+        ATT_T(a1);
+        mbar_wait(&bars->s_empty[buffer], (static_cast<uint32_t>(j >> 1) & 1u) ^ 1u, abort_flag, p.status);
+        ATT_T(a2);
+        ATT_ADD(m_k, a0, a1);
+        ATT_ADD(m_s, a1, a2);
+        tcgen05_fence_after();
+        const uint32_t k_addr = smem_u32(k_tiles + buffer * kTileBytes);
+        const uint32_t d_tmem = tmem_base + (buffer ? kColsS1 : kColsS0);
+#pragma unroll
+        for (int ks = 0; ks < kD / 16; ++ks) {
+          // 16 values further along the row: 32 bytes inside a half, the other half after 4 steps
+          const uint32_t offset = static_cast<uint32_t>((ks >> 2) * kHalfBytes + (ks & 3) * 32);
+          tcgen05_mma_bf16(d_tmem, desc_k_major(q_addr + offset), desc_k_major(k_addr + offset), kIdescS, ks > 0 ? 1u : 0u);
+        }
+        tcgen05_commit(&bars->k_empty[buffer]);
+        tcgen05_commit(&bars->s_full[buffer]);
+      };
+      mbar_wait(&bars->q_full, 0, abort_flag, p.status);
+      issue_scores(0);
+      for (int j = 0; j < num_tiles; ++j) {
+        if (j + 1 < num_tiles) issue_scores(j + 1);
+        const int buffer = j & 1;
+        ATT_T(b0);
+        mbar_wait(&bars->v_full[buffer], static_cast<uint32_t>(j >> 1) & 1u, abort_flag, p.status);
+        ATT_T(b1);
+        mbar_wait(&bars->p_full, static_cast<uint32_t>(j) & 1u, abort_flag, p.status);
+        ATT_T(b2);
+        ATT_ADD(m_v, b0, b1);
+        ATT_ADD(m_p, b1, b2);
+        tcgen05_fence_after();
+        const uint32_t v_addr = smem_u32(v_tiles + buffer * kTileBytes);
+#pragma unroll
+        for (int ks = 0; ks < kKeys / 16; ++ks) {
+          // P: 16 keys further along its rows; V: 16 rows (two groups of 8) further down
+          const uint32_t p_offset = static_cast<uint32_t>((ks >> 2) * kHalfBytes + (ks & 3) * 32);
+          tcgen05_mma_bf16(tmem_base + kColsO, desc_k_major(p_addr + p_offset), desc_mn_major(v_addr + ks * 2048), kIdescO,
+                           (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        tcgen05_commit(&bars->v_empty[buffer]);
+        tcgen05_commit(&bars->pv_done);
+      }
+#ifdef VIPERA_ATTN_TIMING
+      if (blockIdx.x == 1 && blockIdx.y == 0)
+        printf("mma: wait k_full %lld s_empty %lld v_full %lld p_full %lld (cycles per tile)\n", m_k / num_tiles, m_s / num_tiles,
+               m_v / num_tiles, m_p / num_tiles);
+#endif
+    }
+    tcgen05_fence_before();
+  } else {
+    // ---------------- loaders: queries once, then keys and values tile by tile ----------------
+    const int t = threadIdx.x - (kMmaWarp + 1) * 32;  // 0..127
+    if (num_tiles > 0) {
+      const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
+      for (int index = t; index < kQ * 16; index += kLoaderThreads) {
+        const int row = index >> 4, chunk = index & 15;
+        const bool valid = row < tokens_here;
+        const __nv_bfloat16* src = p.q + (static_cast<size_t>(token0 + (valid ? row : 0)) * p.num_heads + head) * kD + chunk * 8;
+        cp_async_16(smem_u32(q_tile) + tile_offset(row, chunk), src, valid);
+      }
+      cp_async_commit();
+      if constexpr (TMA_KV) {
+        // ---- keys and values by TMA: the first loader warp issues one box per page and half ----
+        const int rows_per_box = min(p.page_size, kKeys);
+        const int boxes = kKeys / rows_per_box;
+        const int loader_warp = t >> 5;
+        auto issue_boxes = [&](int j, const CUtensorMap* map, uint8_t* tile, uint64_t* landed) {
+          const int key = (first_tile + j) * kKeys + lane * rows_per_box;
+          int page = -1;
+          // a box is fetched when it holds a visible key; the others stay as they are (keys) or are zeroed (values)
+          if (lane < boxes && key + rows_per_box > first_key && key < end_key) page = table[key / p.page_size];
+          const unsigned fetched = __ballot_sync(0xffffffffu, page >= 0);
+          if (lane == 0) mbar_expect_tx(landed, static_cast<uint32_t>(__popc(fetched) * rows_per_box * 256));
+          __syncwarp();
+          if (page >= 0) {
+            uint8_t* dst = tile + lane * rows_per_box * 128;
+            tma_load_box(dst, map, landed, 0, kv_head, key % p.page_size, page);
+            tma_load_box(dst + kHalfBytes, map, landed, 64, kv_head, key % p.page_size, page);
+          }
+        };
+        auto issue_keys = [&](int j) {
+          const int buffer = j & 1;
+          if (j >= 2) mbar_wait(&bars->k_empty[buffer], static_cast<uint32_t>((j >> 1) - 1) & 1u, abort_flag, p.status);
+          if (!*abort_flag) issue_boxes(j, &k_map, k_tiles + buffer * kTileBytes, &bars->k_full[buffer]);
+        };
+        auto issue_values = [&](int j) {
+          const int buffer = j & 1;
+          if (j >= 2) mbar_wait(&bars->v_empty[buffer], static_cast<uint32_t>((j >> 1) - 1) & 1u, abort_flag, p.status);
+          if (!*abort_flag) issue_boxes(j, &v_map, v_tiles + buffer * kTileBytes, &bars->v_landed[buffer]);
+        };
+        if (loader_warp == 0) {
+          issue_keys(0);
+          issue_values(0);
+          if (num_tiles > 1) { issue_keys(1); issue_values(1); }
+        }
+        cp_async_wait<0>();
+        fence_async_shared();
+        mbar_arrive(&bars->q_full);
+        for (int j = 0; j < num_tiles; ++j) {
+          const int buffer = j & 1;
+          const int key0 = (first_tile + j) * kKeys;
+          // a value row that holds no visible key must be zero: its weight is zero, but what lies
+          // in the cache there may be anything
+          mbar_wait(&bars->v_landed[buffer], static_cast<uint32_t>(j >> 1) & 1u, abort_flag, p.status);
+          if (key0 < first_key || key0 + kKeys > end_key) {
+            const int key = key0 + t;
+            if (key < first_key || key >= end_key) {
+              uint8_t* tile = v_tiles + buffer * kTileBytes;
+#pragma unroll
+              for (int chunk = 0; chunk < 16; ++chunk) *reinterpret_cast<uint4*>(tile + tile_offset(t, chunk)) = make_uint4(0, 0, 0, 0);
+            }
+          }
+          fence_async_shared();
+          mbar_arrive(&bars->v_full[buffer]);
+          if (loader_warp == 0) {
+            if (j >= 1 && j + 1 < num_tiles) issue_values(j + 1);
+            if (j + 2 < num_tiles) issue_keys(j + 2);
+          }
+        }
+      } else {
+      // A tile is copied in 16 passes of 8 rows: 16 consecutive threads copy the 16 chunks of
+      // one cache row, so that global reads are whole 256-byte rows.  Where a page holds a power
+      // of two of keys, page and slot come from a shift and a mask.
+      const int page_shift = (p.page_size & (p.page_size - 1)) == 0 ? 31 - __clz(p.page_size) : -1;
+      const long long row_stride = static_cast<long long>(p.num_kv_heads) * kD;
+      auto copy_tile = [&](int j, const __nv_bfloat16* pool, uint32_t dst) {
+        const int key_base = (first_tile + j) * kKeys + (t >> 4);
+        const int chunk = t & 15;
+        const __nv_bfloat16* base = pool + static_cast<long long>(kv_head) * kD + chunk * 8;
+        // the block table first (independent reads), then the copies
+        int pages[16];
+#pragma unroll
+        for (int pass = 0; pass < 16; ++pass) {
+          const int key = key_base + pass * 8;
+          pages[pass] = -1;
+          if (key >= first_key && key < end_key) pages[pass] = table[page_shift >= 0 ? key >> page_shift : key / p.page_size];
+        }
+#pragma unroll
+        for (int pass = 0; pass < 16; ++pass) {
+          const int key = key_base + pass * 8;
+          const int slot = page_shift >= 0 ? key & (p.page_size - 1) : key % p.page_size;
+          const bool valid = pages[pass] >= 0;
+          const long long at = valid ? (static_cast<long long>(pages[pass]) * p.page_size + slot) * row_stride : 0;
+          cp_async_16(dst + tile_offset(pass * 8 + (t >> 4), chunk), base + at, valid);
+        }
+        cp_async_commit();
+      };
+#ifdef VIPERA_ATTN_TIMING
+      long long l_ke = 0, l_ve = 0, l_copy = 0, l_land = 0;
+#endif
+      auto issue_keys = [&](int j) {    // waits until the scores of tile j - 2 have read the buffer
+        const int buffer = j & 1;
+        ATT_T(c0);
+        if (j >= 2) mbar_wait(&bars->k_empty[buffer], static_cast<uint32_t>((j >> 1) - 1) & 1u, abort_flag, p.status);
+        ATT_T(c1);
+        copy_tile(j, p.k_pool, smem_u32(k_tiles + buffer * kTileBytes));
+        ATT_T(c2);
+        ATT_ADD(l_ke, c0, c1);
+        ATT_ADD(l_copy, c1, c2);
+      };
+      auto issue_values = [&](int j) {  // waits until the output product of tile j - 2 has read the buffer
+        const int buffer = j & 1;
+        ATT_T(c0);
+        if (j >= 2) mbar_wait(&bars->v_empty[buffer], static_cast<uint32_t>((j >> 1) - 1) & 1u, abort_flag, p.status);
+        ATT_T(c1);
+        copy_tile(j, p.v_pool, smem_u32(v_tiles + buffer * kTileBytes));
+        ATT_T(c2);
+        ATT_ADD(l_ve, c0, c1);
+        ATT_ADD(l_copy, c1, c2);
+      };
+      auto wait_pending = [&](int groups) {  // until at most `groups` of this thread's copy groups are in flight
+        if (groups <= 0) cp_async_wait<0>();
+        else if (groups == 1) cp_async_wait<1>();
+        else if (groups == 2) cp_async_wait<2>();
+        else if (groups == 3) cp_async_wait<3>();
+        else cp_async_wait<4>();
+      };
+      // Copy groups are committed in this order: Q, K0, V0, K1, V1, then K(j+2) in round j and
+      // V(j+2) in round j + 1.  A round hands over what has landed before it waits for a buffer
+      // to be free: the products that free it need the data handed over.
+      issue_keys(0);
+      issue_values(0);
+      if (num_tiles > 1) { issue_keys(1); issue_values(1); }
+      wait_pending(num_tiles > 1 ? 4 : 2);
+      fence_async_shared();
+      mbar_arrive(&bars->q_full);
+      for (int j = 0; j < num_tiles; ++j) {
+        const int buffer = j & 1;
+        // groups committed after K_j so far: V_j, K_j+1 (and V_1 in round 0)
+        const int after_keys = j == 0 ? (num_tiles > 1 ? 3 : 1) : (j + 1 < num_tiles ? 2 : 1);
+        ATT_T(d0);
+        wait_pending(after_keys);
+        fence_async_shared();
+        mbar_arrive(&bars->k_full[buffer]);
+        wait_pending(after_keys - 1);
+        fence_async_shared();
+        mbar_arrive(&bars->v_full[buffer]);
+        ATT_T(d1);
+        ATT_ADD(l_land, d0, d1);
+        if (j >= 1 && j + 1 < num_tiles) issue_values(j + 1);
+        if (j + 2 < num_tiles) issue_keys(j + 2);
+      }
+#ifdef VIPERA_ATTN_TIMING
+      if (blockIdx.x == 1 && blockIdx.y == 0 && t == 0)
+        printf("loader: wait k_empty %lld v_empty %lld issue %lld landing %lld (cycles per tile)\n", l_ke / num_tiles,
+               l_ve / num_tiles, l_copy / num_tiles, l_land / num_tiles);
+#endif
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));
+  }
+}
+
+constexpr int kSmemBytes = 6 * kTileBytes + 1024 /* alignment */ + static_cast<int>(sizeof(Barriers)) + 64;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool looked = false;
+  if (!looked) {
+    looked = true;
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(entry);
+  }
+  return fn;
+}
+
+// Pages the TMA path takes: boxes of whole pages (or of 128 rows of a longer page) that start
+// on a multiple of 8 rows of the tile.
+bool tma_takes_page(int page_size) {
+  return page_size % 8 == 0 && (kKeys % page_size == 0 || page_size % kKeys == 0);
+}
+
+// A cache pool [pages, page_size, kv_heads, 128] as TMA reads it: boxes of one page's rows
+// (at most 128) of one KV head and 64 values, 128-byte swizzle.  Maps are kept by pool.
+const CUtensorMap* pool_map(const void* pool, int pages, int page_size, int kv_heads) {
+  static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> kept;
+  static std::mutex guard;
+  std::lock_guard<std::mutex> lock(guard);
+  const auto key = std::make_tuple(pool, pages, page_size, kv_heads);
+  auto found = kept.find(key);
+  if (found != kept.end()) return &found->second;
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (!encode || (reinterpret_cast<uintptr_t>(pool) & 15)) return nullptr;
+  CUtensorMap map;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(kv_heads), static_cast<cuuint64_t>(page_size),
+                        static_cast<cuuint64_t>(pages)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(kD) * 2, static_cast<cuuint64_t>(kv_heads) * kD * 2,
+                           static_cast<cuuint64_t>(page_size) * kv_heads * kD * 2};
+  cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(page_size < kKeys ? page_size : kKeys), 1};
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(pool), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return nullptr;
+  if (kept.size() > 4096) kept.clear();
+  return &kept.emplace(key, map).first->second;
+}
+
+template <bool TMA_KV>
+int launch_attention(const CUtensorMap& k_map, const CUtensorMap& v_map, const Params& p, dim3 grid, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<TMA_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  return vipera_launch(attention_prefill_tc_kernel<TMA_KV>, grid, dim3(kThreads), kSmemBytes, stream, k_map, v_map, p);
+}
+
+}  // namespace
+
+// Attention of a step with portions of any length, head size 128 (see attention_mma.cu for the
+// meaning of the arguments; `num_pages` is the pools' first extent).  `status` is a device word
+// that must be 0 before the launch; it is non-zero afterwards when a bounded wait inside the
+// kernel ran out.
+VIPERA_API int vipera_attention_prefill_tc(const void* q, void* out, const void* k_pool, const void* v_pool,
+                                           const int* entry_starts, const int* entry_pos0, const int* block_table,
+                                           int table_width, int page_size, int num_entries, int num_tokens,
+                                           int num_heads, int num_kv_heads, int head_dim, float scale, int window,
+                                           int num_pages, int* status, void* stream) {
+  if (num_tokens <= 0 || num_entries <= 0) return VIPERA_OK;
+  if (head_dim != kD || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || num_pages <= 0)
+    return VIPERA_BAD_SHAPE;
+  if (!status) return VIPERA_BAD_ARGUMENT;
+  Params p{};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.k_pool = static_cast<const __nv_bfloat16*>(k_pool);
+  p.v_pool = static_cast<const __nv_bfloat16*>(v_pool);
+  p.entry_starts = entry_starts;
+  p.entry_pos0 = entry_pos0;
+  p.block_table = block_table;
+  p.table_width = table_width;
+  p.page_size = page_size;
+  p.num_entries = num_entries;
+  p.num_heads = num_heads;
+  p.num_kv_heads = num_kv_heads;
+  p.window = window;
+  p.scale = scale;
+  p.status = status;
+  // at most one partly filled tile per entry beyond the full ones
+  dim3 grid((num_tokens + kQ - 1) / kQ + num_entries, num_heads);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (tma_takes_page(page_size) && std::getenv("VIPERA_ATTENTION_NO_TMA") == nullptr) {
+    const CUtensorMap* k_map = pool_map(k_pool, num_pages, page_size, num_kv_heads);
+    const CUtensorMap* v_map = pool_map(v_pool, num_pages, page_size, num_kv_heads);
+    if (k_map && v_map) return launch_attention<true>(*k_map, *v_map, p, grid, s);
+  }
+  CUtensorMap none{};
+  return launch_attention<false>(none, none, p, grid, s);
+}
+
+VIPERA_API const char* vipera_attention_tc_status_text(int status) { return vipera_status_text(status); }

@@ -8,6 +8,7 @@ compiler or a kernel that reports an error raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -317,6 +318,7 @@ def check_kernel_status(device) -> None:
 # bfloat16 attention on the tensor cores
 # ----------------------------------------------------------------------------------------
 MMA_HEAD_DIMS = (64, 128)
+TC_ATTENTION_HEAD_DIM = 128
 
 
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
@@ -324,10 +326,8 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
                       num_entries: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                       window: int = 0) -> None:
     """Flash-style attention of a step whose entries bring any number of tokens (bfloat16,
-    head sizes 64 and 128)."""
-    fn = _function("attention_mma", "vipera_attention_prefill",
-                   [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
-                    _c_int, _c_int, _c_int, _c_float, _c_int, _c_void])
+    head sizes 64 and 128).  Head size 128 runs on tcgen05 with accumulators in tensor memory
+    (VIPERA_ATTENTION_TC=0 keeps it on the mma.sync kernel, which also serves head size 64)."""
     if head_dim not in MMA_HEAD_DIMS:
         raise UnsupportedError(f"attention_prefill: head size {head_dim} (built: 64, 128)")
     count = q.shape[0]
@@ -335,11 +335,19 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
         raise InvalidArgumentError("attention_prefill: q and out must be [tokens, heads * d]")
     if k_pool.shape[2:] != (num_kv_heads, head_dim) or v_pool.shape != k_pool.shape:
         raise InvalidArgumentError("attention_prefill: cache pools must be [pages, page_size, kv_heads, d]")
-    _check(fn(_gpu(q, "q", torch.bfloat16), _gpu(out, "out", torch.bfloat16), _gpu(k_pool, "k_pool", torch.bfloat16),
-              _gpu(v_pool, "v_pool", torch.bfloat16), _gpu(entry_starts, "entry_starts", torch.int32),
-              _gpu(entry_pos0, "entry_pos0", torch.int32), _gpu(block_table, "block_table", torch.int32),
-              block_table.shape[1], k_pool.shape[1], num_entries, count, num_heads, num_kv_heads, head_dim,
-              float(scale), int(window or 0), _stream()), "attention_prefill")
+    pointers = (_gpu(q, "q", torch.bfloat16), _gpu(out, "out", torch.bfloat16), _gpu(k_pool, "k_pool", torch.bfloat16),
+                _gpu(v_pool, "v_pool", torch.bfloat16), _gpu(entry_starts, "entry_starts", torch.int32),
+                _gpu(entry_pos0, "entry_pos0", torch.int32), _gpu(block_table, "block_table", torch.int32))
+    sizes = (block_table.shape[1], k_pool.shape[1], num_entries, count, num_heads, num_kv_heads, head_dim,
+             float(scale), int(window or 0))
+    kinds = [_c_void] * 7 + [_c_int] * 7 + [_c_float, _c_int]
+    if head_dim == TC_ATTENTION_HEAD_DIM and os.environ.get("VIPERA_ATTENTION_TC", "1") != "0":
+        fn = _function("attention_tc", "vipera_attention_prefill_tc", kinds + [_c_int, _c_void, _c_void])
+        _check(fn(*pointers, *sizes, k_pool.shape[0], kernel_status_word(q.device).data_ptr(), _stream()),
+               "attention_prefill_tc")
+        return
+    fn = _function("attention_mma", "vipera_attention_prefill", kinds + [_c_void])
+    _check(fn(*pointers, *sizes, _stream()), "attention_prefill")
 
 
 def decode_splits(num_entries: int, num_kv_heads: int, max_keys: int, sm_count: int = 148):

@@ -27,7 +27,7 @@ class GQAttention(Mixer):
     count of keys), softmax_scale, position (a PartSpec of a position encoding) and,
     optionally, ``projection_names`` (defaults q_proj, k_proj, v_proj, o_proj)."""
 
-    kernels = ("rope_cache", "attention", "attention_mma")
+    kernels = ("rope_cache", "attention", "attention_mma", "attention_tc")
     takes_lazy_input = True
 
     @staticmethod
