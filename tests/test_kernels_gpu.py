@@ -1,6 +1,7 @@
 """Each kernel alone against a plain float32/float64 reference of the same operation, at
 sizes other than the engine's configurations."""
 import math
+import os
 
 import numpy as np
 import pytest
@@ -252,6 +253,68 @@ def test_attention_portions(heads, kv_heads, d, page, dtype, window):
                               num_entries=entries, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
                               scale=scale, window=window)
         assert _rel(out2.float().cpu().view(total, heads, d), want) < limit
+
+
+@pytest.mark.parametrize("page", [8, 16, 24, 64, 128, 256])
+@pytest.mark.parametrize("window", [0, 300])
+def test_attention_prefill_tensor_memory(page, window):
+    """The tcgen05 kernel (head size 128) on portions that span several tiles of 128 queries and
+    of 128 keys: whole prompts, a portion at the end of a longer history, two tokens, one
+    token; pages from 8 to 256 keys (TMA boxes per page; 24 goes the cp.async way), pages a
+    window has passed given back and filled with NaN, and once with TMA switched off."""
+    ops = _ops()
+    heads, kv_heads, d = 6, 2, 128
+    lengths = [700, 333, 130, 1]
+    counts = [700, 200, 2, 1]
+    entries = len(lengths)
+    lengths, counts, table, k_pool, v_pool, keys, values, q = _paged_case(
+        entries, heads, kv_heads, d, page, torch.bfloat16, seed=page + window, lengths=lengths, counts=counts)
+    scale = 1.0 / math.sqrt(d)
+    want = _attention_reference(q, keys, values, lengths, counts, heads, kv_heads, scale, window)
+    _give_back_passed_pages(table, k_pool, v_pool, lengths, counts, page, window)
+    total = sum(counts)
+    qd = q.to(torch.bfloat16).reshape(total, heads * d).to(DEV)
+    kp, vp, tb = k_pool.to(DEV), v_pool.to(DEV), table.to(DEV)
+    starts = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=DEV)
+    pos0 = torch.tensor([n - c for n, c in zip(lengths, counts)], dtype=torch.int32, device=DEV)
+    for no_tma in (False, True):
+        if no_tma:
+            if page != 16:
+                continue
+            os.environ["VIPERA_ATTENTION_NO_TMA"] = "1"
+        try:
+            out = torch.full_like(qd, float("nan"))
+            ops.attention_prefill(qd, out, kp, vp, entry_starts=starts, entry_pos0=pos0, block_table=tb,
+                                  num_entries=entries, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
+                                  scale=scale, window=window)
+            torch.cuda.synchronize()
+            ops.check_kernel_status(DEV)
+        finally:
+            os.environ.pop("VIPERA_ATTENTION_NO_TMA", None)
+        assert _rel(out.float().cpu().view(total, heads, d), want) < 1e-2, (page, window, no_tma)
+
+
+def test_attention_prefill_tensor_memory_finds_one_far_key():
+    """One key far back, in a tile of its own, scaled so that its score stands out: every
+    query of a long portion must return that key's value."""
+    ops = _ops()
+    heads, kv_heads, d, page, n = 2, 1, 128, 16, 900
+    for far in (0, 127, 128, 511, 640):
+        lengths, counts, table, k_pool, v_pool, keys, values, q = _paged_case(
+            1, heads, kv_heads, d, page, torch.bfloat16, seed=far + 5, lengths=[n], counts=[200])
+        direction = torch.nn.functional.normalize(torch.randn(d), dim=0)
+        q[:, :] = direction * 40
+        physical = int(table[0, far // page])
+        k_pool[physical, far % page, :] = (direction * 40).to(torch.bfloat16)
+        v_pool[physical, far % page] = torch.full((kv_heads, d), 7.0).to(torch.bfloat16)
+        qd = q.to(torch.bfloat16).reshape(200, heads * d).to(DEV)
+        out = torch.empty_like(qd)
+        ops.attention_prefill(qd, out, k_pool.to(DEV), v_pool.to(DEV),
+                              entry_starts=torch.tensor([0, 200], dtype=torch.int32, device=DEV),
+                              entry_pos0=torch.tensor([n - 200], dtype=torch.int32, device=DEV),
+                              block_table=table.to(DEV), num_entries=1, num_heads=heads, num_kv_heads=kv_heads,
+                              head_dim=d, scale=1.0, window=0)
+        assert torch.allclose(out.float().cpu(), torch.full((200, heads * d), 7.0), atol=0.05), far
 
 
 def test_attention_finds_one_far_key():
