@@ -282,6 +282,7 @@ def main():
     parser.add_argument("--history", type=int, default=2048)
     parser.add_argument("--layers", type=int, default=FULL_LAYERS)
     parser.add_argument("--skip-points", action="store_true")
+    parser.add_argument("--page-size", type=int, default=16, help="keys per cache page (the engine's default is 16)")
     parser.add_argument("--only", choices=["decode", "prefill"], default=None,
                         help="run one part only and print a short line (for profiling a small case)")
     args = parser.parse_args()
@@ -309,18 +310,18 @@ def main():
 
     model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
     if args.only == "prefill":
-        ms = measure_prefill(model, 2048, repeats=2, warmup=warmup)
+        ms = measure_prefill(model, 2048, repeats=2, warmup=warmup, page_size=args.page_size)
         print(json.dumps({"only": "prefill", "layers": args.layers, "ms": round(ms, 3)}))
         return 0
     if args.only == "decode":
-        harness = DecodeHarness(model, args.batch, args.history, args.steps + 2 * warmup + 2)
+        harness = DecodeHarness(model, args.batch, args.history, args.steps + 2 * warmup + 2, page_size=args.page_size)
         ms, _ = harness.timed(args.steps, warmup)
         print(json.dumps({"only": "decode", "layers": args.layers, "batch": args.batch, "ms_per_step": round(ms, 4)}))
         return 0
     sampler = ClockSampler()
     sampler.start()
 
-    harness = DecodeHarness(model, args.batch, args.history, args.steps + warmup)
+    harness = DecodeHarness(model, args.batch, args.history, args.steps + warmup, page_size=args.page_size)
     harness.timed(2, warmup)  # graphs captured, buffers sized
     launches_before = ops.launches
     ms_per_step, mean_history = harness.timed(args.steps, warmup)
@@ -333,7 +334,7 @@ def main():
     points = {}
     if not args.skip_points:
         for batch in (1, 64):
-            other = DecodeHarness(model, batch, args.history, 32 + warmup)
+            other = DecodeHarness(model, batch, args.history, 32 + warmup, page_size=args.page_size)
             ms, _ = other.timed(32, warmup)
             other.close()
             points[f"decode_b{batch}"] = round(batch * 1000.0 / ms, 1)
@@ -341,11 +342,11 @@ def main():
             torch.cuda.empty_cache()
 
     prefill_tokens = 2048
-    prefill_ms = measure_prefill(model, prefill_tokens, repeats=5, warmup=3)
+    prefill_ms = measure_prefill(model, prefill_tokens, repeats=5, warmup=3, page_size=args.page_size)
     flops = prefill_flops(config, args.layers, prefill_tokens)
     prefill_frac = flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)
 
-    e2e_value, h2d, d2h = measure_e2e(model, args.batch, args.history, args.steps, warmup)
+    e2e_value, h2d, d2h = measure_e2e(model, args.batch, args.history, args.steps, warmup, page_size=args.page_size)
     clocks = sampler.stop()
 
     line = {
@@ -360,7 +361,7 @@ def main():
             "kv_heads": config["num_key_value_heads"], "head_dim": 128,
             "intermediate": config["intermediate_size"], "vocab": config["vocab_size"],
             "tied_head": True, "global_batch": args.batch, "seq_len": args.history,
-            "new_tokens": args.steps, "page_size": 16, "parallelism": "single GPU",
+            "new_tokens": args.steps, "page_size": args.page_size, "parallelism": "single GPU",
             "l2": "inputs larger than L2: 3.1 GB of weights per step against 126 MB",
             "peaks": peak_source,
         },

@@ -120,13 +120,16 @@ def test_gemm_tc_repeats_exactly():
 
 
 # ---------------------------------------------------------------------------------------
-def _paged_case(entries, heads, kv_heads, d, page, dtype, seed, window=0, lengths=None, counts=None):
-    """Random q and a paged cache whose pages are handed out in a shuffled order."""
+def _paged_case(entries, heads, kv_heads, d, page, dtype, seed, window=0, lengths=None, counts=None, shuffle=True):
+    """Random q and a paged cache whose pages are handed out in a shuffled order (or, with
+    ``shuffle=False``, one after another, as a fresh cache hands them out)."""
     g = torch.Generator().manual_seed(seed)
     lengths = lengths or [int(torch.randint(1, 300, (1,), generator=g)) for _ in range(entries)]
     counts = counts or [1] * entries
     total_pages = sum((n + page - 1) // page for n in lengths) + 3
     order = torch.randperm(total_pages, generator=g).tolist()
+    if not shuffle:
+        order = list(range(total_pages))[::-1]
     width = max((n + page - 1) // page for n in lengths)
     table = torch.full((entries, width), -1, dtype=torch.int32)
     k_pool = torch.full((total_pages, page, kv_heads, d), float("nan"))
@@ -257,10 +260,12 @@ def test_attention_portions(heads, kv_heads, d, page, dtype, window):
 
 @pytest.mark.parametrize("page", [8, 16, 24, 64, 128, 256])
 @pytest.mark.parametrize("window", [0, 300])
-def test_attention_prefill_tensor_memory(page, window):
+@pytest.mark.parametrize("shuffle", [True, False])
+def test_attention_prefill_tensor_memory(page, window, shuffle):
     """The tcgen05 kernel (head size 128) on portions that span several tiles of 128 queries and
     of 128 keys: whole prompts, a portion at the end of a longer history, two tokens, one
-    token; pages from 8 to 256 keys (TMA boxes per page; 24 goes the cp.async way), pages a
+    token; pages from 8 to 256 keys (TMA boxes per page; 24 goes the cp.async way), handed out
+    in shuffled order or one after another (runs of pages are then fetched as one box), pages a
     window has passed given back and filled with NaN, and once with TMA switched off."""
     ops = _ops()
     heads, kv_heads, d = 6, 2, 128
@@ -268,7 +273,8 @@ def test_attention_prefill_tensor_memory(page, window):
     counts = [700, 200, 2, 1]
     entries = len(lengths)
     lengths, counts, table, k_pool, v_pool, keys, values, q = _paged_case(
-        entries, heads, kv_heads, d, page, torch.bfloat16, seed=page + window, lengths=lengths, counts=counts)
+        entries, heads, kv_heads, d, page, torch.bfloat16, seed=page + window, lengths=lengths, counts=counts,
+        shuffle=shuffle)
     scale = 1.0 / math.sqrt(d)
     want = _attention_reference(q, keys, values, lengths, counts, heads, kv_heads, scale, window)
     _give_back_passed_pages(table, k_pool, v_pool, lengths, counts, page, window)

@@ -109,6 +109,13 @@ __device__ __forceinline__ void tma_load_box(void* dst, const CUtensorMap* map, 
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(d0), "r"(kv_head), "r"(slot), "r"(page)
       : "memory");
 }
+// one box [128 rows of the pool, whatever pages they lie in][1 KV head][64 values]
+__device__ __forceinline__ void tma_load_run(void* dst, const CUtensorMap* map, uint64_t* bar, int d0, int kv_head, int row) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(d0), "r"(kv_head), "r"(row)
+      : "memory");
+}
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
   const int bytes = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
@@ -214,7 +221,9 @@ struct Barriers {
 
 template <bool TMA_KV>
 __global__ void __launch_bounds__(kThreads, 1)
-attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, const Params p) {
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                            const __grid_constant__ CUtensorMap k_run_map, const __grid_constant__ CUtensorMap v_run_map,
+                            const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* q_tile = smem;
@@ -492,12 +501,29 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         const int rows_per_box = min(p.page_size, kKeys);
         const int boxes = kKeys / rows_per_box;
         const int loader_warp = t >> 5;
-        auto issue_boxes = [&](int j, const CUtensorMap* map, uint8_t* tile, uint64_t* landed) {
+        auto issue_boxes = [&](int j, const CUtensorMap* map, const CUtensorMap* run_map, uint8_t* tile, uint64_t* landed) {
           const int key = (first_tile + j) * kKeys + lane * rows_per_box;
           int page = -1;
           // a box is fetched when it holds a visible key; the others stay as they are (keys) or are zeroed (values)
           if (lane < boxes && key + rows_per_box > first_key && key < end_key) page = table[key / p.page_size];
           const unsigned fetched = __ballot_sync(0xffffffffu, page >= 0);
+          // Pages that follow one another in memory (what a fresh request gets) are fetched as one
+          // run of 128 rows: two boxes instead of two per page.  Rows of the run past the pages
+          // wanted are rows of other pages or past the pool; they are masked (keys) or zeroed (values).
+          if (boxes > 1) {
+            const int page0 = __shfl_sync(0xffffffffu, page, 0);
+            const bool in_run = page < 0 || page == page0 + lane;
+            const unsigned wanted = fetched;
+            // the wanted boxes must be the first ones, one after another
+            if (page0 >= 0 && __all_sync(0xffffffffu, in_run) && (wanted & (wanted + 1u)) == 0u) {
+              if (lane == 0) {
+                mbar_expect_tx(landed, static_cast<uint32_t>(kKeys * 256));
+                tma_load_run(tile, run_map, landed, 0, kv_head, page0 * p.page_size);
+                tma_load_run(tile + kHalfBytes, run_map, landed, 64, kv_head, page0 * p.page_size);
+              }
+              return;
+            }
+          }
           if (lane == 0) mbar_expect_tx(landed, static_cast<uint32_t>(__popc(fetched) * rows_per_box * 256));
           __syncwarp();
           if (page >= 0) {
@@ -509,12 +535,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         auto issue_keys = [&](int j) {
           const int buffer = j & 1;
           if (j >= 2) mbar_wait(&bars->k_empty[buffer], static_cast<uint32_t>((j >> 1) - 1) & 1u, abort_flag, p.status);
-          if (!*abort_flag) issue_boxes(j, &k_map, k_tiles + buffer * kTileBytes, &bars->k_full[buffer]);
+          if (!*abort_flag) issue_boxes(j, &k_map, &k_run_map, k_tiles + buffer * kTileBytes, &bars->k_full[buffer]);
         };
         auto issue_values = [&](int j) {
           const int buffer = j & 1;
           if (j >= 2) mbar_wait(&bars->v_empty[buffer], static_cast<uint32_t>((j >> 1) - 1) & 1u, abort_flag, p.status);
-          if (!*abort_flag) issue_boxes(j, &v_map, v_tiles + buffer * kTileBytes, &bars->v_landed[buffer]);
+          if (!*abort_flag) issue_boxes(j, &v_map, &v_run_map, v_tiles + buffer * kTileBytes, &bars->v_landed[buffer]);
         };
         if (loader_warp == 0) {
           issue_keys(0);
@@ -671,16 +697,31 @@ bool tma_takes_page(int page_size) {
 
 // A cache pool [pages, page_size, kv_heads, 128] as TMA reads it: boxes of one page's rows
 // (at most 128) of one KV head and 64 values, 128-byte swizzle.  Maps are kept by pool.
-const CUtensorMap* pool_map(const void* pool, int pages, int page_size, int kv_heads) {
-  static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> kept;
+// `run`: the same pool as rows that follow one another whatever page they are in,
+// [pages * page_size, kv_heads, 128], in boxes of 128 rows.
+const CUtensorMap* pool_map(const void* pool, int pages, int page_size, int kv_heads, bool run) {
+  static std::map<std::tuple<const void*, int, int, int, bool>, CUtensorMap> kept;
   static std::mutex guard;
   std::lock_guard<std::mutex> lock(guard);
-  const auto key = std::make_tuple(pool, pages, page_size, kv_heads);
+  const auto key = std::make_tuple(pool, pages, page_size, kv_heads, run);
   auto found = kept.find(key);
   if (found != kept.end()) return &found->second;
   EncodeTiledFn encode = encode_tiled_fn();
   if (!encode || (reinterpret_cast<uintptr_t>(pool) & 15)) return nullptr;
   CUtensorMap map;
+  if (run) {
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(kv_heads),
+                          static_cast<cuuint64_t>(pages) * page_size};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(kD) * 2, static_cast<cuuint64_t>(kv_heads) * kD * 2};
+    cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(kKeys)};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(pool), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return nullptr;
+    if (kept.size() > 4096) kept.clear();
+    return &kept.emplace(key, map).first->second;
+  }
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(kv_heads), static_cast<cuuint64_t>(page_size),
                         static_cast<cuuint64_t>(pages)};
   cuuint64_t strides[3] = {static_cast<cuuint64_t>(kD) * 2, static_cast<cuuint64_t>(kv_heads) * kD * 2,
@@ -696,14 +737,16 @@ const CUtensorMap* pool_map(const void* pool, int pages, int page_size, int kv_h
 }
 
 template <bool TMA_KV>
-int launch_attention(const CUtensorMap& k_map, const CUtensorMap& v_map, const Params& p, dim3 grid, cudaStream_t stream) {
+int launch_attention(const CUtensorMap& k_map, const CUtensorMap& v_map, const CUtensorMap& k_run_map,
+                     const CUtensorMap& v_run_map, const Params& p, dim3 grid, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<TMA_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  return vipera_launch(attention_prefill_tc_kernel<TMA_KV>, grid, dim3(kThreads), kSmemBytes, stream, k_map, v_map, p);
+  return vipera_launch(attention_prefill_tc_kernel<TMA_KV>, grid, dim3(kThreads), kSmemBytes, stream, k_map, v_map, k_run_map,
+                       v_run_map, p);
 }
 
 }  // namespace
@@ -741,12 +784,14 @@ VIPERA_API int vipera_attention_prefill_tc(const void* q, void* out, const void*
   dim3 grid((num_tokens + kQ - 1) / kQ + num_entries, num_heads);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (tma_takes_page(page_size) && std::getenv("VIPERA_ATTENTION_NO_TMA") == nullptr) {
-    const CUtensorMap* k_map = pool_map(k_pool, num_pages, page_size, num_kv_heads);
-    const CUtensorMap* v_map = pool_map(v_pool, num_pages, page_size, num_kv_heads);
-    if (k_map && v_map) return launch_attention<true>(*k_map, *v_map, p, grid, s);
+    const CUtensorMap* k_map = pool_map(k_pool, num_pages, page_size, num_kv_heads, false);
+    const CUtensorMap* v_map = pool_map(v_pool, num_pages, page_size, num_kv_heads, false);
+    const CUtensorMap* k_run = pool_map(k_pool, num_pages, page_size, num_kv_heads, true);
+    const CUtensorMap* v_run = pool_map(v_pool, num_pages, page_size, num_kv_heads, true);
+    if (k_map && v_map && k_run && v_run) return launch_attention<true>(*k_map, *v_map, *k_run, *v_run, p, grid, s);
   }
   CUtensorMap none{};
-  return launch_attention<false>(none, none, p, grid, s);
+  return launch_attention<false>(none, none, none, none, p, grid, s);
 }
 
 VIPERA_API const char* vipera_attention_tc_status_text(int status) { return vipera_status_text(status); }

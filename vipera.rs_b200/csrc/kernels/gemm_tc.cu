@@ -419,7 +419,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 uint32_t packed[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
+#ifdef GEMM_DEBUG_NO_MATH
+                  packed[i] = pack_bf16x2(v[2 * i] + v[16 + 2 * i], v[2 * i + 1] + v[16 + 2 * i + 1]);
+#else
                   packed[i] = pack_bf16x2(silu_mul(v[2 * i], v[16 + 2 * i]), silu_mul(v[2 * i + 1], v[16 + 2 * i + 1]));
+#endif
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                   const int chunk = (q4 * 2 + h) ^ (lane & 7);
@@ -429,10 +433,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               }
               fence_async_shared();
               __syncwarp();
+#ifndef GEMM_DEBUG_NO_STORE
               if (lane == 0) {
                 tma_store_2d(&map_out, buffer, (ty * BN + c) >> 1, row0);
                 tma_store_commit();
               }
+#endif
               use ^= 1;
             }
           } else {

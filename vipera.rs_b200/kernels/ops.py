@@ -18,6 +18,7 @@ from ..errors import InternalError, InvalidArgumentError, UnsupportedError
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+EPI_DISCARD = 3  # tensor-core kernel only: the products without their ending, for timing
 ROPE_NONE, ROPE_NEOX, ROPE_INTERLEAVED = 0, 1, 2
 SAMPLE_OK, SAMPLE_NO_FINITE, SAMPLE_NO_MASS, SAMPLE_NEEDS_HOST = 0, 1, 2, 3
 
@@ -183,6 +184,9 @@ def _check_gemm_outputs(m, n, epilogue, bias, out, resid) -> None:
             raise UnsupportedError("gemm: SwiGLU needs an intermediate size that is a multiple of 16")
         if out is None or tuple(out.shape) != (m, n // 2):
             raise InvalidArgumentError(f"gemm: out must be [{m}, {n // 2}]")
+    elif epilogue == EPI_DISCARD:
+        if out is None:
+            raise InvalidArgumentError("gemm: the timing mode still takes an out tensor (it is left untouched)")
     else:
         raise InvalidArgumentError(f"gemm: unknown epilogue {epilogue}")
 
