@@ -555,3 +555,55 @@ def test_gemv_small_rope_cache():
         physical = int(table[int(token_entry[t]), p // page])
         assert _rel(k_pool[physical, p % page].cpu(), rotated[t, heads:heads + kv_heads]) < 5e-3
         assert _rel(v_pool[physical, p % page].cpu(), x[t, heads + kv_heads:]) < 5e-3
+
+
+@pytest.mark.parametrize("heads,kv_heads,d", [(3, 1, 128), (6, 2, 64), (12, 2, 128)])
+@pytest.mark.parametrize("style_name", ["neox", "none"])
+def test_gemm_tc_rope_cache(heads, kv_heads, d, style_name):
+    """The q/k/v product of many tokens on the tensor cores with its ending: bias, rotation of
+    the q and k pairs, q to its buffer, k and v to their pages; two entries, one of them at the
+    end of a longer history, pages in shuffled order."""
+    ops = _ops()
+    page, hidden = 16, 320
+    counts, firsts = [200, 131], [0, 77]
+    tokens = sum(counts)
+    style = ops.ROPE_NEOX if style_name == "neox" else ops.ROPE_NONE
+    torch.manual_seed(heads * 7 + d)
+    n = (heads + 2 * kv_heads) * d
+    assert ops.gemm_tc_rope_takes(tokens, n, hidden, d)
+    w = (torch.randn(n, hidden, device=DEV) * 0.1).bfloat16()
+    bias = torch.randn(n, device=DEV)
+    a = torch.randn(tokens, hidden, device=DEV).bfloat16()
+    positions = torch.cat([torch.arange(f, f + c) for f, c in zip(firsts, counts)]).to(torch.int32).to(DEV)
+    token_entry = torch.cat([torch.full((c,), e) for e, c in enumerate(counts)]).to(torch.int32).to(DEV)
+    width = 16
+    pages = torch.randperm(2 * width)[: 2 * width].view(2, width).to(torch.int32)
+    table = pages.to(DEV)
+    half = d // 2
+    inv = 1.0 / torch.pow(torch.tensor(10000.0), 2.0 * torch.arange(half, dtype=torch.float32) / d)
+    angle = torch.arange(256, dtype=torch.float32)[:, None] * inv[None, :]
+    cos, sin = torch.cos(angle).to(DEV), torch.sin(angle).to(DEV)
+    k_pool = torch.zeros(2 * width, page, kv_heads, d, device=DEV, dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    q_out = torch.full((tokens, heads * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.gemm_tc_rope(a, w, bias=bias, q_out=q_out, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
+                     positions=positions, cos=cos if style == ops.ROPE_NEOX else None,
+                     sin=sin if style == ops.ROPE_NEOX else None, style=style, k_pool=k_pool, v_pool=v_pool,
+                     token_entry=token_entry, block_table=table, page_size=page, write_cache=True)
+    torch.cuda.synchronize()
+    ops.check_kernel_status(DEV)
+    x = (a.double() @ w.double().T + bias.double()).view(tokens, heads + 2 * kv_heads, d).cpu()
+    if style == ops.ROPE_NEOX:
+        c = cos[positions.long()].cpu().double()[:, None, :]
+        s = sin[positions.long()].cpu().double()[:, None, :]
+        low, high = x[..., :half], x[..., half:]
+        rotated = torch.cat([low * c - high * s, low * s + high * c], dim=-1)
+    else:
+        rotated = x
+    assert _rel(q_out.float().cpu().view(tokens, heads, d), rotated[:, :heads]) < 8e-3
+    k_rows = torch.stack([k_pool[int(pages[int(token_entry[t]), int(positions[t]) // page]), int(positions[t]) % page].float().cpu()
+                          for t in range(tokens)])
+    v_rows = torch.stack([v_pool[int(pages[int(token_entry[t]), int(positions[t]) // page]), int(positions[t]) % page].float().cpu()
+                          for t in range(tokens)])
+    assert _rel(k_rows, rotated[:, heads:heads + kv_heads]) < 8e-3
+    assert _rel(v_rows, x[:, heads + kv_heads:]) < 8e-3

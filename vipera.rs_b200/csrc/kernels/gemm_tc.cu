@@ -29,7 +29,8 @@
 #include "common.cuh"
 
 // EPI_DISCARD drops the result: it exists to time the products without their ending.
-enum GemmEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_DISCARD = 3 };
+enum GemmEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_DISCARD = 3, EPI_ROPE_CACHE = 4 };
+enum { GEMM_ROPE_NONE = 0, GEMM_ROPE_NEOX = 1 };
 enum { GEMM_TC_WAIT_EXPIRED = 1 };
 
 constexpr int kBlockK = 64;        // bf16 elements per k-block: one 128-byte swizzle row
@@ -50,6 +51,18 @@ struct GemmParams {
   int tma_ending;    // 1: the ending goes through shared memory and TMA stores (map_out)
   float* scratch;    // split partials: [item][BN][128] floats
   int* status;       // device word: 0, or an error code
+  // EPI_ROPE_CACHE: the columns are the q, k and v heads of a step's tokens; the ending adds the
+  // bias, turns the rotary pairs of q and k, and writes q to q_out and k and v into their pages
+  int num_heads, num_kv_heads, head_dim, rope_style, write_cache;
+  const int* positions;      // [T]
+  const int* token_entry;    // [T] row of the block table
+  const int* block_table;    // [entries, table_width]
+  int table_width, page_size;
+  const float* cos_table;    // [positions, d / 2]
+  const float* sin_table;
+  __nv_bfloat16* q_out;      // [T, heads * d]
+  __nv_bfloat16* k_pool;     // [pages, page_size, kv_heads, d]
+  __nv_bfloat16* v_pool;
 };
 
 // ---------------------------------------------------------------------------------------
@@ -157,7 +170,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-__device__ __forceinline__ float silu_mul(float gate, float up) { return up * (gate / (1.0f + __expf(-gate))); }
+// up * silu(gate); the quotient with the hardware's reciprocal (the result is rounded to
+// bfloat16 by every caller on the tensor-core path, which hides the last bits)
+__device__ __forceinline__ float silu_mul(float gate, float up) { return up * __fdividef(gate, 1.0f + __expf(-gate)); }
 
 #ifndef VIPERA_SMALL_BUDGET
 #define VIPERA_SMALL_BUDGET 100
@@ -393,7 +408,75 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const int row = tx * kTileX + row_in_tile;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(acc * BN);
       if (p.splits == 1) {
-        if (!SWAP && BN >= 128 && p.tma_ending) {
+        if (!SWAP && BN >= 128 && p.epilogue == EPI_ROPE_CACHE) {
+          // The q/k/v product's ending: thread = token; a head's d columns are read as pairs of
+          // 32-column chunks (i, i + d/2), the halves of the rotary pairs.
+          const int d = p.head_dim, half = d >> 1;
+          const int t = row;
+          const bool live = t < p.tokens;
+          const int position = live ? p.positions[t] : 0;
+          const float* cos_row = p.cos_table + static_cast<size_t>(position) * half;
+          const float* sin_row = p.sin_table + static_cast<size_t>(position) * half;
+#pragma unroll 1
+          for (int hc = 0; hc < BN; hc += d) {
+            const int n0 = ty * BN + hc;
+            if (n0 >= p.features) break;
+            const int head = n0 / d;
+            const bool is_q = head < p.num_heads;
+            const bool is_v = head >= p.num_heads + p.num_kv_heads;
+            __nv_bfloat16* dst = nullptr;
+            if (live) {
+              if (is_q) {
+                dst = p.q_out + (static_cast<size_t>(t) * p.num_heads + head) * d;
+              } else if (p.write_cache) {
+                const int page = p.block_table[static_cast<size_t>(p.token_entry[t]) * p.table_width + position / p.page_size];
+                if (page >= 0) {
+                  const int kv_head = is_v ? head - p.num_heads - p.num_kv_heads : head - p.num_heads;
+                  dst = (is_v ? p.v_pool : p.k_pool) +
+                        ((static_cast<size_t>(page) * p.page_size + position % p.page_size) * p.num_kv_heads + kv_head) * d;
+                }
+              }
+            }
+#pragma unroll 1
+            for (int i0 = 0; i0 < half; i0 += 32) {
+              float lo[32], hi[32];
+              tmem_load_32(taddr + hc + i0, lo);
+              tmem_load_32(taddr + hc + half + i0, hi);
+              if (dst == nullptr) continue;
+              if (p.bias) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  lo[i] += p.bias[n0 + i0 + i];
+                  hi[i] += p.bias[n0 + half + i0 + i];
+                }
+              }
+              if (!is_v && p.rope_style == GEMM_ROPE_NEOX) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                  const float4 c4 = *reinterpret_cast<const float4*>(cos_row + i0 + i);
+                  const float4 s4 = *reinterpret_cast<const float4*>(sin_row + i0 + i);
+                  const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                  for (int u = 0; u < 4; ++u) {
+                    const float a = lo[i + u], b = hi[i + u];
+                    lo[i + u] = a * cs[u] - b * sn[u];
+                    hi[i + u] = a * sn[u] + b * cs[u];
+                  }
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint4 packed_lo, packed_hi;
+                packed_lo.x = pack_bf16x2(lo[i], lo[i + 1]); packed_lo.y = pack_bf16x2(lo[i + 2], lo[i + 3]);
+                packed_lo.z = pack_bf16x2(lo[i + 4], lo[i + 5]); packed_lo.w = pack_bf16x2(lo[i + 6], lo[i + 7]);
+                packed_hi.x = pack_bf16x2(hi[i], hi[i + 1]); packed_hi.y = pack_bf16x2(hi[i + 2], hi[i + 3]);
+                packed_hi.z = pack_bf16x2(hi[i + 4], hi[i + 5]); packed_hi.w = pack_bf16x2(hi[i + 6], hi[i + 7]);
+                *reinterpret_cast<uint4*>(dst + i0 + i) = packed_lo;
+                *reinterpret_cast<uint4*>(dst + half + i0 + i) = packed_hi;
+              }
+            }
+          }
+        } else if (!SWAP && BN >= 128 && p.tma_ending) {
           // The ending through shared memory: each warp lays 32 rows x 128 bytes into a
           // swizzled buffer (no bank conflicts), and one lane hands the box to TMA, which
           // writes whole lines, clips at the matrix's edges and, for the residual stream,
@@ -666,7 +749,7 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
     plan.bn = 128;
     for (int bn : candidates) {
       if (bn > 128 && N < bn) continue;
-      if (bn == 192 && epilogue == EPI_SWIGLU) continue;  // the SwiGLU ending works in 128-column steps
+      if (bn == 192 && (epilogue == EPI_SWIGLU || epilogue == EPI_ROPE_CACHE)) continue;  // these endings work in steps of 128 (or of a head)
       const long items = static_cast<long>(plan.tiles_x) * ((N + bn - 1) / bn);
       const long waves = (items + sms - 1) / sms;
       double efficiency = static_cast<double>(plan.tiles_x) * N / (static_cast<double>(waves) * sms * bn);
@@ -720,14 +803,16 @@ static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, co
 // A is [T, K] bfloat16, W is [N, K] bfloat16, both row-major and contiguous with K a
 // multiple of 8 (TMA needs 16-byte row strides).  `status` is a device word that must be 0
 // before the launch; it is non-zero afterwards when a bounded wait inside the kernel ran out.
-VIPERA_API int vipera_gemm_tc(const void* A, const void* W, int T, int N, int K, int epilogue, const float* bias,
-                              void* out, int out_dtype, float* resid, float* scratch, size_t scratch_bytes,
-                              int* status, void* stream) {
+// `rope`: for EPI_ROPE_CACHE, the fields of that ending (the others are filled in here).
+static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilogue, const float* bias, void* out,
+                    int out_dtype, float* resid, float* scratch, size_t scratch_bytes, int* status, void* stream,
+                    const GemmParams* rope) {
   if (T <= 0) return VIPERA_OK;
   if (N <= 0 || K <= 0 || (K % 8) != 0) return VIPERA_BAD_SHAPE;
   if (epilogue == EPI_SWIGLU && (N % 32) != 0) return VIPERA_BAD_SHAPE;
   if (out_dtype != VIPERA_F32 && out_dtype != VIPERA_BF16) return VIPERA_BAD_DTYPE;
-  if ((epilogue == EPI_RESIDUAL && !resid) || (epilogue != EPI_RESIDUAL && !out) || !status) return VIPERA_BAD_ARGUMENT;
+  if ((epilogue == EPI_RESIDUAL && !resid) || (epilogue != EPI_RESIDUAL && epilogue != EPI_ROPE_CACHE && !out) || !status)
+    return VIPERA_BAD_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return VIPERA_BAD_ARGUMENT;
   const int sms = sm_count();
   const GemmPlan plan = make_plan(T, N, K, sms, epilogue);
@@ -744,6 +829,7 @@ VIPERA_API int vipera_gemm_tc(const void* A, const void* W, int T, int N, int K,
     if ((r = make_map(&map_y, W, N, K, plan.bn)) != VIPERA_OK) return r;
   }
   GemmParams p{};
+  if (rope) p = *rope;
   p.tokens = T;
   p.features = N;
   p.num_k_blocks = plan.num_k_blocks;
@@ -791,6 +877,67 @@ VIPERA_API int vipera_gemm_tc(const void* A, const void* W, int T, int N, int K,
     case 128: return launch_variant<128, true>(map_x, map_y, map_out, p, grid, s);
     default: return launch_variant<256, true>(map_x, map_y, map_out, p, grid, s);
   }
+}
+
+VIPERA_API int vipera_gemm_tc(const void* A, const void* W, int T, int N, int K, int epilogue, const float* bias,
+                              void* out, int out_dtype, float* resid, float* scratch, size_t scratch_bytes,
+                              int* status, void* stream) {
+  if (epilogue == EPI_ROPE_CACHE) return VIPERA_BAD_ARGUMENT;  // that ending has an entry point of its own
+  return run_gemm(A, W, T, N, K, epilogue, bias, out, out_dtype, resid, scratch, scratch_bytes, status, stream, nullptr);
+}
+
+// What the q/k/v ending needs beside the product itself (mirrored by the caller).
+struct GemmRope {
+  const int* positions;
+  const int* token_entry;
+  const int* block_table;
+  const float* cos_table;
+  const float* sin_table;
+  void* q_out;
+  void* k_pool;
+  void* v_pool;
+  int table_width, page_size, num_heads, num_kv_heads, head_dim, rope_style, write_cache;
+};
+
+VIPERA_API int vipera_gemm_tc_rope_size() { return static_cast<int>(sizeof(GemmRope)); }
+
+// Whether vipera_gemm_tc_rope takes these sizes: enough tokens for tiles with the tokens on
+// the 128-row side, heads of 64 or 128 values, whole heads in every 128-column step.
+VIPERA_API int vipera_gemm_tc_rope_takes(int T, int N, int K, int head_dim) {
+  if (T < 128 + 64 || K <= 0 || K % 8 || N <= 0) return 0;
+  if (head_dim != 64 && head_dim != 128) return 0;
+  return N % head_dim == 0 ? 1 : 0;
+}
+
+// The q/k/v product of a step with its ending: out = A . W^T + bias, rotary pairs of the q and k
+// heads turned by the tokens' positions, q written to q_out [T, heads * d] and k, v into their
+// cache pages (rope_style 0: no rotation).  N = (heads + 2 * kv_heads) * d.
+VIPERA_API int vipera_gemm_tc_rope(const void* A, const void* W, int T, int N, int K, const float* bias,
+                                   const GemmRope* rope, int* status, void* stream) {
+  if (!rope || !vipera_gemm_tc_rope_takes(T, N, K, rope->head_dim)) return VIPERA_BAD_SHAPE;
+  if (N != (rope->num_heads + 2 * rope->num_kv_heads) * rope->head_dim) return VIPERA_BAD_SHAPE;
+  if (!rope->positions || !rope->q_out) return VIPERA_BAD_ARGUMENT;
+  if (rope->rope_style == GEMM_ROPE_NEOX && (!rope->cos_table || !rope->sin_table)) return VIPERA_BAD_ARGUMENT;
+  if (rope->rope_style != GEMM_ROPE_NEOX && rope->rope_style != GEMM_ROPE_NONE) return VIPERA_BAD_ARGUMENT;
+  if (rope->write_cache && (!rope->k_pool || !rope->v_pool || !rope->token_entry || !rope->block_table || rope->page_size <= 0))
+    return VIPERA_BAD_ARGUMENT;
+  GemmParams p{};
+  p.positions = rope->positions;
+  p.token_entry = rope->token_entry;
+  p.block_table = rope->block_table;
+  p.cos_table = rope->cos_table;
+  p.sin_table = rope->sin_table;
+  p.q_out = static_cast<__nv_bfloat16*>(rope->q_out);
+  p.k_pool = static_cast<__nv_bfloat16*>(rope->k_pool);
+  p.v_pool = static_cast<__nv_bfloat16*>(rope->v_pool);
+  p.table_width = rope->table_width;
+  p.page_size = rope->page_size;
+  p.num_heads = rope->num_heads;
+  p.num_kv_heads = rope->num_kv_heads;
+  p.head_dim = rope->head_dim;
+  p.rope_style = rope->rope_style;
+  p.write_cache = rope->write_cache;
+  return run_gemm(A, W, T, N, K, EPI_ROPE_CACHE, bias, nullptr, VIPERA_BF16, nullptr, nullptr, 0, status, stream, &p);
 }
 
 VIPERA_API const char* vipera_gemm_tc_status_text(int status) { return vipera_status_text(status); }

@@ -307,6 +307,59 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE,
               state["status"].data_ptr(), _stream()), "gemm_tc", kernels=2 if scratch_bytes else 1)
 
 
+class _GemmRope(ctypes.Structure):
+    _fields_ = [
+        ("positions", _c_void), ("token_entry", _c_void), ("block_table", _c_void), ("cos_table", _c_void),
+        ("sin_table", _c_void), ("q_out", _c_void), ("k_pool", _c_void), ("v_pool", _c_void),
+        ("table_width", _c_int), ("page_size", _c_int), ("num_heads", _c_int), ("num_kv_heads", _c_int),
+        ("head_dim", _c_int), ("rope_style", _c_int), ("write_cache", _c_int),
+    ]
+
+
+def gemm_tc_rope_takes(tokens: int, n: int, k: int, head_dim: int) -> bool:
+    """Whether the tensor-core product can end with rotation and cache write for these sizes."""
+    fn = getattr(load_kernel_library("gemm_tc"), "vipera_gemm_tc_rope_takes")
+    fn.argtypes, fn.restype = [_c_int] * 4, _c_int
+    return bool(fn(int(tokens), int(n), int(k), int(head_dim)))
+
+
+def gemm_tc_rope(a: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+                 num_heads: int, num_kv_heads: int, head_dim: int, positions: torch.Tensor,
+                 cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], style: int, k_pool: torch.Tensor,
+                 v_pool: torch.Tensor, token_entry: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                 write_cache: bool) -> None:
+    """The q/k/v product of a step on the tensor cores with bias, rotation of q and k and the
+    write of keys and values into their pages as its ending (bfloat16, at least 192 tokens)."""
+    size = _function("gemm_tc", "vipera_gemm_tc_rope_size", [])()
+    if size != ctypes.sizeof(_GemmRope):
+        raise InternalError("the q/k/v ending's structure differs from its Python mirror")
+    fn = _function("gemm_tc", "vipera_gemm_tc_rope",
+                   [_c_void, _c_void, _c_int, _c_int, _c_int, _c_void, ctypes.POINTER(_GemmRope), _c_void, _c_void])
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or n != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise InvalidArgumentError("gemm_tc_rope: the matrix must be [(heads + 2 kv_heads) * d, K]")
+    if tuple(q_out.shape) != (m, num_heads * head_dim):
+        raise InvalidArgumentError("gemm_tc_rope: q_out must be [tokens, heads * d]")
+    if style not in (ROPE_NONE, ROPE_NEOX):
+        raise UnsupportedError("gemm_tc_rope: rotary styles none and neox")
+    r = _GemmRope()
+    r.positions = _gpu(positions, "positions", torch.int32)
+    r.token_entry = _gpu(token_entry, "token_entry", torch.int32)
+    r.block_table = _gpu(block_table, "block_table", torch.int32)
+    r.cos_table = _opt(cos, "cos", torch.float32)
+    r.sin_table = _opt(sin, "sin", torch.float32)
+    r.q_out = _gpu(q_out, "q_out", torch.bfloat16)
+    r.k_pool = _gpu(k_pool, "k_pool", torch.bfloat16)
+    r.v_pool = _gpu(v_pool, "v_pool", torch.bfloat16)
+    r.table_width, r.page_size = int(block_table.shape[1]), int(page_size)
+    r.num_heads, r.num_kv_heads, r.head_dim = int(num_heads), int(num_kv_heads), int(head_dim)
+    r.rope_style, r.write_cache = int(style), 1 if write_cache else 0
+    state = _tc_buffers(a.device, 0)
+    _check(fn(_gpu(a, "a", torch.bfloat16), _gpu(w, "w", torch.bfloat16), m, n, k, _opt(bias, "bias", torch.float32),
+              ctypes.byref(r), state["status"].data_ptr(), _stream()), "gemm_tc_rope")
+
+
 def check_kernel_status(device) -> None:
     """After a synchronisation: raise if a tensor-core kernel's bounded wait ran out."""
     state = _tc_state.get(str(device))

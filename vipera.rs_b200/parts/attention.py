@@ -104,6 +104,20 @@ class GQAttention(Mixer):
             self._attend(ctx, q, mixed, cache, table)
             self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
             return
+        if (ctx.dtype == torch.bfloat16 and style in (ops.ROPE_NONE, ops.ROPE_NEOX)
+                and self.qkv._tensor_core is not None
+                and ops.gemm_tc_rope_takes(count, self.qkv.out_features, self.qkv.in_features, d)):
+            # many tokens: the tensor-core product ends with bias, rotation and cache write
+            cos, sin = self.position.tables()
+            a = h.tensor() if isinstance(h, NormedInput) else h
+            ops.gemm_tc_rope(a, self.qkv.weight, bias=self.qkv.bias, q_out=q, num_heads=heads, num_kv_heads=kv_heads,
+                             head_dim=d, positions=ctx.positions, cos=cos, sin=sin, style=style, k_pool=cache.k,
+                             v_pool=cache.v, token_entry=ctx.token_entry, block_table=table,
+                             page_size=cache.page_size, write_cache=writes_cache)
+            mixed = ws.get("attention.out", (count, heads * d), ctx.dtype)
+            self._attend(ctx, q, mixed, cache, table)
+            self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
+            return
         qkv = ws.get("attention.qkv", (count, (heads + 2 * kv_heads) * d), torch.float32)
         self.qkv(ctx, h, epilogue=ops.EPI_STORE, out=qkv)
         if style is None:
