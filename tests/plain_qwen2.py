@@ -6,9 +6,16 @@ itself (the latter with the ``safetensors`` library) and works on host tensors.
 
 It rests on the reference's formulas, each cited by file:line below.  The
 reference's own model code is Rust and reads GGUF files only; neither a Rust
-toolchain nor a GGUF model exists on the machines these tests run on, so this
-file cannot be compared with a run of the reference and no golden outputs of it
-are committed: every function here is a restatement of the cited lines.
+toolchain nor a GGUF model exists on the machines these tests run on, so the
+whole model cannot be compared with a run of the reference.  What can be run is
+the reference's CUDA port of the small operations of a layer
+(crates/vipera-backend-gpu/src/layer.cu, "a straight port of the CPU function of
+the same name"): ``tests/golden/make_reference_ops.py`` ran those kernels once on
+seeded inputs, ``tests/golden/reference_ops.npz`` holds what they computed, and
+``tests/test_golden.py`` holds ``rms_norm``, ``rope_angles`` + ``rope_neox``,
+``attention`` and ``silu`` of this file to it (agreement to about 5e-7 of the
+largest value).  Embedding, the products and their order are restatements of the
+cited lines.
 
 ``dtype`` chooses the arithmetic (float64 by default, so that this side of a
 comparison adds no rounding of its own).  Rotation angles are always computed in
