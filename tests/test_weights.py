@@ -98,6 +98,46 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     assert error.exit_code == 2
 
 
+def test_the_references_tensor_names_are_accepted(tmp_path):
+    """A file that names its tensors as the reference's files do (token_embd.weight,
+    blk.3.attn_q.bias, ...) loads like one with the usual names; a name that is neither still
+    shows up as unexpected."""
+    from vipera_rs_b200.weights import AliasedSource
+
+    folder = str(tmp_path / "m")
+    write_random_model(folder, helpers.TINY_B, seed=5, dtype="float32")
+    source = SafetensorsSource(folder)
+    renames = {"model.embed_tokens.weight": "token_embd.weight", "model.norm.weight": "output_norm.weight",
+               "lm_head.weight": "output.weight"}
+    layer = {"input_layernorm.weight": "attn_norm.weight", "self_attn.q_proj.weight": "attn_q.weight",
+             "self_attn.q_proj.bias": "attn_q.bias", "self_attn.k_proj.weight": "attn_k.weight",
+             "self_attn.k_proj.bias": "attn_k.bias", "self_attn.v_proj.weight": "attn_v.weight",
+             "self_attn.v_proj.bias": "attn_v.bias", "self_attn.o_proj.weight": "attn_output.weight",
+             "post_attention_layernorm.weight": "ffn_norm.weight", "mlp.gate_proj.weight": "ffn_gate.weight",
+             "mlp.up_proj.weight": "ffn_up.weight", "mlp.down_proj.weight": "ffn_down.weight"}
+    tensors = {}
+    for name in source.names():
+        new = renames.get(name)
+        if new is None:
+            _, _, index, tail = name.split(".", 3)
+            new = f"blk.{index}.{layer[tail]}"
+        tensors[new] = source.get(name)
+    tensors["blk.0.attn_sinks"] = torch.zeros(3)
+    renamed = str(tmp_path / "renamed")
+    os.makedirs(renamed)
+    with open(os.path.join(folder, "config.json")) as src, open(os.path.join(renamed, "config.json"), "w") as dst:
+        dst.write(src.read())
+    write_safetensors(os.path.join(renamed, "model.safetensors"), tensors.items())
+    arch, config = load_config(renamed)
+    schema = model_schema(arch.model_spec(config))
+    seen = AliasedSource(SafetensorsSource(renamed), arch.tensor_alias)
+    with pytest.raises(errors.UnsupportedError) as info:
+        check_source(schema, seen)
+    assert info.value.missing == [] and info.value.wrong_shape == [] and info.value.unexpected == ["blk.0.attn_sinks"]
+    assert torch.equal(seen.get("model.layers.2.self_attn.k_proj.bias"), source.get("model.layers.2.self_attn.k_proj.bias"))
+    assert torch.equal(seen.get("lm_head.weight"), source.get("lm_head.weight"))
+
+
 def test_run_dtypes():
     assert to_run_dtype(torch.zeros(2, dtype=torch.bfloat16), torch.bfloat16).dtype == torch.bfloat16
     assert to_run_dtype(torch.zeros(2, dtype=torch.float16), torch.bfloat16).dtype == torch.bfloat16

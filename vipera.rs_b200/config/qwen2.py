@@ -253,4 +253,37 @@ def qwen2_model_spec(config: Qwen2Config) -> ModelSpec:
     return spec
 
 
-register_architecture("Qwen2ForCausalLM", Qwen2Config.from_dict, qwen2_model_spec)
+# The names the reference's files use for the same tensors (GGUF names; same memory layout:
+# a GGUF [cols, rows] matrix is a row-major [out, in] matrix).
+_GGUF_GLOBAL = {
+    "token_embd.weight": "model.embed_tokens.weight",
+    "output_norm.weight": "model.norm.weight",
+    "output.weight": "lm_head.weight",
+}
+_GGUF_LAYER = {
+    "attn_norm.weight": "input_layernorm.weight",
+    "attn_q.weight": "self_attn.q_proj.weight", "attn_q.bias": "self_attn.q_proj.bias",
+    "attn_k.weight": "self_attn.k_proj.weight", "attn_k.bias": "self_attn.k_proj.bias",
+    "attn_v.weight": "self_attn.v_proj.weight", "attn_v.bias": "self_attn.v_proj.bias",
+    "attn_output.weight": "self_attn.o_proj.weight",
+    "ffn_norm.weight": "post_attention_layernorm.weight",
+    "ffn_gate.weight": "mlp.gate_proj.weight",
+    "ffn_up.weight": "mlp.up_proj.weight",
+    "ffn_down.weight": "mlp.down_proj.weight",
+}
+
+
+def qwen2_tensor_alias(name: str):
+    """``blk.{i}.attn_q.weight`` -> ``model.layers.{i}.self_attn.q_proj.weight`` and so on."""
+    if name in _GGUF_GLOBAL:
+        return _GGUF_GLOBAL[name]
+    if name.startswith("blk."):
+        _, _, rest = name.partition(".")
+        index, _, tail = rest.partition(".")
+        if index.isdigit() and tail in _GGUF_LAYER:
+            return f"model.layers.{int(index)}.{_GGUF_LAYER[tail]}"
+    return None
+
+
+register_architecture("Qwen2ForCausalLM", Qwen2Config.from_dict, qwen2_model_spec,
+                      tensor_alias=qwen2_tensor_alias)

@@ -10,7 +10,7 @@ position encodings and block arrangements alike.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Generic, List, TypeVar
+from typing import Optional, Any, Callable, Dict, Generic, List, TypeVar
 
 from ..errors import UnsupportedError
 
@@ -60,6 +60,9 @@ class Architecture:
     name: str
     config_from_dict: Callable[[Dict[str, Any]], Any]
     model_spec: Callable[[Any], "ModelSpec"]  # noqa: F821
+    # Other names a weight file may use: ``tensor_alias(name_in_file)`` returns the name the
+    # parts ask for, or None where the name is not an alias.
+    tensor_alias: Optional[Callable[[str], Optional[str]]] = None
 
 
 ARCHITECTURES: Registry[Architecture] = Registry("architecture")
@@ -70,7 +73,7 @@ POSITION_ENCODINGS: Registry[type] = Registry("position encoding")
 BLOCKS: Registry[type] = Registry("block arrangement")
 
 
-def register_architecture(name, config_from_dict, model_spec, *, replace=False) -> Architecture:
+def register_architecture(name, config_from_dict, model_spec, *, tensor_alias=None, replace=False) -> Architecture:
     return ARCHITECTURES.register(
-        name, Architecture(name, config_from_dict, model_spec), replace=replace
+        name, Architecture(name, config_from_dict, model_spec, tensor_alias), replace=replace
     )

@@ -11,7 +11,7 @@ from ..build import build_kernels
 from ..config import architecture_of, load_config, read_config_json
 from ..errors import InvalidArgumentError
 from ..parts.model import DecoderModel, model_schema
-from ..weights import RandomSource, SafetensorsSource, write_model_folder
+from ..weights import AliasedSource, RandomSource, SafetensorsSource, write_model_folder
 
 
 def _kernel_families(model) -> list:
@@ -44,7 +44,10 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0") -> DecoderMode
     and compile the kernels it needs."""
     arch, config = load_config(model_dir)
     spec = arch.model_spec(config)
-    model = DecoderModel(spec, SafetensorsSource(model_dir), parse_dtype(dtype), device)
+    source = SafetensorsSource(model_dir)
+    if arch.tensor_alias is not None:
+        source = AliasedSource(source, arch.tensor_alias)
+    model = DecoderModel(spec, source, parse_dtype(dtype), device)
     model.config = config
     build_kernels(_kernel_families(model))
     return model

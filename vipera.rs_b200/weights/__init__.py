@@ -1,5 +1,6 @@
 """Weights: the safetensors container, sources of tensors, the schema check."""
 from .loader import (
+    AliasedSource,
     INIT,
     RandomSource,
     SafetensorsSource,
@@ -13,6 +14,6 @@ from .loader import (
 from .safetensors_io import SafetensorsFile, write_safetensors
 
 __all__ = [
-    "INIT", "RandomSource", "SafetensorsSource", "Schema", "TensorSpec", "WeightSource",
+    "AliasedSource", "INIT", "RandomSource", "SafetensorsSource", "Schema", "TensorSpec", "WeightSource",
     "check_source", "to_run_dtype", "write_model_folder", "SafetensorsFile", "write_safetensors",
 ]

@@ -104,6 +104,37 @@ class SafetensorsSource(WeightSource):
         return self.model_dir
 
 
+class AliasedSource(WeightSource):
+    """A source seen under the names the parts ask for: a tensor the file stores under another
+    name the architecture knows (``alias(name_in_file)`` gives the name asked for) appears under
+    that name.  A name that is not an alias stays as it is, so that the check still reports it
+    when nothing asks for it."""
+
+    def __init__(self, source: WeightSource, alias):
+        self._source = source
+        self._stored: Dict[str, str] = {}
+        for name in source.names():
+            wanted = alias(name) or name
+            if wanted in self._stored:
+                raise UnsupportedError(f"{source.describe()} holds both {self._stored[wanted]!r} and {name!r} for {wanted!r}")
+            self._stored[wanted] = name
+
+    def names(self) -> List[str]:
+        return list(self._stored)
+
+    def shape(self, name: str) -> Tuple[int, ...]:
+        return self._source.shape(self._stored[name])
+
+    def stored_dtype(self, name: str) -> torch.dtype:
+        return self._source.stored_dtype(self._stored[name])
+
+    def get(self, name: str) -> torch.Tensor:
+        return self._source.get(self._stored[name])
+
+    def describe(self) -> str:
+        return self._source.describe()
+
+
 def _fnv1a64(text: str) -> int:
     value = 0xCBF29CE484222325
     for byte in text.encode("utf-8"):
