@@ -12,8 +12,8 @@ from vipera_rs_b200 import errors
 from vipera_rs_b200.build import runtime_module
 
 
-def manager(groups, slots=4):
-    return runtime_module().CacheManager(groups, slots)
+def manager(groups, slots=4, reuse=False):
+    return runtime_module().CacheManager(groups, slots, reuse)
 
 
 def test_pages_are_handed_out_lowest_first_and_counted():
@@ -21,7 +21,7 @@ def test_pages_are_handed_out_lowest_first_and_counted():
     assert cache.open(7) == 0
     cache.reserve(7, 33)                      # 33 tokens need 3 pages of 16
     assert cache.table(7, 0).tolist() == [0, 1, 2]
-    assert cache.stats(0) == {"total_pages": 8, "free_pages": 5, "used_pages": 3}
+    assert cache.stats(0) == {"total_pages": 8, "free_pages": 5, "used_pages": 3, "kept_pages": 0}
     cache.reserve(7, 48)                      # still 3 pages
     assert cache.table(7, 0).tolist() == [0, 1, 2]
     cache.commit(7, 48)
@@ -150,3 +150,114 @@ def test_random_orders_never_lose_or_duplicate_a_page(seed):
             cache.close(request)                   # a second release is refused, not repeated
     assert cache.audit() == ""
     assert all(cache.stats(g)["free_pages"] == groups[g][1] for g in range(len(groups)))
+
+
+def test_published_pages_are_shared_not_copied_and_given_up_when_pages_are_needed():
+    """The reference parks a finished sequence's blocks, copies a matching prefix and evicts
+    parked blocks oldest first when the free list runs dry (crates/vipera-runtime/src/kv.rs:
+    427-514, tests :730-901).  Here the pages themselves are shared."""
+    cache = manager([(4, 8, 0)], slots=3, reuse=True)
+    assert cache.reuse
+    prompt = list(range(100, 114))                       # 14 tokens: three full pages and a rest
+    cache.open(1)
+    assert cache.match(1, prompt) == 0                   # nothing is known yet
+    cache.reserve(1, 14)
+    cache.commit(1, 14)
+    cache.publish(1, prompt, 14)
+    assert cache.table(1, 0).tolist() == [0, 1, 2, 3]
+    cache.open(2)                                        # same beginning, then something else
+    other = prompt[:9] + [7, 7, 7]
+    assert cache.match(2, other) == 8                    # two full pages agree
+    assert cache.table(2, 0).tolist() == [0, 1] and cache.computed(2) == 8
+    cache.reserve(2, 12)
+    assert cache.table(2, 0).tolist() == [0, 1, 4]       # its own page from the free stack
+    assert cache.audit() == ""
+    cache.close(1)
+    assert cache.stats(0) == {"total_pages": 8, "free_pages": 4, "used_pages": 4, "kept_pages": 1}
+    cache.open(3)                                        # the whole prompt again: one token must stay to compute
+    assert cache.match(3, prompt[:13]) == 12
+    cache.close(3)
+    cache.close(2)
+    assert cache.stats(0)["kept_pages"] == 3 and cache.stats(0)["free_pages"] == 5
+    # a request that needs every page gets them: the published ones are given up, deepest first
+    cache.open(4)
+    assert cache.fits(4, 32) and not cache.fits(4, 33)
+    cache.reserve(4, 30)
+    assert cache.stats(0)["kept_pages"] == 0 and cache.audit() == ""
+    cache.close(4)
+    cache.open(5)
+    assert cache.match(5, prompt) == 0                   # given up means forgotten
+    cache.close(5)
+    assert cache.stats(0)["free_pages"] == 8 and cache.audit() == ""
+
+
+def test_no_sharing_with_windows_or_unequal_pages():
+    assert not manager([(16, 8, 0), (16, 8, 24)], reuse=True).reuse
+    assert not manager([(16, 8, 0), (8, 8, 0)], reuse=True).reuse
+    assert manager([(16, 8, 0), (16, 4, 0)], reuse=True).reuse
+    assert not manager([(16, 8, 0)], reuse=False).reuse
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_with_shared_prefixes(seed):
+    """Requests drawn from a few prompts with common beginnings come, grow, publish and go in
+    random order, in a pool so small that published pages are given up all the time.  After
+    every action the books are sound, and a page a request was given by a match holds what
+    that request's own tokens say (the test keeps, for every page, the tokens whose keys were
+    written to it)."""
+    rng = random.Random(seed)
+    page = 4
+    cache = manager([(page, 14, 0), (page, 14, 0)], slots=4, reuse=True)
+    stems = [[rng.randrange(50) for _ in range(40)] for _ in range(3)]
+    written = {}                                         # physical page -> (first position, tokens)
+    live = {}
+    next_id = 0
+
+    def check_tables(request):
+        tokens, done = live[request]
+        table = cache.table(request, 0)
+        assert len(cache.table(request, 1)) == len(table)
+        for index in range(done // page):
+            first, content = written[int(table[index])]
+            assert first == index * page and content == tokens[index * page:(index + 1) * page], (request, index)
+
+    for _ in range(500):
+        action = rng.random()
+        if action < 0.3 and len(live) < 4:
+            stem = rng.choice(stems)
+            cut = rng.randint(2, 40)
+            tokens = stem[:cut] + [rng.randrange(50) for _ in range(rng.randint(0, 12))]
+            cache.open(next_id)
+            reused = cache.match(next_id, tokens)
+            assert reused % page == 0 and reused < len(tokens) and reused == cache.computed(next_id)
+            live[next_id] = (tokens, reused)
+            check_tables(next_id)
+            next_id += 1
+        elif action < 0.75 and live:
+            request = rng.choice(list(live))
+            tokens, done = live[request]
+            if done == len(tokens):
+                continue
+            target = min(len(tokens), done + rng.randint(1, 9))
+            target = cache.longest_fit(request, target)
+            if target == done:
+                continue
+            cache.reserve(request, target)
+            table = cache.table(request, 0)
+            for index in range(done // page, (target + page - 1) // page):     # pages this portion writes
+                written[int(table[index])] = (index * page, list(tokens[index * page:min(target, (index + 1) * page)]))
+            cache.commit(request, target)
+            live[request] = (tokens, target)
+            cache.publish(request, tokens, target)
+            check_tables(request)
+        elif live:
+            request = rng.choice(list(live))
+            cache.close(request)
+            del live[request]
+        assert cache.audit() == "", cache.audit()
+        stats = cache.stats(0)
+        distinct = {int(p) for r in live for p in cache.table(r, 0) if p >= 0}
+        assert stats["used_pages"] == len(distinct) + stats["kept_pages"]
+    for request in list(live):
+        cache.close(request)
+    assert cache.audit() == ""

@@ -41,7 +41,8 @@ def test_greedy_generation_tiny_a(dtype):
         assert result.finish == "length" and len(result.tokens) == 16
         _check_greedy(folder, prompt, result.tokens, dtype)
     stats = engine.stats()
-    assert stats["kv_used_pages"] == 0 and stats["sequences"] == 0
+    # only the pages kept for requests that begin the same way are still in use
+    assert stats["kv_used_pages"] == stats["kv_kept_pages"] == 6 and stats["sequences"] == 0
     assert engine.pools.manager.audit() == ""
 
 
@@ -80,7 +81,8 @@ def test_few_pages_preempt_and_recompute():
         assert len(result.tokens) == 40
         _check_greedy(folder, prompt, result.tokens, "float32")
     assert engine.pools.manager.audit() == ""
-    assert engine.stats()["kv_used_pages"] == 0
+    assert engine.stats()["kv_used_pages"] == engine.stats()["kv_kept_pages"]   # nothing but pages kept for reuse
+    assert sum(r.reused_tokens for r in results if r.preemptions) > 0             # who was put back found its pages
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -123,3 +125,33 @@ def test_sampling_options_through_the_entry_point():
     stop = SamplingParams(max_new_tokens=8, eos_ids=[greedy[2]])
     ended = engine.generate([prompt], stop)[0]
     assert ended.finish == "stop" and ended.tokens == greedy[:greedy.index(greedy[2]) + 1]   # the end token is kept
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_prompt_seen_before_shares_its_pages(dtype):
+    """The pages of a prompt stay known after its request ends; a request that begins with the
+    same tokens takes them over instead of computing them (at least one token is computed),
+    produces tokens the plain implementation agrees with, and a tiny B model with windowed
+    layers (pages given back) does not share at all."""
+    from vipera_rs_b200 import SamplingParams
+
+    folder, engine = _engine("A", dtype, page_size=16, num_pages=24, max_num_seqs=2)
+    vocab = helpers.CONFIGS["A"]["vocab_size"]
+    prompt = helpers.random_tokens(vocab, 75, 900)
+    params = SamplingParams(max_new_tokens=10)
+    first = engine.generate([prompt], params)[0]
+    assert first.reused_tokens == 0 and engine.stats()["kv_kept_pages"] == 4
+    again, branch = engine.generate([prompt, prompt[:40] + helpers.random_tokens(vocab, 9, 901)], params)
+    assert again.reused_tokens == 64 and again.processed_tokens == 75 - 64 + 9
+    assert branch.reused_tokens == 32
+    _check_greedy(folder, prompt, again.tokens, dtype)
+    _check_greedy(folder, prompt[:40] + helpers.random_tokens(vocab, 9, 901), branch.tokens, dtype)
+    if dtype == "float32":
+        assert again.tokens == first.tokens
+    # without it nothing is kept
+    _, plain_engine = _engine("A", dtype, page_size=16, num_pages=24, max_num_seqs=2, prefix_cache=False)
+    plain_engine.generate([prompt], params)
+    assert plain_engine.generate([prompt], params)[0].reused_tokens == 0
+    assert plain_engine.stats()["kv_kept_pages"] == 0
+    _, windowed = _engine("B", dtype, page_size=32, ctx=256, max_num_seqs=2)
+    assert not windowed.pools.manager.reuse

@@ -21,17 +21,20 @@ def toy_token(tokens, position):
 class ToyEngine:
     """Scheduler + cache manager + a step that needs no model."""
 
-    def __init__(self, pages=64, page_size=16, max_num_seqs=4, budget=64, portion=64, window_group=False):
+    def __init__(self, pages=64, page_size=16, max_num_seqs=4, budget=64, portion=64, window_group=False, reuse=False):
         rt = runtime_module()
         groups = [(page_size, pages, 0)] + ([(page_size, pages, 24)] if window_group else [])
-        self.cache = rt.CacheManager(groups, max_num_seqs)
-        self.scheduler = rt.Scheduler(self.cache, max_num_seqs, budget, portion, 0)
+        self.cache = rt.CacheManager(groups, max_num_seqs, reuse)
+        self.scheduler = rt.Scheduler(self.cache, max_num_seqs, budget, portion, 0, reuse)
         self.history = {}       # request -> every token the step function has seen, by position
+        self.prompts = {}
+        self.cached = {}        # physical page -> the tokens whose keys the step function "wrote" there
         self.steps = []
         self.finished = {}
 
     def add(self, request, prompt, **params):
         params.setdefault("temperature", 0.0)
+        self.prompts[request] = list(prompt)
         self.scheduler.add(request, list(prompt), params)
 
     def step(self):
@@ -42,12 +45,23 @@ class ToyEngine:
             offset = 0
             for request, start, count, fresh in zip(plan.requests, plan.starts, plan.counts, plan.fresh):
                 seen = self.history.setdefault(request, [])
+                page = self.cache.group(0)[0]
                 if fresh:
-                    assert start == 0
+                    # what was not computed again must lie in the pages the request was given
+                    assert start == 0 or self.cache.reuse
+                    assert start % page == 0
                     del seen[:]
+                    table = self.cache.table(request, 0)
+                    for index in range(start // page):
+                        seen.extend(self.cached[int(table[index])])
+                    assert seen == (self.prompts[request] + self.finished.get(request, {}).get("tokens", []))[:start] \
+                        or seen == self.known(request)[:start]
                 assert len(seen) == start, "portions of a request must arrive in order, without gaps"
                 assert positions[offset:offset + count].tolist() == list(range(start, start + count))
                 seen.extend(tokens[offset:offset + count].tolist())
+                table = self.cache.table(request, 0)
+                for index in range(start // page, (start + count + page - 1) // page):
+                    self.cached[int(table[index])] = seen[index * page:(index + 1) * page]
                 # every position of the portion has its page
                 table = self.cache.table(request, 0)
                 assert all(table[p // self.cache.group(0)[0]] >= 0 for p in range(start, start + count))
@@ -62,6 +76,13 @@ class ToyEngine:
             self.finished[item["request"]] = item
         assert self.cache.audit() == ""
         return plan, outcome
+
+    def known(self, request):
+        """The request's tokens so far as the test knows them: prompt, then what the toy step drew."""
+        tokens = list(self.prompts[request])
+        while len(tokens) < len(self.history.get(request, [])) + 64:
+            tokens.append(toy_token(tokens, len(tokens) - 1))
+        return tokens
 
     def run(self, limit=10000):
         for _ in range(limit):
@@ -275,3 +296,47 @@ def test_windowed_group_keeps_the_scheduler_going_past_its_pages():
         produced += len(outcome["tokens"])
         assert cache.audit() == "" and cache.stats(1)["used_pages"] <= 5
     assert produced == 100
+
+
+def test_a_prompt_seen_before_is_not_computed_again():
+    """Prefix reuse (the reference: crates/vipera-runtime/src/engine.rs:432-491 and its tests
+    :2005-2110): whole pages of a prompt an earlier request computed are taken over, at least
+    one token is always computed, the tokens drawn are the same, and the pages are given up
+    when others need them."""
+    engine = ToyEngine(pages=12, page_size=8, max_num_seqs=2, budget=64, portion=64, reuse=True)
+    prompt = [(i * 5 + 2) % VOCAB for i in range(37)]
+    engine.add(1, prompt, max_new_tokens=6)
+    engine.run()
+    first = engine.finished[1]
+    assert first["reused_tokens"] == 0 and first["processed_tokens"] == 37 + 5
+    assert engine.cache.stats(0)["kept_pages"] == 4          # 37 tokens: four full pages of the prompt stay
+    engine.add(2, prompt, max_new_tokens=6)
+    engine.add(3, prompt[:20] + [1, 2, 3], max_new_tokens=4)
+    engine.run()
+    again, branch = engine.finished[2], engine.finished[3]
+    assert again["tokens"] == first["tokens"] == expected_tokens(prompt, 6)
+    assert again["reused_tokens"] == 32 and again["processed_tokens"] == 5 + 5
+    assert branch["reused_tokens"] == 16 and branch["tokens"] == expected_tokens(prompt[:20] + [1, 2, 3], 4)
+    # the whole prompt is known, one token is computed all the same
+    engine.add(4, prompt[:32], max_new_tokens=2)
+    engine.run()
+    assert engine.finished[4]["reused_tokens"] == 24 and engine.finished[4]["tokens"] == expected_tokens(prompt[:32], 2)
+    # requests with other prompts need the pages: the kept ones go, nobody is refused
+    for request in range(10, 16):
+        engine.add(request, [(request * 11 + i) % VOCAB for i in range(40)], max_new_tokens=8)
+    engine.run()
+    assert all(engine.finished[r]["reason"] == "length" for r in range(10, 16))
+    assert engine.cache.audit() == ""
+
+
+def test_a_request_put_back_finds_its_own_pages_again():
+    """Preemption by recomputation costs little when prefixes are shared: the request put back
+    published its prompt's pages, and takes them over when it is admitted again."""
+    engine = ToyEngine(pages=7, page_size=8, max_num_seqs=2, budget=64, portion=64, reuse=True)
+    engine.add(1, [(i * 3) % VOCAB for i in range(20)], max_new_tokens=30)
+    engine.add(2, [(i * 7 + 1) % VOCAB for i in range(20)], max_new_tokens=12)
+    engine.run()
+    assert engine.finished[1]["tokens"] == expected_tokens([(i * 3) % VOCAB for i in range(20)], 30)
+    assert engine.finished[2]["tokens"] == expected_tokens([(i * 7 + 1) % VOCAB for i in range(20)], 12)
+    put_back = [item for item in engine.finished.values() if item["preemptions"] >= 1]
+    assert put_back and all(item["reused_tokens"] >= 16 for item in put_back)

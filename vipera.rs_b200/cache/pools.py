@@ -59,7 +59,7 @@ class CachePools:
     """Allocates the pools and the native manager for one engine."""
 
     def __init__(self, cache_requests: Dict[int, object], *, page_size: int, num_pages, num_state_slots: int,
-                 dtype: torch.dtype, device):
+                 dtype: torch.dtype, device, reuse_prefixes: bool = False):
         self.groups, self.states = plan_groups(cache_requests)
         self.page_size = int(page_size)
         self.dtype = dtype
@@ -72,7 +72,10 @@ class CachePools:
         runtime = runtime_module()
         self.manager = runtime.CacheManager(
             [(self.page_size, pages, group.window or 0) for group, pages in zip(self.groups, self.num_pages)],
-            int(num_state_slots))
+            int(num_state_slots),
+            # pages of a prompt prefix can be shared only where the pages are all a request keeps:
+            # a mixer with a state of its own would have to store that state at every page's end
+            bool(reuse_prefixes) and not self.states)
         self.pool_tensors: List[torch.Tensor] = []
         self.views: Dict[int, object] = {}
         for index, (group, pages) in enumerate(zip(self.groups, self.num_pages)):

@@ -241,7 +241,7 @@ def generate(args: List[str]) -> int:
     elapsed = time.time() - started
     if as_json:
         print(json.dumps({
-            "prompt_tokens": result.prompt_tokens, "reused_tokens": 0,
+            "prompt_tokens": result.prompt_tokens, "reused_tokens": result.reused_tokens,
             "processed_tokens": result.processed_tokens, "generated_tokens": len(result.tokens),
             "finish": result.finish, "tokens": result.tokens,
             "tokens_per_second": len(result.tokens) / elapsed if elapsed > 0 else 0.0,

@@ -58,6 +58,7 @@ py::dict finished_to_dict(const Finished& f) {
   d["tokens"] = f.tokens;
   d["prompt_tokens"] = f.prompt_tokens;
   d["processed_tokens"] = f.processed_tokens;
+  d["reused_tokens"] = f.reused_tokens;
   d["preemptions"] = f.preemptions;
   return d;
 }
@@ -100,7 +101,7 @@ PYBIND11_MODULE(_vipera_runtime, m) {
 
   // ---- cache manager ---------------------------------------------------------------
   py::class_<CacheManager>(m, "CacheManager")
-      .def(py::init([](const std::vector<std::tuple<int, int, int>>& groups, int slots) {
+      .def(py::init([](const std::vector<std::tuple<int, int, int>>& groups, int slots, bool reuse) {
              std::vector<GroupConfig> configs;
              for (const auto& g : groups) {
                GroupConfig c;
@@ -109,9 +110,17 @@ PYBIND11_MODULE(_vipera_runtime, m) {
                c.window = std::get<2>(g);
                configs.push_back(c);
              }
-             return new CacheManager(configs, slots);
+             return new CacheManager(configs, slots, reuse);
            }),
-           py::arg("groups"), py::arg("num_state_slots"))
+           py::arg("groups"), py::arg("num_state_slots"), py::arg("reuse") = false)
+      .def_property_readonly("reuse", &CacheManager::reuse)
+      .def("match", [](CacheManager& c, int64_t request, const std::vector<int32_t>& tokens) {
+        return c.match(request, tokens.data(), static_cast<int>(tokens.size()));
+      })
+      .def("publish", [](CacheManager& c, int64_t request, const std::vector<int32_t>& tokens, int upto) {
+        if (upto > static_cast<int>(tokens.size())) throw InvalidArgument("publish beyond the tokens given");
+        c.publish(request, tokens.data(), upto);
+      })
       .def_property_readonly("num_groups", &CacheManager::num_groups)
       .def_property_readonly("num_state_slots", &CacheManager::num_state_slots)
       .def_property_readonly("free_state_slots", &CacheManager::free_state_slots)
@@ -139,6 +148,7 @@ PYBIND11_MODULE(_vipera_runtime, m) {
         d["total_pages"] = s.total_pages;
         d["free_pages"] = s.free_pages;
         d["used_pages"] = s.used_pages;
+        d["kept_pages"] = s.kept_pages;
         return d;
       })
       .def("open_requests", &CacheManager::open_requests)
@@ -251,8 +261,9 @@ PYBIND11_MODULE(_vipera_runtime, m) {
 
   py::class_<Scheduler>(m, "Scheduler")
       .def(py::init([](CacheManager* cache, int max_num_seqs, int max_tokens_per_step, int max_portion,
-                       int max_model_len) {
+                       int max_model_len, bool reuse_prefixes) {
              SchedulerConfig config;
+             config.reuse_prefixes = reuse_prefixes;
              config.max_num_seqs = max_num_seqs;
              config.max_tokens_per_step = max_tokens_per_step;
              config.max_portion = max_portion;
@@ -260,7 +271,8 @@ PYBIND11_MODULE(_vipera_runtime, m) {
              return new Scheduler(cache, config);
            }),
            py::arg("cache"), py::arg("max_num_seqs"), py::arg("max_tokens_per_step"),
-           py::arg("max_portion"), py::arg("max_model_len") = 0, py::keep_alive<1, 2>())
+           py::arg("max_portion"), py::arg("max_model_len") = 0, py::arg("reuse_prefixes") = true,
+           py::keep_alive<1, 2>())
       .def("add", [](Scheduler& s, int64_t request, std::vector<int32_t> prompt, const py::dict& params) {
         s.add(request, std::move(prompt), request_params_from(params));
       })

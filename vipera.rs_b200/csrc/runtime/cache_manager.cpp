@@ -6,7 +6,7 @@
 
 namespace vipera {
 
-CacheManager::CacheManager(std::vector<GroupConfig> groups, int num_state_slots) {
+CacheManager::CacheManager(std::vector<GroupConfig> groups, int num_state_slots, bool reuse) {
   if (num_state_slots <= 0) throw InvalidArgument("a cache needs at least one state slot");
   for (const GroupConfig& config : groups) {
     if (config.page_size <= 0) throw InvalidArgument("page size must be at least 1 token");
@@ -14,7 +14,7 @@ CacheManager::CacheManager(std::vector<GroupConfig> groups, int num_state_slots)
     if (config.window < 0) throw InvalidArgument("a window cannot be negative");
     Group group;
     group.config = config;
-    group.held.assign(config.num_pages, 0);
+    group.refs.assign(config.num_pages, 0);
     // Reverse order on the stack, so that the lowest page number is handed out first
     // (crates/vipera-runtime/src/kv.rs:261-264).
     group.free.reserve(config.num_pages);
@@ -23,7 +23,140 @@ CacheManager::CacheManager(std::vector<GroupConfig> groups, int num_state_slots)
   }
   slot_owner_.assign(num_state_slots, -1);
   for (int slot = num_state_slots - 1; slot >= 0; --slot) free_slots_.push_back(slot);
+  // Shared prefixes need pages that are never given back early and one page size for all groups.
+  reuse_ = reuse && !groups_.empty();
+  for (const Group& group : groups_)
+    if (group.config.window > 0 || group.config.page_size != groups_[0].config.page_size) reuse_ = false;
 }
+
+// ---------------------------------------------------------------------------------------
+// shared prefixes
+// ---------------------------------------------------------------------------------------
+uint64_t CacheManager::chain_key(uint64_t parent, const int32_t* tokens, int count) {
+  uint64_t value = parent ^ 0xCBF29CE484222325ull;
+  for (int i = 0; i < count; ++i) {
+    value ^= static_cast<uint32_t>(tokens[i]);
+    value *= 0x100000001B3ull;
+    value ^= value >> 29;
+  }
+  return value ? value : 1;  // 0 stands for "no prefix"
+}
+
+bool CacheManager::unheld(const Kept& kept) const {
+  for (size_t g = 0; g < groups_.size(); ++g)
+    if (groups_[g].refs[kept.pages[g]] != 1) return false;
+  return true;
+}
+
+int CacheManager::evictable_pages() const {
+  if (evictable_cache_ >= 0) return evictable_cache_;
+  // A published page can be given up when no request holds it and every page published
+  // behind it can be given up too (they go first).  Deepest pages are looked at first.
+  std::vector<std::pair<uint64_t, const Kept*>> order;
+  order.reserve(kept_.size());
+  for (const auto& item : kept_) order.emplace_back(item.first, &item.second);
+  std::sort(order.begin(), order.end(),
+            [](const std::pair<uint64_t, const Kept*>& a, const std::pair<uint64_t, const Kept*>& b) {
+              return a.second->depth > b.second->depth;
+            });
+  std::map<uint64_t, int> blocked;  // key -> children that stay
+  int count = 0;
+  for (const auto& item : order) {
+    const Kept& kept = *item.second;
+    const bool goes = unheld(kept) && blocked[item.first] == 0;
+    if (goes) ++count; else if (kept.parent) ++blocked[kept.parent];
+  }
+  evictable_cache_ = count;
+  return count;
+}
+
+void CacheManager::release_page(Group& group, int32_t page) {
+  if (--group.refs[page] == 0) group.free.push_back(page);
+}
+
+bool CacheManager::evict_one() {
+  auto victim = kept_.end();
+  for (auto it = kept_.begin(); it != kept_.end(); ++it) {
+    if (it->second.children != 0 || !unheld(it->second)) continue;
+    if (victim == kept_.end() || it->second.tick < victim->second.tick ||
+        (it->second.tick == victim->second.tick && it->second.depth > victim->second.depth))
+      victim = it;
+  }
+  if (victim == kept_.end()) return false;
+  for (size_t g = 0; g < groups_.size(); ++g) release_page(groups_[g], victim->second.pages[g]);
+  auto parent = kept_.find(victim->second.parent);
+  if (victim->second.parent && parent != kept_.end()) --parent->second.children;
+  kept_.erase(victim);
+  evictable_cache_ = -1;
+  return true;
+}
+
+int CacheManager::match(int64_t request, const int32_t* tokens, int length) {
+  Request& entry = find(request);
+  if (!reuse_ || length <= 1) return 0;
+  if (entry.computed != 0) throw InvalidArgument("a prefix is matched before anything of the request is computed");
+  const int ps = groups_[0].config.page_size;
+  const int most = (length - 1) / ps;  // at least one token stays to be computed
+  uint64_t key = 0;
+  int pages = 0;
+  ++tick_;
+  for (; pages < most; ++pages) {
+    const uint64_t next = chain_key(key, tokens + pages * ps, ps);
+    auto found = kept_.find(next);
+    if (found == kept_.end() || found->second.parent != key || found->second.depth != pages ||
+        !std::equal(found->second.tokens.begin(), found->second.tokens.end(), tokens + pages * ps))
+      break;
+    found->second.tick = tick_;
+    for (size_t g = 0; g < groups_.size(); ++g) {
+      entry.tables[g].push_back(found->second.pages[g]);
+      ++groups_[g].refs[found->second.pages[g]];
+    }
+    key = next;
+  }
+  entry.computed = pages * ps;
+  entry.published = pages;
+  entry.chain = key;
+  if (pages) evictable_cache_ = -1;
+  return entry.computed;
+}
+
+void CacheManager::publish(int64_t request, const int32_t* tokens, int upto) {
+  Request& entry = find(request);
+  if (!reuse_) return;
+  const int ps = groups_[0].config.page_size;
+  const int full = std::min(upto, entry.computed) / ps;
+  while (entry.published < full) {
+    const int page = entry.published;
+    const uint64_t key = chain_key(entry.chain, tokens + page * ps, ps);
+    auto found = kept_.find(key);
+    if (found == kept_.end()) {
+      Kept kept;
+      kept.parent = entry.chain;
+      kept.depth = page;
+      kept.tick = ++tick_;
+      kept.tokens.assign(tokens + page * ps, tokens + (page + 1) * ps);
+      for (size_t g = 0; g < groups_.size(); ++g) {
+        kept.pages.push_back(entry.tables[g].at(page));
+        ++groups_[g].refs[entry.tables[g][page]];
+      }
+      auto parent = kept_.find(entry.chain);
+      if (entry.chain && parent != kept_.end()) ++parent->second.children;
+      // a parent that was given up meanwhile: this page cannot be reached by a match until
+      // the parent is published again; it is given up like any other
+      if (entry.chain && parent == kept_.end()) kept.parent = entry.chain;
+      kept_.emplace(key, std::move(kept));
+      evictable_cache_ = -1;
+    } else if (found->second.parent != entry.chain || found->second.depth != page ||
+               !std::equal(found->second.tokens.begin(), found->second.tokens.end(), tokens + page * ps)) {
+      break;  // two prefixes under one key: the first one stays, this request publishes no further
+    } else {
+      found->second.tick = ++tick_;
+    }
+    entry.chain = key;
+    ++entry.published;
+  }
+}
+
 
 const CacheManager::Request& CacheManager::find(int64_t request) const {
   auto it = requests_.find(request);
@@ -76,8 +209,9 @@ std::vector<int> CacheManager::pages_missing(int64_t request, int new_length) co
 
 bool CacheManager::fits(int64_t request, int new_length) const {
   std::vector<int> missing = pages_missing(request, new_length);
+  const int extra = kept_.empty() ? 0 : evictable_pages();  // published pages nobody holds can be taken
   for (size_t g = 0; g < groups_.size(); ++g)
-    if (missing[g] > static_cast<int>(groups_[g].free.size())) return false;
+    if (missing[g] > static_cast<int>(groups_[g].free.size()) + extra) return false;
   return true;
 }
 
@@ -87,7 +221,8 @@ bool CacheManager::admits(int length, int portion) const {
     int tokens = length;
     if (group.config.window > 0) tokens = std::min(length, group.config.window + portion + ps);
     const int pages = (tokens + ps - 1) / ps;
-    if (pages > static_cast<int>(group.free.size())) return false;
+    const int extra = kept_.empty() ? 0 : evictable_pages();
+    if (pages > static_cast<int>(group.free.size()) + extra) return false;
   }
   return true;
 }
@@ -105,6 +240,10 @@ int CacheManager::longest_fit(int64_t request, int new_length) const {
 
 void CacheManager::reserve(int64_t request, int new_length) {
   std::vector<int> missing = pages_missing(request, new_length);
+  // published pages that nobody holds make room first, least recently used first
+  for (size_t g = 0; g < groups_.size(); ++g)
+    while (missing[g] > static_cast<int>(groups_[g].free.size()) && evict_one()) {
+    }
   for (size_t g = 0; g < groups_.size(); ++g) {
     if (missing[g] > static_cast<int>(groups_[g].free.size())) {
       // (plain string building: stream formatting has crashed inside processes that load
@@ -125,7 +264,7 @@ void CacheManager::reserve(int64_t request, int new_length) {
       if (table[page] >= 0) continue;
       int32_t physical = group.free.back();
       group.free.pop_back();
-      group.held[physical] = 1;
+      group.refs[physical] = 1;
       table[page] = physical;
     }
   }
@@ -156,8 +295,7 @@ void CacheManager::commit(int64_t request, int new_length) {
     std::vector<int32_t>& table = entry.tables[g];
     for (int page = 0; page < keep_from && page < static_cast<int>(table.size()); ++page) {
       if (table[page] < 0) continue;
-      group.held[table[page]] = 0;
-      group.free.push_back(table[page]);
+      release_page(group, table[page]);
       table[page] = -1;
     }
   }
@@ -172,10 +310,10 @@ void CacheManager::close(int64_t request) {
     std::vector<int32_t>& table = entry.tables[g];
     for (int page = static_cast<int>(table.size()) - 1; page >= 0; --page) {
       if (table[page] < 0) continue;
-      group.held[table[page]] = 0;
-      group.free.push_back(table[page]);
+      release_page(group, table[page]);
     }
   }
+  evictable_cache_ = -1;
   slot_owner_[entry.slot] = -1;
   free_slots_.push_back(entry.slot);
   requests_.erase(request);
@@ -211,6 +349,8 @@ GroupStats CacheManager::stats(int g) const {
   out.total_pages = group.config.num_pages;
   out.free_pages = static_cast<int>(group.free.size());
   out.used_pages = out.total_pages - out.free_pages;
+  for (const auto& item : kept_)
+    if (group.refs[item.second.pages.at(g)] == 1) ++out.kept_pages;
   return out;
 }
 
@@ -223,36 +363,43 @@ std::vector<int64_t> CacheManager::open_requests() const {
 std::string CacheManager::audit() const {
   for (size_t g = 0; g < groups_.size(); ++g) {
     const Group& group = groups_[g];
-    std::vector<int> seen(group.config.num_pages, 0);
+    const std::string where = "group " + std::to_string(g) + ": ";
+    std::vector<int> free_seen(group.config.num_pages, 0), holders(group.config.num_pages, 0);
     for (int32_t page : group.free) {
-      if (page < 0 || page >= group.config.num_pages) {
-        return std::string("group ") + std::to_string(g) + std::string(": free stack holds page ") + std::to_string(page) + std::string(" outside the pool");
-      }
-      if (++seen[page] > 1) {
-        return std::string("group ") + std::to_string(g) + std::string(": page ") + std::to_string(page) + std::string(" is on the free stack twice");
-      }
-      if (group.held[page]) {
-        return std::string("group ") + std::to_string(g) + std::string(": page ") + std::to_string(page) + std::string(" is free and marked held");
-      }
+      if (page < 0 || page >= group.config.num_pages)
+        return where + "free stack holds page " + std::to_string(page) + " outside the pool";
+      if (++free_seen[page] > 1) return where + "page " + std::to_string(page) + " is on the free stack twice";
+      if (group.refs[page] != 0) return where + "page " + std::to_string(page) + " is free and marked held";
     }
     for (const auto& item : requests_) {
+      std::vector<int> mine(group.config.num_pages, 0);
       for (int32_t page : item.second.tables[g]) {
         if (page < 0) continue;
-        if (page >= group.config.num_pages) {
-          return std::string("group ") + std::to_string(g) + std::string(": request ") + std::to_string(item.first) + std::string(" holds page ") + std::to_string(page) + std::string(" outside the pool");
-        }
-        if (++seen[page] > 1) {
-          return std::string("group ") + std::to_string(g) + std::string(": page ") + std::to_string(page) + std::string(" is held twice or held and free");
-        }
-        if (!group.held[page]) {
-          return std::string("group ") + std::to_string(g) + std::string(": page ") + std::to_string(page) + std::string(" is in a table but not marked held");
-        }
+        if (page >= group.config.num_pages)
+          return where + "request " + std::to_string(item.first) + " holds page " + std::to_string(page) + " outside the pool";
+        if (++mine[page] > 1)
+          return where + "request " + std::to_string(item.first) + " holds page " + std::to_string(page) + " twice";
+        ++holders[page];
       }
     }
+    std::vector<int> published(group.config.num_pages, 0);
+    for (const auto& item : kept_) {
+      const int32_t page = item.second.pages.at(g);
+      if (page < 0 || page >= group.config.num_pages) return where + "a published page lies outside the pool";
+      if (++published[page] > 1) return where + "page " + std::to_string(page) + " is published twice";
+      ++holders[page];
+    }
     for (int page = 0; page < group.config.num_pages; ++page) {
-      if (seen[page] == 0) {
-        return std::string("group ") + std::to_string(g) + std::string(": page ") + std::to_string(page) + std::string(" is lost (neither free nor held)");
-      }
+      if (free_seen[page] && holders[page])
+        return where + "page " + std::to_string(page) + " is held twice or held and free";
+      if (!free_seen[page] && holders[page] == 0)
+        return where + "page " + std::to_string(page) + " is lost (neither free nor held)";
+      if (holders[page] != group.refs[page])
+        return where + "page " + std::to_string(page) + " is counted " + std::to_string(group.refs[page]) +
+               " times and held " + std::to_string(holders[page]) + " times";
+      // only a published page may be in more than one table
+      if (holders[page] > 1 && !published[page])
+        return where + "page " + std::to_string(page) + " is held twice without being published";
     }
   }
   std::vector<int> slots(slot_owner_.size(), 0);

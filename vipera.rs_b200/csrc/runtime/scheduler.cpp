@@ -61,6 +61,7 @@ Finished Scheduler::finish(Request& request, const std::string& reason) {
   out.tokens.assign(request.tokens.begin() + request.prompt_len, request.tokens.end());
   out.prompt_tokens = request.prompt_len;
   out.processed_tokens = request.processed;
+  out.reused_tokens = request.reused;
   out.preemptions = request.preemptions;
   return out;
 }
@@ -186,7 +187,12 @@ StepPlan Scheduler::schedule() {
     Request& head = waiting_.front();
     int length = static_cast<int>(head.tokens.size());
     cache_->open(head.id);
-    if (!cache_->admits(length, config_.max_portion)) {
+    // Pages of a prompt prefix an earlier request computed are shared, not computed again
+    // (the reference copies them: engine.rs:432-491).
+    const bool reuse = config_.reuse_prefixes && cache_->reuse();
+    const int reused = reuse ? cache_->match(head.id, head.tokens.data(), length) : 0;
+    const bool room = reuse ? cache_->fits(head.id, length) : cache_->admits(length, config_.max_portion);
+    if (!room) {
       cache_->close(head.id);
       if (running_.empty()) {
         // Nothing runs and it still does not fit: it never will.
@@ -197,23 +203,24 @@ StepPlan Scheduler::schedule() {
       }
       break;
     }
-    int want = std::min({length, config_.max_portion, config_.max_tokens_per_step - used});
-    want = cache_->longest_fit(head.id, want);
+    int want = std::min({length - reused, config_.max_portion, config_.max_tokens_per_step - used});
+    want = cache_->longest_fit(head.id, reused + want) - reused;
     if (want <= 0) {
       cache_->close(head.id);
       break;
     }
-    cache_->reserve(head.id, want);
+    cache_->reserve(head.id, reused + want);
     Request request = std::move(waiting_.front());
     waiting_.pop_front();
     request.order = next_order_++;
+    request.reused += reused;
     StepEntry entry;
     entry.request = request.id;
-    entry.start = 0;
+    entry.start = reused;
     entry.count = want;
     entry.state_slot = cache_->state_slot(request.id);
     entry.fresh = true;
-    entry.wants_logits = want == length;
+    entry.wants_logits = reused + want == length;
     plan.entries.push_back(entry);
     used += want;
     running_.emplace(request.id, std::move(request));
@@ -248,6 +255,10 @@ StepOutcome Scheduler::complete(const StepPlan& plan, const std::vector<int32_t>
     cache_->commit(entry.request, entry.start + entry.count);
     it->second.processed += entry.count;
     it->second.fresh = false;
+    // full pages of the prompt become available to requests that begin the same way
+    if (config_.reuse_prefixes && cache_->reuse())
+      cache_->publish(entry.request, it->second.tokens.data(),
+                      std::min(entry.start + entry.count, it->second.prompt_len));
   }
   for (size_t i = 0; i < plan.rows.size(); ++i) {
     auto it = running_.find(plan.rows[i].request);

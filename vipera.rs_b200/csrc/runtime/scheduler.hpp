@@ -37,6 +37,7 @@ struct SchedulerConfig {
   int max_tokens_per_step = 512; // budget of one step
   int max_portion = 512;         // longest portion of one prompt in one step
   int max_model_len = 0;         // 0: bounded by the cache only
+  bool reuse_prefixes = true;    // share the pages of prompt prefixes seen before (where the cache can)
 };
 
 struct StepEntry {
@@ -76,6 +77,7 @@ struct Finished {
   std::vector<int32_t> tokens;  // generated tokens, the end token included
   int prompt_tokens = 0;
   int processed_tokens = 0;  // tokens run through the model, recomputation included
+  int reused_tokens = 0;     // prompt tokens taken from pages an earlier request computed
   int preemptions = 0;
 };
 
@@ -109,6 +111,7 @@ class Scheduler {
     std::vector<int32_t> tokens;  // prompt, then generated
     int prompt_len = 0;
     int processed = 0;
+    int reused = 0;
     int preemptions = 0;
     uint64_t order = 0;  // admission order, for the choice of whom to put back
     bool fresh = true;

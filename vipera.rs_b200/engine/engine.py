@@ -35,6 +35,7 @@ class Generation:
     prompt_tokens: int
     processed_tokens: int        # tokens run through the model, recomputation included
     preemptions: int
+    reused_tokens: int = 0       # prompt tokens whose keys and values an earlier request had computed
 
 
 @dataclass
@@ -50,6 +51,10 @@ class Engine:
     """One model on one GPU, a paged cache and a scheduler.
 
     ``model`` is a folder (config.json and model.safetensors) or a built ``DecoderModel``.
+    ``prefix_cache``: full pages of prompts stay known after their request ends and are shared
+    with requests that begin with the same tokens (the reference's prefix cache,
+    crates/vipera-runtime/src/engine.rs:432-491, which copies them); they are given up, least
+    recently used first, when pages are needed.
     ``ctx`` is the context length each of ``max_num_seqs`` requests can reach with the
     pages allocated (default: the smaller of the model's limit and 2048, as the reference's
     ``--ctx``, bins/vipera/src/main.rs:655-663); ``num_pages`` overrides that sizing.
@@ -58,7 +63,7 @@ class Engine:
     def __init__(self, model, dtype="bfloat16", device="cuda:0", *, page_size: int = 16,
                  num_pages: Optional[int] = None, ctx: Optional[int] = None, max_num_seqs: int = 4,
                  max_tokens_per_step: int = 2048, max_portion: Optional[int] = None,
-                 max_model_len: Optional[int] = None, decode_graphs: bool = True):
+                 max_model_len: Optional[int] = None, decode_graphs: bool = True, prefix_cache: bool = True):
         if isinstance(model, str):
             model = load_model(model, dtype, device)
         self.model = model
@@ -69,12 +74,14 @@ class Engine:
         if num_pages is None:
             num_pages = max_num_seqs * ((ctx + page_size - 1) // page_size)
         self.pools = CachePools(model.cache_requests, page_size=page_size, num_pages=num_pages,
-                                num_state_slots=max_num_seqs, dtype=model.dtype, device=model.device)
+                                num_state_slots=max_num_seqs, dtype=model.dtype, device=model.device,
+                                reuse_prefixes=prefix_cache)
         self.runner = ModelRunner(model, self.pools, max_model_len=self.max_model_len)
         self.runner.decode_graphs = decode_graphs
         runtime = runtime_module()
         self.scheduler = runtime.Scheduler(self.pools.manager, int(max_num_seqs), int(max_tokens_per_step),
-                                           int(max_portion or max_tokens_per_step), int(self.max_model_len))
+                                           int(max_portion or max_tokens_per_step), int(self.max_model_len),
+                                           bool(prefix_cache))
         self.sampler = DeviceSampler(model.device)
         self.default_eos = tuple(getattr(getattr(model, "config", None), "eos_token_ids", ()) or ())
         self._next_id = 0
@@ -132,7 +139,7 @@ class Engine:
             report.finished.append(Generation(
                 request=int(item["request"]), tokens=[int(t) for t in item["tokens"]], finish=item["reason"],
                 prompt_tokens=int(item["prompt_tokens"]), processed_tokens=int(item["processed_tokens"]),
-                preemptions=int(item["preemptions"])))
+                preemptions=int(item["preemptions"]), reused_tokens=int(item["reused_tokens"])))
             self.generations += 1
 
     def generate(self, prompts: Sequence[Sequence[int]], params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
@@ -165,6 +172,7 @@ class Engine:
             "running": self.scheduler.num_running,
             "kv_used_pages": sum(g["used_pages"] for g in groups),
             "kv_free_pages": sum(g["free_pages"] for g in groups),
+            "kv_kept_pages": sum(g["kept_pages"] for g in groups),
             "kv_total_bytes": self.pools.bytes(),
             "groups": groups,
             "generations": self.generations,
