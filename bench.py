@@ -268,7 +268,7 @@ def measure_e2e(model, batch, history, steps, warmup, page_size=16):
     torch.cuda.synchronize()
     elapsed = time.perf_counter() - started
     h2d = 4 * (8 * batch + 1 + batch * 256)  # packed int32 inputs of a decode step (tables 256 wide at most)
-    d2h = 8 * batch                           # token ids and status words
+    d2h = 4 * (8 + 2 * batch)                 # token ids, row states and the kernels' status word, one copy
     return produced / elapsed, h2d, d2h
 
 

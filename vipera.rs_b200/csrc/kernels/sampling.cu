@@ -437,3 +437,9 @@ int vipera_argmax_static(const float* logits, int rows, int vocab, int* tokens, 
   argmax_final_kernel<<<rows, 32, 0, s>>>(slice_value, slice_id, tokens, status);
   return vipera_launch_status();
 }
+
+// Wait until everything queued on `stream` so far has run.
+VIPERA_API int vipera_stream_synchronize(void* stream) {
+  const cudaError_t error = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  return error == cudaSuccess ? VIPERA_OK : static_cast<int>(error);
+}

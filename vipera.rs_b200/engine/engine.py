@@ -120,10 +120,12 @@ class Engine:
                                  pos0=plan.starts.tolist(), fresh=plan.fresh.tolist(),
                                  logit_rows=plan.row_token_index)
                 logits = self.runner.run(step)
-                sampled = self.sampler.draw(logits, plan) if logits is not None else []
-                if logits is None:
+                if logits is not None:
+                    sampled = self.sampler.draw(logits, plan)   # also reads the kernels' status word
+                else:
+                    sampled = []
                     torch.cuda.current_stream().synchronize()
-                ops.check_kernel_status(self.model.device)
+                    ops.check_kernel_status(self.model.device)
                 outcome = self.scheduler.complete(plan, sampled)
             except InternalError:
                 outcome = self.scheduler.fail(plan)

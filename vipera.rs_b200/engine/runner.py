@@ -61,6 +61,7 @@ class ModelRunner:
         self._copy_pending = False
         self.steps_run = 0
         self.decode_graphs = True
+        self._graph_safe = None  # asked of the model once
         self.max_graph_entries = 256
         self._graphs = {}
         # Decode steps of few tokens run as one persistent kernel where the model qualifies.
@@ -164,7 +165,9 @@ class ModelRunner:
         step is launched kernel by kernel."""
         self.steps_run += 1
         counts = step.counts
-        if (self.decode_graphs and self.model.graph_safe and len(counts) <= self.max_graph_entries
+        if self._graph_safe is None:
+            self._graph_safe = bool(self.model.graph_safe)
+        if (self.decode_graphs and self._graph_safe and len(counts) <= self.max_graph_entries
                 and max(counts) == 1 and len(step.logit_rows) == len(counts)
                 and np.array_equal(step.logit_rows, np.arange(len(counts)))):
             return self._run_graph(step)

@@ -54,7 +54,17 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The raw handle of torch's current stream on the current device."""
+    try:
+        return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
+    except AttributeError:  # a torch without that shortcut
+        return torch.cuda.current_stream().cuda_stream
+
+
+def stream_synchronize() -> None:
+    """Wait for the current stream (a direct call; torch's own builds a stream object first)."""
+    fn = _function("sampling", "vipera_stream_synchronize", [_c_void])
+    _check(fn(_stream()), "stream_synchronize", kernels=0)
 
 
 launches = 0  # kernels launched through this module (replayed graphs add what they captured)
@@ -260,18 +270,41 @@ _tc_state = {}
 buffer_generation = 0  # goes up whenever a shared kernel buffer moves; captured graphs are then stale
 
 
+SAMPLER_MAX_ROWS = 4096
+_WORDS_HEAD = 8  # int32 words in front of the sampler's outputs; the first is the kernel status word
+
+
 def _tc_buffers(device, scratch_bytes: int):
-    """Scratch for the partial sums of split products and the status word of the tensor-core
-    kernels, per device.  The scratch grows on demand and is shared by all products, which
-    run one after another on one stream."""
+    """Scratch for the partial sums of split products and the status word of the kernels with
+    bounded waits, per device.  The scratch grows on demand and is shared by all products,
+    which run one after another on one stream.  The status word is the first word of a small
+    buffer that also receives the sampler's token ids and row states, so that one copy to the
+    host brings all three."""
     global buffer_generation
-    state = _tc_state.setdefault(str(device), {"scratch": None, "status": None})
+    state = _tc_state.setdefault(str(device), {"scratch": None, "status": None, "words": None})
     if state["status"] is None:
-        state["status"] = torch.zeros(1, dtype=torch.int32, device=device)
+        state["words"] = torch.zeros(_WORDS_HEAD + 2 * SAMPLER_MAX_ROWS, dtype=torch.int32, device=device)
+        state["status"] = state["words"][:1]
     if scratch_bytes and (state["scratch"] is None or state["scratch"].numel() * 4 < scratch_bytes):
         state["scratch"] = torch.empty(max(scratch_bytes // 4, 8 << 20), dtype=torch.float32, device=device)
         buffer_generation += 1
     return state
+
+
+def sampler_words(device, rows: int):
+    """(whole, tokens, states): int32 device views for `rows` sampled rows, laid out so that
+    ``whole`` (the status word's neighbourhood, then tokens, then row states) is one
+    contiguous copy."""
+    words = _tc_buffers(device, 0)["words"]
+    return (words[:_WORDS_HEAD + 2 * rows], words[_WORDS_HEAD:_WORDS_HEAD + rows],
+            words[_WORDS_HEAD + rows:_WORDS_HEAD + 2 * rows])
+
+
+def raise_on_kernel_status(device, code: int) -> None:
+    """`code` is the status word as just read: non-zero means a bounded wait ran out."""
+    if code:
+        _tc_buffers(device, 0)["status"].zero_()
+        raise InternalError(f"a tensor-core kernel gave up waiting (code {code}); the step's results are invalid")
 
 
 def gemm_tc_workspace(m: int, n: int, k: int):
@@ -365,10 +398,7 @@ def check_kernel_status(device) -> None:
     state = _tc_state.get(str(device))
     if state is None or state["status"] is None:
         return
-    code = int(state["status"].item())
-    if code:
-        state["status"].zero_()
-        raise InternalError(f"a tensor-core kernel gave up waiting (code {code}); the step's results are invalid")
+    raise_on_kernel_status(device, int(state["status"].item()))
 
 
 # ----------------------------------------------------------------------------------------

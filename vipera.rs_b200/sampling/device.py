@@ -16,17 +16,16 @@ from ..kernels import ops
 class DeviceSampler:
     def __init__(self, device):
         self.device = device
-        self._tokens = torch.empty(4096, dtype=torch.int32, device=device)
-        self._status = torch.empty(4096, dtype=torch.int32, device=device)
-        self._host = torch.empty(2, 4096, dtype=torch.int32, pin_memory=True)
+        self._host = torch.empty(ops._WORDS_HEAD + 2 * ops.SAMPLER_MAX_ROWS, dtype=torch.int32, pin_memory=True)
 
     def draw(self, logits: torch.Tensor, plan) -> List[int]:
         rows = logits.shape[0]
-        if rows > self._tokens.numel():
-            raise InternalError(f"{rows} rows to sample exceed the sampler's 4096")
+        if rows > ops.SAMPLER_MAX_ROWS:
+            raise InternalError(f"{rows} rows to sample exceed the sampler's {ops.SAMPLER_MAX_ROWS}")
         if plan.any_penalty:
             self._penalties(logits, plan)
-        tokens, status = self._tokens[:rows], self._status[:rows]
+        # token ids and row states land beside the kernels' status word: one copy brings all
+        whole, tokens, status = ops.sampler_words(self.device, rows)
         if plan.all_greedy:
             ops.argmax(logits, tokens, status)
         else:
@@ -38,11 +37,13 @@ class DeviceSampler:
                        min_p=torch.from_numpy(plan.row_min_p).to(dev, non_blocking=True),
                        uniform=torch.from_numpy(plan.row_uniform).to(dev, non_blocking=True),
                        tokens=tokens, status=status)
-        self._host[0, :rows].copy_(tokens, non_blocking=True)
-        self._host[1, :rows].copy_(status, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        drawn = self._host[0, :rows].tolist()
-        codes = self._host[1, :rows].tolist()
+        host = self._host[:whole.numel()]
+        host.copy_(whole, non_blocking=True)
+        ops.stream_synchronize()
+        values = host.tolist()
+        ops.raise_on_kernel_status(self.device, values[0])
+        drawn = values[ops._WORDS_HEAD:ops._WORDS_HEAD + rows]
+        codes = values[ops._WORDS_HEAD + rows:]
         for row, code in enumerate(codes):
             if code == ops.SAMPLE_OK:
                 continue
