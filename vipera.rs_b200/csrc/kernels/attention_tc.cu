@@ -629,8 +629,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         else if (groups == 3) cp_async_wait<3>();
         else cp_async_wait<4>();
       };
-      // Copy groups are committed in this order: Q, K0, V0, K1, V1, then K(j+2) in round j and
-      // V(j+2) in round j + 1.  A round hands over what has landed before it waits for a buffer
+      // Copy groups are committed in this order: Q, K0, V0, K1, V1, then K(j+2) in pass j and
+      // V(j+2) in pass j + 1.  A pass hands over what has landed before it waits for a buffer
       // to be free: the products that free it need the data handed over.
       issue_keys(0);
       issue_values(0);
@@ -640,7 +640,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       mbar_arrive(&bars->q_full);
       for (int j = 0; j < num_tiles; ++j) {
         const int buffer = j & 1;
-        // groups committed after K_j so far: V_j, K_j+1 (and V_1 in round 0)
+        // groups committed after K_j so far: V_j, K_j+1 (and V_1 in pass 0)
         const int after_keys = j == 0 ? (num_tiles > 1 ? 3 : 1) : (j + 1 < num_tiles ? 2 : 1);
         ATT_T(d0);
         wait_pending(after_keys);
