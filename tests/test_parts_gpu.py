@@ -321,6 +321,59 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     assert engine.pools.manager.audit() == "" and engine.stats()["sequences"] == 0
 
 
+def _plain_toy_routed(folder, tokens):
+    """Layer 0's feed-forward sends every token to one expert; the rest is the plain model."""
+    config, weights = plain.read_config(folder), plain.read_weights(folder)
+    n = len(tokens)
+    heads, kv_heads, d = config["heads"], config["kv_heads"], config["head_dim"]
+    sin, cos = plain.rope_angles(range(n), d, config["rope_base"])
+    x = plain.embedding(weights["model.embed_tokens.weight"], tokens, torch.float64)
+    for layer in range(2):
+        p = f"model.layers.{layer}."
+        h = plain.rms_norm(x, weights[p + "input_layernorm.weight"], config["eps"])
+        proj = lambda name: h @ weights[p + f"self_attn.{name}.weight"].double().T + weights[p + f"self_attn.{name}.bias"].double()  # noqa: E731
+        q = plain.rope_neox(proj("q_proj").view(n, heads, d), sin, cos)
+        k = plain.rope_neox(proj("k_proj").view(n, kv_heads, d), sin, cos)
+        v = proj("v_proj").view(n, kv_heads, d)
+        x = x + plain.attention(q, k, v).reshape(n, heads * d) @ weights[p + "self_attn.o_proj.weight"].double().T
+        h = plain.rms_norm(x, weights[p + "post_attention_layernorm.weight"], config["eps"])
+        if layer == 0:
+            scores = h @ weights[p + "mlp.router.weight"].double().T
+            out = torch.zeros_like(x)
+            for t in range(n):
+                e = int(scores[t].argmax())
+                up = weights[p + f"mlp.experts.{e}.up.weight"].double()
+                down = weights[p + f"mlp.experts.{e}.down.weight"].double()
+                out[t] = torch.relu(h[t] @ up.T) @ down.T
+            x = x + out
+        else:
+            x = x + plain.swiglu(h, weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"],
+                                 weights[p + "mlp.down_proj.weight"])
+    h = plain.rms_norm(x, weights["model.norm.weight"], config["eps"])
+    return (h @ weights["model.embed_tokens.weight"].double().T).numpy()
+
+
+def test_toy_feed_forward_with_routing_is_registered_built_and_stepped():
+    """A feed-forward that routes tokens to experts, defined in the tests and chosen for one
+    layer only: in portions beside another request and token by token (from a captured graph:
+    the part stays on the device) it gives the plain result."""
+    _register_toys()
+    folder = _toy_folder("ToyRoutedLM", "float32")
+    vocab = helpers.TINY_A["vocab_size"]
+    requests = {"a": helpers.random_tokens(vocab, 52, 5), "b": helpers.random_tokens(vocab, 30, 6)}
+    builder = helpers.TraceBuilder()
+    builder.step([("a", requests["a"][:20], range(20)), ("b", requests["b"][:7], range(7))])
+    builder.step([("a", requests["a"][20:22], range(2)), ("b", requests["b"][7:30], range(23))], end=["b"])
+    builder.step([("a", requests["a"][22:40], range(18))])
+    for position in range(40, 52):
+        builder.step([("a", requests["a"][position:position + 1], [0])], end=["a"] if position == 51 else [])
+    outputs = helpers.run_trace(folder, "float32", builder.steps, max_tokens=128, page_size=16,
+                                env_extra={"VIPERA_PLUGINS": _toy_plugin()})
+    reference = {name: _plain_toy_routed(folder, tokens) for name, tokens in requests.items()}
+    worst = helpers.compare(outputs, builder, reference, 1e-4, "toy routed model")
+    assert worst < 1e-4
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_schedule_runs_a_layer_twice_and_shares_a_cache(dtype):
     _register_toys()

@@ -1,6 +1,7 @@
 """Toy parts and toy architectures for the tests: a mixer with state of its own, another
-position encoding, an architecture that mixes both kinds of layer, and one whose execution
-order names a layer twice and lets a layer read another layer's cache.  They are defined and
+position encoding, a feed-forward that routes every token to one of several experts, an
+architecture that mixes both kinds of layer, and one whose execution order names a layer
+twice and lets a layer read another layer's cache.  They are defined and
 registered here, outside the package; ``register()`` is called by the tests, and by a process
 that lists this file in VIPERA_PLUGINS (bin/trace_run in the replay tests)."""
 import torch
@@ -9,9 +10,9 @@ import torch
 def register():
     import vipera_rs_b200  # noqa: F401
     from vipera_rs_b200 import parts  # noqa: F401
-    from vipera_rs_b200.config import (ARCHITECTURES, MIXERS, POSITION_ENCODINGS, LayerSpec, ModelSpec, PartSpec,
-                                       Qwen2Config, ScheduleEntry, qwen2_model_spec, register_architecture)
-    from vipera_rs_b200.parts import FixedState, Mixer, PositionEncoding
+    from vipera_rs_b200.config import (ARCHITECTURES, FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, LayerSpec, ModelSpec,
+                                       PartSpec, Qwen2Config, ScheduleEntry, qwen2_model_spec, register_architecture)
+    from vipera_rs_b200.parts import FeedForward, FixedState, Mixer, PositionEncoding
     from vipera_rs_b200.weights import TensorSpec
 
     if "toy_running_mean" in MIXERS:
@@ -70,8 +71,39 @@ def register():
             q += shift
             k += shift
 
+    class RoutedExperts(FeedForward):
+        """A feed-forward with routing: every token goes to the expert whose router row scores
+        it highest (the lowest index wins a tie), and the expert is ``down(relu(up(h)))``.
+        Written with torch operations that stay on the device (every expert is computed and the
+        others are masked out), so it can be captured in a graph."""
+
+        @classmethod
+        def schema(cls, params, prefix):
+            hidden, inter, experts = params["hidden_size"], params["expert_size"], params["experts"]
+            schema = {f"{prefix}.router.weight": TensorSpec((experts, hidden), store="float32")}
+            for e in range(experts):
+                schema[f"{prefix}.experts.{e}.up.weight"] = TensorSpec((inter, hidden))
+                schema[f"{prefix}.experts.{e}.down.weight"] = TensorSpec((hidden, inter))
+            return schema
+
+        def __init__(self, params, prefix, tensors, dtype, device):
+            super().__init__(params, prefix, tensors, dtype, device)
+            self.experts = params["experts"]
+            to = lambda name: tensors[f"{prefix}.{name}"].to(device=device, dtype=torch.float32)  # noqa: E731
+            self.router = to("router.weight")
+            self.up = torch.stack([to(f"experts.{e}.up.weight") for e in range(self.experts)])
+            self.down = torch.stack([to(f"experts.{e}.down.weight") for e in range(self.experts)])
+
+        def forward(self, ctx, h, residual):
+            x = h.float()
+            scores = x @ self.router.T                                            # [tokens, experts], 32-bit
+            chosen = torch.nn.functional.one_hot(scores.argmax(dim=1), self.experts).to(x.dtype)
+            every = torch.einsum("eti,ehi->eth", torch.relu(torch.einsum("th,eih->eti", x, self.up)), self.down)
+            residual += torch.einsum("eth,te->th", every, chosen)
+
     MIXERS.register("toy_running_mean", RunningMean)
     POSITION_ENCODINGS.register("toy_learned_shift", LearnedShift)
+    FEED_FORWARDS.register("toy_routed_experts", RoutedExperts)
 
     def toy_state_spec(config):
         """Layer 0 mixes with the running mean, layer 1 with attention."""
@@ -88,6 +120,17 @@ def register():
         return ModelSpec(**{**base.__dict__, "architecture": "ToySharedLM",
                             "schedule": [ScheduleEntry(0, 0), ScheduleEntry(0, 1), ScheduleEntry(1, 0, False)]})
 
+    def toy_routed_spec(config):
+        """Layer 0 feeds forward through routed experts, layer 1 through SwiGLU."""
+        base = qwen2_model_spec(config)
+        first = base.layers[0]
+        routed = LayerSpec(block="prenorm", prefix=first.prefix, mixer_norm=first.mixer_norm, ffn_norm=first.ffn_norm,
+                           mixer=first.mixer, names=first.names,
+                           ffn=PartSpec("toy_routed_experts", {"hidden_size": config.hidden_size, "expert_size": 48,
+                                                               "experts": 5}))
+        return ModelSpec(**{**base.__dict__, "layers": [routed] + base.layers[1:], "architecture": "ToyRoutedLM"})
+
+    register_architecture("ToyRoutedLM", Qwen2Config.from_dict, toy_routed_spec)
     register_architecture("ToyStateLM", Qwen2Config.from_dict, toy_state_spec)
     register_architecture("ToySharedLM", Qwen2Config.from_dict, toy_shared_spec)
 
