@@ -739,7 +739,13 @@ static int sm_count() {
 static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE) {
   GemmPlan plan{};
   plan.num_k_blocks = (K + kBlockK - 1) / kBlockK;
-  if (T >= 128 + 64) {
+  // Tokens go on the 128-row side from 192 tokens on.  A matrix wide enough to give half
+  // the SMs a tile of 128 features each takes that form from 33 tokens on: its ending
+  // leaves through shared memory and TMA in whole rows, where the swapped form writes
+  // 32-feature pieces of a row (measured at 64 tokens on a [17920, 1536] matrix with the
+  // SwiGLU ending: 14.1 us against 17.4; at 128 tokens 14.4 against 22.8).
+  static const int nonswap_from = std::getenv("VIPERA_GEMM_NONSWAP_FROM") ? std::atoi(std::getenv("VIPERA_GEMM_NONSWAP_FROM")) : 33;
+  if (T >= 128 + 64 || (T >= nonswap_from && N >= 64 * sms)) {
     plan.swap = false;
     plan.tiles_x = (T + kTileX - 1) / kTileX;
     // The widest tile that keeps the SMs busy: a tile of 256 columns reads the least per
