@@ -6,21 +6,28 @@
 // (crates/vipera-backend-cpu/src/model.rs:2752-2857; definition model.rs:1804-1859):
 //
 //   scores  S = Q . K^T        tcgen05.mma, 128 x 128 x 128, into tensor memory
-//   softmax                    four warps, one query row per thread: running max and sum in
-//                              32-bit, p = 2^(s * scale * log2 e - max), rounded to bfloat16
-//                              into shared memory
+//   softmax                    one query row per thread: running max and sum in 32-bit,
+//                              p = 2^(s * scale * log2 e - max), rounded to bfloat16 into
+//                              shared memory
 //   output  O += P . V         tcgen05.mma, 128 x 128 x 128, accumulated in tensor memory;
 //                              when a row's max grows, its accumulator is scaled first
 //
-// Roles: warps 0-7 softmax and ending, warp 8 issues the MMAs, warps 9-12 bring keys and values
-// through the block table into shared memory, two tiles in flight: with TMA, one box per page
-// and half of the head (pages of 8, 16, 32, 64 or multiples of 128 keys; the copies of four
-// warps' 16-byte cp.async cannot keep enough bytes in flight), else with cp.async.  Two score
-// accumulators alternate, so the scores of the next 128 keys are computed while the softmax
-// of the current ones runs.  Keys and values share one shared-memory image, 128-byte rows
-// with 16-byte chunks XOR-swizzled by the row: for the scores it is read K-major (the
-// contraction runs along the head dimension), for the output MN-major (the contraction runs
-// along the keys), so no transposed copy of V is made.
+// The key tiles are dealt to two softmax groups of four warps, even tiles to one and odd tiles
+// to the other.  Each group has a score accumulator, a P tile, an output accumulator and a
+// running max and sum of its own, so the two folds never wait for one another: while one
+// group's P . V runs, the other group computes its exponentials.  The ending joins the two
+// partial results the way two splits of the keys are joined:
+// O = (O_a 2^(m_a - m) + O_b 2^(m_b - m)) / (l_a 2^(m_a - m) + l_b 2^(m_b - m)).
+//
+// Roles: warps 0-3 and 4-7 the two softmax groups (and the ending), warp 8 issues the MMAs,
+// warps 9-12 bring keys and values through the block table into shared memory, two tiles in
+// flight: with TMA, one box per page and half of the head, or one box per 128 rows where the
+// pages follow one another in memory (pages of 8, 16, 32, 64 or multiples of 128 keys; the
+// copies of four warps' 16-byte cp.async cannot keep enough bytes in flight), else with
+// cp.async.  Keys and values share one shared-memory image, 128-byte rows with 16-byte chunks
+// XOR-swizzled by the row: for the scores it is read K-major (the contraction runs along the
+// head dimension), for the output MN-major (the contraction runs along the keys), so no
+// transposed copy of V is made.
 //
 // Rows of a tile that hold no visible key (before a window, after the causal limit, past the
 // written part of the cache) are zero-filled, never read: they may lie in pages the request
@@ -40,9 +47,11 @@ enum { ATTENTION_TC_WAIT_EXPIRED = 3 };
 #include <cstdio>
 #define ATT_T(var) const long long var = clock64()
 #define ATT_ADD(acc, a, b) acc += (b) - (a)
+#define ATT_EVENT(kind, j) do { if (blockIdx.y == 1 && blockIdx.x == 0 && (j) < 16) bars->trace[kind][j] = clock64(); } while (0)
 #else
 #define ATT_T(var)
 #define ATT_ADD(acc, a, b)
+#define ATT_EVENT(kind, j)
 #endif
 
 namespace {
@@ -52,16 +61,18 @@ constexpr int kQ = 128;                 // queries per block
 constexpr int kKeys = 128;              // keys per tile
 constexpr int kTileBytes = 128 * 256;   // a [128][128] bfloat16 tile: two halves of [128 rows][128 bytes]
 constexpr int kHalfBytes = 128 * 128;
-constexpr int kSoftmaxWarps = 8, kLoaderWarps = 4;
-constexpr int kHalfCols = 64;            // columns of a row one softmax thread takes
-constexpr int kMmaWarp = kSoftmaxWarps;
-constexpr int kThreads = (kSoftmaxWarps + 1 + kLoaderWarps) * 32;
+constexpr int kSoftmaxWarps = 8, kLoaderWarps = 4;   // two softmax groups of four warps
+constexpr int kGroupThreads = 128;
+constexpr int kHalfCols = 64;            // output columns of a row one thread writes in the ending
+constexpr int kMmaWarp = kSoftmaxWarps;           // and the next one: an MMA issuer per softmax group
+constexpr int kFirstLoaderWarp = kSoftmaxWarps + 2;
+constexpr int kThreads = (kSoftmaxWarps + 2 + kLoaderWarps) * 32;
 constexpr int kLoaderThreads = kLoaderWarps * 32;
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMaxSlack = 8.0f;       // in powers of two
-// tensor memory columns: two score accumulators and the output accumulator
-constexpr uint32_t kColsS0 = 0, kColsS1 = 128, kColsO = 256, kTmemCols = 512;
+// tensor memory columns: a score accumulator and an output accumulator per softmax group
+constexpr uint32_t kColsS0 = 0, kColsS1 = 128, kColsO0 = 256, kColsO1 = 384, kTmemCols = 512;
 
 struct Params {
   const __nv_bfloat16* q;      // [tokens, heads, 128]
@@ -211,12 +222,13 @@ struct Barriers {
   uint64_t q_full;
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   uint64_t v_landed[2];  // TMA path: the boxes of a value tile have arrived (rows outside the visible keys are zeroed after that)
-  uint64_t s_full[2], s_empty[2];
-  uint64_t p_full, pv_done;
+  uint64_t s_full[2], s_empty[2];  // per softmax group
+  uint64_t p_full[2], pv_done[2];  // per softmax group
   uint32_t tmem_base;
   int abort_flag;
-  float half_max[2][2][128];  // [score buffer][half of the columns][row]: what the two halves of a row tell each other
-  float half_sum[2][128];
+#ifdef VIPERA_ATTN_TIMING
+  long long trace[10][16];  // [event][tile]: when things happened in one block
+#endif
 };
 
 template <bool TMA_KV>
@@ -229,8 +241,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   uint8_t* q_tile = smem;
   uint8_t* k_tiles = smem + kTileBytes;       // two tiles
   uint8_t* v_tiles = smem + 3 * kTileBytes;   // two tiles
-  uint8_t* p_tile = smem + 5 * kTileBytes;
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + 6 * kTileBytes);
+  uint8_t* p_tiles = smem + 5 * kTileBytes;   // one per softmax group
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + 7 * kTileBytes);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -239,15 +251,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     mbar_init(&bars->q_full, kLoaderThreads);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->k_full[i], TMA_KV ? 1 : kLoaderThreads);
-      mbar_init(&bars->v_full[i], kLoaderThreads);
+      mbar_init(&bars->v_full[i], TMA_KV ? 32 : kLoaderThreads);
       mbar_init(&bars->v_landed[i], 1);
       mbar_init(&bars->k_empty[i], 1);
       mbar_init(&bars->v_empty[i], 1);
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->s_empty[i], kSoftmaxWarps * 32);
+      mbar_init(&bars->s_empty[i], kGroupThreads);
+      mbar_init(&bars->p_full[i], kGroupThreads);
+      mbar_init(&bars->pv_done[i], 1);
     }
-    mbar_init(&bars->p_full, kSoftmaxWarps * 32);
-    mbar_init(&bars->pv_done, 1);
     bars->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -261,11 +273,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   const uint32_t tmem_base = bars->tmem_base;
   pdl_wait();
 
-  // Which (entry, tile of that entry) is this block?  Blocks are numbered from the back, so
-  // that the tiles with the longest history (the last of each entry) start first.
+  // Which (entry, tile of that entry) is this block?  Blocks are numbered from the back, and
+  // the heads run along x (the index that changes fastest as blocks are handed out), so that
+  // the tiles with the longest history, of every head, start first.
   int entry = -1, tile_in_entry = 0;
   {
-    int remaining = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+    int remaining = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);
     for (int e = 0; e < p.num_entries; ++e) {
       const int tiles = (p.entry_starts[e + 1] - p.entry_starts[e] + kQ - 1) / kQ;
       if (remaining < tiles) { entry = e; tile_in_entry = remaining; break; }
@@ -273,7 +286,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     }
   }
   int num_tiles = 0, first_tile = 0, token0 = 0, tokens_here = 0, pos0 = 0, first_key = 0, end_key = 0;
-  const int head = blockIdx.y;
+  const int head = blockIdx.x;
   const int kv_head = head / (p.num_heads / p.num_kv_heads);
   if (entry >= 0) {
     token0 = p.entry_starts[entry] + tile_in_entry * kQ;
@@ -286,55 +299,62 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   }
 
   if (warp < kSoftmaxWarps) {
-    // ---------------- softmax and ending: thread = (query row, half of the columns) ----------------
+    // ---------------- softmax and ending: thread = query row, group = every other key tile ----------------
     // Warps w and w + 4 share the rows 32 (w % 4) .. + 31 (a warp reaches only its quarter of
-    // the tensor memory's lanes) and take 64 columns each; two warps per scheduler hide each
-    // other's latencies.  The two halves of a row agree on the row's max through shared memory.
-    const int quarter = warp & 3, half = warp >> 2;
+    // the tensor memory's lanes); they belong to different groups and so work on different key
+    // tiles, independently, and fill each other's waits.
+    const int quarter = warp & 3, group = warp >> 2;
     const int row = quarter * 32 + lane;
-    const int col0 = half * kHalfCols;
     const int position = pos0 + row;
     const int row_limit = row < tokens_here ? position : -1;  // rows past the entry's end see nothing
     const int row_first = p.window > 0 ? max(0, position - p.window + 1) : 0;
     const float scale_log2 = p.scale * kLog2e;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t s_addr = lane_base + (group ? kColsS1 : kColsS0);
+    const uint32_t o_addr = lane_base + (group ? kColsO1 : kColsO0);
+    uint8_t* p_tile = p_tiles + group * kTileBytes;
+    const int group_tiles = (num_tiles - group + 1) / 2;  // tiles group, group + 2, ...
     float row_max = -INFINITY, row_sum = 0.0f;
 #ifdef VIPERA_ATTN_TIMING
     long long w_s = 0, w_pv = 0, c_p1 = 0, c_rs = 0, c_p2 = 0;
 #endif
-    for (int j = 0; j < num_tiles; ++j) {
-      const int buffer = j & 1;
-      const uint32_t s_addr = lane_base + (buffer ? kColsS1 : kColsS0) + col0;
-      const int key0 = (first_tile + j) * kKeys + col0;
+    for (int i = 0; i < group_tiles; ++i) {
+      const int j = 2 * i + group;
+      const int key0 = (first_tile + j) * kKeys;
       ATT_T(t0);
-      mbar_wait(&bars->s_full[buffer], static_cast<uint32_t>(j >> 1) & 1u, abort_flag, p.status);
+      mbar_wait(&bars->s_full[group], static_cast<uint32_t>(i) & 1u, abort_flag, p.status);
       tcgen05_fence_after();
       ATT_T(t1);
       ATT_ADD(w_s, t0, t1);
+      if (quarter == 0 && lane == 0) ATT_EVENT(2, j);
       // does any row of this block need a mask in this tile?
-      const bool edge = (first_tile + j) * kKeys + kKeys - 1 > pos0 ||
-                        (p.window > 0 && (first_tile + j) * kKeys < pos0 + tokens_here - p.window + 1) || tokens_here < kQ;
-      // the thread's 64 scores into registers; the accumulator is then free for the next tile but one
-      uint32_t sv[kHalfCols];
-#pragma unroll
-      for (int c = 0; c < kHalfCols; c += 32) tmem_load_32_nowait(s_addr + c, *reinterpret_cast<uint32_t(*)[32]>(&sv[c]));
-      tmem_load_wait();
-      tcgen05_fence_before();
-      mbar_arrive(&bars->s_empty[buffer]);
-      // the row's largest visible score
+      const bool edge = key0 + kKeys - 1 > pos0 || (p.window > 0 && key0 < pos0 + tokens_here - p.window + 1) || tokens_here < kQ;
+      // first pass over the row's 128 scores: the largest visible one
       float tile_max = -INFINITY;
-      if (edge) {
+#pragma unroll 1
+      for (int c = 0; c < kKeys; c += 64) {
+        uint32_t sv[64];
+        tmem_load_32_nowait(s_addr + c, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        tmem_load_32_nowait(s_addr + c + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+        tmem_load_wait();
+        if (edge) {
 #pragma unroll
-        for (int i = 0; i < kHalfCols; ++i) {
-          const int key = key0 + i;
-          if (key < row_first || key > row_limit) sv[i] = __float_as_uint(-INFINITY);
+          for (int k = 0; k < 64; ++k) {
+            const int key = key0 + c + k;
+            if (key < row_first || key > row_limit) sv[k] = __float_as_uint(-INFINITY);
+          }
         }
-      }
+        // four chains, so that the 128 comparisons do not wait for one another
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < kHalfCols; ++i) tile_max = fmaxf(tile_max, __uint_as_float(sv[i]));
-      bars->half_max[buffer][half][row] = tile_max;
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-      tile_max = fmaxf(tile_max, bars->half_max[buffer][half ^ 1][row]);
+        for (int k = 0; k < 64; k += 4) {
+          m0 = fmaxf(m0, __uint_as_float(sv[k]));
+          m1 = fmaxf(m1, __uint_as_float(sv[k + 1]));
+          m2 = fmaxf(m2, __uint_as_float(sv[k + 2]));
+          m3 = fmaxf(m3, __uint_as_float(sv[k + 3]));
+        }
+        tile_max = fmaxf(tile_max, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+      }
       tile_max *= scale_log2;
       // The running max only has to keep the exponentials in range: it follows the row's true
       // max when that has grown by more than kMaxSlack (weights then stay below 2^kMaxSlack,
@@ -345,148 +365,191 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       const float alpha = new_max == row_max ? 1.0f : fast_exp2(row_max - new_max);
       row_max = new_max;
       row_sum *= alpha;
-      // the output accumulator and the P tile are free once the products of the tile before are done
+      // the group's output accumulator and P tile are free once the product of its tile before is done
       ATT_T(t2);
       ATT_ADD(c_p1, t1, t2);
-      if (j > 0) mbar_wait(&bars->pv_done, static_cast<uint32_t>(j - 1) & 1u, abort_flag, p.status);
+      if (quarter == 0 && lane == 0) ATT_EVENT(3, j);
+      if (i > 0) mbar_wait(&bars->pv_done[group], static_cast<uint32_t>(i - 1) & 1u, abort_flag, p.status);
       tcgen05_fence_after();
       ATT_T(t3);
       ATT_ADD(w_pv, t2, t3);
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+      if (quarter == 0 && lane == 0) ATT_EVENT(4, j);
+      if (i > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
-        for (int c = 0; c < kHalfCols; c += 32) {
+        for (int c = 0; c < kD; c += 32) {
           uint32_t v[32];
-          tmem_load_32(lane_base + kColsO + col0 + c, v);
+          tmem_load_32(o_addr + c, v);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_store_32(lane_base + kColsO + col0 + c, v);
+          for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) * alpha);
+          tmem_store_32(o_addr + c, v);
         }
         tmem_store_wait();
       }
-      // p = 2^(s * scale * log2 e - max), summed in 32-bit, rounded to bfloat16 into the P tile
+      // second pass: p = 2^(s * scale * log2 e - max), summed in 32-bit, rounded to bfloat16 into the P tile
       ATT_T(t4);
       ATT_ADD(c_rs, t3, t4);
-      float tile_sum = 0.0f;
+      float tile_sum = 0.0f, tile_sum_b = 0.0f;
       const float shift = row_max == -INFINITY ? 0.0f : row_max;  // a row without visible keys: 2^(-inf) = 0 everywhere
-#pragma unroll
-      for (int c = 0; c < kHalfCols; c += 8) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c + i]), scale_log2, -shift));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c + i + 1]), scale_log2, -shift));
-          tile_sum += p0 + p1;
-          __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
-          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+#pragma unroll 1
+      for (int c = 0; c < kKeys; c += 64) {
+        uint32_t sv[64];
+        tmem_load_32_nowait(s_addr + c, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        tmem_load_32_nowait(s_addr + c + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+        tmem_load_wait();
+        if (c + 64 == kKeys) {
+          // the scores are in registers: the accumulator is free for the group's next tile
+          tcgen05_fence_before();
+          mbar_arrive(&bars->s_empty[group]);
+          if (quarter == 0 && lane == 0) ATT_EVENT(9, j);
         }
-        *reinterpret_cast<uint4*>(p_tile + tile_offset(row, (col0 + c) >> 3)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        if (edge) {
+#pragma unroll
+          for (int k = 0; k < 64; ++k) {
+            const int key = key0 + c + k;
+            if (key < row_first || key > row_limit) sv[k] = __float_as_uint(-INFINITY);
+          }
+        }
+#pragma unroll
+        for (int k8 = 0; k8 < 64; k8 += 8) {
+          uint32_t packed[4];
+#pragma unroll
+          for (int k = 0; k < 8; k += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[k8 + k]), scale_log2, -shift));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[k8 + k + 1]), scale_log2, -shift));
+            tile_sum += p0;
+            tile_sum_b += p1;
+            __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+            packed[k >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+          }
+          *reinterpret_cast<uint4*>(p_tile + tile_offset(row, (c + k8) >> 3)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
       }
-      row_sum += tile_sum;
+      row_sum += tile_sum + tile_sum_b;
       // P is written: hand it over to the MMA warp
       tcgen05_fence_before();
       fence_async_shared();
-      mbar_arrive(&bars->p_full);
+      mbar_arrive(&bars->p_full[group]);
       ATT_T(t5);
       ATT_ADD(c_p2, t4, t5);
+      if (quarter == 0 && lane == 0) ATT_EVENT(5, j);
     }
 #ifdef VIPERA_ATTN_TIMING
-    if (blockIdx.x == 1 && blockIdx.y == 0 && threadIdx.x == 0 && num_tiles > 0)
-      printf("softmax: tiles %d wait_s %lld pass1 %lld wait_pv %lld rescale %lld pass2 %lld (cycles per tile)\n", num_tiles,
-             w_s / num_tiles, c_p1 / num_tiles, w_pv / num_tiles, c_rs / num_tiles, c_p2 / num_tiles);
+    if (blockIdx.y == 1 && blockIdx.x == 0 && lane == 0 && quarter == 0 && group_tiles > 0)
+      printf("softmax group %d: tiles %d wait_s %lld pass1 %lld wait_pv %lld rescale %lld pass2 %lld (cycles per tile)\n", group,
+             group_tiles, w_s / group_tiles, c_p1 / group_tiles, w_pv / group_tiles, c_rs / group_tiles, c_p2 / group_tiles);
 #endif
-    // ---------------- ending: out = O / sum ----------------
+    // ---------------- ending: join the two groups' folds, out = O / sum ----------------
     if (num_tiles > 0) {
-      // the row's sum is the sum of its two halves
-      bars->half_sum[half][row] = row_sum;
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-      row_sum += bars->half_sum[half ^ 1][row];
-      mbar_wait(&bars->pv_done, static_cast<uint32_t>(num_tiles - 1) & 1u, abort_flag, p.status);
+      // A group's last product must be done before its P tile carries the group's max and sum
+      // to the other group (and before anyone reads its output accumulator).
+      if (group_tiles > 0) mbar_wait(&bars->pv_done[group], static_cast<uint32_t>(group_tiles - 1) & 1u, abort_flag, p.status);
       tcgen05_fence_after();
-      const float inverse = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;
+      float2* told = reinterpret_cast<float2*>(p_tile);
+      told[row] = make_float2(row_max, row_sum);
+      tcgen05_fence_before();
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      const float2 other = reinterpret_cast<const float2*>(p_tiles + (group ^ 1) * kTileBytes)[row];
+      tcgen05_fence_after();
+      const bool other_has_tiles = group == 1 || num_tiles > 1;  // the other group's accumulator holds numbers
+      const float joint_max = fmaxf(row_max, other.x);
+      const float own_weight = row_max == -INFINITY ? 0.0f : fast_exp2(row_max - joint_max);
+      const float other_weight = other.x == -INFINITY ? 0.0f : fast_exp2(other.x - joint_max);
+      const float joint_sum = row_sum * own_weight + other.y * other_weight;
+      const float inverse = joint_sum > 0.0f ? 1.0f / joint_sum : 0.0f;
+      const float own_factor = own_weight * inverse, other_factor = other_weight * inverse;
+      const uint32_t other_o = lane_base + (group ? kColsO0 : kColsO1);
+      const bool own_has_tiles = group_tiles > 0;
+      // each group writes half of the row's columns
+      const int col0 = group * kHalfCols;
       __nv_bfloat16* dst = p.out + (static_cast<size_t>(token0 + row) * p.num_heads + head) * kD + col0;
 #pragma unroll 1
       for (int c = 0; c < kHalfCols; c += 32) {
-        uint32_t v[32];
-        tmem_load_32(lane_base + kColsO + col0 + c, v);
+        uint32_t v[32], w[32];
+        if (own_has_tiles) tmem_load_32_nowait(o_addr + col0 + c, v);
+        if (other_has_tiles) tmem_load_32_nowait(other_o + col0 + c, w);
+        tmem_load_wait();
         if (row < tokens_here && !*abort_flag) {
+          float joined[32];
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
+          for (int k = 0; k < 32; ++k) {
+            joined[k] = own_has_tiles ? __uint_as_float(v[k]) * own_factor : 0.0f;
+            if (other_has_tiles) joined[k] = fmaf(__uint_as_float(w[k]), other_factor, joined[k]);
+          }
+#pragma unroll
+          for (int k = 0; k < 32; k += 8) {
             uint4 packed;
             __nv_bfloat162* halves = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-            for (int h = 0; h < 4; ++h)
-              halves[h] = __floats2bfloat162_rn(__uint_as_float(v[i + 2 * h]) * inverse, __uint_as_float(v[i + 2 * h + 1]) * inverse);
-            *reinterpret_cast<uint4*>(dst + c + i) = packed;
+            for (int h = 0; h < 4; ++h) halves[h] = __floats2bfloat162_rn(joined[k + 2 * h], joined[k + 2 * h + 1]);
+            *reinterpret_cast<uint4*>(dst + c + k) = packed;
           }
         }
       }
     }
     tcgen05_fence_before();
-  } else if (warp == kMmaWarp) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0 && num_tiles > 0) {
+  } else if (warp < kFirstLoaderWarp) {
+    // ---------------- MMA issuers, one per softmax group ----------------
+    const int g = warp - kMmaWarp;
+    const int group_tiles = (num_tiles - g + 1) / 2;
+    if (lane == 0 && group_tiles > 0) {
       // instruction descriptors: bf16 x bf16 -> f32, M = 128, N = 128; B K-major for the scores, MN-major for the output
       constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) | (static_cast<uint32_t>(kQ >> 4) << 24);
       constexpr uint32_t kIdescO = kIdescS | (1u << 16);
-      const uint32_t q_addr = smem_u32(q_tile), p_addr = smem_u32(p_tile);
-#ifdef VIPERA_ATTN_TIMING
-      long long m_k = 0, m_s = 0, m_v = 0, m_p = 0;
-#endif
-      auto issue_scores = [&](int j) {
-        const int buffer = j & 1;
-        ATT_T(a0);
-        mbar_wait(&bars->k_full[buffer], static_cast<uint32_t>(j >> 1) & 1u, abort_flag, p.status);
-        ATT_T(a1);
-        mbar_wait(&bars->s_empty[buffer], (static_cast<uint32_t>(j >> 1) & 1u) ^ 1u, abort_flag, p.status);
-        ATT_T(a2);
-        ATT_ADD(m_k, a0, a1);
-        ATT_ADD(m_s, a1, a2);
+      const uint32_t q_addr = smem_u32(q_tile);
+      // Tile j belongs to softmax group j & 1 and is that group's tile number j >> 1; its keys
+      // and values lie in buffer j & 1 as well.  The two groups drift against one another, so
+      // each has an issuer of its own, which follows its group's order of events: the scores
+      // of the next tile as soon as the group has taken the current ones into registers (in the
+      // middle of its second pass), then the output product of the current tile when P is written.
+      const uint32_t k_addr = smem_u32(k_tiles + g * kTileBytes);
+      const uint32_t v_addr = smem_u32(v_tiles + g * kTileBytes);
+      const uint32_t p_addr = smem_u32(p_tiles + g * kTileBytes);
+      const uint32_t s_tmem = tmem_base + (g ? kColsS1 : kColsS0);
+      const uint32_t o_tmem = tmem_base + (g ? kColsO1 : kColsO0);
+      auto issue_scores = [&](int i) {   // the group's tile i
+        mbar_wait(&bars->k_full[g], static_cast<uint32_t>(i) & 1u, abort_flag, p.status);
+        if (i > 0) mbar_wait(&bars->s_empty[g], static_cast<uint32_t>(i - 1) & 1u, abort_flag, p.status);
+        ATT_EVENT(0, 2 * i + g);
         tcgen05_fence_after();
-        const uint32_t k_addr = smem_u32(k_tiles + buffer * kTileBytes);
-        const uint32_t d_tmem = tmem_base + (buffer ? kColsS1 : kColsS0);
 #pragma unroll
         for (int ks = 0; ks < kD / 16; ++ks) {
           // 16 values further along the row: 32 bytes inside a half, the other half after 4 steps
           const uint32_t offset = static_cast<uint32_t>((ks >> 2) * kHalfBytes + (ks & 3) * 32);
-          tcgen05_mma_bf16(d_tmem, desc_k_major(q_addr + offset), desc_k_major(k_addr + offset), kIdescS, ks > 0 ? 1u : 0u);
+          tcgen05_mma_bf16(s_tmem, desc_k_major(q_addr + offset), desc_k_major(k_addr + offset), kIdescS, ks > 0 ? 1u : 0u);
         }
-        tcgen05_commit(&bars->k_empty[buffer]);
-        tcgen05_commit(&bars->s_full[buffer]);
+        tcgen05_commit(&bars->k_empty[g]);
+        tcgen05_commit(&bars->s_full[g]);
       };
       mbar_wait(&bars->q_full, 0, abort_flag, p.status);
       issue_scores(0);
-      for (int j = 0; j < num_tiles; ++j) {
-        if (j + 1 < num_tiles) issue_scores(j + 1);
-        const int buffer = j & 1;
-        ATT_T(b0);
-        mbar_wait(&bars->v_full[buffer], static_cast<uint32_t>(j >> 1) & 1u, abort_flag, p.status);
-        ATT_T(b1);
-        mbar_wait(&bars->p_full, static_cast<uint32_t>(j) & 1u, abort_flag, p.status);
-        ATT_T(b2);
-        ATT_ADD(m_v, b0, b1);
-        ATT_ADD(m_p, b1, b2);
+      for (int i = 0; i < group_tiles; ++i) {
+        // With TMA the next keys land without a loader thread's doing, so their scores can be
+        // asked for first.  The cp.async loaders hand tiles over in one fixed order, in which
+        // they wait for this tile's output product before they hand over the next keys: there
+        // the output product goes first.
+        if (TMA_KV && i + 1 < group_tiles) issue_scores(i + 1);
+        const int key0 = (first_tile + 2 * i + g) * kKeys;
+        const bool zeroed_rows = key0 < first_key || key0 + kKeys > end_key;  // then a loader warp hands the tile over (as the cp.async path always does)
+        mbar_wait(&bars->p_full[g], static_cast<uint32_t>(i) & 1u, abort_flag, p.status);
+        mbar_wait((zeroed_rows || !TMA_KV) ? &bars->v_full[g] : &bars->v_landed[g], static_cast<uint32_t>(i) & 1u, abort_flag, p.status);
+        ATT_EVENT(1, 2 * i + g);
         tcgen05_fence_after();
-        const uint32_t v_addr = smem_u32(v_tiles + buffer * kTileBytes);
 #pragma unroll
         for (int ks = 0; ks < kKeys / 16; ++ks) {
           // P: 16 keys further along its rows; V: 16 rows (two groups of 8) further down
           const uint32_t p_offset = static_cast<uint32_t>((ks >> 2) * kHalfBytes + (ks & 3) * 32);
-          tcgen05_mma_bf16(tmem_base + kColsO, desc_k_major(p_addr + p_offset), desc_mn_major(v_addr + ks * 2048), kIdescO,
-                           (j > 0 || ks > 0) ? 1u : 0u);
+          tcgen05_mma_bf16(o_tmem, desc_k_major(p_addr + p_offset), desc_mn_major(v_addr + ks * 2048), kIdescO,
+                           (i > 0 || ks > 0) ? 1u : 0u);
         }
-        tcgen05_commit(&bars->v_empty[buffer]);
-        tcgen05_commit(&bars->pv_done);
+        tcgen05_commit(&bars->v_empty[g]);
+        tcgen05_commit(&bars->pv_done[g]);
+        if (!TMA_KV && i + 1 < group_tiles) issue_scores(i + 1);
       }
-#ifdef VIPERA_ATTN_TIMING
-      if (blockIdx.x == 1 && blockIdx.y == 0)
-        printf("mma: wait k_full %lld s_empty %lld v_full %lld p_full %lld (cycles per tile)\n", m_k / num_tiles, m_s / num_tiles,
-               m_v / num_tiles, m_p / num_tiles);
-#endif
     }
     tcgen05_fence_before();
   } else {
     // ---------------- loaders: queries once, then keys and values tile by tile ----------------
-    const int t = threadIdx.x - (kMmaWarp + 1) * 32;  // 0..127
+    const int t = threadIdx.x - kFirstLoaderWarp * 32;  // 0..127
     if (num_tiles > 0) {
       const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
       for (int index = t; index < kQ * 16; index += kLoaderThreads) {
@@ -501,11 +564,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         const int rows_per_box = min(p.page_size, kKeys);
         const int boxes = kKeys / rows_per_box;
         const int loader_warp = t >> 5;
-        auto issue_boxes = [&](int j, const CUtensorMap* map, const CUtensorMap* run_map, uint8_t* tile, uint64_t* landed) {
+        // the page a lane's box lies in (-1: no visible key in it, or no such box)
+        auto look_up = [&](int j) {
           const int key = (first_tile + j) * kKeys + lane * rows_per_box;
           int page = -1;
-          // a box is fetched when it holds a visible key; the others stay as they are (keys) or are zeroed (values)
           if (lane < boxes && key + rows_per_box > first_key && key < end_key) page = table[key / p.page_size];
+          return page;
+        };
+        auto issue_boxes = [&](int j, int page, const CUtensorMap* map, const CUtensorMap* run_map, uint8_t* tile, uint64_t* landed) {
+          const int key = (first_tile + j) * kKeys + lane * rows_per_box;
+          // a box is fetched when it holds a visible key; the others stay as they are (keys) or are zeroed (values)
           const unsigned fetched = __ballot_sync(0xffffffffu, page >= 0);
           // Pages that follow one another in memory (what a fresh request gets) are fetched as one
           // run of 128 rows: two boxes instead of two per page.  Rows of the run past the pages
@@ -532,44 +600,53 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
             tma_load_box(dst + kHalfBytes, map, landed, 64, kv_head, key % p.page_size, page);
           }
         };
-        auto issue_keys = [&](int j) {
-          const int buffer = j & 1;
-          if (j >= 2) mbar_wait(&bars->k_empty[buffer], static_cast<uint32_t>((j >> 1) - 1) & 1u, abort_flag, p.status);
-          if (!*abort_flag) issue_boxes(j, &k_map, &k_run_map, k_tiles + buffer * kTileBytes, &bars->k_full[buffer]);
+        // Four streams with waits of their own, a loader warp each: the keys and the values of
+        // either softmax group's tiles (a key buffer is free once the scores of the group's tile
+        // before are computed, a value buffer once that tile's output product is done, which is
+        // much later; and the groups drift against one another).  The block table entries of a
+        // stream's next tile are read before the wait for this tile's buffer, so that the read
+        // adds to no wait.
+        const int stream_group = loader_warp >> 1;
+        const bool values = (loader_warp & 1) != 0;
+        const int stream_tiles = (num_tiles - stream_group + 1) / 2;
+        int pages = stream_tiles > 0 ? look_up(stream_group) : -1;
+        auto issue_tile = [&](int i) {   // the group's tile i
+          const int j = 2 * i + stream_group;
+          const int page = pages;
+          if (i + 1 < stream_tiles) pages = look_up(j + 2);
+          uint64_t* empty = values ? &bars->v_empty[stream_group] : &bars->k_empty[stream_group];
+          if (i >= 1) mbar_wait(empty, static_cast<uint32_t>(i - 1) & 1u, abort_flag, p.status);
+          if (!*abort_flag) {
+            if (values) issue_boxes(j, page, &v_map, &v_run_map, v_tiles + stream_group * kTileBytes, &bars->v_landed[stream_group]);
+            else issue_boxes(j, page, &k_map, &k_run_map, k_tiles + stream_group * kTileBytes, &bars->k_full[stream_group]);
+          }
+          if (lane == 0) ATT_EVENT(values ? 7 : 6, j);
         };
-        auto issue_values = [&](int j) {
-          const int buffer = j & 1;
-          if (j >= 2) mbar_wait(&bars->v_empty[buffer], static_cast<uint32_t>((j >> 1) - 1) & 1u, abort_flag, p.status);
-          if (!*abort_flag) issue_boxes(j, &v_map, &v_run_map, v_tiles + buffer * kTileBytes, &bars->v_landed[buffer]);
-        };
-        if (loader_warp == 0) {
-          issue_keys(0);
-          issue_values(0);
-          if (num_tiles > 1) { issue_keys(1); issue_values(1); }
-        }
+        if (stream_tiles > 0) issue_tile(0);
         cp_async_wait<0>();
         fence_async_shared();
         mbar_arrive(&bars->q_full);
-        for (int j = 0; j < num_tiles; ++j) {
-          const int buffer = j & 1;
-          const int key0 = (first_tile + j) * kKeys;
-          // a value row that holds no visible key must be zero: its weight is zero, but what lies
-          // in the cache there may be anything
-          mbar_wait(&bars->v_landed[buffer], static_cast<uint32_t>(j >> 1) & 1u, abort_flag, p.status);
+        for (int i = 0; i < stream_tiles; ++i) {
+          if (i >= 1) issue_tile(i);
+          if (!values) continue;
+          // A value row that holds no visible key must be zero: its weight is zero, but what lies
+          // in the cache there may be anything.  Only the first tiles of a window and the last
+          // tile have such rows; the MMA issuer takes every other tile as it lands.
+          const int key0 = (first_tile + 2 * i + stream_group) * kKeys;
           if (key0 < first_key || key0 + kKeys > end_key) {
-            const int key = key0 + t;
-            if (key < first_key || key >= end_key) {
-              uint8_t* tile = v_tiles + buffer * kTileBytes;
+            mbar_wait(&bars->v_landed[stream_group], static_cast<uint32_t>(i) & 1u, abort_flag, p.status);
+            uint8_t* tile = v_tiles + stream_group * kTileBytes;
+            for (int r = lane; r < kKeys; r += 32) {
+              const int key = key0 + r;
+              if (key < first_key || key >= end_key) {
 #pragma unroll
-              for (int chunk = 0; chunk < 16; ++chunk) *reinterpret_cast<uint4*>(tile + tile_offset(t, chunk)) = make_uint4(0, 0, 0, 0);
+                for (int chunk = 0; chunk < 16; ++chunk) *reinterpret_cast<uint4*>(tile + tile_offset(r, chunk)) = make_uint4(0, 0, 0, 0);
+              }
             }
+            fence_async_shared();
           }
-          fence_async_shared();
-          mbar_arrive(&bars->v_full[buffer]);
-          if (loader_warp == 0) {
-            if (j >= 1 && j + 1 < num_tiles) issue_values(j + 1);
-            if (j + 2 < num_tiles) issue_keys(j + 2);
-          }
+          mbar_arrive(&bars->v_full[stream_group]);
+          if (lane == 0) ATT_EVENT(8, 2 * i + stream_group);
         }
       } else {
       // A tile is copied in 16 passes of 8 rows: 16 consecutive threads copy the 16 chunks of
@@ -655,7 +732,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         if (j + 2 < num_tiles) issue_keys(j + 2);
       }
 #ifdef VIPERA_ATTN_TIMING
-      if (blockIdx.x == 1 && blockIdx.y == 0 && t == 0)
+      if (blockIdx.y == 1 && blockIdx.x == 0 && t == 0)
         printf("loader: wait k_empty %lld v_empty %lld issue %lld landing %lld (cycles per tile)\n", l_ke / num_tiles,
                l_ve / num_tiles, l_copy / num_tiles, l_land / num_tiles);
 #endif
@@ -663,13 +740,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     }
   }
   __syncthreads();
+#ifdef VIPERA_ATTN_TIMING
+  if (blockIdx.y == 1 && blockIdx.x == 0 && threadIdx.x == 0 && num_tiles > 0) {
+    const long long base = bars->trace[6][0];
+    printf("tile: K issued, S issued, S seen, pass 1 done, P.V seen done, S taken, P handed, V issued, V handed, P.V issued\n");
+    for (int j = 0; j < min(num_tiles, 16); ++j)
+      printf("%2d: %6lld %6lld %6lld %6lld %6lld %6lld %6lld %6lld %6lld %6lld\n", j, bars->trace[6][j] - base, bars->trace[0][j] - base,
+             bars->trace[2][j] - base, bars->trace[3][j] - base, bars->trace[4][j] - base, bars->trace[9][j] - base,
+             bars->trace[5][j] - base, bars->trace[7][j] - base, bars->trace[8][j] - base, bars->trace[1][j] - base);
+  }
+#endif
   if (warp == kMmaWarp) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));
   }
 }
 
-constexpr int kSmemBytes = 6 * kTileBytes + 1024 /* alignment */ + static_cast<int>(sizeof(Barriers)) + 64;
+constexpr int kSmemBytes = 7 * kTileBytes + 1024 /* alignment */ + static_cast<int>(sizeof(Barriers)) + 64;
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -781,7 +868,7 @@ VIPERA_API int vipera_attention_prefill_tc(const void* q, void* out, const void*
   p.scale = scale;
   p.status = status;
   // at most one partly filled tile per entry beyond the full ones
-  dim3 grid((num_tokens + kQ - 1) / kQ + num_entries, num_heads);
+  dim3 grid(num_heads, (num_tokens + kQ - 1) / kQ + num_entries);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (tma_takes_page(page_size) && std::getenv("VIPERA_ATTENTION_NO_TMA") == nullptr) {
     const CUtensorMap* k_map = pool_map(k_pool, num_pages, page_size, num_kv_heads, false);
