@@ -24,7 +24,9 @@ def _rel(got, want):
 
 
 # ---------------------------------------------------------------------------------------
-@pytest.mark.parametrize("rows,hidden", [(1, 16), (5, 250), (33, 1536), (3, 5000)])
+@pytest.mark.parametrize("rows,hidden", [(1, 16), (5, 250), (33, 1536), (3, 5000),
+                                         # many rows: a warp per row where the width is a multiple of four up to 4096
+                                         (300, 1536), (131, 1000), (200, 3584), (129, 250), (130, 4100), (128, 4096)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_rmsnorm(rows, hidden, dtype):
     ops = _ops()
@@ -36,11 +38,12 @@ def test_rmsnorm(rows, hidden, dtype):
     xd = x.double()
     want = xd * (1.0 / torch.sqrt((xd * xd).mean(-1, keepdim=True) + 1e-5)) * w.double()
     assert _rel(out, want) < (1e-6 if dtype == torch.float32 else 5e-3)
-    # a choice of rows
-    pick = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
-    out2 = torch.empty(2, hidden, device=DEV, dtype=dtype)
+    # a choice of rows (as many as before where there are many, so that the same kernel serves them)
+    chosen = list(range(rows - 1, -1, -1)) if rows >= 128 else [rows - 1, 0]
+    pick = torch.tensor(chosen, dtype=torch.int32, device=DEV)
+    out2 = torch.empty(len(chosen), hidden, device=DEV, dtype=dtype)
     ops.rmsnorm(x, w, out2, 1e-5, rows=pick)
-    assert torch.equal(out2, out[[rows - 1, 0]])
+    assert torch.equal(out2, out[chosen])
 
 
 @pytest.mark.parametrize("table_dtype", [torch.float32, torch.bfloat16])
