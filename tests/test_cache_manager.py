@@ -261,3 +261,46 @@ def test_random_orders_with_shared_prefixes(seed):
     for request in list(live):
         cache.close(request)
     assert cache.audit() == ""
+
+
+def test_decode_step_inputs_are_filled_in_the_graphs_layout():
+    """The native routine behind the decode graphs: tokens, positions, state slots, fresh marks
+    and block tables of the step's requests in one buffer, entries past the step's own
+    repeating its first; -1 for a step that is not a plain decode step; errors for a token
+    outside the vocabulary, a position past the limit, and a position without a page."""
+    cache = manager([(16, 8, 0), (8, 8, 0)], slots=4)
+    for request, length in ((5, 20), (9, 3)):
+        cache.open(request)
+        cache.reserve(request, length)
+    bucket, widths = 4, [2, 4]
+    total = 8 * bucket + 1 + bucket * sum(widths)
+    buffer = np.full(total, -7, dtype=np.int32)
+
+    def fill(tokens, counts, pos0, fresh, rows, requests=(5, 9), vocab=100, limit=64):
+        return cache.fill_decode(list(requests), np.asarray(tokens, dtype=np.int32), counts, pos0, fresh, rows,
+                                 buffer.ctypes.data, bucket, widths, vocab, limit)
+
+    assert fill([11, 22], [1, 1], [19, 2], [0, 1], [0, 1]) == 2
+    b = bucket
+    assert buffer[:b].tolist() == [11, 22, 11, 11]                      # tokens
+    assert buffer[b:2 * b].tolist() == [19, 2, 19, 19]                  # positions
+    assert buffer[2 * b:4 * b + 1].tolist() == [-7] * (2 * b + 1)       # the caller's constant parts
+    assert buffer[4 * b + 1:5 * b + 1].tolist() == [19, 2, 19, 19]      # first positions
+    assert buffer[5 * b + 1:6 * b + 1].tolist() == [0, 1, 0, 0]         # state slots
+    assert buffer[6 * b + 1:7 * b + 1].tolist() == [0, 1, 0, 0]         # fresh
+    assert buffer[7 * b + 1:8 * b + 1].tolist() == [-7] * b
+    first = buffer[8 * b + 1:8 * b + 1 + b * 2].reshape(b, 2)
+    assert first.tolist() == [cache.table(5, 0).tolist(), cache.table(9, 0).tolist() + [-1]] + [cache.table(5, 0).tolist()] * 2
+    second = buffer[8 * b + 1 + b * 2:].reshape(b, 4)
+    assert second[0].tolist() == cache.table(5, 1).tolist() + [-1] and second[1].tolist() == cache.table(9, 1).tolist() + [-1] * 3
+    assert second[2].tolist() == second[0].tolist()
+    # not a plain decode step: a portion of two tokens, rows in another order, fewer rows than entries
+    assert fill([1, 2, 3], [2, 1], [18, 2], [0, 0], [0, 1]) == -1
+    assert fill([1, 2], [1, 1], [19, 2], [0, 0], [1, 0]) == -1
+    assert fill([1, 2], [1, 1], [19, 2], [0, 0], [0]) == -1
+    with pytest.raises(errors.InvalidArgumentError):
+        fill([1, 100], [1, 1], [19, 2], [0, 0], [0, 1])                 # token outside the vocabulary
+    with pytest.raises(errors.InvalidArgumentError):
+        fill([1, 2], [1, 1], [19, 2], [0, 0], [0, 1], limit=19)         # position past the limit
+    with pytest.raises(errors.InvalidArgumentError):
+        fill([1, 2], [1, 1], [19, 9], [0, 0], [0, 1])                   # request 9 has no page of 8 keys for position 9

@@ -153,6 +153,72 @@ PYBIND11_MODULE(_vipera_runtime, m) {
       })
       .def("open_requests", &CacheManager::open_requests)
       .def("audit", &CacheManager::audit)
+      // The inputs of a decode step (every entry one token, every token's logits wanted), written
+      // into a host buffer the caller owns (pinned staging memory) in the layout of the captured
+      // graphs: [tokens b][positions b][token entry b][entry starts b + 1][first positions b]
+      // [state slots b][fresh b][wanted rows b][block table of group g, b x widths[g]] ..., b being
+      // the graph's entry count.  Entries past the step's own repeat its first entry.  The
+      // constant parts (token entry, entry starts, wanted rows) are the caller's.  Returns the
+      // number of entries, or -1 when the step is not of that kind; raises for a step no path
+      // may run.
+      .def("fill_decode",
+           [](const CacheManager& c, const std::vector<int64_t>& requests, py::array_t<int32_t, py::array::c_style | py::array::forcecast> tokens,
+              py::array_t<int32_t, py::array::c_style | py::array::forcecast> counts, py::array_t<int32_t, py::array::c_style | py::array::forcecast> pos0,
+              py::array_t<int32_t, py::array::c_style | py::array::forcecast> fresh, py::array_t<int32_t, py::array::c_style | py::array::forcecast> rows,
+              uintptr_t host, int bucket, const std::vector<int>& widths, int vocab, int max_model_len) -> int {
+             const int n = static_cast<int>(requests.size());
+             if (n == 0 || n > bucket) throw InvalidArgument("a decode step needs between one entry and the graph's entry count");
+             if (counts.size() != n || pos0.size() != n || fresh.size() != n)
+               throw InvalidArgument("requests, counts and first positions must have one item per entry");
+             if (tokens.size() != n || rows.size() != n) return -1;
+             const int32_t* tok = tokens.data();
+             const int32_t* cnt = counts.data();
+             const int32_t* pos = pos0.data();
+             const int32_t* fr = fresh.data();
+             const int32_t* row = rows.data();
+             for (int i = 0; i < n; ++i) {
+               if (cnt[i] != 1 || row[i] != i) return -1;
+             }
+             if (static_cast<int>(widths.size()) != c.num_groups()) throw InvalidArgument("one table width is needed for each group");
+             int32_t* out = reinterpret_cast<int32_t*>(host);
+             const size_t b = static_cast<size_t>(bucket);
+             int32_t* out_tokens = out;
+             int32_t* out_positions = out + b;
+             int32_t* out_pos0 = out + 4 * b + 1;
+             int32_t* out_slots = out + 5 * b + 1;
+             int32_t* out_fresh = out + 6 * b + 1;
+             int32_t* out_tables = out + 8 * b + 1;
+             for (int i = 0; i < n; ++i) {
+               if (tok[i] < 0 || tok[i] >= vocab) throw InvalidArgument("token id outside the vocabulary of " + std::to_string(vocab));
+               if (pos[i] < 0 || pos[i] + 1 > max_model_len)
+                 throw InvalidArgument("request " + std::to_string(requests[i]) + ": position " + std::to_string(pos[i]) +
+                                       " exceeds the limit of " + std::to_string(max_model_len));
+             }
+             for (size_t i = 0; i < b; ++i) {
+               const int from = i < static_cast<size_t>(n) ? static_cast<int>(i) : 0;
+               out_tokens[i] = tok[from];
+               out_positions[i] = pos[from];
+               out_pos0[i] = pos[from];
+               out_slots[i] = c.state_slot(requests[from]);
+               out_fresh[i] = fr[from];
+             }
+             for (int g = 0; g < c.num_groups(); ++g) {
+               const int width = widths[g];
+               const int page_size = c.group(g).page_size;
+               for (size_t i = 0; i < b; ++i) {
+                 const int from = i < static_cast<size_t>(n) ? static_cast<int>(i) : 0;
+                 const std::vector<int32_t>& table = c.table(requests[from], g);
+                 if (static_cast<int>(table.size()) > width) throw InvalidArgument("a block table is longer than the width asked for");
+                 const int page = pos[from] / page_size;
+                 if (page >= static_cast<int>(table.size()) || table[page] < 0)
+                   throw InvalidArgument("a request of the step has no page reserved for its position");
+                 int32_t* dst = out_tables + i * width;
+                 for (int k = 0; k < width; ++k) dst[k] = k < static_cast<int>(table.size()) ? table[k] : -1;
+               }
+               out_tables += b * width;
+             }
+             return n;
+           })
       // Block tables of several requests as one [len(requests), width] int32 array; logical
       // pages a request does not hold are -1.
       .def("tables", [](const CacheManager& c, const std::vector<int64_t>& requests, int g, int width) {

@@ -116,9 +116,8 @@ class Engine:
             outcome = self.scheduler.complete(plan, [])
         else:
             try:
-                step = StepInput(requests=plan.requests, tokens=plan.tokens, counts=plan.counts.tolist(),
-                                 pos0=plan.starts.tolist(), fresh=plan.fresh.tolist(),
-                                 logit_rows=plan.row_token_index)
+                step = StepInput(requests=plan.requests, tokens=plan.tokens, counts=plan.counts, pos0=plan.starts,
+                                 fresh=plan.fresh, logit_rows=plan.row_token_index)
                 logits = self.runner.run(step)
                 if logits is not None:
                     sampled = self.sampler.draw(logits, plan)   # also reads the kernels' status word

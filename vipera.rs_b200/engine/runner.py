@@ -64,6 +64,7 @@ class ModelRunner:
         self._graph_safe = None  # asked of the model once
         self.max_graph_entries = 256
         self._graphs = {}
+        self._page_sizes = [self.manager.group(g)[0] for g in range(self.manager.num_groups)]
         # Decode steps of few tokens run as one persistent kernel where the model qualifies.
         from .fused_decode import FusedDecode
 
@@ -164,37 +165,42 @@ class ModelRunner:
         (a decode step) is replayed from a captured CUDA graph of its size class; every other
         step is launched kernel by kernel."""
         self.steps_run += 1
-        counts = step.counts
+        entries = len(step.counts)
         if self._graph_safe is None:
             self._graph_safe = bool(self.model.graph_safe)
-        if (self.decode_graphs and self._graph_safe and len(counts) <= self.max_graph_entries
-                and max(counts) == 1 and len(step.logit_rows) == len(counts)
-                and np.array_equal(step.logit_rows, np.arange(len(counts)))):
-            return self._run_graph(step)
+        if (self.decode_graphs and self._graph_safe and 0 < entries <= self.max_graph_entries
+                and len(step.tokens) == entries and len(step.logit_rows) == entries):
+            logits = self._run_graph(step)
+            if logits is not None:
+                return logits
         ctx = self.build_context(step, self.model.dtype)
         return self.forward(ctx)
 
     # ------------------------------------------------------------------------------
     # decode steps through CUDA graphs
     # ------------------------------------------------------------------------------
-    def _run_graph(self, step: StepInput) -> torch.Tensor:
-        self.validate(step)
+    def _run_graph(self, step: StepInput) -> Optional[torch.Tensor]:
+        """The step through the graph of its size class, or None when it turns out not to be
+        a plain decode step (the native routine that fills the graph's inputs checks the step)."""
         entries = len(step.counts)
         bucket = _round_up_pow2(entries, 1)
-        pos0 = np.asarray(step.pos0, dtype=np.int32)
+        last = int(max(step.pos0))
         widths = []
-        for g in range(self.manager.num_groups):
-            page_size = self.manager.group(g)[0]
-            widths.append(_round_up_pow2((int(pos0.max()) + page_size) // page_size))
+        for g, page_size in enumerate(self._page_sizes):
+            widths.append(_round_up_pow2((last + page_size) // page_size))
         key = (bucket, tuple(widths))
         graph = self._graphs.get(key)
         if graph is not None and graph.stale():
             graph = None
         if graph is None:
             graph = _DecodeGraph(self, bucket, widths)
+            if graph.fill(step) < 0:
+                return None
             self._graphs[key] = graph
-            graph.capture(step)
-        return graph.replay(step)
+            graph.capture()
+        elif graph.fill(step) < 0:
+            return None
+        return graph.replay(entries)
 
 
 class _DecodeGraph:
@@ -205,13 +211,20 @@ class _DecodeGraph:
     def __init__(self, runner: ModelRunner, bucket: int, widths):
         self.runner = runner
         self.bucket = bucket
-        self.widths = list(widths)
+        self.widths = [int(w) for w in widths]
         b = bucket
         self.sizes = [b, b, b, b + 1, b, b, b, b] + [b * w for w in self.widths]
         self.offsets = np.concatenate([[0], np.cumsum(self.sizes)]).astype(np.int64)
         total = int(self.offsets[-1])
         self.host = torch.empty(total, dtype=torch.int32, pin_memory=True)
         self.dev = torch.empty(total, dtype=torch.int32, device=runner.device)
+        # the parts that are the same in every step: each token is its own entry and wants its logits
+        view, o = self.host.numpy(), self.offsets
+        view[int(o[2]):int(o[3])] = np.arange(b, dtype=np.int32)
+        view[int(o[3]):int(o[4])] = np.arange(b + 1, dtype=np.int32)
+        view[int(o[7]):int(o[8])] = np.arange(b, dtype=np.int32)
+        self.host_address = self.host.data_ptr()
+        self.vocab = int(runner.model.spec.vocab_size)
         self.copy_done = torch.cuda.Event()
         self.pending = False
         self.graph = None
@@ -226,37 +239,17 @@ class _DecodeGraph:
     def _part(self, index):
         return self.dev[int(self.offsets[index]):int(self.offsets[index + 1])]
 
-    def _fill(self, step: StepInput) -> int:
-        runner, b = self.runner, self.bucket
-        n = len(step.counts)
+    def fill(self, step: StepInput) -> int:
+        """The step's inputs into the staging buffer and on their way to the device; -1 (and
+        nothing copied) when the step is not a plain decode step."""
+        runner = self.runner
         if self.pending:
             self.copy_done.synchronize()
-        view = self.host.numpy()
-        o = self.offsets
-
-        def put(index, values):
-            chunk = view[int(o[index]):int(o[index + 1])]
-            chunk[:n] = values
-            chunk[n:] = values[0]
-
-        put(0, np.asarray(step.tokens, dtype=np.int32))
-        pos0 = np.asarray(step.pos0, dtype=np.int32)
-        put(1, pos0)
-        view[int(o[2]):int(o[3])] = np.arange(b, dtype=np.int32)
-        view[int(o[3]):int(o[4])] = np.arange(b + 1, dtype=np.int32)
-        put(4, pos0)
-        put(5, np.asarray([runner.manager.state_slot(r) for r in step.requests], dtype=np.int32))
-        put(6, np.asarray(step.fresh, dtype=np.int32))
-        view[int(o[7]):int(o[8])] = np.arange(b, dtype=np.int32)
-        requests = list(step.requests)
-        for g, width in enumerate(self.widths):
-            table = runner.manager.tables(requests, g, width)
-            page_size = runner.manager.group(g)[0]
-            if (table[np.arange(n), pos0 // page_size] < 0).any():
-                raise InvalidArgumentError("a request of the step has no page reserved for its position")
-            chunk = view[int(o[8 + g]):int(o[9 + g])].reshape(b, width)
-            chunk[:n] = table
-            chunk[n:] = table[0]
+            self.pending = False
+        n = runner.manager.fill_decode(step.requests, step.tokens, step.counts, step.pos0, step.fresh, step.logit_rows,
+                                       self.host_address, self.bucket, self.widths, self.vocab, runner.max_model_len)
+        if n < 0:
+            return n
         self.dev.copy_(self.host, non_blocking=True)
         self.copy_done.record()
         self.pending = True
@@ -274,11 +267,11 @@ class _DecodeGraph:
             all_single=True, dtype=runner.model.dtype, workspace=runner.workspace, logits_all_rows=True,
             extras={"graph": True})
 
-    def capture(self, step: StepInput) -> None:
+    def capture(self) -> None:
+        """Capture the step whose inputs `fill` has just put on their way."""
         from ..kernels import ops
 
         runner = self.runner
-        self._fill(step)
         ctx = self._context()
         # Once outside a graph: buffers get their final sizes, kernels are loaded.  The step's
         # own keys and values are written here and again, identically, by the replay.
@@ -293,10 +286,9 @@ class _DecodeGraph:
         self.graph = graph
         self.generations = (runner.workspace.generation, ops.buffer_generation)
 
-    def replay(self, step: StepInput) -> torch.Tensor:
+    def replay(self, entries: int) -> torch.Tensor:
         from ..kernels import ops
 
-        n = self._fill(step)
         self.graph.replay()
         ops.launches += self.kernels
-        return self.logits[:n]
+        return self.logits if entries == self.bucket else self.logits[:entries]
