@@ -155,3 +155,46 @@ def test_a_prompt_seen_before_shares_its_pages(dtype):
     assert plain_engine.stats()["kv_kept_pages"] == 0
     _, windowed = _engine("B", dtype, page_size=32, ctx=256, max_num_seqs=2)
     assert not windowed.pools.manager.reuse
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_change_no_token(dtype):
+    """Greedy decoding with the step after launched before a step's tokens are read: the same
+    tokens as without it, also where a request ends on an end token while the step after it
+    already runs (that step is dropped), where a request arrives in the middle of decoding,
+    and where requests of different lengths end one after the other."""
+    from vipera_rs_b200 import SamplingParams
+
+    vocab = helpers.CONFIGS["A"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, 900 + n) for n in (3, 20, 41)]
+    folder, plain_engine = _engine("A", dtype, page_size=16, ctx=160, max_num_seqs=4, lookahead=False)
+    _, ahead_engine = _engine("A", dtype, page_size=16, ctx=160, max_num_seqs=4, lookahead=True)
+    lengths = [SamplingParams(max_new_tokens=n) for n in (30, 9, 17)]
+    want = plain_engine.generate(prompts, lengths)
+    got = ahead_engine.generate(prompts, lengths)
+    assert [g.tokens for g in got] == [w.tokens for w in want]
+    assert ahead_engine.steps_ahead > 0 and plain_engine.steps_ahead == 0
+    _check_greedy(folder, prompts[0], got[0].tokens, dtype)
+    # an end token in the middle: the first token the first request produces after its third
+    # that it has not produced before
+    produced = want[0].tokens
+    first = next(i for i in range(3, len(produced)) if produced[i] not in produced[:i])
+    stop = SamplingParams(max_new_tokens=30, eos_ids=[produced[first]])
+    for engine in (plain_engine, ahead_engine):
+        result = engine.generate([prompts[0], prompts[2]], [stop, SamplingParams(max_new_tokens=17)])
+        assert result[0].finish == "stop" and result[0].tokens == want[0].tokens[:first + 1]
+        assert result[1].tokens == want[2].tokens
+    assert ahead_engine.steps_ahead_dropped > 0
+    # a request that arrives while another decodes
+    request = ahead_engine.add_request(prompts[1], SamplingParams(max_new_tokens=9))
+    for _ in range(4):
+        ahead_engine.step()
+    late = ahead_engine.add_request(prompts[2], SamplingParams(max_new_tokens=17))
+    results = {}
+    while ahead_engine.has_work():
+        for generation in ahead_engine.step().finished:
+            results[generation.request] = generation.tokens
+    assert results[request] == want[1].tokens and results[late] == want[2].tokens
+    assert ahead_engine.pools.manager.audit() == "" and plain_engine.pools.manager.audit() == ""
+    stats = ahead_engine.stats()
+    assert stats["sequences"] == 0 and stats["kv_used_pages"] == stats["kv_kept_pages"]

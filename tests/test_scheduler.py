@@ -340,3 +340,77 @@ def test_a_request_put_back_finds_its_own_pages_again():
     assert engine.finished[2]["tokens"] == expected_tokens([(i * 7 + 1) % VOCAB for i in range(20)], 12)
     put_back = [item for item in engine.finished.values() if item["preemptions"] >= 1]
     assert put_back and all(item["reused_tokens"] >= 16 for item in put_back)
+
+
+def test_the_step_after_is_foreseen_only_where_nothing_can_change_it():
+    """plan_ahead(): true in a step where every running request decodes greedily and cannot end
+    but by an end token; the pages for the token after are then reserved, and the next
+    schedule() returns the same requests one position further.  False with a request waiting,
+    a prompt portion in the step, a temperature, a penalty, or a request at its last token."""
+    engine = ToyEngine(pages=32, max_num_seqs=2, budget=64, portion=64)
+    engine.add(1, [3, 4, 5, 6, 7], max_new_tokens=6)
+    engine.add(2, list(range(10, 27)), max_new_tokens=40)
+    plan = engine.scheduler.schedule()
+    assert not engine.scheduler.plan_ahead(plan)             # prompt portions
+    engine.scheduler.complete(plan, [11, 12])
+    foreseen = 0
+    for step in range(12):
+        plan = engine.scheduler.schedule()
+        if plan.empty:
+            break
+        ahead = engine.scheduler.plan_ahead(plan)
+        starts, requests = plan.starts.copy(), list(plan.requests)
+        if ahead:
+            foreseen += 1
+            for request, start in zip(requests, starts):      # the page of the token after is there
+                assert engine.cache.table(request, 0)[(start + 1) // 16] >= 0
+        outcome = engine.scheduler.complete(plan, [20 + step] * plan.num_rows)
+        assert engine.cache.audit() == ""
+        following = engine.scheduler.schedule()
+        if ahead:
+            assert not outcome["finished"]
+            assert list(following.requests) == requests and (following.starts == starts + 1).all()
+            assert (following.counts == 1).all() and following.all_greedy
+        # undo nothing: the plan just made is simply completed in the next round
+        outcome = engine.scheduler.complete(following, [50 + step] * following.num_rows)
+        assert engine.cache.audit() == ""
+    assert foreseen >= 1
+
+    # a request at its last token by the limit is not foreseen; one waiting blocks it too
+    engine = ToyEngine(pages=32, max_num_seqs=1, budget=64, portion=64)
+    engine.add(1, [3, 4, 5], max_new_tokens=2)
+    engine.add(2, [9, 9], max_new_tokens=8)
+    plan = engine.scheduler.schedule()
+    engine.scheduler.complete(plan, [7])                       # first token of request 1; request 2 waits
+    plan = engine.scheduler.schedule()
+    assert not engine.scheduler.plan_ahead(plan)               # request 2 waits, and request 1 ends with this token
+    outcome = engine.scheduler.complete(plan, [8])
+    assert [item["request"] for item in outcome["finished"]] == [1]
+    plan = engine.scheduler.schedule()                         # request 2's prompt
+    engine.scheduler.complete(plan, [5])
+    plan = engine.scheduler.schedule()
+    assert engine.scheduler.plan_ahead(plan)                   # alone, greedy, 7 tokens to go
+    engine.scheduler.complete(plan, [6])
+
+    for params in ({"temperature": 0.8}, {"temperature": 0.0, "repetition_penalty": 1.3}):
+        engine = ToyEngine(pages=32, max_num_seqs=1)
+        engine.add(1, [3, 4, 5], max_new_tokens=8, **params)
+        engine.scheduler.complete(engine.scheduler.schedule(), [7])
+        plan = engine.scheduler.schedule()
+        assert not engine.scheduler.plan_ahead(plan)
+        engine.scheduler.complete(plan, [7])
+
+
+def test_a_request_that_ends_after_its_next_step_was_foreseen_gives_every_page_back():
+    engine = ToyEngine(pages=8, page_size=4, max_num_seqs=2)
+    engine.add(1, [3, 4, 5, 6], max_new_tokens=20, eos_ids=[42])
+    engine.scheduler.complete(engine.scheduler.schedule(), [7])
+    plan = engine.scheduler.schedule()
+    assert engine.scheduler.plan_ahead(plan)
+    used = engine.cache.stats(0)["used_pages"]
+    assert used == 2                                           # positions 0..5: the token after has its page
+    outcome = engine.scheduler.complete(plan, [42])            # the end token, drawn while the step after ran
+    assert [item["reason"] for item in outcome["finished"]] == ["stop"]
+    assert engine.cache.stats(0)["used_pages"] == engine.cache.stats(0)["kept_pages"]
+    assert engine.cache.audit() == ""
+    assert not engine.scheduler.has_work()

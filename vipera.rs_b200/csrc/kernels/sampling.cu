@@ -438,6 +438,22 @@ int vipera_argmax_static(const float* logits, int rows, int vocab, int* tokens, 
   return vipera_launch_status();
 }
 
+// The tokens a step has drawn become the next step's input without a trip to the host:
+// dst[i] = src[i] for the step's own entries; the entries a captured graph adds to fill its
+// size repeat entry 0, as they do in every other input.
+__global__ void feed_tokens_kernel(const int* __restrict__ src, int* __restrict__ dst, int own, int total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) dst[i] = src[i < own ? i : 0];
+}
+
+VIPERA_API int vipera_feed_tokens(const int* src, int* dst, int own, int total, void* stream) {
+  if (own <= 0 || total < own) return VIPERA_BAD_SHAPE;
+  return vipera_launch(feed_tokens_kernel, dim3((total + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), src, dst,
+                       own, total);
+}
+
 // Wait until everything queued on `stream` so far has run.
 VIPERA_API int vipera_stream_synchronize(void* stream) {
   const cudaError_t error = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));

@@ -347,6 +347,7 @@ PYBIND11_MODULE(_vipera_runtime, m) {
       .def_property_readonly("num_waiting", &Scheduler::num_waiting)
       .def_property_readonly("num_running", &Scheduler::num_running)
       .def("schedule", &Scheduler::schedule)
+      .def("plan_ahead", &Scheduler::plan_ahead)
       .def("complete", [](Scheduler& s, const StepPlan& plan, const std::vector<int32_t>& sampled) {
         return outcome_to_dict(s.complete(plan, sampled));
       })

@@ -243,6 +243,29 @@ StepPlan Scheduler::schedule() {
   return plan;
 }
 
+bool Scheduler::plan_ahead(const StepPlan& plan) {
+  if (plan.entries.empty() || !plan.preempted.empty() || !waiting_.empty() || !cancelled_.empty()) return false;
+  if (plan.entries.size() != running_.size() || plan.rows.size() != plan.entries.size()) return false;
+  for (const StepEntry& entry : plan.entries) {
+    auto it = running_.find(entry.request);
+    if (it == running_.end()) return false;
+    const Request& request = it->second;
+    const int length = static_cast<int>(request.tokens.size());  // before this step's token
+    if (entry.count != 1 || !entry.wants_logits || entry.start + 1 != length) return false;
+    const SamplerConfig& sampler = request.params.sampler;
+    if (sampler.temperature > 0.0f || sampler.has_penalty()) return false;
+    // the ends complete() finds without looking at the token
+    if (length + 1 - request.prompt_len >= request.params.max_new_tokens) return false;
+    if (config_.max_model_len > 0 && length + 1 >= config_.max_model_len) return false;
+    if (!cache_->could_ever_fit(length + 1)) return false;
+  }
+  for (const StepEntry& entry : plan.entries) {
+    if (!cache_->fits(entry.request, entry.start + 2)) return false;  // what was reserved so far stays: harmless
+    cache_->reserve(entry.request, entry.start + 2);
+  }
+  return true;
+}
+
 StepOutcome Scheduler::complete(const StepPlan& plan, const std::vector<int32_t>& sampled) {
   if (sampled.size() != plan.rows.size())
     throw InvalidArgument("complete() needs one sampled token for each row of the plan");

@@ -99,6 +99,14 @@ class Scheduler {
   int num_running() const { return static_cast<int>(running_.size()); }
 
   StepPlan schedule();
+  // Whether the step after `plan` (made by schedule() and not yet completed) is known already:
+  // every running request decodes greedily in `plan`, nobody waits, and none of them can end
+  // with this step's token except by drawing an end token.  If so, the pages for the token
+  // after are reserved now and the caller may launch that step (the same requests, positions
+  // one further, the tokens `plan` draws) before it has read `plan`'s tokens.  The scheduler's
+  // own state does not change: complete() and the next schedule() go on as ever, and the
+  // caller compares what schedule() then returns with what it launched.
+  bool plan_ahead(const StepPlan& plan);
   // `sampled[i]` is the token drawn for plan.rows[i].
   StepOutcome complete(const StepPlan& plan, const std::vector<int32_t>& sampled);
   // The step failed as a whole: its requests end with reason "error" and free their pages

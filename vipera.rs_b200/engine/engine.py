@@ -47,6 +47,23 @@ class StepReport:
     num_entries: int = 0
 
 
+class _Ahead:
+    """A decode step launched before the plan that asks for it exists."""
+
+    __slots__ = ("requests", "positions", "logits", "drawn")
+
+    def __init__(self, requests, positions, logits, drawn):
+        self.requests, self.positions, self.logits, self.drawn = list(requests), positions, logits, drawn
+
+    def serves(self, plan) -> bool:
+        """Whether `plan` is the step that was launched: the same requests, one token each at
+        the positions foreseen, every row drawn greedily."""
+        rows = len(self.requests)
+        return (plan.num_entries == rows and plan.num_tokens == rows and plan.num_rows == rows
+                and plan.all_greedy and not plan.any_penalty and plan.requests == self.requests
+                and np.array_equal(plan.starts, self.positions))
+
+
 class Engine:
     """One model on one GPU, a paged cache and a scheduler.
 
@@ -55,6 +72,9 @@ class Engine:
     with requests that begin with the same tokens (the reference's prefix cache,
     crates/vipera-runtime/src/engine.rs:432-491, which copies them); they are given up, least
     recently used first, when pages are needed.
+    ``lookahead``: while a step of greedy decoding runs, the step after it is launched already
+    where the scheduler can foresee it, so that the host's share of a step (scheduling, input
+    copies, the launch, reading tokens back) hides behind the device's.
     ``ctx`` is the context length each of ``max_num_seqs`` requests can reach with the
     pages allocated (default: the smaller of the model's limit and 2048, as the reference's
     ``--ctx``, bins/vipera/src/main.rs:655-663); ``num_pages`` overrides that sizing.
@@ -63,7 +83,8 @@ class Engine:
     def __init__(self, model, dtype="bfloat16", device="cuda:0", *, page_size: int = 16,
                  num_pages: Optional[int] = None, ctx: Optional[int] = None, max_num_seqs: int = 4,
                  max_tokens_per_step: int = 2048, max_portion: Optional[int] = None,
-                 max_model_len: Optional[int] = None, decode_graphs: bool = True, prefix_cache: bool = True):
+                 max_model_len: Optional[int] = None, decode_graphs: bool = True, prefix_cache: bool = True,
+                 lookahead: bool = True):
         if isinstance(model, str):
             model = load_model(model, dtype, device)
         self.model = model
@@ -87,6 +108,10 @@ class Engine:
         self._next_id = 0
         self.generations = 0
         self.failed = 0
+        self.lookahead = bool(lookahead)
+        self._ahead: Optional[_Ahead] = None
+        self.steps_ahead = 0          # steps launched before their plan existed ...
+        self.steps_ahead_dropped = 0  # ... and those of them whose plan turned out otherwise
 
     # ------------------------------------------------------------------------------
     def add_request(self, prompt_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -112,27 +137,63 @@ class Engine:
         plan = self.scheduler.schedule()
         report = StepReport(preempted=list(plan.preempted), num_tokens=int(plan.num_tokens),
                             num_entries=int(plan.num_entries))
+        ahead, self._ahead = self._ahead, None
         if plan.empty:
             outcome = self.scheduler.complete(plan, [])
         else:
             try:
-                step = StepInput(requests=plan.requests, tokens=plan.tokens, counts=plan.counts, pos0=plan.starts,
-                                 fresh=plan.fresh, logit_rows=plan.row_token_index)
-                logits = self.runner.run(step)
-                if logits is not None:
-                    sampled = self.sampler.draw(logits, plan)   # also reads the kernels' status word
+                drawn = logits = None
+                if ahead is not None and ahead.serves(plan):
+                    # this step was launched while the one before still ran
+                    drawn, logits = ahead.drawn, ahead.logits
+                    ahead = None
+                else:
+                    step = StepInput(requests=plan.requests, tokens=plan.tokens, counts=plan.counts, pos0=plan.starts,
+                                     fresh=plan.fresh, logit_rows=plan.row_token_index)
+                    logits = self.runner.run(step)
+                    if logits is not None:
+                        drawn = self.sampler.launch(logits, plan)
+                if drawn is not None:
+                    if self.lookahead:
+                        self._ahead = self._launch_ahead(plan)
+                    sampled = self.sampler.collect(drawn, logits, plan)   # also reads the kernels' status word
                 else:
                     sampled = []
                     torch.cuda.current_stream().synchronize()
                     ops.check_kernel_status(self.model.device)
                 outcome = self.scheduler.complete(plan, sampled)
+                if self._ahead is not None and outcome["finished"]:
+                    # a request ended on the token just read: the step launched ahead is not the next one
+                    self._ahead = None
+                    self.steps_ahead_dropped += 1
             except InternalError:
+                self._ahead = None
                 outcome = self.scheduler.fail(plan)
                 self.failed += len(outcome["finished"])
                 self._collect(report, outcome)
                 raise
+        if ahead is not None:
+            self.steps_ahead_dropped += 1
         self._collect(report, outcome)
         return report
+
+    def _launch_ahead(self, plan) -> Optional["_Ahead"]:
+        """Where the scheduler can tell what the next step is before this one's tokens are
+        read (everybody decodes greedily and nobody can end but by an end token), launch it now:
+        its input tokens pass from this step's draw to its embedding on the device.  The next
+        call of step() takes it over if its plan is the one foreseen, and drops it otherwise;
+        a dropped step has only written keys and values that the step run in its stead writes
+        again, or that belong to requests that ended."""
+        if not self.scheduler.plan_ahead(plan):
+            return None
+        requests = plan.requests
+        positions = plan.starts + 1
+        rows = len(requests)
+        logits = self.runner.run_ahead(requests, positions, self.sampler.device_tokens(rows))
+        if logits is None:
+            return None
+        self.steps_ahead += 1
+        return _Ahead(requests, positions, logits, self.sampler.launch(logits, None))
 
     def _collect(self, report: StepReport, outcome: dict) -> None:
         report.tokens.extend((int(r), int(t)) for r, t in outcome["tokens"])

@@ -203,6 +203,25 @@ class ModelRunner:
         return graph.replay(entries)
 
 
+    def run_ahead(self, requests: Sequence[int], pos0: np.ndarray, token_source: torch.Tensor) -> Optional[torch.Tensor]:
+        """Launch the decode step of `requests` at positions `pos0` whose input tokens are the
+        first len(requests) of `token_source` (device, int32: what the step before draws), or
+        return None when no captured graph serves it yet.  The pages of the positions must be
+        reserved.  Nothing waits: the step before may still be running."""
+        entries = len(requests)
+        if not (self.decode_graphs and self._graph_safe and 0 < entries <= self.max_graph_entries):
+            return None
+        bucket = _round_up_pow2(entries, 1)
+        last = int(pos0.max())
+        widths = tuple(_round_up_pow2((last + page_size) // page_size) for page_size in self._page_sizes)
+        graph = self._graphs.get((bucket, widths))
+        if graph is None or graph.stale():
+            return None
+        self.steps_run += 1
+        graph.fill_ahead(requests, pos0, token_source)
+        return graph.replay(entries)
+
+
 class _DecodeGraph:
     """One captured decode step for `bucket` entries and block tables of the given widths.
     Steps with fewer entries are padded with copies of their first entry, which computes and
@@ -230,6 +249,7 @@ class _DecodeGraph:
         self.graph = None
         self.logits = None
         self.generations = None
+        self._plain = {}  # per entry count: the constant arrays of a step launched ahead
 
     def stale(self) -> bool:
         from ..kernels import ops
@@ -254,6 +274,27 @@ class _DecodeGraph:
         self.copy_done.record()
         self.pending = True
         return n
+
+    def fill_ahead(self, requests: Sequence[int], pos0: np.ndarray, token_source: torch.Tensor) -> None:
+        """As fill(), for a step whose tokens are still being drawn on the device: everything
+        but the tokens comes from the host, then the tokens are fed from `token_source`."""
+        from ..kernels import ops
+
+        runner = self.runner
+        n = len(requests)
+        if self.pending:
+            self.copy_done.synchronize()
+            self.pending = False
+        plain = self._plain.get(n)
+        if plain is None:
+            plain = self._plain[n] = (np.zeros(n, dtype=np.int32), np.ones(n, dtype=np.int32), np.arange(n, dtype=np.int32))
+        zeros, ones, rows = plain
+        runner.manager.fill_decode(requests, zeros, ones, pos0, zeros, rows, self.host_address, self.bucket, self.widths,
+                                   self.vocab, runner.max_model_len)
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copy_done.record()
+        self.pending = True
+        ops.feed_tokens(token_source, self._part(0), n)
 
     def _context(self) -> StepContext:
         runner, b = self.runner, self.bucket

@@ -61,6 +61,14 @@ def _stream() -> int:
         return torch.cuda.current_stream().cuda_stream
 
 
+def feed_tokens(src: torch.Tensor, dst: torch.Tensor, own: int) -> None:
+    """dst[i] = src[i] for i < own, src[0] for the rest of dst: a step's drawn tokens as the next
+    step's input, on the device."""
+    fn = _function("sampling", "vipera_feed_tokens", [_c_void, _c_void, _c_int, _c_int, _c_void])
+    _check(fn(_gpu(src, "src", torch.int32), _gpu(dst, "dst", torch.int32), int(own), int(dst.numel()), _stream()),
+           "feed_tokens", kernels=1)
+
+
 def stream_synchronize() -> None:
     """Wait for the current stream (a direct call; torch's own builds a stream object first)."""
     fn = _function("sampling", "vipera_stream_synchronize", [_c_void])

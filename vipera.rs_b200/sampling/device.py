@@ -13,20 +13,39 @@ from ..errors import InternalError
 from ..kernels import ops
 
 
+class _Drawn:
+    """Tokens on their way to the host: which pinned buffer, how many rows, and the event
+    recorded behind the copy."""
+
+    __slots__ = ("buffer", "rows", "event")
+
+    def __init__(self, buffer, rows, event):
+        self.buffer, self.rows, self.event = buffer, rows, event
+
+
 class DeviceSampler:
     def __init__(self, device):
         self.device = device
-        self._host = torch.empty(ops._WORDS_HEAD + 2 * ops.SAMPLER_MAX_ROWS, dtype=torch.int32, pin_memory=True)
+        # two pinned buffers: a step's tokens may be read while the step after already copies its own
+        size = ops._WORDS_HEAD + 2 * ops.SAMPLER_MAX_ROWS
+        self._hosts = [torch.empty(size, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._events = [torch.cuda.Event() for _ in range(2)]
+        self._turn = 0
 
-    def draw(self, logits: torch.Tensor, plan) -> List[int]:
+    def device_tokens(self, rows: int) -> torch.Tensor:
+        """Where the tokens of a launch() with `rows` rows lie on the device."""
+        return ops.sampler_words(self.device, rows)[1]
+
+    def launch(self, logits: torch.Tensor, plan) -> _Drawn:
+        """Queue the draw of every row and the copy of the results; nothing waits."""
         rows = logits.shape[0]
         if rows > ops.SAMPLER_MAX_ROWS:
             raise InternalError(f"{rows} rows to sample exceed the sampler's {ops.SAMPLER_MAX_ROWS}")
-        if plan.any_penalty:
+        if plan is not None and plan.any_penalty:
             self._penalties(logits, plan)
         # token ids and row states land beside the kernels' status word: one copy brings all
         whole, tokens, status = ops.sampler_words(self.device, rows)
-        if plan.all_greedy:
+        if plan is None or plan.all_greedy:   # no plan: a greedy step launched ahead of its plan
             ops.argmax(logits, tokens, status)
         else:
             dev = self.device
@@ -37,23 +56,35 @@ class DeviceSampler:
                        min_p=torch.from_numpy(plan.row_min_p).to(dev, non_blocking=True),
                        uniform=torch.from_numpy(plan.row_uniform).to(dev, non_blocking=True),
                        tokens=tokens, status=status)
-        host = self._host[:whole.numel()]
+        turn = self._turn
+        self._turn ^= 1
+        host = self._hosts[turn][:whole.numel()]
         host.copy_(whole, non_blocking=True)
-        ops.stream_synchronize()
-        values = host.tolist()
+        self._events[turn].record()
+        return _Drawn(turn, rows, self._events[turn])
+
+    def collect(self, drawn: _Drawn, logits: torch.Tensor, plan) -> List[int]:
+        """Wait for a launch()'s copy and return its tokens (rows the device could not draw
+        are drawn on the host)."""
+        rows = drawn.rows
+        drawn.event.synchronize()
+        values = self._hosts[drawn.buffer][:ops._WORDS_HEAD + 2 * rows].tolist()
         ops.raise_on_kernel_status(self.device, values[0])
-        drawn = values[ops._WORDS_HEAD:ops._WORDS_HEAD + rows]
+        tokens = values[ops._WORDS_HEAD:ops._WORDS_HEAD + rows]
         codes = values[ops._WORDS_HEAD + rows:]
         for row, code in enumerate(codes):
             if code == ops.SAMPLE_OK:
                 continue
             if code == ops.SAMPLE_NEEDS_HOST:
-                drawn[row] = self._host_draw(logits[row], plan, row)
+                tokens[row] = self._host_draw(logits[row], plan, row)
             elif code == ops.SAMPLE_NO_FINITE:
                 raise InternalError("no finite logits to sample from")
             else:
                 raise InternalError("the distribution has no mass")
-        return drawn
+        return tokens
+
+    def draw(self, logits: torch.Tensor, plan) -> List[int]:
+        return self.collect(self.launch(logits, plan), logits, plan)
 
     def _host_draw(self, row_logits: torch.Tensor, plan, row: int) -> int:
         # Penalties were already applied to the row on the device.
