@@ -366,7 +366,8 @@ def main():
             "peaks": peak_source,
         },
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h},
+                "d2h_bytes_per_step": d2h,
+                "overlap": "Engine.step() launches the step after while a step runs; both copies happen every step"},
         "gpu_launches": timed_launches,
         "prefill": {"value": round(prefill_tokens * 1000.0 / prefill_ms, 1), "tokens": prefill_tokens,
                     "ms": round(prefill_ms, 3), "frac": round(prefill_frac, 4)},
