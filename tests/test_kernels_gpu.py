@@ -70,7 +70,9 @@ def _gemm_reference(a, w, epilogue, bias, resid0):
     return (up * (gate / (1 + torch.exp(-gate)))).reshape(m, n // 2)
 
 
-GEMM_SHAPES = [(1, 48, 40), (3, 130, 72), (17, 1003, 384), (70, 96, 1000), (129, 352, 136), (300, 672, 264)]
+GEMM_SHAPES = [(1, 48, 40), (3, 130, 72), (17, 1003, 384), (70, 96, 1000), (129, 352, 136), (300, 672, 264),
+               # portions of a few hundred tokens over narrow matrices: several token tiles, K cut into splits
+               (700, 520, 1024), (1100, 1536, 200)]
 
 
 @pytest.mark.parametrize("m,n,k", GEMM_SHAPES)

@@ -26,6 +26,10 @@
 // the 32-bit residual stream), SWIGLU over gate and up rows interleaved in groups of 16.
 #include <cuda.h>
 
+#include <map>
+#include <mutex>
+#include <tuple>
+
 #include "common.cuh"
 
 // EPI_DISCARD drops the result: it exists to time the products without their ending.
@@ -690,7 +694,41 @@ static EncodeTiledFn encode_tiled_fn() {
 
 // A [rows, K] bf16 row-major matrix, read in boxes of [box_rows, 64] with 128-byte swizzle;
 // rows and K beyond the matrix read as zero.
+// Maps already made, by what they describe: the same weights and workspace buffers come
+// back step after step, and encoding a map costs about as much as the launch's own
+// bookkeeping.  (A map holds an address and sizes only, so it stays valid while that memory
+// is what the caller says it is.)
+struct MapKey {
+  const void* base;
+  int rows, cols, box_rows, kind;
+  bool operator<(const MapKey& o) const {
+    return std::tie(base, rows, cols, box_rows, kind) < std::tie(o.base, o.rows, o.cols, o.box_rows, o.kind);
+  }
+};
+static std::map<MapKey, CUtensorMap>& kept_maps() {
+  static std::map<MapKey, CUtensorMap> kept;
+  return kept;
+}
+static std::mutex& kept_maps_guard() {
+  static std::mutex guard;
+  return guard;
+}
+static bool find_map(const MapKey& key, CUtensorMap* map) {
+  std::lock_guard<std::mutex> lock(kept_maps_guard());
+  auto found = kept_maps().find(key);
+  if (found == kept_maps().end()) return false;
+  *map = found->second;
+  return true;
+}
+static void keep_map(const MapKey& key, const CUtensorMap& map) {
+  std::lock_guard<std::mutex> lock(kept_maps_guard());
+  if (kept_maps().size() > 8192) kept_maps().clear();
+  kept_maps()[key] = map;
+}
+
 static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  const MapKey key{base, rows, K, box_rows, 0};
+  if (find_map(key, map)) return VIPERA_OK;
   EncodeTiledFn encode = encode_tiled_fn();
   if (!encode) return VIPERA_NO_DRIVER_ENTRY;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
@@ -700,11 +738,15 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
   CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? VIPERA_OK : VIPERA_BAD_ARGUMENT;
+  if (r != CUDA_SUCCESS) return VIPERA_BAD_ARGUMENT;
+  keep_map(key, *map);
+  return VIPERA_OK;
 }
 
 // The output as TMA sees it: [rows, cols] of float32 or bfloat16, in boxes of 32 rows x 128 bytes.
 static int make_out_map(CUtensorMap* map, void* base, int rows, int cols, bool bf16) {
+  const MapKey key{base, rows, cols, 32, bf16 ? 1 : 2};
+  if (find_map(key, map)) return VIPERA_OK;
   EncodeTiledFn encode = encode_tiled_fn();
   if (!encode) return VIPERA_NO_DRIVER_ENTRY;
   const int element = bf16 ? 2 : 4;
@@ -715,7 +757,9 @@ static int make_out_map(CUtensorMap* map, void* base, int rows, int cols, bool b
   CUresult r = encode(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims,
                       strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                       CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? VIPERA_OK : VIPERA_BAD_ARGUMENT;
+  if (r != CUDA_SUCCESS) return VIPERA_BAD_ARGUMENT;
+  keep_map(key, *map);
+  return VIPERA_OK;
 }
 
 struct GemmPlan {
@@ -745,6 +789,7 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
   // 32-feature pieces of a row (measured at 64 tokens on a [17920, 1536] matrix with the
   // SwiGLU ending: 14.1 us against 17.4; at 128 tokens 14.4 against 22.8).
   static const int nonswap_from = std::getenv("VIPERA_GEMM_NONSWAP_FROM") ? std::atoi(std::getenv("VIPERA_GEMM_NONSWAP_FROM")) : 33;
+  plan.swap = true;
   if (T >= 128 + 64 || (T >= nonswap_from && N >= 64 * sms)) {
     plan.swap = false;
     plan.tiles_x = (T + kTileX - 1) / kTileX;
@@ -765,8 +810,14 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
     plan.tiles_y = (N + plan.bn - 1) / plan.bn;
     plan.splits = 1;
     plan.k_blocks_per_split = plan.num_k_blocks;
-  } else {
-    plan.swap = true;
+    // A narrow matrix under a portion of a few hundred tokens has tiles for a fraction of the
+    // SMs only (1,536 columns, 512 tokens: 32 tiles), and this form does not cut K.  The other
+    // form does: its tiles of 128 features x 256 tokens are cut along K until every SM has one.
+    // (The q/k/v ending exists in this form only.)
+    static const bool narrow_swaps = std::getenv("VIPERA_GEMM_NARROW_NONSWAP") == nullptr;
+    if (narrow_swaps && epilogue != EPI_ROPE_CACHE && 4 * plan.tiles_x * plan.tiles_y < 3 * sms) plan.swap = true;
+  }
+  if (plan.swap) {
     plan.bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
     plan.tiles_x = (N + kTileX - 1) / kTileX;
     plan.tiles_y = (T + plan.bn - 1) / plan.bn;

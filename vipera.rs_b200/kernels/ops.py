@@ -315,12 +315,20 @@ def raise_on_kernel_status(device, code: int) -> None:
         raise InternalError(f"a tensor-core kernel gave up waiting (code {code}); the step's results are invalid")
 
 
+_workspace_sizes = {}
+
+
 def gemm_tc_workspace(m: int, n: int, k: int):
-    fn = _function("gemm_tc", "vipera_gemm_tc_workspace",
-                   [_c_int, _c_int, _c_int, ctypes.POINTER(ctypes.c_size_t)])
-    scratch = ctypes.c_size_t(0)
-    _check(fn(m, n, k, ctypes.byref(scratch)), "gemm_tc_workspace", kernels=0)
-    return scratch.value
+    size = _workspace_sizes.get((m, n, k))
+    if size is None:
+        fn = _function("gemm_tc", "vipera_gemm_tc_workspace",
+                       [_c_int, _c_int, _c_int, ctypes.POINTER(ctypes.c_size_t)])
+        scratch = ctypes.c_size_t(0)
+        _check(fn(m, n, k, ctypes.byref(scratch)), "gemm_tc_workspace", kernels=0)
+        if len(_workspace_sizes) > 65536:
+            _workspace_sizes.clear()
+        size = _workspace_sizes[(m, n, k)] = scratch.value
+    return size
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE,

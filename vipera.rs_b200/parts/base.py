@@ -73,10 +73,15 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}  # (name, dtype, shape) -> the view handed out last time
         self.frozen = False
         self.generation = 0  # goes up whenever a buffer moves; captured graphs are then stale
 
     def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        shape = tuple(shape)
+        view = self._views.get((name, dtype, shape))
+        if view is not None:
+            return view
         count = 1
         for extent in shape:
             count *= int(extent)
@@ -88,7 +93,13 @@ class Workspace:
             buffer = torch.empty(max(count, 1), dtype=dtype, device=self.device)
             self._buffers[key] = buffer
             self.generation += 1
-        return buffer[:count].view(*shape)
+            # views of the buffer that was replaced are no longer handed out
+            self._views = {k: v for k, v in self._views.items() if (k[0], k[1]) != key}
+        view = buffer[:count].view(*shape)
+        if len(self._views) > 4096:
+            self._views.clear()
+        self._views[(name, dtype, shape)] = view
+        return view
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
