@@ -365,11 +365,19 @@ class _GemmRope(ctypes.Structure):
     ]
 
 
+_rope_takes = {}
+
+
 def gemm_tc_rope_takes(tokens: int, n: int, k: int, head_dim: int) -> bool:
     """Whether the tensor-core product can end with rotation and cache write for these sizes."""
-    fn = getattr(load_kernel_library("gemm_tc"), "vipera_gemm_tc_rope_takes")
-    fn.argtypes, fn.restype = [_c_int] * 4, _c_int
-    return bool(fn(int(tokens), int(n), int(k), int(head_dim)))
+    key = (int(tokens), int(n), int(k), int(head_dim))
+    known = _rope_takes.get(key)
+    if known is None:
+        fn = _function("gemm_tc", "vipera_gemm_tc_rope_takes", [_c_int] * 4)
+        if len(_rope_takes) > 65536:
+            _rope_takes.clear()
+        known = _rope_takes[key] = bool(fn(*key))
+    return known
 
 
 def gemm_tc_rope(a: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor], q_out: torch.Tensor,

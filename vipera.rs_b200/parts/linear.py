@@ -93,12 +93,11 @@ class Linear:
         if (self._tensor_core is None or self.out_features > SMALL_KERNEL_MAX_ROWS
                 or self.in_features > SMALL_KERNEL_MAX_INNER):
             return False
-        most = min(int(os.environ.get("VIPERA_GEMV_MAX_TOKENS", ops.GEMV_MAX_TOKENS)), ops.GEMV_MAX_TOKENS)
-        if tokens > most:
-            return False
         known = self._small_ok.get(tokens)
         if known is None:
-            known = self._small_ok[tokens] = ops.gemv_small_takes(tokens, self.in_features, self.out_features)
+            most = min(int(os.environ.get("VIPERA_GEMV_MAX_TOKENS", ops.GEMV_MAX_TOKENS)), ops.GEMV_MAX_TOKENS)
+            known = self._small_ok[tokens] = (tokens <= most and
+                                              ops.gemv_small_takes(tokens, self.in_features, self.out_features))
         return known
 
     def __call__(self, ctx, a, *, epilogue: int = ops.EPI_STORE,
