@@ -310,6 +310,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     engine = Engine(folder, dtype="float32", page_size=16, num_pages=9, max_num_seqs=3, max_tokens_per_step=32)
     assert any(isinstance(r, FixedState) for r in engine.model.cache_requests.values())
     assert not engine.model.graph_safe
+    assert not engine.lookahead   # a step launched ahead and dropped would move the mixer's state twice
     prompts = [helpers.random_tokens(vocab, n, 10 + n) for n in (30, 45, 20)]
     results = engine.generate(prompts, SamplingParams(max_new_tokens=30))
     assert sum(r.preemptions for r in results) >= 1

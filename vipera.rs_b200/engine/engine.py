@@ -108,7 +108,10 @@ class Engine:
         self._next_id = 0
         self.generations = 0
         self.failed = 0
-        self.lookahead = bool(lookahead)
+        # A step launched ahead may be dropped and run again; keys and values are then written
+        # twice with the same numbers, but a state of fixed size that a mixer updates in place
+        # would move twice.  Models with such state decode step by step.
+        self.lookahead = bool(lookahead) and not self.pools.states
         self._ahead: Optional[_Ahead] = None
         self.steps_ahead = 0          # steps launched before their plan existed ...
         self.steps_ahead_dropped = 0  # ... and those of them whose plan turned out otherwise
