@@ -195,6 +195,14 @@ def test_steps_launched_ahead_change_no_token(dtype):
         for generation in ahead_engine.step().finished:
             results[generation.request] = generation.tokens
     assert results[request] == want[1].tokens and results[late] == want[2].tokens
+    # rows drawn with a temperature (and a top-k the device draws alone) are launched ahead too,
+    # with the draws their generators hand out next: the same tokens
+    sampling = SamplingParams(max_new_tokens=20, temperature=0.9, top_k=50, top_p=0.9, seed=77)
+    before = ahead_engine.steps_ahead
+    drawn_ahead = ahead_engine.generate(prompts, sampling)
+    drawn_plain = plain_engine.generate(prompts, sampling)
+    assert [g.tokens for g in drawn_ahead] == [g.tokens for g in drawn_plain]
+    assert ahead_engine.steps_ahead > before
     assert ahead_engine.pools.manager.audit() == "" and plain_engine.pools.manager.audit() == ""
     stats = ahead_engine.stats()
     assert stats["sequences"] == 0 and stats["kv_used_pages"] == stats["kv_kept_pages"]

@@ -414,3 +414,29 @@ def test_a_request_that_ends_after_its_next_step_was_foreseen_gives_every_page_b
     assert engine.cache.stats(0)["used_pages"] == engine.cache.stats(0)["kept_pages"]
     assert engine.cache.audit() == ""
     assert not engine.scheduler.has_work()
+
+
+def test_rows_with_a_temperature_are_foreseen_with_their_next_draws():
+    """With a top-k the device sampler draws alone, a temperature does not stop plan_ahead();
+    peek_uniforms() gives the draws the next schedule() hands out, without taking them."""
+    engine = ToyEngine(pages=32, max_num_seqs=2)
+    engine.add(1, [3, 4, 5], max_new_tokens=12, temperature=0.8, top_k=40, seed=7)
+    engine.add(2, [6, 7], max_new_tokens=12, temperature=0.0)
+    engine.scheduler.complete(engine.scheduler.schedule(), [9, 9])
+    for step in range(4):
+        plan = engine.scheduler.schedule()
+        assert not engine.scheduler.plan_ahead(plan)            # greedy rows only, by default
+        assert engine.scheduler.plan_ahead(plan, 4096)
+        assert not engine.scheduler.plan_ahead(plan, 39)        # a top-k above what the caller's sampler takes
+        peeked = engine.scheduler.peek_uniforms(plan)
+        assert peeked[1] == 0.0 and 0.0 <= peeked[0] < 1.0
+        assert np.array_equal(peeked, engine.scheduler.peek_uniforms(plan))   # looking takes nothing
+        engine.scheduler.complete(plan, [10 + step, 20 + step])
+        following = engine.scheduler.schedule()
+        assert np.array_equal(following.row_uniform, peeked)
+        engine.scheduler.complete(following, [30 + step, 40 + step])
+    # without a top-k the whole vocabulary may be needed on the host: not foreseen
+    engine = ToyEngine(pages=32, max_num_seqs=1)
+    engine.add(1, [3, 4, 5], max_new_tokens=8, temperature=0.8, top_k=0)
+    engine.scheduler.complete(engine.scheduler.schedule(), [7])
+    assert not engine.scheduler.plan_ahead(engine.scheduler.schedule(), 4096)

@@ -347,7 +347,8 @@ PYBIND11_MODULE(_vipera_runtime, m) {
       .def_property_readonly("num_waiting", &Scheduler::num_waiting)
       .def_property_readonly("num_running", &Scheduler::num_running)
       .def("schedule", &Scheduler::schedule)
-      .def("plan_ahead", &Scheduler::plan_ahead)
+      .def("plan_ahead", &Scheduler::plan_ahead, py::arg("plan"), py::arg("max_top_k") = 0)
+      .def("peek_uniforms", [](const Scheduler& s, const StepPlan& plan) { return to_array(s.peek_uniforms(plan)); })
       .def("complete", [](Scheduler& s, const StepPlan& plan, const std::vector<int32_t>& sampled) {
         return outcome_to_dict(s.complete(plan, sampled));
       })

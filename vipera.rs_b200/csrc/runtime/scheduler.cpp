@@ -243,7 +243,22 @@ StepPlan Scheduler::schedule() {
   return plan;
 }
 
-bool Scheduler::plan_ahead(const StepPlan& plan) {
+std::vector<double> Scheduler::peek_uniforms(const StepPlan& plan) const {
+  std::vector<double> draws;
+  draws.reserve(plan.rows.size());
+  for (const SampleRow& row : plan.rows) {
+    auto it = running_.find(row.request);
+    if (it == running_.end() || it->second.params.sampler.temperature <= 0.0f) {
+      draws.push_back(0.0);
+      continue;
+    }
+    Rng generator = it->second.rng;  // a copy: the request's own generator is not advanced
+    draws.push_back(generator.next_f64());
+  }
+  return draws;
+}
+
+bool Scheduler::plan_ahead(const StepPlan& plan, int max_top_k) {
   if (plan.entries.empty() || !plan.preempted.empty() || !waiting_.empty() || !cancelled_.empty()) return false;
   if (plan.entries.size() != running_.size() || plan.rows.size() != plan.entries.size()) return false;
   for (const StepEntry& entry : plan.entries) {
@@ -253,7 +268,8 @@ bool Scheduler::plan_ahead(const StepPlan& plan) {
     const int length = static_cast<int>(request.tokens.size());  // before this step's token
     if (entry.count != 1 || !entry.wants_logits || entry.start + 1 != length) return false;
     const SamplerConfig& sampler = request.params.sampler;
-    if (sampler.temperature > 0.0f || sampler.has_penalty()) return false;
+    if (sampler.has_penalty()) return false;
+    if (sampler.temperature > 0.0f && (sampler.top_k < 1 || sampler.top_k > max_top_k)) return false;
     // the ends complete() finds without looking at the token
     if (length + 1 - request.prompt_len >= request.params.max_new_tokens) return false;
     if (config_.max_model_len > 0 && length + 1 >= config_.max_model_len) return false;

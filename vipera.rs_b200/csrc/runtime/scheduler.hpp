@@ -101,12 +101,18 @@ class Scheduler {
   StepPlan schedule();
   // Whether the step after `plan` (made by schedule() and not yet completed) is known already:
   // every running request decodes greedily in `plan`, nobody waits, and none of them can end
-  // with this step's token except by drawing an end token.  If so, the pages for the token
-  // after are reserved now and the caller may launch that step (the same requests, positions
+  // with this step's token except by drawing an end token, and no row has penalties (they
+  // depend on the token).  If so, the pages for the token after are reserved now and the caller may launch that step (the same requests, positions
   // one further, the tokens `plan` draws) before it has read `plan`'s tokens.  The scheduler's
   // own state does not change: complete() and the next schedule() go on as ever, and the
   // caller compares what schedule() then returns with what it launched.
-  bool plan_ahead(const StepPlan& plan);
+  // `max_top_k`: rows that draw with a temperature are foreseen only with a top-k between 1 and
+  // this bound (what the caller's sampler draws on the device without a second look at the
+  // logits, which the step launched ahead overwrites); 0 foresees greedy rows only.
+  bool plan_ahead(const StepPlan& plan, int max_top_k = 0);
+  // The uniform draws that schedule() will hand the rows of the step after `plan` (one per row of
+  // `plan`, 0 for greedy rows), looked at without being taken.
+  std::vector<double> peek_uniforms(const StepPlan& plan) const;
   // `sampled[i]` is the token drawn for plan.rows[i].
   StepOutcome complete(const StepPlan& plan, const std::vector<int32_t>& sampled);
   // The step failed as a whole: its requests end with reason "error" and free their pages

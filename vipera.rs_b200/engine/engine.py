@@ -47,21 +47,44 @@ class StepReport:
     num_entries: int = 0
 
 
+class _RowsAhead:
+    """What the sampler needs to know about the rows of a step launched ahead: the rows of
+    the step before (the same requests in the same order) with the uniform draws the scheduler
+    will hand out next."""
+
+    any_penalty = False
+    all_greedy = False
+
+    def __init__(self, plan, uniforms: np.ndarray):
+        self.row_temperature, self.row_top_k = plan.row_temperature, plan.row_top_k
+        self.row_top_p, self.row_min_p = plan.row_top_p, plan.row_min_p
+        self.row_uniform = uniforms
+
+    def same_as(self, plan) -> bool:
+        return (not plan.any_penalty and np.array_equal(plan.row_temperature, self.row_temperature)
+                and np.array_equal(plan.row_top_k, self.row_top_k) and np.array_equal(plan.row_top_p, self.row_top_p)
+                and np.array_equal(plan.row_min_p, self.row_min_p) and np.array_equal(plan.row_uniform, self.row_uniform))
+
+
 class _Ahead:
     """A decode step launched before the plan that asks for it exists."""
 
-    __slots__ = ("requests", "positions", "logits", "drawn")
+    __slots__ = ("requests", "positions", "logits", "drawn", "rows")
 
-    def __init__(self, requests, positions, logits, drawn):
+    def __init__(self, requests, positions, logits, drawn, rows):
         self.requests, self.positions, self.logits, self.drawn = list(requests), positions, logits, drawn
+        self.rows = rows  # None: every row greedy
 
     def serves(self, plan) -> bool:
         """Whether `plan` is the step that was launched: the same requests, one token each at
-        the positions foreseen, every row drawn greedily."""
-        rows = len(self.requests)
-        return (plan.num_entries == rows and plan.num_tokens == rows and plan.num_rows == rows
-                and plan.all_greedy and not plan.any_penalty and plan.requests == self.requests
-                and np.array_equal(plan.starts, self.positions))
+        the positions foreseen, every row drawn the way it was drawn."""
+        count = len(self.requests)
+        if not (plan.num_entries == count and plan.num_tokens == count and plan.num_rows == count
+                and plan.requests == self.requests and np.array_equal(plan.starts, self.positions)):
+            return False
+        if self.rows is None:
+            return plan.all_greedy and not plan.any_penalty
+        return self.rows.same_as(plan)
 
 
 class Engine:
@@ -159,7 +182,8 @@ class Engine:
                 if drawn is not None:
                     if self.lookahead:
                         self._ahead = self._launch_ahead(plan)
-                    sampled = self.sampler.collect(drawn, logits, plan)   # also reads the kernels' status word
+                    # also reads the kernels' status word
+                    sampled = self.sampler.collect(drawn, logits, plan, logits_intact=self._ahead is None)
                 else:
                     sampled = []
                     torch.cuda.current_stream().synchronize()
@@ -182,21 +206,23 @@ class Engine:
 
     def _launch_ahead(self, plan) -> Optional["_Ahead"]:
         """Where the scheduler can tell what the next step is before this one's tokens are
-        read (everybody decodes greedily and nobody can end but by an end token), launch it now:
+        read (everybody decodes, greedily or with a top-k the device draws alone, without
+        penalties, and nobody can end but by an end token), launch it now:
         its input tokens pass from this step's draw to its embedding on the device.  The next
         call of step() takes it over if its plan is the one foreseen, and drops it otherwise;
         a dropped step has only written keys and values that the step run in its stead writes
         again, or that belong to requests that ended."""
-        if not self.scheduler.plan_ahead(plan):
+        if not self.scheduler.plan_ahead(plan, ops.SAMPLER_MAX_TOP_K):
             return None
         requests = plan.requests
         positions = plan.starts + 1
-        rows = len(requests)
-        logits = self.runner.run_ahead(requests, positions, self.sampler.device_tokens(rows))
+        count = len(requests)
+        logits = self.runner.run_ahead(requests, positions, self.sampler.device_tokens(count))
         if logits is None:
             return None
         self.steps_ahead += 1
-        return _Ahead(requests, positions, logits, self.sampler.launch(logits, None))
+        rows = None if plan.all_greedy else _RowsAhead(plan, self.scheduler.peek_uniforms(plan))
+        return _Ahead(requests, positions, logits, self.sampler.launch(logits, rows), rows)
 
     def _collect(self, report: StepReport, outcome: dict) -> None:
         report.tokens.extend((int(r), int(t)) for r, t in outcome["tokens"])

@@ -279,6 +279,7 @@ buffer_generation = 0  # goes up whenever a shared kernel buffer moves; captured
 
 
 SAMPLER_MAX_ROWS = 4096
+SAMPLER_MAX_TOP_K = 4096  # the largest top-k the device sampler draws without the host (kMaxCandidates in sampling.cu)
 _WORDS_HEAD = 8  # int32 words in front of the sampler's outputs; the first is the kernel status word
 
 

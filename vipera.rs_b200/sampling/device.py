@@ -63,9 +63,10 @@ class DeviceSampler:
         self._events[turn].record()
         return _Drawn(turn, rows, self._events[turn])
 
-    def collect(self, drawn: _Drawn, logits: torch.Tensor, plan) -> List[int]:
+    def collect(self, drawn: _Drawn, logits: torch.Tensor, plan, logits_intact: bool = True) -> List[int]:
         """Wait for a launch()'s copy and return its tokens (rows the device could not draw
-        are drawn on the host)."""
+        are drawn on the host, from `logits`; ``logits_intact=False`` says that a later step
+        has overwritten them, which is only allowed where no row can need them)."""
         rows = drawn.rows
         drawn.event.synchronize()
         values = self._hosts[drawn.buffer][:ops._WORDS_HEAD + 2 * rows].tolist()
@@ -76,6 +77,8 @@ class DeviceSampler:
             if code == ops.SAMPLE_OK:
                 continue
             if code == ops.SAMPLE_NEEDS_HOST:
+                if not logits_intact:
+                    raise InternalError("a row needs the host sampler, but the step after has overwritten its logits")
                 tokens[row] = self._host_draw(logits[row], plan, row)
             elif code == ops.SAMPLE_NO_FINITE:
                 raise InternalError("no finite logits to sample from")
