@@ -213,15 +213,54 @@ def test_attention_single_tokens(heads, kv_heads, d, page, dtype, window):
     limit = 2e-6 if dtype == torch.float32 else 1e-2
     assert _rel(out.float().cpu().view(entries, heads, d), want) < limit
     if dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS:
-        for chunk_splits in (ops.decode_splits(entries, kv_heads, max(lengths)), (32, 10), (512, 1)):
-            chunk, splits = chunk_splits
-            scratch = torch.full((ops.attention_decode_scratch_floats(entries, heads, d, splits),), float("nan"),
-                                 device=DEV)
-            out2 = torch.full_like(qd, float("nan"))
-            ops.attention_decode(qd, out2, kp, vp, positions=positions, block_table=tb, num_heads=heads,
+        # the one-kernel forms (a cluster of 8 or 16 blocks per entry and KV head, with and without
+        # the next keys on their way) and the two-kernel form
+        for cluster in ("8", "8p", "16", "16p", "0"):
+            os.environ["VIPERA_ATTENTION_CLUSTER"] = cluster
+            try:
+                for chunk_splits in (ops.decode_splits(entries, kv_heads, max(lengths)), (32, 10), (512, 1)):
+                    chunk, splits = chunk_splits
+                    scratch = torch.full((ops.attention_decode_scratch_floats(entries, heads, d, splits),),
+                                         float("nan"), device=DEV)
+                    out2 = torch.full_like(qd, float("nan"))
+                    ops.attention_decode(qd, out2, kp, vp, positions=positions, block_table=tb, num_heads=heads,
+                                         num_kv_heads=kv_heads, head_dim=d, scale=scale, window=window, chunk=chunk,
+                                         num_splits=splits, scratch=scratch)
+                    assert _rel(out2.float().cpu().view(entries, heads, d), want) < limit, (cluster, chunk_splits)
+            finally:
+                os.environ.pop("VIPERA_ATTENTION_CLUSTER", None)
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,page", [(12, 2, 128, 16), (8, 4, 64, 32), (16, 1, 128, 64)])
+@pytest.mark.parametrize("window", [0, 700])
+def test_attention_decode_long_histories(heads, kv_heads, d, page, window):
+    """Decode over histories of up to 5,000 keys, so that a block of the one-kernel form walks
+    several blocks of 128 keys with the next ones on their way, the cluster's blocks get uneven
+    shares (one key; 129 keys: one block has all; lengths that are no multiple of anything) and
+    some blocks of a cluster see no key at all; both forms against the reference."""
+    ops = _ops()
+    lengths = [5000, 1, 129, 2047, 1025, 3333, 128, 640, 4096, 77, 2500, 911]
+    entries = len(lengths)
+    lengths, counts, table, k_pool, v_pool, keys, values, q = _paged_case(
+        entries, heads, kv_heads, d, page, torch.bfloat16, seed=heads + d + window, lengths=lengths)
+    scale = 1.0 / math.sqrt(d)
+    want = _attention_reference(q, keys, values, lengths, counts, heads, kv_heads, scale, window)
+    _give_back_passed_pages(table, k_pool, v_pool, lengths, counts, page, window)
+    qd = q.to(torch.bfloat16).reshape(entries, heads * d).to(DEV)
+    kp, vp, tb = k_pool.to(DEV), v_pool.to(DEV), table.to(DEV)
+    positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+    chunk, splits = ops.decode_splits(entries, kv_heads, 8192)
+    for cluster in ("8", "8p", "16", "16p", "0"):
+        os.environ["VIPERA_ATTENTION_CLUSTER"] = cluster
+        try:
+            scratch = torch.full((ops.attention_decode_scratch_floats(entries, heads, d, splits),), float("nan"), device=DEV)
+            out = torch.full_like(qd, float("nan"))
+            ops.attention_decode(qd, out, kp, vp, positions=positions, block_table=tb, num_heads=heads,
                                  num_kv_heads=kv_heads, head_dim=d, scale=scale, window=window, chunk=chunk,
                                  num_splits=splits, scratch=scratch)
-            assert _rel(out2.float().cpu().view(entries, heads, d), want) < limit, chunk_splits
+            assert _rel(out.float().cpu().view(entries, heads, d), want) < 1e-2, cluster
+        finally:
+            os.environ.pop("VIPERA_ATTENTION_CLUSTER", None)
 
 
 @pytest.mark.parametrize("heads,kv_heads,d,page", [(4, 2, 64, 16), (3, 1, 128, 32), (5, 5, 48, 8), (12, 2, 128, 64)])

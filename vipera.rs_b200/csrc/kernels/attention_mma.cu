@@ -327,6 +327,208 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
   out[row * D + threadIdx.x] = __float2bfloat16_rn(value / total);
 }
 
+// ---------------------------------------------------------------------------------------
+// Decode attention as one kernel: the splits of an (entry, KV head) form a thread-block
+// cluster, keep their partial results in their own shared memory and combine them through
+// distributed shared memory, so that no partial goes to global memory and no second kernel
+// runs.  A block walks its share of the keys 128 at a time (32 per warp) with the next 128
+// already on their way.  The share is cut from the entry's own length, not from the longest
+// length the step allows, so the cluster's blocks carry equal loads.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+// a float at `local` (a shared-memory address of this block) in the block of rank `rank`
+__device__ __forceinline__ float cluster_load(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  float value;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
+  return value;
+}
+
+template <int D, int kClusterBlocks, bool PREFETCH>
+__global__ void __launch_bounds__(128, PREFETCH ? 1 : 3)
+attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+                                const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
+                                const int* __restrict__ block_table, int table_width, int page_size, int page_shift,
+                                int num_heads, int num_kv_heads, float scale, int window, __nv_bfloat16* __restrict__ out) {
+  constexpr int kKeys = 32;
+  constexpr int kWarpTile = 2 * kKeys * D * 2;  // bytes of one warp's key and value tiles
+  constexpr int kRow = D + 4;                   // floats of a partial row: D outputs, max, sum, padding
+  static_assert(16 * kRow * 4 <= kWarpTile, "a warp's partial must fit in its tiles");
+  extern __shared__ __align__(128) uint8_t smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int entry = blockIdx.x, kv_head = blockIdx.y;
+  const int rank = static_cast<int>(cluster_rank());
+  const int group = num_heads / num_kv_heads;   // at most 16 (the launcher sees to it)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int position = positions[entry];
+  const int* table = block_table + static_cast<size_t>(entry) * table_width;
+  const int first_visible = window > 0 ? max(0, position - window + 1) : 0;
+  // this block's share of the visible keys, in steps of 128
+  const int first = first_visible / kKeys * kKeys;
+  const int visible = position + 1 - first;
+  const int chunk = ((visible + kClusterBlocks - 1) / kClusterBlocks + 127) / 128 * 128;
+  const int begin = first + rank * chunk;
+  const int end = min(begin + chunk, position + 1);
+
+  uint8_t* q_bytes = smem;                                              // [16][D] bf16
+  constexpr int kBuffers = PREFETCH ? 2 : 1;
+  uint8_t* warp_bytes = smem + 16 * D * 2 + warp * kBuffers * kWarpTile;  // one or two buffers of (keys, values)
+  float* merged = reinterpret_cast<float*>(smem + 16 * D * 2 + 4 * kBuffers * kWarpTile);  // [16][kRow]
+  const uint32_t q_tile = smem_addr(q_bytes);
+  const uint32_t tiles = smem_addr(warp_bytes);
+
+  // queries of the group, and this warp's first block of keys
+  {
+    constexpr int kChunks = D / 8;
+    for (int index = threadIdx.x; index < 16 * kChunks; index += 128) {
+      const int row = index / kChunks, c = index % kChunks;
+      const bool valid = row < group;
+      const __nv_bfloat16* src = q + (static_cast<size_t>(entry) * num_heads + kv_head * group + (valid ? row : 0)) * D + c * 8;
+      cp_async_16(q_tile + tile_offset<D>(row, c), src, valid);
+    }
+  }
+  int key0 = begin + warp * kKeys;
+  if (key0 < end)
+    load_kv_rows32<D>(tiles, tiles + kKeys * D * 2, k_pool, v_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0,
+                      first_visible, end, lane);
+  cp_async_commit();
+
+  float acc[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+  const int row_first[2] = {first_visible, first_visible};
+  const int row_limit[2] = {position, position};
+  const float scale_log2 = scale * kLog2e;
+  uint32_t q_frag[D / 16][4];
+  bool have_q = false;
+  int buffer = 0;
+  for (; key0 < end; key0 += 4 * kKeys, buffer ^= PREFETCH ? 1 : 0) {
+    const uint32_t k_tile = tiles + buffer * kWarpTile, v_tile = k_tile + kKeys * D * 2;
+    const int next = key0 + 4 * kKeys;
+    if (PREFETCH && next < end) {
+      const uint32_t k_next = tiles + (buffer ^ 1) * kWarpTile;
+      load_kv_rows32<D>(k_next, k_next + kKeys * D * 2, k_pool, v_pool, table, page_size, page_shift, num_kv_heads, kv_head,
+                        next, first_visible, end, lane);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      if (!PREFETCH && key0 != begin + warp * kKeys) {
+        load_kv_rows32<D>(k_tile, v_tile, k_pool, v_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0,
+                          first_visible, end, lane);
+        cp_async_commit();
+      }
+      cp_async_wait<0>();
+    }
+    if (!have_q) {
+      __syncthreads();  // the queries were copied by all threads; every warp with keys comes here once
+      have_q = true;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks)
+        ldmatrix_x4(q_frag[ks], q_tile + tile_offset<D>(lane & 15, ks * 2 + (lane >> 4)));
+    }
+    __syncwarp();
+    fold_block<D, kKeys>(q_frag, k_tile, v_tile, key0, row_first, row_limit, scale_log2, row_max, row_sum, acc);
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+  if (!have_q) __syncthreads();  // warps without keys meet the others at the same barrier
+
+  // each warp leaves its partial in its own first buffer: [16 rows][kRow] floats
+  float* mine = reinterpret_cast<float*>(warp_bytes);
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float sum = row_sum[r];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    const int row = (lane >> 2) + r * 8;
+    float* dst = mine + row * kRow;
+    if ((lane & 3) == 0) {
+      dst[D] = row_max[r];
+      dst[D + 1] = sum;
+    }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      const int col = n * 8 + 2 * (lane & 3);
+      dst[col] = acc[n][2 * r];
+      dst[col + 1] = acc[n][2 * r + 1];
+    }
+  }
+  __syncthreads();
+  // the block's four partials become one: thread = (row, eighth of the columns)
+  {
+    const int row = threadIdx.x >> 3, part = threadIdx.x & 7;
+    float m[4], best = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      m[w] = reinterpret_cast<const float*>(smem + 16 * D * 2 + w * kBuffers * kWarpTile)[row * kRow + D];
+      best = fmaxf(best, m[w]);
+    }
+    float weight[4], total = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      weight[w] = m[w] == -INFINITY ? 0.0f : exp2f(m[w] - best);
+      total += weight[w] * reinterpret_cast<const float*>(smem + 16 * D * 2 + w * kBuffers * kWarpTile)[row * kRow + D + 1];
+    }
+    if (part == 0) {
+      merged[row * kRow + D] = best;
+      merged[row * kRow + D + 1] = total;
+    }
+#pragma unroll
+    for (int c = 0; c < D / 8; c += 4) {
+      const int col = part * (D / 8) + c;
+      float4 value = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float4 v = *reinterpret_cast<const float4*>(
+            reinterpret_cast<const float*>(smem + 16 * D * 2 + w * kBuffers * kWarpTile) + row * kRow + col);
+        value.x += weight[w] * v.x;
+        value.y += weight[w] * v.y;
+        value.z += weight[w] * v.z;
+        value.w += weight[w] * v.w;
+      }
+      *reinterpret_cast<float4*>(merged + row * kRow + col) = value;
+    }
+  }
+  // every block's partial is in place; the blocks share the heads among them and each reads
+  // the eight partials of its heads through distributed shared memory
+  cluster_sync_all();
+  const uint32_t merged_addr = smem_addr(merged);
+  for (int head_in_group = rank; head_in_group < group; head_in_group += kClusterBlocks) {
+    const int col = threadIdx.x;
+    if (col < D) {
+      float maxima[kClusterBlocks], best = -INFINITY;
+#pragma unroll
+      for (int b = 0; b < kClusterBlocks; ++b) {
+        maxima[b] = cluster_load(merged_addr + (head_in_group * kRow + D) * 4, b);
+        best = fmaxf(best, maxima[b]);
+      }
+      float total = 0.0f, value = 0.0f;
+#pragma unroll
+      for (int b = 0; b < kClusterBlocks; ++b) {
+        const float w = maxima[b] == -INFINITY ? 0.0f : exp2f(maxima[b] - best);  // a block that saw no key
+        total += w * cluster_load(merged_addr + (head_in_group * kRow + D + 1) * 4, b);
+        value += w * cluster_load(merged_addr + (head_in_group * kRow + col) * 4, b);
+      }
+      const int head = kv_head * group + head_in_group;
+      out[(static_cast<size_t>(entry) * num_heads + head) * D + col] = __float2bfloat16_rn(value / total);
+    }
+  }
+  // nobody leaves while its partial may still be read
+  cluster_sync_all();
+}
+
 template <int D, int HPC>
 int launch_prefill_variant(const void* q, void* out, const void* k_pool, const void* v_pool, const int* entry_starts,
                            const int* entry_pos0, const int* block_table, int table_width, int page_size,
@@ -359,6 +561,71 @@ int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_p
                                       page_size, num_entries, num_tokens, num_heads, num_kv_heads, scale, window, s);
 }
 
+// The one-kernel form serves a step of few entries whose groups of heads fit one MMA tile.
+// How many blocks a cluster has is chosen by how many clusters the step has (an experiment
+// may force a form: VIPERA_ATTENTION_CLUSTER=8p, 8, 16p, 16, where p keeps the next keys on
+// their way; "0" means the two-kernel form always).
+struct ClusterChoice {
+  int blocks;     // 0: the two-kernel form
+  bool prefetch;
+};
+static ClusterChoice cluster_decode_choice(int num_entries, int num_heads, int num_kv_heads, int max_keys) {
+  const char* choice = std::getenv("VIPERA_ATTENTION_CLUSTER");
+  if ((choice && choice[0] == '0') || num_heads / num_kv_heads > 16) return {0, false};
+  if (choice && choice[0] == '8') return {8, choice[1] == 'p'};
+  if (choice && choice[0] == '1') return {16, choice[2] == 'p'};
+  // Measured on the 1.5B shape at 2,048 keys (ms a step; two-kernel form, 8 blocks, 16 blocks):
+  // batch 1: 1.60, 1.52, 1.47; batch 2: 1.60, 1.53, 1.44; batch 4: 1.68, 1.49, 1.56; batch 8: 1.60,
+  // 1.64, 1.78; batch 64: 2.42, 3.56, 5.24.  Clusters pay where the step has few blocks and the
+  // second kernel is a large part of it; with many clusters their placement costs more than
+  // the second kernel did.  A block's share is kept to about 512 keys.
+  const long clusters = static_cast<long>(num_entries) * num_kv_heads;
+  if (clusters <= 4 && max_keys <= 8192) return {16, true};
+  if (clusters <= 8 && max_keys <= 4096) return {8, true};
+  return {0, false};
+}
+
+template <int D, int BLOCKS, bool PREFETCH>
+int launch_decode_cluster(const void* q, void* out, const void* k_pool, const void* v_pool, const int* positions,
+                          const int* block_table, int table_width, int page_size, int page_shift, int num_entries,
+                          int num_heads, int num_kv_heads, float scale, int window, cudaStream_t s) {
+  constexpr int kSmem = 16 * D * 2 + 4 * (PREFETCH ? 2 : 1) * (2 * 32 * D * 2) + 16 * (D + 4) * 4;
+  static int configured = 0;  // 1: ready, -1: this cluster size cannot be launched here
+  if (configured == 0) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_cluster_kernel<D, BLOCKS, PREFETCH>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e == cudaSuccess && BLOCKS > 8)
+      e = cudaFuncSetAttribute(attention_decode_cluster_kernel<D, BLOCKS, PREFETCH>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      configured = -1;
+    } else {
+      configured = 1;
+    }
+  }
+  if (configured < 0) return VIPERA_BAD_SHAPE;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(num_entries, num_kv_heads, BLOCKS);
+  config.blockDim = dim3(128);
+  config.dynamicSmemBytes = kSmem;
+  config.stream = s;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[0].val.programmaticStreamSerializationAllowed = vipera_pdl_enabled() ? 1 : 0;
+  attributes[1].id = cudaLaunchAttributeClusterDimension;
+  attributes[1].val.clusterDim.x = 1;
+  attributes[1].val.clusterDim.y = 1;
+  attributes[1].val.clusterDim.z = BLOCKS;
+  config.attrs = attributes;
+  config.numAttrs = 2;
+  cudaError_t error = cudaLaunchKernelEx(&config, attention_decode_cluster_kernel<D, BLOCKS, PREFETCH>,
+                                         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
+                                         static_cast<const __nv_bfloat16*>(v_pool), positions, block_table, table_width,
+                                         page_size, page_shift, num_heads, num_kv_heads, scale, window,
+                                         static_cast<__nv_bfloat16*>(out));
+  return error == cudaSuccess ? VIPERA_OK : static_cast<int>(error);
+}
+
 template <int D>
 int launch_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int* positions,
                   const int* block_table, int table_width, int page_size, int num_entries, int num_heads,
@@ -370,6 +637,19 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
     page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
   }
+  const ClusterChoice cluster = cluster_decode_choice(num_entries, num_heads, num_kv_heads, chunk * num_splits);
+  if (cluster.blocks == 8 && cluster.prefetch)
+    return launch_decode_cluster<D, 8, true>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size,
+                                             page_shift, num_entries, num_heads, num_kv_heads, scale, window, s);
+  if (cluster.blocks == 8)
+    return launch_decode_cluster<D, 8, false>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size,
+                                              page_shift, num_entries, num_heads, num_kv_heads, scale, window, s);
+  if (cluster.blocks == 16 && cluster.prefetch)
+    return launch_decode_cluster<D, 16, true>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size,
+                                              page_shift, num_entries, num_heads, num_kv_heads, scale, window, s);
+  if (cluster.blocks == 16)
+    return launch_decode_cluster<D, 16, false>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size,
+                                               page_shift, num_entries, num_heads, num_kv_heads, scale, window, s);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
