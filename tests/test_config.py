@@ -74,12 +74,12 @@ def test_model_spec_is_layer_by_layer():
     config = Qwen2Config.from_dict(helpers.TINY_B)
     spec = qwen2_model_spec(config)
     assert len(spec.layers) == 3 and [e.layer for e in spec.schedule] == [0, 1, 2]
-    windows = [layer.mixer.params["window"] for layer in spec.layers]
+    windows = [layer.parts["mixer"].params["window"] for layer in spec.layers]
     assert windows == [None, 80, 80]                # layers from max_window_layers up see a window
     assert spec.head_name == "lm_head.weight"
     tied = qwen2_model_spec(Qwen2Config.from_dict(helpers.TINY_A))
     assert tied.head_name is None
-    assert tied.layers[0].mixer.params["position"].params["theta"] == 10000.0
+    assert tied.layers[0].parts["mixer"].params["position"].params["theta"] == 10000.0
     assert spec.layers[0].part_prefix("mixer") == "model.layers.0.self_attn"
 
 

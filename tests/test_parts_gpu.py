@@ -205,17 +205,17 @@ def test_feed_forward_and_block_parts(dtype, tokens):
     block_tensors["L.n2.weight"] = 1 + 0.1 * torch.randn(hidden, generator=g)
     norm = PartSpec("rmsnorm", {"size": hidden, "eps": 1e-5})
     spec = LayerSpec(
-        block="prenorm", prefix="L", mixer_norm=norm, ffn_norm=norm,
-        mixer=PartSpec("gqa_attention", {
+        block="prenorm", prefix="L", parts={"mixer_norm": norm, "ffn_norm": norm,
+        "mixer": PartSpec("gqa_attention", {
             "hidden_size": hidden, "num_heads": heads, "num_kv_heads": kv_heads, "head_dim": d, "qkv_bias": True,
             "window": None, "softmax_scale": 1 / math.sqrt(d),
             "position": PartSpec("rope_neox", {"head_dim": d, "theta": 10000.0, "max_positions": 512})}),
-        ffn=PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": inter}),
+        "ffn": PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": inter})},
         names={"mixer_norm": "n1", "mixer": "att", "ffn_norm": "n2", "ffn": "ffn"})
     block_cls = BLOCKS.find("prenorm")
     assert set(block_cls.schema(spec)) == set(block_tensors)
     block = block_cls(spec, block_tensors, dtype, DEV)
-    pools, runner = _context(dtype, {0: block.mixer.cache_request()}, [])
+    pools, runner = _context(dtype, {0: block.cache_request()}, [])
     ctx = _step(pools, runner, [(0, 0, tokens, 1)])
     x0 = torch.randn(tokens, hidden, generator=g)
     x = x0.to(DEV)
@@ -372,6 +372,65 @@ def test_toy_feed_forward_with_routing_is_registered_built_and_stepped():
                                 env_extra={"VIPERA_PLUGINS": _toy_plugin()})
     reference = {name: _plain_toy_routed(folder, tokens) for name, tokens in requests.items()}
     worst = helpers.compare(outputs, builder, reference, 1e-4, "toy routed model")
+    assert worst < 1e-4
+
+
+def _plain_toy_arranged(folder, tokens):
+    """Layer 0 with four norms and half-weight branches, layer 1 with mixer and feed-forward side
+    by side under one norm, embedding rows times three; by the plain functions."""
+    config, weights = plain.read_config(folder), plain.read_weights(folder)
+    n = len(tokens)
+    heads, kv_heads, d, eps = config["heads"], config["kv_heads"], config["head_dim"], config["eps"]
+    sin, cos = plain.rope_angles(range(n), d, config["rope_base"])
+
+    def attend(p, h):
+        proj = lambda name: h @ weights[p + f"self_attn.{name}.weight"].double().T + weights[p + f"self_attn.{name}.bias"].double()  # noqa: E731
+        q = plain.rope_neox(proj("q_proj").view(n, heads, d), sin, cos)
+        k = plain.rope_neox(proj("k_proj").view(n, kv_heads, d), sin, cos)
+        v = proj("v_proj").view(n, kv_heads, d)
+        return plain.attention(q, k, v).reshape(n, heads * d) @ weights[p + "self_attn.o_proj.weight"].double().T
+
+    def feed(p, h):
+        return plain.swiglu(h, weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"],
+                            weights[p + "mlp.down_proj.weight"])
+
+    x = 3.0 * plain.embedding(weights["model.embed_tokens.weight"], tokens, torch.float64)
+    p = "model.layers.0."
+    branch = attend(p, plain.rms_norm(x, weights[p + "input_layernorm.weight"], eps))
+    x = x + 0.5 * plain.rms_norm(branch, weights[p + "post_mixer_norm.weight"], eps)
+    branch = feed(p, plain.rms_norm(x, weights[p + "post_attention_layernorm.weight"], eps))
+    x = x + 0.5 * plain.rms_norm(branch, weights[p + "post_ffn_norm.weight"], eps)
+    p = "model.layers.1."
+    h = plain.rms_norm(x, weights[p + "input_layernorm.weight"], eps)
+    x = x + attend(p, h) + feed(p, h)
+    h = plain.rms_norm(x, weights["model.norm.weight"], eps)
+    return (h @ weights["model.embed_tokens.weight"].double().T).numpy()
+
+
+def test_other_arrangements_of_a_layer_need_a_block_class_only():
+    """A layer with four norms, a layer whose mixer and feed-forward run side by side, and scaled
+    embedding rows: two block arrangements registered from the tests and one field of the model's
+    description; replayed in portions beside another request and token by token."""
+    _register_toys()
+    from vipera_rs_b200.config import BLOCKS, load_config, read_config_json
+
+    folder = _toy_folder("ToyArrangedLM", "float32")
+    names = set(plain.read_weights(folder))
+    assert "model.layers.0.post_mixer_norm.weight" in names and "model.layers.0.post_ffn_norm.weight" in names
+    assert "model.layers.1.post_attention_layernorm.weight" not in names   # the parallel layer has one norm
+    assert "toy_sandwich" in BLOCKS and "toy_parallel" in BLOCKS
+    vocab = helpers.TINY_A["vocab_size"]
+    requests = {"a": helpers.random_tokens(vocab, 52, 7), "b": helpers.random_tokens(vocab, 30, 8)}
+    builder = helpers.TraceBuilder()
+    builder.step([("a", requests["a"][:20], range(20)), ("b", requests["b"][:7], range(7))])
+    builder.step([("a", requests["a"][20:22], range(2)), ("b", requests["b"][7:30], range(23))], end=["b"])
+    builder.step([("a", requests["a"][22:40], range(18))])
+    for position in range(40, 52):
+        builder.step([("a", requests["a"][position:position + 1], [0])], end=["a"] if position == 51 else [])
+    outputs = helpers.run_trace(folder, "float32", builder.steps, max_tokens=128, page_size=16,
+                                env_extra={"VIPERA_PLUGINS": _toy_plugin()})
+    reference = {name: _plain_toy_arranged(folder, tokens) for name, tokens in requests.items()}
+    worst = helpers.compare(outputs, builder, reference, 1e-4, "toy arranged model")
     assert worst < 1e-4
 
 

@@ -1,7 +1,9 @@
 """Toy parts and toy architectures for the tests: a mixer with state of its own, another
 position encoding, a feed-forward that routes every token to one of several experts, an
-architecture that mixes both kinds of layer, and one whose execution order names a layer
-twice and lets a layer read another layer's cache.  They are defined and
+architecture that mixes both kinds of layer, one whose execution order names a layer
+twice and lets a layer read another layer's cache, and two other arrangements of a layer (four
+norms around the two sub-layers; mixer and feed-forward side by side under one norm) in a model
+that also scales its embedding rows.  They are defined and
 registered here, outside the package; ``register()`` is called by the tests, and by a process
 that lists this file in VIPERA_PLUGINS (bin/trace_run in the replay tests)."""
 import torch
@@ -10,9 +12,10 @@ import torch
 def register():
     import vipera_rs_b200  # noqa: F401
     from vipera_rs_b200 import parts  # noqa: F401
-    from vipera_rs_b200.config import (ARCHITECTURES, FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, LayerSpec, ModelSpec,
-                                       PartSpec, Qwen2Config, ScheduleEntry, qwen2_model_spec, register_architecture)
-    from vipera_rs_b200.parts import FeedForward, FixedState, Mixer, PositionEncoding
+    from vipera_rs_b200.config import (ARCHITECTURES, BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, LayerSpec,
+                                       ModelSpec, PartSpec, Qwen2Config, ScheduleEntry, qwen2_model_spec,
+                                       register_architecture)
+    from vipera_rs_b200.parts import Block, FeedForward, FixedState, Mixer, NormedInput, PositionEncoding
     from vipera_rs_b200.weights import TensorSpec
 
     if "toy_running_mean" in MIXERS:
@@ -34,8 +37,9 @@ def register():
             self.hidden = params["hidden_size"]
             self.weight = tensors[f"{prefix}.mix.weight"].to(device=device, dtype=torch.float32)
 
-        def cache_request(self):
-            return FixedState((self.hidden + 1,), torch.float32)
+        @classmethod
+        def cache_request_for(cls, params):
+            return FixedState((params["hidden_size"] + 1,), torch.float32)
 
         def forward(self, ctx, h, residual, cache, writes_cache):
             slots, fresh = ctx.state_slots.tolist(), ctx.fresh.tolist()
@@ -101,6 +105,39 @@ def register():
             every = torch.einsum("eti,ehi->eth", torch.relu(torch.einsum("th,eih->eti", x, self.up)), self.down)
             residual += torch.einsum("eth,te->th", every, chosen)
 
+    class SandwichBlock(Block):
+        """Four norms: ``x += post_norm(mixer(pre_norm(x)))`` and the same around the feed-forward.
+        Mixers and feed-forwards add into the stream they are given, so each sub-layer is run on a
+        zeroed stream of its own, which the second norm then reads."""
+
+        roles = {"mixer_norm": NORMS, "mixer": MIXERS, "mixer_post_norm": NORMS,
+                 "ffn_norm": NORMS, "ffn": FEED_FORWARDS, "ffn_post_norm": NORMS}
+
+        def _sub_layer(self, ctx, residual, norm, run, post_norm):
+            branch = torch.zeros_like(residual)
+            run(NormedInput(ctx, norm, residual).tensor(), branch)
+            out = torch.empty(residual.shape, dtype=ctx.dtype, device=residual.device)
+            post_norm.forward(ctx, branch, out)
+            residual += out.float() * self.params.get("branch_scale", 1.0)
+
+        def forward(self, ctx, residual, cache, writes_cache):
+            self._sub_layer(ctx, residual, self.mixer_norm,
+                            lambda h, branch: self.mixer.forward(ctx, h, branch, cache, writes_cache), self.mixer_post_norm)
+            self._sub_layer(ctx, residual, self.ffn_norm,
+                            lambda h, branch: self.ffn.forward(ctx, h, branch), self.ffn_post_norm)
+
+    class ParallelBlock(Block):
+        """One norm; mixer and feed-forward both read it and both add into the stream."""
+
+        roles = {"norm": NORMS, "mixer": MIXERS, "ffn": FEED_FORWARDS}
+
+        def forward(self, ctx, residual, cache, writes_cache):
+            h = NormedInput(ctx, self.norm, residual).tensor()
+            self.mixer.forward(ctx, h, residual, cache, writes_cache)
+            self.ffn.forward(ctx, h, residual)
+
+    BLOCKS.register("toy_sandwich", SandwichBlock)
+    BLOCKS.register("toy_parallel", ParallelBlock)
     MIXERS.register("toy_running_mean", RunningMean)
     POSITION_ENCODINGS.register("toy_learned_shift", LearnedShift)
     FEED_FORWARDS.register("toy_routed_experts", RoutedExperts)
@@ -109,9 +146,7 @@ def register():
         """Layer 0 mixes with the running mean, layer 1 with attention."""
         base = qwen2_model_spec(config)
         first = base.layers[0]
-        toy = LayerSpec(block="prenorm", prefix=first.prefix, mixer_norm=first.mixer_norm, ffn_norm=first.ffn_norm,
-                        mixer=PartSpec("toy_running_mean", {"hidden_size": config.hidden_size}), ffn=first.ffn,
-                        names=first.names)
+        toy = first.with_parts(mixer=PartSpec("toy_running_mean", {"hidden_size": config.hidden_size}))
         return ModelSpec(**{**base.__dict__, "layers": [toy] + base.layers[1:], "architecture": "ToyStateLM"})
 
     def toy_shared_spec(config):
@@ -124,12 +159,27 @@ def register():
         """Layer 0 feeds forward through routed experts, layer 1 through SwiGLU."""
         base = qwen2_model_spec(config)
         first = base.layers[0]
-        routed = LayerSpec(block="prenorm", prefix=first.prefix, mixer_norm=first.mixer_norm, ffn_norm=first.ffn_norm,
-                           mixer=first.mixer, names=first.names,
-                           ffn=PartSpec("toy_routed_experts", {"hidden_size": config.hidden_size, "expert_size": 48,
-                                                               "experts": 5}))
+        routed = first.with_parts(ffn=PartSpec("toy_routed_experts", {"hidden_size": config.hidden_size,
+                                                                      "expert_size": 48, "experts": 5}))
         return ModelSpec(**{**base.__dict__, "layers": [routed] + base.layers[1:], "architecture": "ToyRoutedLM"})
 
+    def toy_arranged_spec(config):
+        """Layer 0 has four norms, layer 1 runs mixer and feed-forward side by side under one
+        norm, and the embedding rows are scaled."""
+        base = qwen2_model_spec(config)
+        first, second = base.layers[0], base.layers[1]
+        norm = first.parts["mixer_norm"]
+        sandwich = LayerSpec(block="toy_sandwich", prefix=first.prefix,
+                             parts={**first.parts, "mixer_post_norm": norm, "ffn_post_norm": norm},
+                             names={**first.names, "mixer_post_norm": "post_mixer_norm", "ffn_post_norm": "post_ffn_norm"},
+                             params={"branch_scale": 0.5})
+        parallel = LayerSpec(block="toy_parallel", prefix=second.prefix,
+                             parts={"norm": norm, "mixer": second.parts["mixer"], "ffn": second.parts["ffn"]},
+                             names={"norm": "input_layernorm", "mixer": "self_attn", "ffn": "mlp"})
+        return ModelSpec(**{**base.__dict__, "layers": [sandwich, parallel], "architecture": "ToyArrangedLM",
+                            "embedding_scale": 3.0})
+
+    register_architecture("ToyArrangedLM", Qwen2Config.from_dict, toy_arranged_spec)
     register_architecture("ToyRoutedLM", Qwen2Config.from_dict, toy_routed_spec)
     register_architecture("ToyStateLM", Qwen2Config.from_dict, toy_state_spec)
     register_architecture("ToySharedLM", Qwen2Config.from_dict, toy_shared_spec)

@@ -21,7 +21,7 @@ import sys
 import time
 from typing import List, Optional
 
-from .errors import InfeasibleError, InvalidArgumentError, UsageError, ViperaError
+from .errors import InfeasibleError, InternalError, InvalidArgumentError, UsageError, ViperaError
 
 USAGE = """usage: vipera <command> [arguments]
 
@@ -30,13 +30,11 @@ commands:
            [--top-p P] [--min-p P] [--repetition-penalty F] [--presence-penalty F]
            [--frequency-penalty F] [--seed S] [--dtype bfloat16|float32] [--page-size N] [--json]
   model-info <model> [--json]
-  plan <model> [--ctx N] [--batch N] [--dtype bfloat16|float32] [--device-bytes N] [--json]
+  plan <model> [--ctx N] [--batch N] [--dtype bfloat16|float32] [--device-bytes N] [--page-size N] [--json]
   random-weights <config.json> <out-dir> [--seed S] [--dtype bfloat16|float32]
 
 exit codes: 0 ok, 1 usage, 2 bad input, 3 infeasible, 4 internal
 """
-
-DEVICE_RESERVE_BYTES = 16 << 20  # kept free on the device (crates/vipera-core/src/planner.rs:23)
 
 
 def _value(args: List[str], index: int, flag: str) -> str:
@@ -76,7 +74,10 @@ def _parse(args: List[str], command: str, valued: dict, switches: set, positiona
 
 
 def _model_report(model_dir: str) -> dict:
+    """What the folder holds, by the architecture-neutral description and the file itself
+    (bins/vipera/src/main.rs:161-184)."""
     from .config import load_config
+    from .engine import planner
     from .parts import model_schema
     from .weights import SafetensorsSource, check_source
 
@@ -93,7 +94,7 @@ def _model_report(model_dir: str) -> dict:
         dtype = str(source.stored_dtype(name)).replace("torch.", "")
         dtypes[dtype] = dtypes.get(dtype, 0) + 1
         parameters += count
-        total_bytes += count * {"float32": 4, "float64": 8}.get(dtype, 2)
+        total_bytes += count * {"float32": 4, "float64": 8, "int32": 4, "int64": 8}.get(dtype, 2)
     return {
         "name": os.path.basename(os.path.normpath(model_dir)),
         "architecture": arch.name,
@@ -103,10 +104,11 @@ def _model_report(model_dir: str) -> dict:
         "file_bytes": total_bytes,
         "context_limit": spec.max_position_embeddings,
         "layer_count": len(spec.layers),
+        "scheduled_layers": len(spec.schedule),
         "vocab_size": spec.vocab_size,
         "hidden_size": spec.hidden_size,
         "tied_output": spec.head_name is None,
-        "kv_bytes_per_token_bf16": config.kv_bytes_per_token(2) if hasattr(config, "kv_bytes_per_token") else None,
+        "kv_bytes_per_token_bf16": planner.kv_bytes_per_token(spec, 2),
     }
 
 
@@ -123,54 +125,25 @@ def model_info(args: List[str]) -> int:
     return 0
 
 
-def plan_memory(model_dir: str, ctx: int, batch: int, dtype: str, device_bytes: Optional[int]) -> dict:
-    """Weights + cache + workspace against the device's memory; what does not fit is
-    listed in ``violations`` (crates/vipera-core/src/planner.rs:224-263, 276-430)."""
+def plan_memory(model_dir: str, ctx: int, batch: int, dtype: str, device_bytes: Optional[int],
+                page_size: int = 16) -> dict:
+    """The memory plan of the model in ``model_dir`` (its config.json is all that is read)."""
     from .config import load_config
+    from .engine import planner
 
     arch, config = load_config(model_dir)
-    element = 4 if dtype in ("float32", "fp32", "f32") else 2
-    weights = config.parameter_count() * element
-    kv = batch * ctx * config.kv_bytes_per_token(element)
-    # Workspace of one step of up to 2048 tokens: residual, activations, q/k/v, feed-forward
-    # activation and the logits rows of a batch.
-    tokens = 2048
-    width = (config.num_attention_heads + 2 * config.num_key_value_heads) * config.head_dim
-    workspace = tokens * (config.hidden_size * (4 + 2 * element) + width * 4 + width * element
-                          + config.intermediate_size * element) + batch * config.vocab_size * 4
-    if device_bytes is None:
-        try:
-            import torch
-
-            device_bytes = torch.cuda.get_device_properties(0).total_memory if torch.cuda.is_available() else None
-        except Exception:
-            device_bytes = None
-    if device_bytes is None:
-        device_bytes = 180 * 10**9  # one B200
-    required = weights + kv + workspace + DEVICE_RESERVE_BYTES
-    violations = []
-    if ctx > config.max_position_embeddings:
-        violations.append({"constraint": "context_limit", "required": ctx,
-                           "available": config.max_position_embeddings,
-                           "message": f"ctx {ctx} exceeds the model's limit of {config.max_position_embeddings}"})
-    if required > device_bytes:
-        violations.append({"constraint": "device_memory", "required_bytes": required,
-                           "available_bytes": device_bytes,
-                           "message": f"{required} bytes needed, {device_bytes} on the device"})
-    return {"ctx": ctx, "batch_size": batch, "dtype": dtype, "weight_bytes": weights, "kv_bytes": kv,
-            "workspace_bytes": workspace, "reserve_bytes": DEVICE_RESERVE_BYTES,
-            "predicted_device_bytes": required, "device_bytes": device_bytes,
-            "feasible": not violations, "violations": violations}
+    return planner.plan_memory(arch.model_spec(config), ctx, batch, dtype, device_bytes, page_size)
 
 
 def plan(args: List[str]) -> int:
     found, places = _parse(args, "plan", {"--ctx": ("ctx", int), "--batch": ("batch", int),
                                           "--dtype": ("dtype", str), "--kv-type": ("kv_type", str),
-                                          "--device-bytes": ("device_bytes", int)}, {"--json"}, 1)
+                                          "--device-bytes": ("device_bytes", int),
+                                          "--page-size": ("page_size", int)}, {"--json"}, 1)
     if not places:
         raise UsageError("plan needs a model path")
     report = plan_memory(places[0], found.get("ctx", 2048), found.get("batch", 1),
-                         found.get("dtype", "bfloat16"), found.get("device_bytes"))
+                         found.get("dtype", "bfloat16"), found.get("device_bytes"), found.get("page_size", 16))
     if found.get("json"):
         print(json.dumps(report, indent=2))
     else:
@@ -269,6 +242,11 @@ def main(argv: Optional[List[str]] = None) -> int:
         if isinstance(error, UsageError):
             print(USAGE, end="", file=sys.stderr)
         return error.exit_code
+    except Exception as error:  # a fault that is not one of the engine's own kinds is internal too
+        if os.environ.get("VIPERA_TRACEBACK"):
+            raise
+        print(f"vipera: internal: {type(error).__name__}: {error}", file=sys.stderr)
+        return InternalError.exit_code
 
 
 if __name__ == "__main__":

@@ -229,10 +229,7 @@ def qwen2_model_spec(config: Qwen2Config) -> ModelSpec:
             LayerSpec(
                 block="prenorm",
                 prefix=f"model.layers.{index}",
-                mixer_norm=norm,
-                mixer=mixer,
-                ffn_norm=norm,
-                ffn=ffn,
+                parts={"mixer_norm": norm, "mixer": mixer, "ffn_norm": norm, "ffn": ffn},
                 names={"mixer_norm": "input_layernorm", "mixer": "self_attn",
                        "ffn_norm": "post_attention_layernorm", "ffn": "mlp"},
             )

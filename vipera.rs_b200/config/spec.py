@@ -25,24 +25,31 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block of the decoder: the arrangement and the four parts it arranges.
+    """One block of the decoder: an arrangement and the parts it arranges, by role.
 
+    ``block`` names the arrangement (a key of the block registry).  ``parts`` maps a role to
+    a part; which roles there are, and which kind of part fills each, is the arrangement's
+    business: ``prenorm`` reads ``mixer_norm``, ``mixer``, ``ffn_norm`` and ``ffn``; an
+    arrangement with four norms, or with a mixer beside the feed-forward, reads others.
+    ``params`` holds constants of the arrangement itself (a residual scale, say).
     ``prefix`` is the tensor-name prefix of this layer in the weight file
-    (``model.layers.3``) and ``names`` the sub-prefix of each of the four parts under it
-    (``input_layernorm``, ``self_attn``, ...); each part appends its own tensor names.
+    (``model.layers.3``) and ``names`` the sub-prefix of each role under it
+    (``input_layernorm``, ``self_attn``, ...; a role not listed uses its own name); each
+    part appends its own tensor names.
     """
 
     block: str
     prefix: str
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    ffn_norm: PartSpec
-    ffn: PartSpec
-    names: Dict[str, str] = field(default_factory=lambda: {
-        "mixer_norm": "mixer_norm", "mixer": "mixer", "ffn_norm": "ffn_norm", "ffn": "ffn"})
+    parts: Dict[str, PartSpec]
+    names: Dict[str, str] = field(default_factory=dict)
+    params: Dict[str, Any] = field(default_factory=dict)
 
-    def part_prefix(self, part: str) -> str:
-        return f"{self.prefix}.{self.names[part]}"
+    def part_prefix(self, role: str) -> str:
+        return f"{self.prefix}.{self.names.get(role, role)}"
+
+    def with_parts(self, **changes: PartSpec) -> "LayerSpec":
+        """This layer with some roles filled by other parts."""
+        return LayerSpec(self.block, self.prefix, {**self.parts, **changes}, dict(self.names), dict(self.params))
 
 
 @dataclass(frozen=True)
@@ -74,7 +81,8 @@ class ModelSpec:
     final_norm: PartSpec
     final_norm_name: str
     head_name: Optional[str]  # None: the embedding matrix is the output matrix
-    logit_scale: float = 1.0
+    logit_scale: float = 1.0      # logits are multiplied by this
+    embedding_scale: float = 1.0  # embedding rows are multiplied by this on their way into the residual stream
 
     def validate(self) -> None:
         from ..errors import InvalidArgumentError

@@ -32,8 +32,7 @@
 
 #include "common.cuh"
 
-// EPI_DISCARD drops the result: it exists to time the products without their ending.
-enum GemmEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_DISCARD = 3, EPI_ROPE_CACHE = 4 };
+enum GemmEpilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_ROPE_CACHE = 4 };
 enum { GEMM_ROPE_NONE = 0, GEMM_ROPE_NEOX = 1 };
 enum { GEMM_TC_WAIT_EXPIRED = 1 };
 
@@ -204,7 +203,6 @@ template <int BN, bool SWAP>
 __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v, int width, int row, int col0) {
   // `row`: global index on the 128-row side; `col0`: global index of v[0] on the other side.
   const int N = p.features;
-  if (p.epilogue == EPI_DISCARD) return;
   if (!SWAP) {
     const int t = row;
     if (t >= p.tokens) return;

@@ -1,17 +1,19 @@
 // Row-wise kernels: embedding lookup into the 32-bit residual stream, and RMSNorm.
 //
-// Embedding: a row lookup without scaling (crates/vipera-backend-cpu/src/model.rs:956-966;
-// the reference's device version dequantises one row, crates/vipera-backend-gpu/src/layer.cu:545-563).
+// Embedding: a row lookup (crates/vipera-backend-cpu/src/model.rs:956-966; the reference's
+// device version dequantises one row, crates/vipera-backend-gpu/src/layer.cu:545-563).  The
+// reference's model does not scale the rows; `scale` is for architectures that do, and a
+// scale of exactly 1 leaves the values as they are.
 // RMSNorm: out = x * rsqrt(mean(x^2) + eps) * w with 32-bit statistics
 // (model.rs:4282-4288; device version layer.cu:32-58, one block per row with a tree sum).
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------
-// embedding: out[t, :] = table[tokens[t], :]  (32-bit out, whatever the table's type)
+// embedding: out[t, :] = scale * table[tokens[t], :]  (32-bit out, whatever the table's type)
 // ---------------------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ out, int hidden, int vocab) {
+                             float* __restrict__ out, int hidden, int vocab, float scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -21,19 +23,19 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
   token = min(max(token, 0), vocab - 1);
   const TW* row = table + static_cast<size_t>(token) * hidden;
   float* dst = out + static_cast<size_t>(t) * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float<TW>(row[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = scale * to_float<TW>(row[i]);
 }
 
 VIPERA_API int vipera_embed(const void* table, int table_dtype, const int* tokens, float* out,
-                            int num_tokens, int hidden, int vocab, void* stream) {
+                            int num_tokens, int hidden, int vocab, float scale, void* stream) {
   if (num_tokens <= 0) return VIPERA_OK;
   if (hidden <= 0 || vocab <= 0) return VIPERA_BAD_SHAPE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == VIPERA_F32)
-    return vipera_launch(embed_kernel<float>, num_tokens, threads, 0, s, static_cast<const float*>(table), tokens, out, hidden, vocab);
+    return vipera_launch(embed_kernel<float>, num_tokens, threads, 0, s, static_cast<const float*>(table), tokens, out, hidden, vocab, scale);
   if (table_dtype == VIPERA_BF16)
-    return vipera_launch(embed_kernel<__nv_bfloat16>, num_tokens, threads, 0, s, static_cast<const __nv_bfloat16*>(table), tokens, out, hidden, vocab);
+    return vipera_launch(embed_kernel<__nv_bfloat16>, num_tokens, threads, 0, s, static_cast<const __nv_bfloat16*>(table), tokens, out, hidden, vocab, scale);
   return VIPERA_BAD_DTYPE;
 }
 

@@ -15,14 +15,9 @@ from ..weights import AliasedSource, RandomSource, SafetensorsSource, write_mode
 
 
 def _kernel_families(model) -> list:
-    """The kernel families the model's parts name, and the fused decode step where the model
-    qualifies for it."""
-    from .fused_decode import FusedDecode
+    """The kernel families the model's parts name."""
+    return list(model.kernel_families())
 
-    names = list(model.kernel_families())
-    if FusedDecode.qualifies(model):
-        names.append("decode_fused")
-    return names
 
 _DTYPES = {
     "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,

@@ -65,10 +65,6 @@ class ModelRunner:
         self.max_graph_entries = 256
         self._graphs = {}
         self._page_sizes = [self.manager.group(g)[0] for g in range(self.manager.num_groups)]
-        # Decode steps of few tokens run as one persistent kernel where the model qualifies.
-        from .fused_decode import FusedDecode
-
-        self.fused = FusedDecode.plan_for(model)
 
     # ------------------------------------------------------------------------------
     def _staging(self, count: int):
@@ -153,12 +149,8 @@ class ModelRunner:
             logits_all_rows=bool(rows.size == total and np.array_equal(rows, np.arange(total))))
 
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
-        """The model's forward pass for a prepared step, through the fused decode kernel
-        where the step and the model qualify."""
-        views = self.pools.views
-        if self.fused is not None and self.fused.takes(ctx, views):
-            return self.fused.run(ctx, views)
-        return self.model.forward(ctx, views)
+        """The model's forward pass for a prepared step."""
+        return self.model.forward(ctx, self.pools.views)
 
     def run(self, step: StepInput) -> Optional[torch.Tensor]:
         """Run one step.  A step in which every entry brings one token and wants its logits

@@ -18,7 +18,6 @@ from ..errors import InternalError, InvalidArgumentError, UnsupportedError
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
-EPI_DISCARD = 3  # tensor-core kernel only: the products without their ending, for timing
 ROPE_NONE, ROPE_NEOX, ROPE_INTERLEAVED = 0, 1, 2
 SAMPLE_OK, SAMPLE_NO_FINITE, SAMPLE_NO_MASS, SAMPLE_NEEDS_HOST = 0, 1, 2, 3
 
@@ -109,15 +108,15 @@ def _opt(tensor: Optional[torch.Tensor], name: str, dtype=None):
 
 
 # ----------------------------------------------------------------------------------------
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, :] = table[tokens[t], :] as float32."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t, :] = scale * table[tokens[t], :] as float32."""
     fn = _function("rowwise", "vipera_embed",
-                   [_c_void, _c_int, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void])
+                   [_c_void, _c_int, _c_void, _c_void, _c_int, _c_int, _c_int, _c_float, _c_void])
     count, hidden = out.shape
     if table.shape[1] != hidden or tokens.numel() != count:
         raise InvalidArgumentError("embed: shapes of table, tokens and out do not agree")
     _check(fn(_gpu(table, "table"), dtype_code(table.dtype), _gpu(tokens, "tokens", torch.int32),
-              _gpu(out, "out", torch.float32), count, hidden, table.shape[0], _stream()), "embed")
+              _gpu(out, "out", torch.float32), count, hidden, table.shape[0], float(scale), _stream()), "embed")
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
@@ -202,9 +201,6 @@ def _check_gemm_outputs(m, n, epilogue, bias, out, resid) -> None:
             raise UnsupportedError("gemm: SwiGLU needs an intermediate size that is a multiple of 16")
         if out is None or tuple(out.shape) != (m, n // 2):
             raise InvalidArgumentError(f"gemm: out must be [{m}, {n // 2}]")
-    elif epilogue == EPI_DISCARD:
-        if out is None:
-            raise InvalidArgumentError("gemm: the timing mode still takes an out tensor (it is left untouched)")
     else:
         raise InvalidArgumentError(f"gemm: unknown epilogue {epilogue}")
 
@@ -591,85 +587,6 @@ def gemv_small(w: torch.Tensor, *, a: Optional[torch.Tensor] = None, x: Optional
         p.out_dtype = dtype_code(out.dtype) if out is not None else F32
         p.resid = _opt(resid, "resid", torch.float32)
     _check(fn(ctypes.byref(p), _stream()), "gemv_small")
-
-
-# ----------------------------------------------------------------------------------------
-# a whole decode step as one persistent kernel
-# ----------------------------------------------------------------------------------------
-FUSED_MAX_TOKENS = 16
-FUSED_HEAD_DIMS = (64, 128)
-
-
-class FusedLayer(ctypes.Structure):
-    """One scheduled layer of the fused decode step (mirrors ``FusedLayer`` in decode_fused.cu)."""
-
-    _fields_ = [
-        ("w_qkv", _c_void), ("b_qkv", _c_void), ("norm1", _c_void), ("w_o", _c_void), ("norm2", _c_void),
-        ("w_gate_up", _c_void), ("w_down", _c_void), ("k_pool", _c_void), ("v_pool", _c_void),
-        ("block_table", _c_void), ("cos_table", _c_void), ("sin_table", _c_void),
-        ("eps1", _c_float), ("eps2", _c_float), ("scale", _c_float),
-        ("table_width", _c_int), ("page_size", _c_int), ("window", _c_int), ("writes_cache", _c_int),
-        ("num_heads", _c_int), ("num_kv_heads", _c_int), ("inter", _c_int), ("rope_style", _c_int),
-    ]
-
-
-class FusedModel(ctypes.Structure):
-    """The step as a whole (mirrors ``FusedModel`` in decode_fused.cu)."""
-
-    _fields_ = [
-        ("layers", _c_void), ("maps", _c_void), ("tokens", _c_void), ("positions", _c_void), ("embedding", _c_void),
-        ("x", _c_void), ("q", _c_void), ("attn", _c_void), ("act", _c_void),
-        ("partial_ml", _c_void), ("partial_out", _c_void),
-        ("final_norm", _c_void), ("head", _c_void), ("logits", _c_void),
-        ("barrier", _c_void), ("status", _c_void), ("trace", _c_void),
-        ("final_eps", _c_float), ("logit_scale", _c_float),
-        ("T", _c_int), ("hidden", _c_int), ("vocab", _c_int), ("num_layers", _c_int),
-        ("max_chunks", _c_int), ("head_dim", _c_int), ("ring_stages", _c_int), ("union_bytes", _c_int),
-    ]
-
-
-def _fused_sizes_checked() -> None:
-    if _functions.get(("decode_fused", "checked")):
-        return
-    layer = _function("decode_fused", "vipera_decode_fused_layer_size", [])()
-    model = _function("decode_fused", "vipera_decode_fused_model_size", [])()
-    if layer != ctypes.sizeof(FusedLayer) or model != ctypes.sizeof(FusedModel):
-        raise InternalError("the fused decode kernel's structures differ from their Python mirrors")
-    _functions[("decode_fused", "checked")] = True
-
-
-def decode_fused_chunk_keys() -> int:
-    return _function("decode_fused", "vipera_decode_fused_chunk_keys", [])()
-
-
-def decode_fused_max_keys() -> int:
-    """The longest history (in keys) the fused step takes."""
-    return decode_fused_chunk_keys() * _function("decode_fused", "vipera_decode_fused_max_chunks", [])()
-
-
-def decode_fused_takes(tokens: int, hidden: int, head_dim: int, max_inter: int, max_q_dim: int) -> bool:
-    fn = _function("decode_fused", "vipera_decode_fused_takes", [_c_int] * 5)
-    return bool(fn(tokens, hidden, head_dim, max_inter, max_q_dim))
-
-
-def decode_fused_weight_maps(weights) -> torch.Tensor:
-    """The matrices in ``weights`` (bfloat16 [rows, K] on one device) as the fused kernel's
-    producer reads them: a device tensor of 128 bytes per matrix."""
-    fn = _function("decode_fused", "vipera_decode_fused_weight_map", [_c_void, _c_void, _c_int, _c_int])
-    raw = (ctypes.c_uint8 * (128 * len(weights)))()
-    base = ctypes.addressof(raw)
-    for index, weight in enumerate(weights):
-        rows, k = weight.shape
-        _check(fn(base + 128 * index, _gpu(weight, "weight", torch.bfloat16), rows, k), "decode_fused_weight_map",
-               kernels=0)
-    return torch.frombuffer(bytearray(bytes(raw)), dtype=torch.uint8).to(weights[0].device)
-
-
-def decode_fused(model: FusedModel) -> None:
-    """Launch the fused decode step described by ``model`` on the current stream."""
-    _fused_sizes_checked()
-    fn = _function("decode_fused", "vipera_decode_fused", [ctypes.POINTER(FusedModel), _c_void])
-    _check(fn(ctypes.byref(model), _stream()), "decode_fused")
 
 
 def kernel_status_word(device) -> torch.Tensor:

@@ -14,10 +14,11 @@ from .base import (
     StepContext,
     Workspace,
 )
-from .linear import Linear, interleave_gate_up
+from .block import Block
+from .linear import Linear, NormedInput, interleave_gate_up
 from .model import DecoderModel, model_schema
 
 __all__ = [
     "FeedForward", "FixedState", "Mixer", "Norm", "PagedKV", "PagedKVView", "Part", "PositionEncoding",
-    "StateView", "StepContext", "Workspace", "Linear", "interleave_gate_up", "DecoderModel", "model_schema",
+    "StateView", "StepContext", "Workspace", "Block", "Linear", "NormedInput", "interleave_gate_up", "DecoderModel", "model_schema",
 ]

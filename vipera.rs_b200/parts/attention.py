@@ -85,8 +85,16 @@ class GQAttention(Mixer):
         return tuple(dict.fromkeys(tuple(own) + self.qkv.kernel_families() + self.out.kernel_families()
                                    + self.position.kernel_families()))
 
-    def cache_request(self):
-        return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+    @classmethod
+    def cache_request_for(cls, params):
+        return PagedKV(int(params["num_kv_heads"]), int(params["head_dim"]), params.get("window"))
+
+    @classmethod
+    def workspace_bytes(cls, params, tokens, element_bytes):
+        q_width = params["num_heads"] * params["head_dim"]
+        qkv_width = q_width + 2 * params["num_kv_heads"] * params["head_dim"]
+        # q and the attention's output in the run's type, and the 32-bit q/k/v product of the unfused route
+        return tokens * (2 * q_width * element_bytes + qkv_width * 4)
 
     def forward(self, ctx, h, residual, cache, writes_cache):
         count = ctx.num_tokens
@@ -112,7 +120,7 @@ class GQAttention(Mixer):
             self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
             return
         if (ctx.dtype == torch.bfloat16 and style in (ops.ROPE_NONE, ops.ROPE_NEOX)
-                and self.qkv._tensor_core is not None
+                and self.qkv.tensor_core
                 and ops.gemm_tc_rope_takes(count, self.qkv.out_features, self.qkv.in_features, d)):
             # many tokens: the tensor-core product ends with bias, rotation and cache write
             cos, sin = self.position.tables()

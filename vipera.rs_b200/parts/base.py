@@ -154,6 +154,12 @@ class Part:
     def kernel_families(self) -> Tuple[str, ...]:
         return self.kernels
 
+    @classmethod
+    def workspace_bytes(cls, params: Dict[str, Any], tokens: int, element_bytes: int) -> int:
+        """Device bytes of the buffers this part asks the workspace for in a step of `tokens`
+        tokens (for the memory plan; parts of one kind share their buffers between layers)."""
+        return 0
+
 
 class Norm(Part):
     def forward(self, ctx: StepContext, x: torch.Tensor, out: torch.Tensor,
@@ -174,9 +180,14 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    def cache_request(self):
-        """PagedKV, FixedState or None."""
+    @classmethod
+    def cache_request_for(cls, params: Dict[str, Any]):
+        """What a mixer with these sizes keeps between steps: PagedKV, FixedState or None.  A
+        class method, so that memory can be planned from a description alone, without weights."""
         return None
+
+    def cache_request(self):
+        return type(self).cache_request_for(self.params)
 
     def forward(self, ctx: StepContext, h: torch.Tensor, residual: torch.Tensor, cache, writes_cache: bool) -> None:
         raise NotImplementedError

@@ -74,15 +74,14 @@ class Linear:
         self.weight = weight.to(device=device, dtype=dtype).contiguous()
         self.bias = None if bias is None else bias.to(device=device, dtype=torch.float32).contiguous()
         self.out_features, self.in_features = self.weight.shape
-        self._tensor_core = None
         self._small_ok = {}
-        if dtype == torch.bfloat16:
-            from . import tensor_core
-
-            self._tensor_core = tensor_core.plan_for(self.weight)
+        # The tcgen05 kernel reads the matrix by TMA: bfloat16, rows a multiple of 16 bytes long
+        # and a 16-byte aligned base.  Other matrices run on the CUDA cores.
+        self.tensor_core = (dtype == torch.bfloat16 and self.weight.shape[1] % 8 == 0
+                            and self.weight.data_ptr() % 16 == 0)
 
     def kernel_families(self):
-        if self._tensor_core is not None:
+        if self.tensor_core:
             return ("gemm_simt", "gemm_tc", "gemv_small")
         return ("gemm_simt",)
 
@@ -90,7 +89,7 @@ class Linear:
         """Whether the small-token kernel runs this product for `tokens` tokens."""
         # The small-token kernel wins where a product is small (its fixed cost is low and it
         # fuses the norm in front); wide or deep products stream better through TMA.
-        if (self._tensor_core is None or self.out_features > SMALL_KERNEL_MAX_ROWS
+        if (not self.tensor_core or self.out_features > SMALL_KERNEL_MAX_ROWS
                 or self.in_features > SMALL_KERNEL_MAX_INNER):
             return False
         known = self._small_ok.get(tokens)
@@ -116,7 +115,7 @@ class Linear:
             return
         if lazy is not None:
             a = lazy.tensor()
-        if self._tensor_core is not None and self._tensor_core.takes(a, epilogue, out):
-            self._tensor_core.run(ctx, a, epilogue=epilogue, bias=bias, out=out, resid=resid)
+        if self.tensor_core and a.dtype == torch.bfloat16 and a.is_contiguous() and a.data_ptr() % 16 == 0:
+            ops.gemm_tc(a, self.weight, epilogue=epilogue, bias=bias, out=out, resid=resid)
             return
         ops.gemm_simt(a, self.weight, epilogue=epilogue, bias=bias, out=out, resid=resid)

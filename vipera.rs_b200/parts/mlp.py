@@ -37,6 +37,10 @@ class SwiGLU(FeedForward):
             f"{prefix}.{down}.weight": TensorSpec((hidden, inter)),
         }
 
+    @classmethod
+    def workspace_bytes(cls, params, tokens, element_bytes):
+        return tokens * params["intermediate_size"] * element_bytes
+
     def __init__(self, params, prefix, tensors, dtype, device):
         super().__init__(params, prefix, tensors, dtype, device)
         self.hidden = int(params["hidden_size"])

@@ -13,7 +13,7 @@ import torch
 
 from ..config.registry import BLOCKS, NORMS
 from ..config.spec import ModelSpec
-from ..errors import InvalidArgumentError
+from ..errors import InternalError, InvalidArgumentError
 from ..kernels import ops
 from ..weights import Schema, TensorSpec, WeightSource, check_source, to_run_dtype
 from .base import StepContext
@@ -39,6 +39,8 @@ class DecoderModel:
         self.spec = spec
         self.dtype = dtype
         self.device = torch.device(device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise InternalError(f"no CUDA device for {device!r}: this engine has no CPU path")
         schema = model_schema(spec)
         check_source(schema, source)
 
@@ -64,7 +66,7 @@ class DecoderModel:
         self.cache_requests: Dict[int, object] = {}
         for entry in spec.schedule:
             if entry.writes_cache:
-                self.cache_requests[entry.cache] = self.blocks[entry.layer].mixer.cache_request()
+                self.cache_requests[entry.cache] = self.blocks[entry.layer].cache_request()
 
     @property
     def graph_safe(self) -> bool:
@@ -106,7 +108,7 @@ class DecoderModel:
         [wanted rows, vocab], or None when no row is wanted."""
         ws = ctx.workspace
         residual = ws.get("model.residual", (ctx.num_tokens, self.spec.hidden_size), torch.float32)
-        ops.embed(self.embedding, ctx.tokens, residual)
+        ops.embed(self.embedding, ctx.tokens, residual, self.spec.embedding_scale)
         for entry in self.spec.schedule:
             self.blocks[entry.layer].forward(ctx, residual, caches.get(entry.cache), entry.writes_cache)
         if ctx.num_logit_rows == 0:
