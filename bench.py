@@ -41,6 +41,20 @@ QWEN25_1P5B = {
     "max_position_embeddings": 32768, "use_sliding_window": False, "sliding_window": 32768,
     "max_window_layers": 21,
 }
+QWEN25_7B = {
+    "architectures": ["Qwen2ForCausalLM"], "num_hidden_layers": 28, "hidden_size": 3584,
+    "num_attention_heads": 28, "num_key_value_heads": 4, "intermediate_size": 18944, "vocab_size": 152064,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+    "max_position_embeddings": 32768, "use_sliding_window": False,
+}
+QWEN25_32B = {
+    "architectures": ["Qwen2ForCausalLM"], "num_hidden_layers": 64, "hidden_size": 5120,
+    "num_attention_heads": 40, "num_key_value_heads": 8, "intermediate_size": 27648, "vocab_size": 152064,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+    "max_position_embeddings": 32768, "use_sliding_window": False,
+}
+SHAPES = {"1.5b": ("Qwen2.5-1.5B shape", QWEN25_1P5B), "7b": ("Qwen2.5-7B shape", QWEN25_7B),
+          "32b": ("Qwen2.5-32B shape", QWEN25_32B)}
 FULL_LAYERS = 28
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -115,8 +129,9 @@ class ClockSampler:
 
 
 def decode_bytes(config, layers, batch, history, element=2):
-    """Bytes one decode step has to read: every weight it uses once, and the cache of the
-    live requests at the mean history of the timed steps."""
+    """Bytes one decode step has to read: every weight it uses once (the embedding matrix only
+    where it is also the output matrix), and the cache of the live requests at the mean history
+    of the timed steps."""
     h, d = config["hidden_size"], config["hidden_size"] // config["num_attention_heads"]
     q, kv = config["num_attention_heads"] * d, config["num_key_value_heads"] * d
     per_layer = h * (q + 2 * kv) + q * h + 3 * h * config["intermediate_size"]
@@ -272,6 +287,120 @@ def measure_e2e(model, batch, history, steps, warmup, page_size=16):
     return produced / elapsed, h2d, d2h
 
 
+def measure_mixed(model, requests, prompt_range, new_tokens, max_portion, token_budget, passes=2, page_size=16):
+    """The engine's normal mode: `requests` requests with prompt lengths uniform in
+    `prompt_range`, all offered at once, prompts cut into portions of `max_portion` under a
+    budget of `token_budget` tokens a step beside the running decodes, `new_tokens` tokens each,
+    through ``Engine.step()`` on the host clock.  The first pass captures the graphs of the
+    step sizes that occur; the last pass is the one reported."""
+    import numpy as np
+    import torch
+
+    from vipera_rs_b200 import Engine, SamplingParams
+
+    rng = np.random.default_rng(7)
+    lengths = rng.integers(prompt_range[0], prompt_range[1] + 1, size=requests)
+    prompts = [rng.integers(0, model.spec.vocab_size, size=int(n)).tolist() for n in lengths]
+    per_request = -(-(int(lengths.max()) + new_tokens + 1) // page_size)
+    engine = Engine(model, page_size=page_size, num_pages=requests * per_request + 1, max_num_seqs=requests,
+                    max_tokens_per_step=token_budget, max_portion=max_portion, prefix_cache=False)
+    params = SamplingParams(max_new_tokens=new_tokens, eos_ids=[])
+    report = {}
+    for index in range(passes):
+        before = dict(engine.totals, stage_micros=dict(engine.totals["stage_micros"]))
+        for prompt in prompts:
+            engine.add_request(prompt, params)
+        torch.cuda.synchronize()
+        started = time.perf_counter()
+        generated = 0
+        while engine.has_work():
+            generated += len(engine.step().tokens)
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - started
+        totals = engine.totals
+        steps = totals["steps"] - before["steps"]
+        host = {stage: totals["stage_micros"][stage] - before["stage_micros"][stage] for stage in totals["stage_micros"]}
+        prompt_tokens = int(lengths.sum())
+        report = {
+            "requests": requests, "prompt_tokens": prompt_tokens, "generated_tokens": generated,
+            "prompt_min": int(prompt_range[0]), "prompt_max": int(prompt_range[1]), "new_tokens_each": new_tokens,
+            "max_portion": max_portion, "token_budget": token_budget, "seconds": round(elapsed, 4),
+            "tokens_per_s": round((prompt_tokens + generated) / elapsed, 1),
+            "generated_tokens_per_s": round(generated / elapsed, 1),
+            "steps": steps, "steps_with_portions": totals["steps_with_portions"] - before["steps_with_portions"],
+            "tokens_per_step": round((totals["tokens"] - before["tokens"]) / max(steps, 1), 1),
+            "ms_per_step": round(elapsed * 1e3 / max(steps, 1), 4),
+            # the host's own work a step: scheduling, building and launching, bookkeeping (the
+            # sample stage is mostly the wait for the device and is left out)
+            "host_us_per_step": round((host["allocate"] + host["compute"] + host["complete"]) / max(steps, 1), 1),
+            "graph_step_share": round((totals["graph_steps"] - before["graph_steps"]) / max(steps, 1), 4),
+            "timing": "host clock around Engine.step() until every request has ended",
+        }
+    del engine
+    torch.cuda.empty_cache()
+    return report
+
+
+def measure_shape(name, config, layers, peaks, history, batches, steps, warmup, page_size=16, prefill_tokens=2048):
+    """Decode at `batches` with `history` tokens of history and one prefill, for another shape."""
+    import torch
+
+    from vipera_rs_b200.engine import random_model
+
+    full_layers = config["num_hidden_layers"]
+    config = dict(config, num_hidden_layers=layers)
+    model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
+    out = {"model": name, "layers": layers, "layers_full": full_layers, "seq_len": history, "dtype": "bf16"}
+    for batch in batches:
+        harness = DecodeHarness(model, batch, history, steps + warmup + 2, page_size=page_size)
+        ms, mean_history = harness.timed(steps, warmup)
+        harness.close()
+        del harness
+        torch.cuda.empty_cache()
+        gbs = decode_bytes(config, layers, batch, mean_history) / (ms * 1e-3) / 1e9
+        out[f"decode_b{batch}"] = round(batch * 1000.0 / ms, 1)
+        out[f"decode_b{batch}_ms"] = round(ms, 4)
+        out[f"decode_b{batch}_hbm_frac"] = round(gbs / peaks["hbm_gbs"], 4)
+    ms = measure_prefill(model, prefill_tokens, repeats=3, warmup=2, page_size=page_size)
+    out["prefill_tokens"] = prefill_tokens
+    out["prefill_ms"] = round(ms, 3)
+    out["prefill_tok_s"] = round(prefill_tokens * 1000.0 / ms, 1)
+    out["prefill_frac"] = round(prefill_flops(config, layers, prefill_tokens) / (ms * 1e-3)
+                                / (peaks["bf16_tflops_sustained"] * 1e12), 4)
+    return out, model
+
+
+def measure_32b(peaks, warmup, page_size):
+    """The 32B shape: what the memory plan says about a batch of 64 at 8,192 tokens (it does not
+    fit), decode at batch 1, 8 and the largest batch that fits, and one 2,048-token prefill."""
+    import torch
+
+    history = 8192
+    refused = plan_report(QWEN25_32B, history + 256, 64)
+    largest = 8
+    for batch in range(8, 65, 8):
+        if plan_report(QWEN25_32B, history + 256, batch)["feasible"]:
+            largest = batch
+    out, model = measure_shape(SHAPES["32b"][0], QWEN25_32B, QWEN25_32B["num_hidden_layers"], peaks, history,
+                               sorted({1, 8, largest}), steps=16, warmup=max(3, min(warmup, 4)), page_size=page_size)
+    del model
+    torch.cuda.empty_cache()
+    out["largest_batch_that_fits"] = largest
+    out["plan_b64_feasible"] = bool(refused["feasible"])
+    out["plan_b64_needs_gb"] = round(refused["predicted_device_bytes"] / 1e9, 1)
+    out["plan_device_gb"] = round(refused["device_bytes"] / 1e9, 1)
+    return out
+
+
+def plan_report(config, ctx, batch):
+    """What `vipera plan` says about the shape at this context and batch on one 180 GB device."""
+    from vipera_rs_b200.config import architecture_of
+    from vipera_rs_b200.engine import planner
+
+    arch = architecture_of(config)
+    return planner.plan_memory(arch.model_spec(arch.config_from_dict(config)), ctx, batch, "bfloat16", 180 * 10**9)
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -283,8 +412,13 @@ def main():
     parser.add_argument("--layers", type=int, default=FULL_LAYERS)
     parser.add_argument("--skip-points", action="store_true")
     parser.add_argument("--page-size", type=int, default=16, help="keys per cache page (the engine's default is 16)")
-    parser.add_argument("--only", choices=["decode", "prefill"], default=None,
+    parser.add_argument("--only", choices=["decode", "prefill", "mixed", "32b"], default=None,
                         help="run one part only and print a short line (for profiling a small case)")
+    parser.add_argument("--config", choices=sorted(SHAPES), default="1.5b",
+                        help="the shape the headline line is measured on (default: the 1.5B shape)")
+    parser.add_argument("--prefill-tokens", type=int, default=2048)
+    parser.add_argument("--skip-workloads", action="store_true",
+                        help="leave out the 7B mixed workload and the 32B shape")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -304,14 +438,28 @@ def main():
     from vipera_rs_b200.engine import random_model
 
     peaks, peak_source = read_peaks()
-    config = dict(QWEN25_1P5B)
+    shape_name, shape = SHAPES[args.config]
+    full_layers = shape["num_hidden_layers"]
+    config = dict(shape)
+    if args.layers == FULL_LAYERS and args.config != "1.5b":
+        args.layers = full_layers
     config["num_hidden_layers"] = args.layers
     from vipera_rs_b200.kernels import ops
 
     model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
     if args.only == "prefill":
-        ms = measure_prefill(model, 2048, repeats=2, warmup=warmup, page_size=args.page_size)
-        print(json.dumps({"only": "prefill", "layers": args.layers, "ms": round(ms, 3)}))
+        ms = measure_prefill(model, args.prefill_tokens, repeats=2, warmup=warmup, page_size=args.page_size)
+        print(json.dumps({"only": "prefill", "layers": args.layers, "tokens": args.prefill_tokens, "ms": round(ms, 3),
+                          "tok_s": round(args.prefill_tokens * 1000.0 / ms, 1)}))
+        return 0
+    if args.only == "mixed":
+        print(json.dumps({"only": "mixed", "model": shape_name, "layers": args.layers,
+                          **measure_mixed(model, 64, (128, 4096), 256, 512, 2048, page_size=args.page_size)}))
+        return 0
+    if args.only == "32b":
+        del model
+        torch.cuda.empty_cache()
+        print(json.dumps({"only": "32b", **measure_32b(peaks, warmup, args.page_size)}))
         return 0
     if args.only == "decode":
         harness = DecodeHarness(model, args.batch, args.history, args.steps + 2 * warmup + 2, page_size=args.page_size)
@@ -341,7 +489,7 @@ def main():
             del other
             torch.cuda.empty_cache()
 
-    prefill_tokens = 2048
+    prefill_tokens = args.prefill_tokens
     prefill_ms = measure_prefill(model, prefill_tokens, repeats=5, warmup=3, page_size=args.page_size)
     flops = prefill_flops(config, args.layers, prefill_tokens)
     prefill_frac = flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12)
@@ -349,20 +497,38 @@ def main():
     e2e_value, h2d, d2h = measure_e2e(model, args.batch, args.history, args.steps, warmup, page_size=args.page_size)
     clocks = sampler.stop()
 
+    # The engine's normal mode on the 7B shape and the 32B shape's decode and prefill: numbers of
+    # their own beside the headline, each with the sizes it ran at.
+    workloads = {}
+    if args.config == "1.5b" and not args.skip_workloads:
+        del model
+        torch.cuda.empty_cache()
+        try:
+            big = random_model(dict(QWEN25_7B), seed=1, dtype="bfloat16", device="cuda:0")
+            workloads["mixed_7b"] = {"model": SHAPES["7b"][0], "layers": 28, "layers_full": 28,
+                                     **measure_mixed(big, 64, (128, 4096), 256, 512, 2048, page_size=args.page_size)}
+            del big
+            torch.cuda.empty_cache()
+            workloads["shape_32b"] = measure_32b(peaks, warmup, args.page_size)
+        except Exception as error:  # the headline stands even where a larger shape does not fit
+            workloads["error"] = f"{type(error).__name__}: {error}"
+
     line = {
-        "metric": "decode tok/s at batch 8, 2048 tokens of history (Qwen2.5-1.5B shape); prefill tok/s at 2,048 tokens",
+        "metric": f"decode tok/s at batch {args.batch}, {args.history} tokens of history ({shape_name}); "
+                  f"prefill tok/s at {prefill_tokens} tokens",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random token ids",
         "impl": "ours",
         "config": {
-            "model": "Qwen2.5-1.5B shape", "layers": args.layers, "layers_full": FULL_LAYERS,
+            "model": shape_name, "layers": args.layers, "layers_full": full_layers,
             "hidden": config["hidden_size"], "heads": config["num_attention_heads"],
-            "kv_heads": config["num_key_value_heads"], "head_dim": 128,
+            "kv_heads": config["num_key_value_heads"],
+            "head_dim": config["hidden_size"] // config["num_attention_heads"],
             "intermediate": config["intermediate_size"], "vocab": config["vocab_size"],
-            "tied_head": True, "global_batch": args.batch, "seq_len": args.history,
+            "tied_head": bool(config["tie_word_embeddings"]), "global_batch": args.batch, "seq_len": args.history,
             "new_tokens": args.steps, "page_size": args.page_size, "parallelism": "single GPU",
-            "l2": "inputs larger than L2: 3.1 GB of weights per step against 126 MB",
+            "l2": "inputs larger than L2: every step reads all weights (GBs) against 126 MB",
             "peaks": peak_source,
         },
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
@@ -376,6 +542,7 @@ def main():
         "points": points,
         "clocks": clocks,
     }
+    line.update(workloads)
     print(json.dumps(line))
     return 0
 

@@ -17,7 +17,7 @@ import plain_qwen2 as plain
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
 
-# Three tiny configurations that differ in every size and option.
+# Three tiny configurations that differ in every size and option (B with windows in layers 1 and 2).
 TINY_A = {
     "architectures": ["Qwen2ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 256,
     "num_attention_heads": 4, "num_key_value_heads": 2, "intermediate_size": 704, "vocab_size": 512,
@@ -38,8 +38,12 @@ TINY_C = {
     "vocab_size": 777, "rope_theta": 50000.0, "rms_norm_eps": 3e-6, "tie_word_embeddings": True,
     "max_position_embeddings": 1024, "attention_bias": False,
 }
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-SEEDS = {"A": 11, "B": 22, "C": 33}
+# The two tiny configurations word for word as the baseline states them: A with 256 positions, B
+# with full attention in all three layers (no window) and 512 positions.
+TINY_A_STATED = dict(TINY_A, max_position_embeddings=256)
+TINY_B_STATED = dict(TINY_B, use_sliding_window=False, max_position_embeddings=512)
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "A_stated": TINY_A_STATED, "B_stated": TINY_B_STATED}
+SEEDS = {"A": 11, "B": 22, "C": 33, "A_stated": 11, "B_stated": 22}
 
 
 @functools.lru_cache(maxsize=None)
@@ -77,7 +81,7 @@ def random_tokens(vocab: int, count: int, seed: int) -> List[int]:
 
 
 def run_trace(folder: str, dtype: str, steps: List[dict], max_tokens: int, page_size: int = 64,
-              env_extra=None, timeout: int = 900) -> Dict[int, np.ndarray]:
+              env_extra=None, timeout: int = 900, max_live: int = 8) -> Dict[int, np.ndarray]:
     """Replay ``steps`` with bin/trace_run as a user would (a process of its own) and return
     the logits files it wrote, by step."""
     vocab = json.load(open(os.path.join(folder, "config.json")))["vocab_size"]
@@ -87,7 +91,7 @@ def run_trace(folder: str, dtype: str, steps: List[dict], max_tokens: int, page_
     env["VIPERA_POISON_CACHE"] = "1"
     env.update(env_extra or {})
     command = [sys.executable, TRACE_RUN, "--model", folder, "--dtype", dtype, "--out", out_dir,
-               "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
+               "--max-tokens", str(max_tokens), "--page-size", str(page_size), "--max-live", str(max_live)]
     result = subprocess.run(command, input=text, capture_output=True, text=True, env=env, timeout=timeout)
     if result.returncode != 0:
         raise AssertionError(f"trace_run exited with {result.returncode}\nstdout:\n{result.stdout[-2000:]}\n"

@@ -66,12 +66,13 @@ def test_batched_equals_alone_and_seed_replays():
     assert engine.pools.manager.audit() == ""
 
 
-def test_few_pages_preempt_and_recompute():
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_few_pages_preempt_and_recompute(dtype):
     """With too few pages for all requests at once, the one admitted last is put back and
     computed again; every request still gets the tokens it gets alone."""
     from vipera_rs_b200 import SamplingParams
 
-    folder, engine = _engine("A", "float32", page_size=16, num_pages=14, max_num_seqs=4, max_tokens_per_step=64)
+    folder, engine = _engine("A", dtype, page_size=16, num_pages=14, max_num_seqs=4, max_tokens_per_step=64)
     vocab = helpers.CONFIGS["A"]["vocab_size"]
     prompts = [helpers.random_tokens(vocab, n, 700 + n) for n in (40, 50, 60, 30)]
     params = SamplingParams(max_new_tokens=40)
@@ -79,7 +80,7 @@ def test_few_pages_preempt_and_recompute():
     assert sum(r.preemptions for r in results) >= 1
     for prompt, result in zip(prompts, results):
         assert len(result.tokens) == 40
-        _check_greedy(folder, prompt, result.tokens, "float32")
+        _check_greedy(folder, prompt, result.tokens, dtype)
     assert engine.pools.manager.audit() == ""
     assert engine.stats()["kv_used_pages"] == engine.stats()["kv_kept_pages"]   # nothing but pages kept for reuse
     assert sum(r.reused_tokens for r in results if r.preemptions) > 0             # who was put back found its pages
@@ -102,6 +103,32 @@ def test_long_decoding_and_the_first_tokens(dtype):
     again = eager.generate([prompt], SamplingParams(max_new_tokens=60))[0]
     if dtype == "float32":
         assert again.tokens == result.tokens[:60]
+
+
+def test_temperature_sampling_is_the_plain_samplers_on_the_plain_logits():
+    """The second tiny configuration's workload as the baseline states it: prompts of 5, 100 and 257
+    tokens in portions of 48 beside running decodes, then 24 tokens each at temperature 0.8 with
+    a fixed seed.  Every token is what the plain restatement of the reference's sampler draws
+    from the plain implementation's logits with the same generator, one draw a token."""
+    import plain_sampler
+    from vipera_rs_b200 import SamplingParams
+
+    folder, engine = _engine("B_stated", "float32", page_size=32, ctx=512, max_num_seqs=3, max_tokens_per_step=64,
+                             max_portion=48)
+    vocab = helpers.CONFIGS["B_stated"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, 800 + n) for n in (5, 100, 257)]
+    seed = 20240
+    results = engine.generate(prompts, SamplingParams(max_new_tokens=24, temperature=0.8, seed=seed, eos_ids=[]))
+    assert engine.stats()["steps_with_portions"] >= 6
+    for prompt, result in zip(prompts, results):
+        assert len(result.tokens) == 24
+        logits = helpers.plain_logits(folder, list(prompt) + result.tokens[:-1])
+        rng = plain_sampler.Rng(seed)
+        for index, token in enumerate(result.tokens):
+            row = [plain_sampler.f32(float(v)) for v in logits[len(prompt) - 1 + index]]
+            want = plain_sampler.temperature(row, 0.8, 40, 0.95, 0.05, rng.next_f64())
+            assert token == want, f"prompt of {len(prompt)}: token {index} is {token}, the plain sampler draws {want}"
+    assert engine.pools.manager.audit() == ""
 
 
 def test_sampling_options_through_the_entry_point():
@@ -206,3 +233,43 @@ def test_steps_launched_ahead_change_no_token(dtype):
     assert ahead_engine.pools.manager.audit() == "" and plain_engine.pools.manager.audit() == ""
     stats = ahead_engine.stats()
     assert stats["sequences"] == 0 and stats["kv_used_pages"] == stats["kv_kept_pages"]
+
+
+def test_counters_and_the_per_step_profile_lines(monkeypatch, capfd):
+    """stats() counts steps, tokens and the host's time by stage; with VIPERA_PROFILE_STEP=1 every
+    step prints what it ran and the split of its device time by class of kernel, and every
+    finished request a line in the shape of the reference's request log
+    (crates/vipera-runtime/src/pipeline.rs:234-271, crates/vipera-backend-cpu/src/profile.rs:226-275)."""
+    import json
+
+    from vipera_rs_b200 import SamplingParams
+    from vipera_rs_b200.kernels import ops
+
+    vocab = helpers.CONFIGS["A"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, 60 + n) for n in (20, 9)]
+    folder, engine = _engine("A", "bfloat16", page_size=16, ctx=64, max_num_seqs=2, max_tokens_per_step=16)
+    results = engine.generate(prompts, SamplingParams(max_new_tokens=5))
+    stats = engine.stats()
+    assert stats["steps"] >= 6 and stats["steps_with_portions"] >= 2
+    assert stats["graph_steps"] == stats["steps"]            # every step replayed a captured graph
+    assert stats["tokens_per_step"] * stats["steps"] == 29 + 2 * 4
+    assert set(stats["host_micros_per_step"]) == {"allocate", "compute", "sample", "complete"}
+    assert all(r.stage_micros["compute"] > 0 for r in results)
+    monkeypatch.setenv("VIPERA_PROFILE_STEP", "1")
+    try:
+        _, profiled = _engine("A", "bfloat16", page_size=16, ctx=64, max_num_seqs=2, max_tokens_per_step=16)
+        capfd.readouterr()
+        again = profiled.generate(prompts, SamplingParams(max_new_tokens=5))
+        lines = capfd.readouterr().err.splitlines()
+    finally:
+        ops.profile = None
+    assert [r.tokens for r in again] == [r.tokens for r in results]
+    steps = [line for line in lines if line.startswith("STEP ")]
+    assert len(steps) == profiled.stats()["steps"] and all(" eager " in line for line in steps)
+    assert any(" chunk " in line for line in steps) and any(" decode " in line for line in steps)
+    split = [line for line in lines if line.startswith("PROFILE decode")]
+    assert split and "proj" in split[-1] and "attention" in split[-1] and "norm" not in split[-1].split(":")[0]
+    logs = [json.loads(line) for line in lines if line.startswith("{")]
+    assert len(logs) == 2 and all(log["event"] == "generation" and log["finish"] == "length" for log in logs)
+    assert {log["prompt_tokens"] for log in logs} == {20, 9}
+    assert all(set(log["stage_micros"]) == {"allocate", "compute", "sample", "complete"} for log in logs)

@@ -7,6 +7,8 @@ import numpy as np
 import pytest
 import torch
 
+import plain_sampler
+
 pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
@@ -218,7 +220,7 @@ def test_attention_single_tokens(heads, kv_heads, d, page, dtype, window):
         for cluster in ("8", "8p", "16", "16p", "0"):
             os.environ["VIPERA_ATTENTION_CLUSTER"] = cluster
             try:
-                for chunk_splits in (ops.decode_splits(entries, kv_heads, max(lengths)), (32, 10), (512, 1)):
+                for chunk_splits in (ops.decode_splits(entries, kv_heads, max(lengths), ops.sm_count(DEV)), (32, 10), (512, 1)):
                     chunk, splits = chunk_splits
                     scratch = torch.full((ops.attention_decode_scratch_floats(entries, heads, d, splits),),
                                          float("nan"), device=DEV)
@@ -249,7 +251,7 @@ def test_attention_decode_long_histories(heads, kv_heads, d, page, window):
     qd = q.to(torch.bfloat16).reshape(entries, heads * d).to(DEV)
     kp, vp, tb = k_pool.to(DEV), v_pool.to(DEV), table.to(DEV)
     positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
-    chunk, splits = ops.decode_splits(entries, kv_heads, 8192)
+    chunk, splits = ops.decode_splits(entries, kv_heads, 8192, ops.sm_count(DEV))
     for cluster in ("8", "8p", "16", "16p", "0"):
         os.environ["VIPERA_ATTENTION_CLUSTER"] = cluster
         try:
@@ -485,6 +487,15 @@ def test_sampler_matches_host():
             else:
                 want = draw_temperature(logits[row].numpy(), config, [], uniform[row])
             assert int(tokens[row]) == want, (config, row)
+            if row in (0, 5) and config["temperature"] > 0.0:
+                # and directly to the plain restatement of the reference's sampler, without the
+                # package's own host sampler in between
+                direct = plain_sampler.temperature([float(v) for v in logits[row]], config["temperature"],
+                                                   config["top_k"], config["top_p"], config["min_p"], uniform[row])
+                assert int(tokens[row]) == direct, (config, row)
+    ops.argmax(dev, tokens, status)
+    for row in (0, 3, 4, 7):
+        assert int(tokens[row]) == plain_sampler.greedy([float(v) for v in logits[row]])
 
 
 def test_sampler_distribution_and_penalties():

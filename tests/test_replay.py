@@ -11,8 +11,9 @@ from helpers import TraceBuilder
 
 pytestmark = pytest.mark.gpu
 
-PAGE = {"A": 16, "B": 32, "C": 64}
-LENGTHS = {"A": [1, 7, 33, 64, 200], "B": [5, 100, 257], "C": [2, 50, 130]}
+PAGE = {"A": 16, "B": 32, "C": 64, "A_stated": 16, "B_stated": 32}
+LENGTHS = {"A": [1, 7, 33, 64, 200], "B": [5, 100, 257], "C": [2, 50, 130],
+           "A_stated": [1, 7, 33, 64], "B_stated": [5, 100, 257]}
 FP32_TOL = 1e-4
 BF16_TOL = 1e-2  # of the request's largest |logit|; bfloat16 keeps 8 bits of mantissa
 
@@ -90,7 +91,7 @@ def build_trace(name, vocab):
     return builder, requests, longest
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "A_stated", "B_stated"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replay_matches_plain(name, dtype):
     folder = helpers.model_folder(name, dtype)

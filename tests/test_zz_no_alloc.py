@@ -4,8 +4,9 @@ with nothing but pointers.  Such a caller (a loop that must not synchronise the 
 host that has given all device memory to its own pool) still owns its inputs and outputs;
 only the scratch comes from inside the library.
 
-Held to the library's ordinary argmax on the same logits, twice in a row with different
-data, so that what the first call left in the shared scratch would show if it were read.
+Held to the library's ordinary argmax on the same logits and, independently of this library,
+to torch's argmax over the finite values (ties to the lowest index), twice in a row with
+different data, so that what the first call left in the shared scratch would show if it were read.
 This file sorts last on purpose: a run that stops at the first failure has then already run
 every other test."""
 import ctypes
@@ -50,6 +51,14 @@ def test_static_argmax_matches_the_ordinary_one_twice():
         assert torch.equal(got, want), f"call {call}"
         assert torch.equal(got_status, want_status), f"call {call}"
         assert int(got[1]) == 0 and int(got[2]) == 11
+        # and to an argmax that shares nothing with this library: non-finite values masked out,
+        # the first of equal maxima taken
+        finite = torch.where(torch.isfinite(logits), logits, torch.full_like(logits, float("-inf")))
+        best = finite.max(dim=1, keepdim=True).values
+        index = torch.arange(vocab, device=device).expand(rows, vocab)
+        first = torch.where(finite == best, index, torch.full_like(index, vocab)).min(dim=1).values
+        assert torch.equal(got.long(), first), f"call {call}"
+        assert int(got_status.abs().sum()) == 0
     # the optional status pointer may be null
     code = fn(logits.data_ptr(), rows, vocab, got.data_ptr(), None, stream)
     torch.cuda.synchronize()

@@ -78,8 +78,11 @@ class CachePools:
             bool(reuse_prefixes) and not self.states)
         self.pool_tensors: List[torch.Tensor] = []
         self.views: Dict[int, object] = {}
+        # One page beyond those the manager hands out, per group: the scratch page.  No request
+        # ever holds it; tokens that pad a captured step to its size class write there.
+        self.scratch_pages: List[int] = list(self.num_pages)
         for index, (group, pages) in enumerate(zip(self.groups, self.num_pages)):
-            pool = torch.zeros((len(group.slots), 2, pages, self.page_size, group.num_kv_heads, group.head_dim),
+            pool = torch.zeros((len(group.slots), 2, pages + 1, self.page_size, group.num_kv_heads, group.head_dim),
                                dtype=dtype, device=device)
             self.pool_tensors.append(pool)
             for position, slot in enumerate(group.slots):

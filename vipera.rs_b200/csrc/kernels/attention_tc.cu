@@ -786,15 +786,19 @@ bool tma_takes_page(int page_size) {
 // (at most 128) of one KV head and 64 values, 128-byte swizzle.  Maps are kept by pool.
 // `run`: the same pool as rows that follow one another whatever page they are in,
 // [pages * page_size, kv_heads, 128], in boxes of 128 rows.
-const CUtensorMap* pool_map(const void* pool, int pages, int page_size, int kv_heads, bool run) {
+// The map is copied out under the lock: the table may be emptied by a later call.
+bool pool_map(const void* pool, int pages, int page_size, int kv_heads, bool run, CUtensorMap* out) {
   static std::map<std::tuple<const void*, int, int, int, bool>, CUtensorMap> kept;
   static std::mutex guard;
   std::lock_guard<std::mutex> lock(guard);
   const auto key = std::make_tuple(pool, pages, page_size, kv_heads, run);
   auto found = kept.find(key);
-  if (found != kept.end()) return &found->second;
+  if (found != kept.end()) {
+    *out = found->second;
+    return true;
+  }
   EncodeTiledFn encode = encode_tiled_fn();
-  if (!encode || (reinterpret_cast<uintptr_t>(pool) & 15)) return nullptr;
+  if (!encode || (reinterpret_cast<uintptr_t>(pool) & 15)) return false;
   CUtensorMap map;
   if (run) {
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(kv_heads),
@@ -805,9 +809,11 @@ const CUtensorMap* pool_map(const void* pool, int pages, int page_size, int kv_h
     CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(pool), dims, strides, box, elem,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return nullptr;
+    if (r != CUDA_SUCCESS) return false;
     if (kept.size() > 4096) kept.clear();
-    return &kept.emplace(key, map).first->second;
+    kept.emplace(key, map);
+    *out = map;
+    return true;
   }
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(kv_heads), static_cast<cuuint64_t>(page_size),
                         static_cast<cuuint64_t>(pages)};
@@ -818,9 +824,11 @@ const CUtensorMap* pool_map(const void* pool, int pages, int page_size, int kv_h
   CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(pool), dims, strides, box, elem,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return nullptr;
+  if (r != CUDA_SUCCESS) return false;
   if (kept.size() > 4096) kept.clear();
-  return &kept.emplace(key, map).first->second;
+  kept.emplace(key, map);
+  *out = map;
+  return true;
 }
 
 template <bool TMA_KV>
@@ -871,11 +879,12 @@ VIPERA_API int vipera_attention_prefill_tc(const void* q, void* out, const void*
   dim3 grid(num_heads, (num_tokens + kQ - 1) / kQ + num_entries);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (tma_takes_page(page_size) && std::getenv("VIPERA_ATTENTION_NO_TMA") == nullptr) {
-    const CUtensorMap* k_map = pool_map(k_pool, num_pages, page_size, num_kv_heads, false);
-    const CUtensorMap* v_map = pool_map(v_pool, num_pages, page_size, num_kv_heads, false);
-    const CUtensorMap* k_run = pool_map(k_pool, num_pages, page_size, num_kv_heads, true);
-    const CUtensorMap* v_run = pool_map(v_pool, num_pages, page_size, num_kv_heads, true);
-    if (k_map && v_map && k_run && v_run) return launch_attention<true>(*k_map, *v_map, *k_run, *v_run, p, grid, s);
+    CUtensorMap k_map, v_map, k_run, v_run;
+    if (pool_map(k_pool, num_pages, page_size, num_kv_heads, false, &k_map) &&
+        pool_map(v_pool, num_pages, page_size, num_kv_heads, false, &v_map) &&
+        pool_map(k_pool, num_pages, page_size, num_kv_heads, true, &k_run) &&
+        pool_map(v_pool, num_pages, page_size, num_kv_heads, true, &v_run))
+      return launch_attention<true>(k_map, v_map, k_run, v_run, p, grid, s);
   }
   CUtensorMap none{};
   return launch_attention<false>(none, none, none, none, p, grid, s);

@@ -93,13 +93,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  When the limit runs out, or another thread's wait already did, the caller
 // goes on as if the barrier had completed: every role then runs to its end without waiting,
 // so the block drains; what it writes is marked invalid by the status word.
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
-  for (uint32_t spin = 0; spin < kWaitLimit; ++spin) {
+__device__ __forceinline__ void mbar_wait_limited(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                  uint32_t limit) {
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     if (mbar_try_wait(bar, parity)) return;
     if ((spin & 1023u) == 1023u && *abort_flag) return;
   }
   *abort_flag = 1;
   atomicExch(status, GEMM_TC_WAIT_EXPIRED);
+}
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  mbar_wait_limited(bar, parity, abort_flag, status, kWaitLimit);
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
@@ -993,6 +997,34 @@ VIPERA_API int vipera_gemm_tc_rope(const void* A, const void* W, int T, int N, i
   p.rope_style = rope->rope_style;
   p.write_cache = rope->write_cache;
   return run_gemm(A, W, T, N, K, EPI_ROPE_CACHE, bias, nullptr, VIPERA_BF16, nullptr, nullptr, 0, status, stream, &p);
+}
+
+// ---------------------------------------------------------------------------------------
+// A wait that runs out, on purpose and harmlessly, so that the way the kernels report it can be
+// tested without a fault: one block waits, with the kernels' own bounded wait and a limit of
+// `limit` polls, on a barrier in its shared memory that is initialised, that nothing arrives at
+// and that no copy is bound to.  Nothing is in flight when the wait gives up; the code lands in
+// the status word as it does from the product kernel, and a second thread that waits on the same
+// barrier leaves through the block's abort flag as the product kernel's other roles do.
+// ---------------------------------------------------------------------------------------
+__global__ void wait_probe_kernel(int* status, uint32_t limit) {
+  __shared__ uint64_t barrier;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&barrier, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait_limited(&barrier, 0, &abort_flag, status, limit);
+  __syncthreads();
+  if (threadIdx.x == 32) mbar_wait_limited(&barrier, 0, &abort_flag, status, 1u << 20);
+}
+
+VIPERA_API int vipera_gemm_tc_wait_probe(int* status, int limit, void* stream) {
+  if (!status || limit < 1 || limit > (1 << 16)) return VIPERA_BAD_ARGUMENT;
+  wait_probe_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(status, static_cast<uint32_t>(limit));
+  return vipera_launch_status();
 }
 
 VIPERA_API const char* vipera_gemm_tc_status_text(int status) { return vipera_status_text(status); }

@@ -27,6 +27,9 @@
 //
 //   The first call on a device looks up the array's device address (cudaGetSymbolAddress,
 //   with that device current) and keeps it; make that first call outside any stream capture.
+//   The kept address is written without a lock: two host threads that both make the first
+//   call on a device both look it up and both store the same value, which is harmless, but
+//   a program that wants no such overlap makes one call per device before it starts its threads.
 //
 //   All calls share the one array.  Every word a call reads was written earlier in the same
 //   call, so nothing has to be cleared and what an earlier call left behind is never seen;

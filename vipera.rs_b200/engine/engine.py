@@ -9,6 +9,8 @@ carries the reference's ``Generation`` fields (engine.rs:62-82).
 """
 from __future__ import annotations
 
+import os
+import sys
 import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Union
@@ -18,7 +20,7 @@ import torch
 
 from ..build import runtime_module
 from ..cache import CachePools
-from ..errors import InternalError, InvalidArgumentError
+from ..errors import InternalError, InvalidArgumentError, ViperaError
 from ..kernels import ops
 from ..sampling import DeviceSampler, SamplingParams
 from .loader import load_model
@@ -36,6 +38,20 @@ class Generation:
     processed_tokens: int        # tokens run through the model, recomputation included
     preemptions: int
     reused_tokens: int = 0       # prompt tokens whose keys and values an earlier request had computed
+    # Host microseconds of the steps the request took part in, by stage (the reference's stage
+    # names, crates/vipera-runtime/src/pipeline.rs:17-72): allocate = scheduling and page
+    # reservation, compute = building and launching the step, sample = drawing and waiting for
+    # the tokens, complete = bookkeeping after the step.  A step's time counts for each of its requests.
+    stage_micros: Dict[str, int] = field(default_factory=dict)
+
+    def to_json(self) -> str:
+        """One line in the shape of the reference's request log (pipeline.rs:234-271)."""
+        import json
+
+        return json.dumps({"event": "generation", "sequence": self.request, "prompt_tokens": self.prompt_tokens,
+                           "reused_tokens": self.reused_tokens, "generated_tokens": len(self.tokens),
+                           "finish": self.finish, "total_micros": sum(self.stage_micros.values()),
+                           "stage_micros": self.stage_micros})
 
 
 @dataclass
@@ -45,6 +61,8 @@ class StepReport:
     preempted: List[int] = field(default_factory=list)
     num_tokens: int = 0                                       # tokens the step ran
     num_entries: int = 0
+    graph: bool = False                                       # the step replayed a captured graph
+    stage_micros: Dict[str, int] = field(default_factory=dict)  # host time of the step by stage
 
 
 class _RowsAhead:
@@ -131,6 +149,9 @@ class Engine:
         self._next_id = 0
         self.generations = 0
         self.failed = 0
+        # The records of requests that ended with a failed step (the step's report is lost with
+        # the exception that step() raises); the caller may read and clear the list.
+        self.failed_generations: List[Generation] = []
         # A step launched ahead may be dropped and run again; keys and values are then written
         # twice with the same numbers, but a state of fixed size that a mixer updates in place
         # would move twice.  Models with such state decode step by step.
@@ -138,6 +159,19 @@ class Engine:
         self._ahead: Optional[_Ahead] = None
         self.steps_ahead = 0          # steps launched before their plan existed ...
         self.steps_ahead_dropped = 0  # ... and those of them whose plan turned out otherwise
+        self.totals = {"steps": 0, "tokens": 0, "entries": 0, "graph_steps": 0, "steps_with_portions": 0,
+                       "stage_micros": {"allocate": 0, "compute": 0, "sample": 0, "complete": 0}}
+        self._request_micros: Dict[int, Dict[str, int]] = {}
+        # VIPERA_PROFILE_STEP=1: a line per step on stderr (what ran, how, the host's time by stage),
+        # and a line per finished request in the shape of the reference's request log.
+        self.profile_steps = os.environ.get("VIPERA_PROFILE_STEP", "0") not in ("", "0")
+        self.kernel_profile = None
+        if self.profile_steps:
+            # the split of a step's device time by class of kernel needs steps launched kernel by
+            # kernel, one at a time
+            self.kernel_profile = ops.profile = ops.KernelProfile()
+            self.runner.decode_graphs = self.runner.step_graphs = False
+            self.lookahead = False
 
     # ------------------------------------------------------------------------------
     def add_request(self, prompt_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -160,25 +194,34 @@ class Engine:
         return self.scheduler.has_work()
 
     def step(self) -> StepReport:
+        clock = time.perf_counter
+        t0 = clock()
         plan = self.scheduler.schedule()
+        t1 = clock()
         report = StepReport(preempted=list(plan.preempted), num_tokens=int(plan.num_tokens),
                             num_entries=int(plan.num_entries))
         ahead, self._ahead = self._ahead, None
+        t2 = t3 = t1
         if plan.empty:
             outcome = self.scheduler.complete(plan, [])
         else:
+            replays = self.runner.graph_replays
             try:
                 drawn = logits = None
                 if ahead is not None and ahead.serves(plan):
                     # this step was launched while the one before still ran
                     drawn, logits = ahead.drawn, ahead.logits
                     ahead = None
+                    replays -= 1
                 else:
                     step = StepInput(requests=plan.requests, tokens=plan.tokens, counts=plan.counts, pos0=plan.starts,
                                      fresh=plan.fresh, logit_rows=plan.row_token_index)
+                    if self.kernel_profile is not None:
+                        self.kernel_profile.begin()
                     logits = self.runner.run(step)
                     if logits is not None:
                         drawn = self.sampler.launch(logits, plan)
+                t2 = clock()
                 if drawn is not None:
                     if self.lookahead:
                         self._ahead = self._launch_ahead(plan)
@@ -188,21 +231,61 @@ class Engine:
                     sampled = []
                     torch.cuda.current_stream().synchronize()
                     ops.check_kernel_status(self.model.device)
+                t3 = clock()
                 outcome = self.scheduler.complete(plan, sampled)
                 if self._ahead is not None and outcome["finished"]:
                     # a request ended on the token just read: the step launched ahead is not the next one
                     self._ahead = None
                     self.steps_ahead_dropped += 1
-            except InternalError:
+            except BaseException as error:
+                # Whatever went wrong, the plan's requests do not stay half-run: they end with
+                # reason "error" and give their pages back, the others go on
+                # (crates/vipera-runtime/src/engine.rs:1625-1672).  A fault of the engine itself
+                # is raised as it is; anything else is raised too, after the same clean-up.
                 self._ahead = None
                 outcome = self.scheduler.fail(plan)
                 self.failed += len(outcome["finished"])
                 self._collect(report, outcome)
-                raise
+                self.failed_generations.extend(report.finished)
+                if isinstance(error, ViperaError) or not isinstance(error, Exception):
+                    raise
+                raise InternalError(f"a step failed: {type(error).__name__}: {error}") from error
+            report.graph = self.runner.graph_replays > replays
         if ahead is not None:
             self.steps_ahead_dropped += 1
+        t4 = clock()
+        stages = {"allocate": int((t1 - t0) * 1e6), "compute": int((t2 - t1) * 1e6),
+                  "sample": int((t3 - t2) * 1e6), "complete": int((t4 - t3) * 1e6)}
+        report.stage_micros = stages
+        self._account(plan, report, stages)
         self._collect(report, outcome)
         return report
+
+    def _account(self, plan, report: StepReport, stages: Dict[str, int]) -> None:
+        """Add the step to the engine's counters and to the stage times of its requests."""
+        if plan.empty:
+            return
+        totals = self.totals
+        totals["steps"] += 1
+        totals["tokens"] += report.num_tokens
+        totals["entries"] += report.num_entries
+        totals["graph_steps"] += 1 if report.graph else 0
+        if report.num_tokens > report.num_entries:
+            totals["steps_with_portions"] += 1
+        for stage, micros in stages.items():
+            totals["stage_micros"][stage] += micros
+        for request in plan.requests:
+            mine = self._request_micros.setdefault(int(request), dict.fromkeys(stages, 0))
+            for stage, micros in stages.items():
+                mine[stage] += micros
+        if self.profile_steps:
+            kind = "chunk" if report.num_tokens > report.num_entries else "decode"
+            if self.kernel_profile is not None:
+                self.kernel_profile.end(kind)
+                print(self.kernel_profile.line(kind), file=sys.stderr, flush=True)
+            print(f"STEP {totals['steps']} {kind} entries {report.num_entries} tokens {report.num_tokens} "
+                  f"{'graph' if report.graph else 'eager'} host_us " +
+                  " ".join(f"{stage} {micros}" for stage, micros in stages.items()), file=sys.stderr, flush=True)
 
     def _launch_ahead(self, plan) -> Optional["_Ahead"]:
         """Where the scheduler can tell what the next step is before this one's tokens are
@@ -227,11 +310,15 @@ class Engine:
     def _collect(self, report: StepReport, outcome: dict) -> None:
         report.tokens.extend((int(r), int(t)) for r, t in outcome["tokens"])
         for item in outcome["finished"]:
-            report.finished.append(Generation(
+            generation = Generation(
                 request=int(item["request"]), tokens=[int(t) for t in item["tokens"]], finish=item["reason"],
                 prompt_tokens=int(item["prompt_tokens"]), processed_tokens=int(item["processed_tokens"]),
-                preemptions=int(item["preemptions"]), reused_tokens=int(item["reused_tokens"])))
+                preemptions=int(item["preemptions"]), reused_tokens=int(item["reused_tokens"]),
+                stage_micros=self._request_micros.pop(int(item["request"]), {}))
+            report.finished.append(generation)
             self.generations += 1
+            if self.profile_steps:
+                print(generation.to_json(), file=sys.stderr, flush=True)
 
     def generate(self, prompts: Sequence[Sequence[int]], params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
                  on_token=None) -> List[Generation]:
@@ -240,7 +327,17 @@ class Engine:
             params = [params or SamplingParams()] * len(prompts)
         if len(params) != len(prompts):
             raise InvalidArgumentError("one SamplingParams is needed for each prompt, or one for all")
-        ids = [self.add_request(prompt, p) for prompt, p in zip(prompts, params)]
+        ids = []
+        try:
+            for prompt, p in zip(prompts, params):
+                ids.append(self.add_request(prompt, p))
+        except BaseException:
+            # A prompt that is refused must not leave the ones before it waiting in the
+            # scheduler for a later call to run: they are cancelled (they hold no pages yet; the
+            # next step reports them as cancelled).
+            for request in ids:
+                self.cancel(request)
+            raise
         results: Dict[int, Generation] = {}
         while len(results) < len(ids):
             if not self.has_work():
@@ -257,7 +354,17 @@ class Engine:
     def stats(self) -> dict:
         manager = self.pools.manager
         groups = [manager.stats(g) for g in range(manager.num_groups)]
+        totals = self.totals
+        steps = max(totals["steps"], 1)
         return {
+            "steps": totals["steps"],
+            "steps_with_portions": totals["steps_with_portions"],
+            "graph_steps": totals["graph_steps"],
+            "tokens_per_step": totals["tokens"] / steps,
+            "entries_per_step": totals["entries"] / steps,
+            "host_micros_per_step": {stage: micros / steps for stage, micros in totals["stage_micros"].items()},
+            "steps_ahead": self.steps_ahead,
+            "steps_ahead_dropped": self.steps_ahead_dropped,
             "sequences": len(manager.open_requests()),
             "waiting": self.scheduler.num_waiting,
             "running": self.scheduler.num_running,

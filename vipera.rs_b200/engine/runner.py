@@ -15,6 +15,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
+import os
+
 import numpy as np
 import torch
 
@@ -42,6 +44,18 @@ def _round_up_pow2(value: int, least: int = 8) -> int:
     return out
 
 
+# Token counts a captured step is padded to.  Steps under a token budget are mostly full, so the
+# steps that matter hit a bucket exactly; in between at most a third of a step is padding.
+_TOKEN_BUCKETS = (8, 16, 32, 64, 96, 128, 192, 256, 384, 512, 768, 1024, 1536, 2048, 3072, 4096, 6144, 8192)
+
+
+def _token_bucket(tokens: int) -> Optional[int]:
+    for bucket in _TOKEN_BUCKETS:
+        if tokens <= bucket:
+            return bucket
+    return None
+
+
 class ModelRunner:
     """Owns the workspace and the staging buffers; turns a StepInput into device tensors,
     runs the model, and returns the logits tensor (device, float32, [rows, vocab])."""
@@ -54,6 +68,9 @@ class ModelRunner:
         self.manager = pools.manager
         self.device = model.device
         self.max_model_len = int(max_model_len)
+        prepare = getattr(model, "prepare", None)
+        if prepare is not None:
+            prepare(self.max_model_len)
         self.workspace = Workspace(self.device)
         self._staging_host: Optional[torch.Tensor] = None
         self._staging_dev: Optional[torch.Tensor] = None
@@ -61,9 +78,16 @@ class ModelRunner:
         self._copy_pending = False
         self.steps_run = 0
         self.decode_graphs = True
+        # Steps that bring portions of prompts replay captured graphs too (padded to a size
+        # class); VIPERA_STEP_GRAPHS=0 launches them kernel by kernel.
+        self.step_graphs = os.environ.get("VIPERA_STEP_GRAPHS", "1") != "0"
         self._graph_safe = None  # asked of the model once
         self.max_graph_entries = 256
+        self.max_kept_graphs = 256
         self._graphs = {}
+        self._step_graphs = {}
+        self.graph_replays = 0   # steps that replayed a captured graph ...
+        self.eager_steps = 0     # ... and steps launched kernel by kernel
         self._page_sizes = [self.manager.group(g)[0] for g in range(self.manager.num_groups)]
 
     # ------------------------------------------------------------------------------
@@ -94,7 +118,10 @@ class ModelRunner:
         if step.logit_rows.size and (int(step.logit_rows.min()) < 0 or int(step.logit_rows.max()) >= total):
             raise InvalidArgumentError("a wanted row lies outside the step's tokens")
 
-    def build_context(self, step: StepInput, dtype: torch.dtype) -> StepContext:
+    def _host_arrays(self, step: StepInput, widths=None):
+        """The step's description as host arrays, checked: per token (positions, entry), per
+        entry (starts, first position, state slot, fresh), wanted rows, and per group the block
+        tables, as wide as `widths` says or as the longest request needs."""
         self.validate(step)
         counts = np.asarray(step.counts, dtype=np.int32)
         pos0 = np.asarray(step.pos0, dtype=np.int32)
@@ -108,8 +135,8 @@ class ModelRunner:
         max_len = int((pos0 + counts).max())
         tables = []
         for g in range(self.manager.num_groups):
-            page_size = self.manager.group(g)[0]
-            width = _round_up_pow2((max_len + page_size - 1) // page_size)
+            page_size = self._page_sizes[g]
+            width = widths[g] if widths is not None else _round_up_pow2((max_len + page_size - 1) // page_size)
             table = self.manager.tables(list(step.requests), g, width)
             # Every position of the step must have its page.
             last_page = (pos0 + counts - 1) // page_size
@@ -118,7 +145,11 @@ class ModelRunner:
             tables.append(table)
         slots = np.asarray([self.manager.state_slot(r) for r in step.requests], dtype=np.int32)
         fresh = np.asarray(step.fresh, dtype=np.int32)
+        return counts, pos0, starts, token_entry, positions, rows, tables, slots, fresh, max_len
 
+    def build_context(self, step: StepInput, dtype: torch.dtype) -> StepContext:
+        counts, pos0, starts, token_entry, positions, rows, tables, slots, fresh, max_len = self._host_arrays(step)
+        entries, total = counts.shape[0], int(starts[-1])
         pieces = [step.tokens.astype(np.int32, copy=False), positions, token_entry, starts, pos0, slots, fresh, rows]
         pieces += [t.reshape(-1) for t in tables]
         sizes = [p.shape[0] for p in pieces]
@@ -164,9 +195,40 @@ class ModelRunner:
                 and len(step.tokens) == entries and len(step.logit_rows) == entries):
             logits = self._run_graph(step)
             if logits is not None:
+                self.graph_replays += 1
                 return logits
+        if self.step_graphs and self._graph_safe and entries < self.max_graph_entries:
+            graph = self._step_graph_for(step)
+            if graph is not None:
+                self.graph_replays += 1
+                return graph.run(step)
+        self.eager_steps += 1
         ctx = self.build_context(step, self.model.dtype)
         return self.forward(ctx)
+
+    def _step_graph_for(self, step: StepInput):
+        """The captured graph of the step's size class (made at the first step of the class), or
+        None where the step is larger than any class."""
+        total = len(step.tokens)
+        bucket = _token_bucket(total)
+        if bucket is None:
+            return None
+        entries = len(step.counts) + (1 if total < bucket else 0)   # padding tokens form an entry of their own
+        entry_bucket = _round_up_pow2(entries, 2)
+        rows = len(step.logit_rows)
+        row_bucket = min(_round_up_pow2(rows, 1), bucket) if rows else 0
+        longest = int(max(first + count for first, count in zip(step.pos0, step.counts)))
+        widths = tuple(_round_up_pow2(max(-(-longest // page_size), -(-bucket // page_size)))
+                       for page_size in self._page_sizes)
+        key = (bucket, entry_bucket, row_bucket, widths)
+        graph = self._step_graphs.get(key)
+        if graph is not None and graph.stale():
+            graph = None
+        if graph is None:
+            if len(self._step_graphs) >= self.max_kept_graphs:
+                self._step_graphs.pop(next(iter(self._step_graphs)))
+            graph = self._step_graphs[key] = _StepGraph(self, bucket, entry_bucket, row_bucket, widths)
+        return graph
 
     # ------------------------------------------------------------------------------
     # decode steps through CUDA graphs
@@ -325,3 +387,117 @@ class _DecodeGraph:
         self.graph.replay()
         ops.launches += self.kernels
         return self.logits if entries == self.bucket else self.logits[:entries]
+
+
+class _StepGraph:
+    """One captured step of any make-up: `tokens` tokens in `entries` entries, `rows` wanted
+    rows, block tables of the given widths.  A step of the class that is smaller is padded:
+    the spare tokens form one more entry that starts at position 0 and whose block table names
+    only the group's scratch page (a page no request ever holds), so what they compute lands
+    nowhere; entries beyond that bring no tokens; spare wanted rows repeat the first."""
+
+    def __init__(self, runner: ModelRunner, tokens: int, entries: int, rows: int, widths):
+        self.runner = runner
+        self.tokens, self.entries, self.rows = int(tokens), int(entries), int(rows)
+        self.widths = [int(w) for w in widths]
+        t, e = self.tokens, self.entries
+        self.sizes = [t, t, t, e + 1, e, e, e, max(self.rows, 1)] + [e * w for w in self.widths]
+        self.offsets = np.concatenate([[0], np.cumsum(self.sizes)]).astype(np.int64)
+        total = int(self.offsets[-1])
+        self.host = torch.empty(total, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.empty(total, dtype=torch.int32, device=runner.device)
+        self.copy_done = torch.cuda.Event()
+        self.pending = False
+        self.graph = None
+        self.logits = None
+        self.generations = None
+        self.kernels = 0
+
+    def stale(self) -> bool:
+        from ..kernels import ops
+
+        return self.graph is not None and self.generations != (self.runner.workspace.generation, ops.buffer_generation)
+
+    def _part(self, index):
+        return self.dev[int(self.offsets[index]):int(self.offsets[index + 1])]
+
+    def _host_part(self, index):
+        return self.host.numpy()[int(self.offsets[index]):int(self.offsets[index + 1])]
+
+    def fill(self, step: StepInput) -> int:
+        """The step's inputs, padded to the class, into the staging buffer and on their way to
+        the device; returns the number of wanted rows."""
+        runner = self.runner
+        counts, pos0, starts, token_entry, positions, rows, tables, slots, fresh, _ = runner._host_arrays(
+            step, self.widths)
+        own_tokens, own_entries = int(starts[-1]), counts.shape[0]
+        if self.pending:
+            self.copy_done.synchronize()
+            self.pending = False
+        t, e = self.tokens, self.entries
+        spare = t - own_tokens
+        part = self._host_part
+        tokens_h, positions_h, entry_h = part(0), part(1), part(2)
+        tokens_h[:own_tokens] = step.tokens
+        positions_h[:own_tokens] = positions
+        entry_h[:own_tokens] = token_entry
+        if spare:
+            tokens_h[own_tokens:] = 0
+            positions_h[own_tokens:] = np.arange(spare, dtype=np.int32)
+            entry_h[own_tokens:] = own_entries
+        starts_h = part(3)
+        starts_h[:own_entries + 1] = starts
+        starts_h[own_entries + 1:] = t          # the padding entry ends the step; the rest bring nothing
+        for index, values in ((4, pos0), (5, slots), (6, fresh)):
+            target = part(index)
+            target[:own_entries] = values
+            target[own_entries:] = 0
+        rows_h = part(7)
+        if self.rows:
+            rows_h[:rows.size] = rows
+            rows_h[rows.size:] = rows[0]
+        for g, table in enumerate(tables):
+            target = part(8 + g).reshape(e, self.widths[g])
+            target[:own_entries] = table
+            target[own_entries:] = runner.pools.scratch_pages[g]
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copy_done.record()
+        self.pending = True
+        return int(rows.size)
+
+    def _context(self) -> StepContext:
+        runner, t, e = self.runner, self.tokens, self.entries
+        tables = [self._part(8 + g).view(e, w) for g, w in enumerate(self.widths)]
+        return StepContext(
+            num_tokens=t, num_entries=e, tokens=self._part(0), positions=self._part(1), token_entry=self._part(2),
+            entry_starts=self._part(3), entry_pos0=self._part(4), state_slots=self._part(5), fresh=self._part(6),
+            block_tables=tables, logit_rows=self._part(7) if self.rows else None, num_logit_rows=self.rows,
+            host_counts=[], host_pos0=[], max_count=t,
+            max_kv_len=min(w * runner._page_sizes[g] for g, w in enumerate(self.widths)) if self.widths else 0,
+            all_single=False, dtype=runner.model.dtype, workspace=runner.workspace,
+            logits_all_rows=False, extras={"graph": True})
+
+    def run(self, step: StepInput) -> Optional[torch.Tensor]:
+        from ..kernels import ops
+
+        rows = self.fill(step)
+        runner = self.runner
+        if self.graph is None or self.stale():
+            ctx = self._context()
+            # Once outside a graph: buffers get their final sizes, kernels are loaded.  The keys
+            # and values of the step are written here and again, identically, by the replay.
+            runner.forward(ctx)
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launches
+            with torch.cuda.graph(graph):
+                self.logits = runner.forward(ctx)
+            self.kernels = ops.launches - before
+            ops.launches = before
+            self.graph = graph
+            self.generations = (runner.workspace.generation, ops.buffer_generation)
+        self.graph.replay()
+        ops.launches += self.kernels
+        if self.logits is None:
+            return None
+        return self.logits if rows == self.rows else self.logits[:rows]

@@ -77,10 +77,86 @@ def stream_synchronize() -> None:
 launches = 0  # kernels launched through this module (replayed graphs add what they captured)
 
 
+class KernelProfile:
+    """Device time of a step by class of kernel, as the reference splits a pass into its kinds
+    of work (crates/vipera-backend-cpu/src/profile.rs:226-275).  While one is installed
+    (``ops.profile = KernelProfile()``) every launcher records a CUDA event behind its launch;
+    the time between two events goes to the class of the later one.  Steps must then be
+    launched kernel by kernel (a replayed graph launches nothing through this module)."""
+
+    CLASSES = {
+        "embed": "embed", "rmsnorm": "norm", "rope_cache": "rope_kv",
+        "gemm_tc": "proj", "gemm_tc_rope": "proj", "gemv_small": "proj", "gemm_simt": "proj",
+        "attention": "attention", "attention_prefill": "attention", "attention_prefill_tc": "attention",
+        "attention_decode": "attention",
+        "argmax": "sample", "sample": "sample", "apply_penalties": "sample", "feed_tokens": "sample",
+    }
+    ORDER = ("proj", "attention", "norm", "rope_kv", "embed", "sample", "other")
+
+    def __init__(self):
+        self._events = []
+        self._marks = []
+        self._start = None
+        self.totals = {}   # kind of step -> {"steps": n, "ms": total, class: ms}
+
+    def _event(self):
+        return self._events.pop() if self._events else torch.cuda.Event(enable_timing=True)
+
+    def begin(self) -> None:
+        self._marks = []
+        self._start = self._event()
+        self._start.record()
+
+    def mark(self, what: str) -> None:
+        if self._start is None:
+            return
+        event = self._event()
+        event.record()
+        self._marks.append((self.CLASSES.get(what, "other"), event))
+
+    def end(self, kind: str) -> dict:
+        """Wait for the step and add it to the totals of its kind; returns the running averages."""
+        if self._start is None:
+            return {}
+        torch.cuda.current_stream().synchronize()
+        split = {}
+        before = self._start
+        for name, event in self._marks:
+            split[name] = split.get(name, 0.0) + before.elapsed_time(event)
+            before = event
+        total = self._start.elapsed_time(before) if self._marks else 0.0
+        self._events.extend(event for _, event in self._marks)
+        self._events.append(self._start)
+        self._start, self._marks = None, []
+        totals = self.totals.setdefault(kind, {"steps": 0, "ms": 0.0})
+        totals["steps"] += 1
+        totals["ms"] += total
+        for name, ms in split.items():
+            totals[name] = totals.get(name, 0.0) + ms
+        return totals
+
+    def line(self, kind: str) -> str:
+        totals = self.totals.get(kind)
+        if not totals or not totals["steps"]:
+            return f"PROFILE {kind} 0"
+        steps, average = totals["steps"], totals["ms"] / totals["steps"]
+        parts = [f"PROFILE {kind} {steps} {average:.3f} ms:"]
+        for name in self.ORDER:
+            if name in totals:
+                ms = totals[name] / steps
+                parts.append(f"{name} {ms:.3f}ms ({100.0 * ms / average if average else 0.0:.0f}%)")
+        return " ".join(parts)
+
+
+profile: Optional[KernelProfile] = None
+
+
 def _check(status: int, what: str, kernels: int = 1) -> None:
     global launches
     if status == 0:
         launches += kernels
+        if profile is not None:
+            profile.mark(what)
         return
     if status > 0:
         text = f"CUDA error {status}"
@@ -135,6 +211,18 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
     _check(fn(_gpu(x, "x", torch.float32), _gpu(weight, "weight", torch.float32),
               _opt(rows, "rows", torch.int32), _gpu(out, "out"), dtype_code(out.dtype), count, hidden,
               float(eps), _stream()), "rmsnorm")
+
+
+_sm_counts = {}
+
+
+def sm_count(device) -> int:
+    """The number of multiprocessors of `device`, asked once."""
+    key = str(device)
+    count = _sm_counts.get(key)
+    if count is None:
+        count = _sm_counts[key] = int(torch.cuda.get_device_properties(device).multi_processor_count)
+    return count
 
 
 def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int,
@@ -414,6 +502,14 @@ def gemm_tc_rope(a: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tenso
               ctypes.byref(r), state["status"].data_ptr(), _stream()), "gemm_tc_rope")
 
 
+def wait_probe(device, limit: int = 4096) -> None:
+    """Launch a block whose bounded wait runs out after `limit` polls (on a barrier nothing
+    arrives at, with no copy in flight): the status word then holds what a product kernel
+    writes when one of its waits gives up.  For testing how that is reported."""
+    fn = _function("gemm_tc", "vipera_gemm_tc_wait_probe", [_c_void, _c_int, _c_void])
+    _check(fn(kernel_status_word(device).data_ptr(), int(limit), _stream()), "wait_probe")
+
+
 def check_kernel_status(device) -> None:
     """After a synchronisation: raise if a tensor-core kernel's bounded wait ran out."""
     state = _tc_state.get(str(device))
@@ -458,7 +554,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
     _check(fn(*pointers, *sizes, _stream()), "attention_prefill")
 
 
-def decode_splits(num_entries: int, num_kv_heads: int, max_keys: int, sm_count: int = 148):
+def decode_splits(num_entries: int, num_kv_heads: int, max_keys: int, sm_count: int):
     """How a decode step's keys are cut: (keys per split, splits).  A split is 128 keys (32
     for each of a block's four warps), so that every block asks for all its keys at once and
     the whole cache of the step is in flight together; only when that would make more than

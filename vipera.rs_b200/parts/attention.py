@@ -85,6 +85,11 @@ class GQAttention(Mixer):
         return tuple(dict.fromkeys(tuple(own) + self.qkv.kernel_families() + self.out.kernel_families()
                                    + self.position.kernel_families()))
 
+    def prepare(self, max_positions: int) -> None:
+        prepare = getattr(self.position, "prepare", None)
+        if prepare is not None:
+            prepare(max_positions)
+
     @classmethod
     def cache_request_for(cls, params):
         return PagedKV(int(params["num_kv_heads"]), int(params["head_dim"]), params.get("window"))
@@ -160,7 +165,8 @@ class GQAttention(Mixer):
         window = self.window or 0
         if ctx.dtype == torch.bfloat16 and d in ops.MMA_HEAD_DIMS:
             if ctx.all_single:
-                chunk, splits = ops.decode_splits(ctx.num_entries, kv_heads, max(ctx.max_kv_len, 1))
+                chunk, splits = ops.decode_splits(ctx.num_entries, kv_heads, max(ctx.max_kv_len, 1),
+                                                  ops.sm_count(q.device))
                 scratch = ctx.workspace.get(
                     "attention.partials",
                     (ops.attention_decode_scratch_floats(ctx.num_entries, heads, d, splits),), torch.float32)

@@ -68,6 +68,15 @@ class DecoderModel:
             if entry.writes_cache:
                 self.cache_requests[entry.cache] = self.blocks[entry.layer].cache_request()
 
+    def prepare(self, max_positions: int) -> None:
+        """Tell every part that sizes something by position (tables of a position encoding)
+        how far the engine goes: positions below `max_positions`."""
+        for block in self.blocks:
+            for part in block.parts():
+                prepare = getattr(part, "prepare", None)
+                if prepare is not None:
+                    prepare(max_positions)
+
     @property
     def graph_safe(self) -> bool:
         """Whether decode steps of this model may be captured in CUDA graphs: every part must

@@ -3,10 +3,13 @@
 Angles as the reference computes them, in 32-bit: ``inv_i = 1 / base^(2i/d)``,
 ``angle = position * inv_i`` (crates/vipera-backend-cpu/src/model.rs:4204-4206).  The
 reference builds the table once per position and step and shares it between layers
-(model.rs:970-973); here one table for all positions is built on the host when the model
-is built and shared by every layer with the same head size and base.
+(model.rs:970-973); here one table is built on the host for the positions the engine can
+reach (``prepare``; the model's own limit where nobody says) and shared by every layer with
+the same head size and base.  Tables live as long as a part holds them.
 """
 from __future__ import annotations
+
+import weakref
 
 import torch
 
@@ -14,11 +17,18 @@ from ..config.registry import POSITION_ENCODINGS
 from ..kernels import ops
 from .base import PositionEncoding
 
-_TABLES = {}
+class _Tables:
+    """(cos, sin) held by the parts that use them; the shared table forgets them with the last part."""
+
+    def __init__(self, cos, sin):
+        self.pair = (cos, sin)
 
 
-def rotary_tables(head_dim: int, theta: float, max_positions: int, device):
-    """(cos, sin), each float32 [max_positions, head_dim / 2], on ``device``."""
+_TABLES = weakref.WeakValueDictionary()
+
+
+def rotary_tables(head_dim: int, theta: float, max_positions: int, device) -> _Tables:
+    """cos and sin, each float32 [max_positions, head_dim / 2], on ``device``."""
     key = (head_dim, float(theta), max_positions, str(device))
     cached = _TABLES.get(key)
     if cached is not None:
@@ -29,7 +39,7 @@ def rotary_tables(head_dim: int, theta: float, max_positions: int, device):
     inverse = 1.0 / torch.pow(torch.tensor(float(theta), dtype=torch.float32), exponent)
     position = torch.arange(max_positions, dtype=torch.float32)
     angle = position[:, None] * inverse[None, :]
-    tables = (torch.cos(angle).contiguous().to(device), torch.sin(angle).contiguous().to(device))
+    tables = _Tables(torch.cos(angle).contiguous().to(device), torch.sin(angle).contiguous().to(device))
     _TABLES[key] = tables
     return tables
 
@@ -45,10 +55,27 @@ class RopeNeox(PositionEncoding):
         self.head_dim = int(params["head_dim"])
         self.theta = float(params["theta"])
         self.max_positions = int(params["max_positions"])
-        self._tables = rotary_tables(self.head_dim, self.theta, self.max_positions, device)
+        self.reach = None   # positions the tables cover; the model's own limit where nobody says
+        self._tables = None
+
+    def prepare(self, max_positions: int) -> None:
+        """An engine reaches positions below `max_positions` only: the tables are sized for the
+        furthest any engine on this model has asked for, and never shrink."""
+        reach = min(self.max_positions, int(max_positions))
+        if self.reach is not None and reach <= self.reach:
+            return
+        self.reach = reach
+        if self._tables is not None:
+            # Tables in use move: graphs that captured their addresses are stale.
+            self._tables = None
+            ops.buffer_generation += 1
 
     def tables(self):
-        return self._tables
+        if self._tables is None:
+            if self.reach is None:
+                self.reach = self.max_positions
+            self._tables = rotary_tables(self.head_dim, self.theta, self.reach, self.device)
+        return self._tables.pair
 
 
 class NoPositions(PositionEncoding):
