@@ -287,12 +287,25 @@ def measure_e2e(model, batch, history, steps, warmup, page_size=16):
     return produced / elapsed, h2d, d2h
 
 
-def measure_mixed(model, requests, prompt_range, new_tokens, max_portion, token_budget, passes=2, page_size=16):
+def release_memory():
+    """Give back what finished harnesses held (runners and their captured graphs refer to one
+    another, so the collector has to run before the allocator can let go)."""
+    import gc
+
+    import torch
+
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
+def measure_mixed(model, requests, prompt_range, new_tokens, max_portion, token_budget, passes=3, page_size=16):
     """The engine's normal mode: `requests` requests with prompt lengths uniform in
     `prompt_range`, all offered at once, prompts cut into portions of `max_portion` under a
     budget of `token_budget` tokens a step beside the running decodes, `new_tokens` tokens each,
-    through ``Engine.step()`` on the host clock.  The first pass captures the graphs of the
-    step sizes that occur; the last pass is the one reported."""
+    through ``Engine.step()`` on the host clock.  The first passes capture the graphs of the
+    step sizes that occur (a buffer that grows in the first pass makes the graphs captured before
+    it stale, so the second pass still captures some); the last pass is the one reported, with
+    the number of graphs it still had to capture."""
     import numpy as np
     import torch
 
@@ -308,6 +321,7 @@ def measure_mixed(model, requests, prompt_range, new_tokens, max_portion, token_
     report = {}
     for index in range(passes):
         before = dict(engine.totals, stage_micros=dict(engine.totals["stage_micros"]))
+        captures_before = engine.runner.graph_captures
         for prompt in prompts:
             engine.add_request(prompt, params)
         torch.cuda.synchronize()
@@ -333,11 +347,16 @@ def measure_mixed(model, requests, prompt_range, new_tokens, max_portion, token_
             # the host's own work a step: scheduling, building and launching, bookkeeping (the
             # sample stage is mostly the wait for the device and is left out)
             "host_us_per_step": round((host["allocate"] + host["compute"] + host["complete"]) / max(steps, 1), 1),
+            "host_us_allocate": round(host["allocate"] / max(steps, 1), 1),
+            "host_us_compute": round(host["compute"] / max(steps, 1), 1),
+            "host_us_complete": round(host["complete"] / max(steps, 1), 1),
+            "wait_us_sample": round(host["sample"] / max(steps, 1), 1),
             "graph_step_share": round((totals["graph_steps"] - before["graph_steps"]) / max(steps, 1), 4),
+            "graphs_captured_in_pass": engine.runner.graph_captures - captures_before,
             "timing": "host clock around Engine.step() until every request has ended",
         }
     del engine
-    torch.cuda.empty_cache()
+    release_memory()
     return report
 
 
@@ -356,7 +375,7 @@ def measure_shape(name, config, layers, peaks, history, batches, steps, warmup, 
         ms, mean_history = harness.timed(steps, warmup)
         harness.close()
         del harness
-        torch.cuda.empty_cache()
+        release_memory()
         gbs = decode_bytes(config, layers, batch, mean_history) / (ms * 1e-3) / 1e9
         out[f"decode_b{batch}"] = round(batch * 1000.0 / ms, 1)
         out[f"decode_b{batch}_ms"] = round(ms, 4)
@@ -377,14 +396,17 @@ def measure_32b(peaks, warmup, page_size):
 
     history = 8192
     refused = plan_report(QWEN25_32B, history + 256, 64)
+    # the largest batch for the measurement is planned against what this device really has, less a
+    # margin for the allocator
+    usable = int(torch.cuda.get_device_properties(0).total_memory * 0.9)
     largest = 8
     for batch in range(8, 65, 8):
-        if plan_report(QWEN25_32B, history + 256, batch)["feasible"]:
+        if plan_report(QWEN25_32B, history + 256, batch, usable)["feasible"]:
             largest = batch
     out, model = measure_shape(SHAPES["32b"][0], QWEN25_32B, QWEN25_32B["num_hidden_layers"], peaks, history,
                                sorted({1, 8, largest}), steps=16, warmup=max(3, min(warmup, 4)), page_size=page_size)
     del model
-    torch.cuda.empty_cache()
+    release_memory()
     out["largest_batch_that_fits"] = largest
     out["plan_b64_feasible"] = bool(refused["feasible"])
     out["plan_b64_needs_gb"] = round(refused["predicted_device_bytes"] / 1e9, 1)
@@ -392,13 +414,14 @@ def measure_32b(peaks, warmup, page_size):
     return out
 
 
-def plan_report(config, ctx, batch):
-    """What `vipera plan` says about the shape at this context and batch on one 180 GB device."""
+def plan_report(config, ctx, batch, device_bytes=180 * 10**9):
+    """What `vipera plan` says about the shape at this context and batch (on one 180 GB device
+    where nothing else is said)."""
     from vipera_rs_b200.config import architecture_of
     from vipera_rs_b200.engine import planner
 
     arch = architecture_of(config)
-    return planner.plan_memory(arch.model_spec(arch.config_from_dict(config)), ctx, batch, "bfloat16", 180 * 10**9)
+    return planner.plan_memory(arch.model_spec(arch.config_from_dict(config)), ctx, batch, "bfloat16", device_bytes)
 
 
 def main():
@@ -458,7 +481,7 @@ def main():
         return 0
     if args.only == "32b":
         del model
-        torch.cuda.empty_cache()
+        release_memory()
         print(json.dumps({"only": "32b", **measure_32b(peaks, warmup, args.page_size)}))
         return 0
     if args.only == "decode":
@@ -487,7 +510,7 @@ def main():
             other.close()
             points[f"decode_b{batch}"] = round(batch * 1000.0 / ms, 1)
             del other
-            torch.cuda.empty_cache()
+            release_memory()
 
     prefill_tokens = args.prefill_tokens
     prefill_ms = measure_prefill(model, prefill_tokens, repeats=5, warmup=3, page_size=args.page_size)
@@ -501,14 +524,14 @@ def main():
     # their own beside the headline, each with the sizes it ran at.
     workloads = {}
     if args.config == "1.5b" and not args.skip_workloads:
-        del model
-        torch.cuda.empty_cache()
+        del model, harness
+        release_memory()
         try:
             big = random_model(dict(QWEN25_7B), seed=1, dtype="bfloat16", device="cuda:0")
             workloads["mixed_7b"] = {"model": SHAPES["7b"][0], "layers": 28, "layers_full": 28,
                                      **measure_mixed(big, 64, (128, 4096), 256, 512, 2048, page_size=args.page_size)}
             del big
-            torch.cuda.empty_cache()
+            release_memory()
             workloads["shape_32b"] = measure_32b(peaks, warmup, args.page_size)
         except Exception as error:  # the headline stands even where a larger shape does not fit
             workloads["error"] = f"{type(error).__name__}: {error}"

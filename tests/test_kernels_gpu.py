@@ -302,6 +302,24 @@ def test_attention_portions(heads, kv_heads, d, page, dtype, window):
                               num_entries=entries, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
                               scale=scale, window=window)
         assert _rel(out2.float().cpu().view(total, heads, d), want) < limit
+        # the two kernels of a mixed step together: the flash kernel leaves entries of one token
+        # out, the split-key kernel runs those and only those, at the rows of their tokens
+        out3 = torch.full_like(qd, float("nan"))
+        ops.attention_prefill(qd, out3, kp, vp, entry_starts=starts, entry_pos0=pos0, block_table=tb,
+                              num_entries=entries, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
+                              scale=scale, window=window, skip_single=True)
+        single = [e for e, c in enumerate(counts) if c == 1]
+        rows = [int(starts[e]) for e in single]
+        assert torch.isnan(out3[rows].float()).all() and not torch.isnan(out3.float()).sum(dim=1)[
+            [t for t in range(total) if t not in rows]].any()
+        for chunk, splits in (ops.decode_splits(entries, kv_heads, 256, ops.sm_count(DEV)), (32, 8)):
+            scratch = torch.full((ops.attention_decode_scratch_floats(entries, heads, d, splits),), float("nan"),
+                                 device=DEV)
+            out4 = out3.clone()
+            ops.attention_decode(qd, out4, kp, vp, positions=pos0, block_table=tb, num_heads=heads,
+                                 num_kv_heads=kv_heads, head_dim=d, scale=scale, window=window, chunk=chunk,
+                                 num_splits=splits, scratch=scratch, entry_starts=starts)
+            assert _rel(out4.float().cpu().view(total, heads, d), want) < limit, (chunk, splits)
 
 
 @pytest.mark.parametrize("page", [8, 16, 24, 64, 128, 256])

@@ -31,7 +31,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
                          const __nv_bfloat16* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
                          const int* __restrict__ entry_starts, const int* __restrict__ entry_pos0,
                          const int* __restrict__ block_table, int table_width, int page_size, int num_entries,
-                         int num_heads, int num_kv_heads, float scale, int window) {
+                         int num_heads, int num_kv_heads, float scale, int window, int skip_single) {
   constexpr int kQ = 64, kKeys = 64, kThreads = 128 * HPC;
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_launch_dependents();
@@ -42,7 +42,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
   {
     int remaining = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
     for (int e = 0; e < num_entries; ++e) {
-      const int tiles = (entry_starts[e + 1] - entry_starts[e] + kQ - 1) / kQ;
+      const int count = entry_starts[e + 1] - entry_starts[e];
+      // entries of one token are left to the split-key kernel where the caller says so
+      const int tiles = (skip_single && count == 1) ? 0 : (count + kQ - 1) / kQ;
       if (remaining < tiles) { entry = e; tile_in_entry = remaining; break; }
       remaining -= tiles;
     }
@@ -155,7 +157,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ positions,
                         const int* __restrict__ block_table, int table_width, int page_size, int page_shift,
                         int num_heads, int num_kv_heads, float scale, int window, int chunk, int num_splits,
-                        float* __restrict__ partial_ml, float* __restrict__ partial_out) {
+                        float* __restrict__ partial_ml, float* __restrict__ partial_out,
+                        const int* __restrict__ entry_starts) {
   constexpr int kKeys = 32;
   constexpr int kWarpTile = 2 * kKeys * D * 2;  // bytes of one warp's key and value tiles
   static_assert(16 * (D + 4) * 4 <= kWarpTile, "a warp's partial must fit in its tiles");
@@ -163,6 +166,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   pdl_launch_dependents();
   pdl_wait();
   const int entry = blockIdx.x, kv_head = blockIdx.y, split = blockIdx.z;
+  // Token i is entry i in a step of single tokens.  In a step with portions (`entry_starts`
+  // given) the entry's token is where its tokens start, and entries that bring more than one
+  // token are the flash kernel's.
+  int token = entry;
+  if (entry_starts) {
+    token = entry_starts[entry];
+    if (entry_starts[entry + 1] - token != 1) return;
+  }
   const int group = num_heads / num_kv_heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int position = positions[entry];
@@ -192,7 +203,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         const int row = index / kChunks, c = index % kChunks;
         const int head_in_group = m_tile * 16 + row;
         const bool valid = head_in_group < group;
-        const __nv_bfloat16* src = q + (static_cast<size_t>(entry) * num_heads + kv_head * group + (valid ? head_in_group : 0)) * D + c * 8;
+        const __nv_bfloat16* src = q + (static_cast<size_t>(token) * num_heads + kv_head * group + (valid ? head_in_group : 0)) * D + c * 8;
         cp_async_16(q_tile + tile_offset<D>(row, c), src, valid);
       }
     }
@@ -295,12 +306,19 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 template <int D>
 __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, const float* __restrict__ partial_out,
                                          int slices, __nv_bfloat16* __restrict__ out, int num_heads,
-                                         const int* __restrict__ positions, int window, int chunk) {
+                                         const int* __restrict__ positions, int window, int chunk,
+                                         const int* __restrict__ entry_starts) {
   __shared__ float maxima[128];
   __shared__ float sums[128];
   pdl_launch_dependents();
   pdl_wait();
   const size_t row = static_cast<size_t>(blockIdx.x) * num_heads + blockIdx.y;
+  size_t out_row = row;
+  if (entry_starts) {   // a step with portions: only entries of one token, written at their token's row
+    const int token = entry_starts[blockIdx.x];
+    if (entry_starts[blockIdx.x + 1] - token != 1) return;
+    out_row = static_cast<size_t>(token) * num_heads + blockIdx.y;
+  }
   const float* ml = partial_ml + 2 * row * slices;
   const float* values = partial_out + row * slices * D + threadIdx.x;
   // only the splits that hold visible keys were written by the decode kernel
@@ -324,7 +342,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
     total += sums[s] * w;
     value += values[static_cast<size_t>(s) * D] * w;
   }
-  out[row * D + threadIdx.x] = __float2bfloat16_rn(value / total);
+  out[out_row * D + threadIdx.x] = __float2bfloat16_rn(value / total);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -533,7 +551,7 @@ template <int D, int HPC>
 int launch_prefill_variant(const void* q, void* out, const void* k_pool, const void* v_pool, const int* entry_starts,
                            const int* entry_pos0, const int* block_table, int table_width, int page_size,
                            int num_entries, int num_tokens, int num_heads, int num_kv_heads, float scale, int window,
-                           cudaStream_t s) {
+                           int skip_single, cudaStream_t s) {
   constexpr int kSmem = (HPC * 64 + 4 * 64) * D * 2;
   static bool configured = false;
   if (!configured) {
@@ -546,19 +564,22 @@ int launch_prefill_variant(const void* q, void* out, const void* k_pool, const v
   return vipera_launch(attention_prefill_kernel<D, HPC>, grid, dim3(128 * HPC), kSmem, s,
       static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(k_pool),
       static_cast<const __nv_bfloat16*>(v_pool), entry_starts, entry_pos0, block_table, table_width, page_size,
-      num_entries, num_heads, num_kv_heads, scale, window);
+      num_entries, num_heads, num_kv_heads, scale, window, skip_single);
 }
 
 template <int D>
 int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int* entry_starts,
                    const int* entry_pos0, const int* block_table, int table_width, int page_size, int num_entries,
-                   int num_tokens, int num_heads, int num_kv_heads, float scale, int window, cudaStream_t s) {
+                   int num_tokens, int num_heads, int num_kv_heads, float scale, int window, int skip_single,
+                   cudaStream_t s) {
   // two heads per block where the heads of a KV group pair up
   if ((num_heads / num_kv_heads) % 2 == 0)
     return launch_prefill_variant<D, 2>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width,
-                                        page_size, num_entries, num_tokens, num_heads, num_kv_heads, scale, window, s);
+                                        page_size, num_entries, num_tokens, num_heads, num_kv_heads, scale, window,
+                                        skip_single, s);
   return launch_prefill_variant<D, 1>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width,
-                                      page_size, num_entries, num_tokens, num_heads, num_kv_heads, scale, window, s);
+                                      page_size, num_entries, num_tokens, num_heads, num_kv_heads, scale, window,
+                                      skip_single, s);
 }
 
 // The one-kernel form serves a step of few entries whose groups of heads fit one MMA tile.
@@ -630,14 +651,16 @@ template <int D>
 int launch_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int* positions,
                   const int* block_table, int table_width, int page_size, int num_entries, int num_heads,
                   int num_kv_heads, float scale, int window, int chunk, int num_splits, float* partial_ml,
-                  float* partial_out, cudaStream_t s) {
+                  float* partial_out, const int* entry_starts, cudaStream_t s) {
   constexpr int kSmem = 16 * D * 2 + 4 * 2 * 32 * D * 2;
   int page_shift = -1;
   if ((page_size & (page_size - 1)) == 0) {
     page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
   }
-  const ClusterChoice cluster = cluster_decode_choice(num_entries, num_heads, num_kv_heads, chunk * num_splits);
+  // the one-kernel forms serve steps of single tokens only
+  const ClusterChoice cluster = entry_starts ? ClusterChoice{0, false}
+                                             : cluster_decode_choice(num_entries, num_heads, num_kv_heads, chunk * num_splits);
   if (cluster.blocks == 8 && cluster.prefetch)
     return launch_decode_cluster<D, 8, true>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size,
                                              page_shift, num_entries, num_heads, num_kv_heads, scale, window, s);
@@ -660,32 +683,33 @@ int launch_decode(const void* q, void* out, const void* k_pool, const void* v_po
   int status = vipera_launch(attention_decode_kernel<D>, grid, 128, kSmem, s,
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pool),
       static_cast<const __nv_bfloat16*>(v_pool), positions, block_table, table_width, page_size, page_shift,
-      num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out);
+      num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, entry_starts);
   if (status != VIPERA_OK) return status;
   return vipera_launch(attention_combine_kernel<D>, dim3(num_entries, num_heads), D, 0, s,
       static_cast<const float*>(partial_ml), static_cast<const float*>(partial_out), num_splits,
-      static_cast<__nv_bfloat16*>(out), num_heads, positions, window, chunk);
+      static_cast<__nv_bfloat16*>(out), num_heads, positions, window, chunk, entry_starts);
 }
 
 }  // namespace
 
 // Attention of a step with portions of any length.  q and out are bfloat16 [tokens, heads, d];
 // entry_starts [entries + 1] are cumulative token counts and entry_pos0 [entries] the position
-// of each entry's first token.  Head sizes: 64 and 128.
+// of each entry's first token.  Head sizes: 64 and 128.  With `skip_single`, entries of one
+// token are left out (the caller runs vipera_attention_decode over them).
 VIPERA_API int vipera_attention_prefill(const void* q, void* out, const void* k_pool, const void* v_pool,
                                         const int* entry_starts, const int* entry_pos0, const int* block_table,
                                         int table_width, int page_size, int num_entries, int num_tokens,
                                         int num_heads, int num_kv_heads, int head_dim, float scale, int window,
-                                        void* stream) {
+                                        int skip_single, void* stream) {
   if (num_tokens <= 0 || num_entries <= 0) return VIPERA_OK;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads) return VIPERA_BAD_SHAPE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (head_dim == 128)
     return launch_prefill<128>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width, page_size,
-                               num_entries, num_tokens, num_heads, num_kv_heads, scale, window, s);
+                               num_entries, num_tokens, num_heads, num_kv_heads, scale, window, skip_single, s);
   if (head_dim == 64)
     return launch_prefill<64>(q, out, k_pool, v_pool, entry_starts, entry_pos0, block_table, table_width, page_size,
-                              num_entries, num_tokens, num_heads, num_kv_heads, scale, window, s);
+                              num_entries, num_tokens, num_heads, num_kv_heads, scale, window, skip_single, s);
   return VIPERA_BAD_SHAPE;
 }
 
@@ -696,13 +720,17 @@ VIPERA_API size_t vipera_attention_decode_scratch(int num_entries, int num_heads
   return ((2 * rows + 3) / 4) * 4 + rows * head_dim;
 }
 
-// Attention of a step in which every entry brings one token (token i belongs to entry i).
+// Attention of the entries that bring one token.  With `entry_starts` null every entry does
+// (token i belongs to entry i, at positions[i]).  With `entry_starts` [entries + 1] given the step
+// has portions too: entry e's token is entry_starts[e], its position positions[e] (the entry's
+// first position), and entries of more tokens are skipped (vipera_attention_prefill with
+// skip_single runs those); q and out are then [tokens, heads, d] of the whole step.
 // The keys of an entry are cut into `num_splits` ranges of `chunk` keys (a multiple of 32).
 VIPERA_API int vipera_attention_decode(const void* q, void* out, const void* k_pool, const void* v_pool,
                                        const int* positions, const int* block_table, int table_width, int page_size,
                                        int num_entries, int num_heads, int num_kv_heads, int head_dim, float scale,
                                        int window, int chunk, int num_splits, float* scratch, size_t scratch_floats,
-                                       void* stream) {
+                                       const int* entry_starts, void* stream) {
   if (num_entries <= 0) return VIPERA_OK;
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads) return VIPERA_BAD_SHAPE;
   if (chunk <= 0 || chunk % 32 || num_splits <= 0 || num_splits > 128) return VIPERA_BAD_ARGUMENT;
@@ -715,10 +743,12 @@ VIPERA_API int vipera_attention_decode(const void* q, void* out, const void* k_p
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (head_dim == 128)
     return launch_decode<128>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries,
-                              num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, s);
+                              num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out,
+                              entry_starts, s);
   if (head_dim == 64)
     return launch_decode<64>(q, out, k_pool, v_pool, positions, block_table, table_width, page_size, num_entries,
-                             num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out, s);
+                             num_heads, num_kv_heads, scale, window, chunk, num_splits, partial_ml, partial_out,
+                             entry_starts, s);
   return VIPERA_BAD_SHAPE;
 }
 

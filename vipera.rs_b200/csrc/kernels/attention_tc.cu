@@ -84,6 +84,7 @@ struct Params {
   const int* block_table;      // [entries, table_width]
   int table_width, page_size, num_entries, num_heads, num_kv_heads, window;
   float scale;
+  int skip_single;             // entries of one token are left out (the split-key kernel runs them)
   int* status;
 };
 
@@ -280,7 +281,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   {
     int remaining = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);
     for (int e = 0; e < p.num_entries; ++e) {
-      const int tiles = (p.entry_starts[e + 1] - p.entry_starts[e] + kQ - 1) / kQ;
+      const int count = p.entry_starts[e + 1] - p.entry_starts[e];
+      // entries of one token are left to the split-key kernel where the caller says so
+      const int tiles = (p.skip_single && count == 1) ? 0 : (count + kQ - 1) / kQ;
       if (remaining < tiles) { entry = e; tile_in_entry = remaining; break; }
       remaining -= tiles;
     }
@@ -854,7 +857,7 @@ VIPERA_API int vipera_attention_prefill_tc(const void* q, void* out, const void*
                                            const int* entry_starts, const int* entry_pos0, const int* block_table,
                                            int table_width, int page_size, int num_entries, int num_tokens,
                                            int num_heads, int num_kv_heads, int head_dim, float scale, int window,
-                                           int num_pages, int* status, void* stream) {
+                                           int num_pages, int skip_single, int* status, void* stream) {
   if (num_tokens <= 0 || num_entries <= 0) return VIPERA_OK;
   if (head_dim != kD || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || num_pages <= 0)
     return VIPERA_BAD_SHAPE;
@@ -874,6 +877,7 @@ VIPERA_API int vipera_attention_prefill_tc(const void* q, void* out, const void*
   p.num_kv_heads = num_kv_heads;
   p.window = window;
   p.scale = scale;
+  p.skip_single = skip_single;
   p.status = status;
   // at most one partly filled tile per entry beyond the full ones
   dim3 grid(num_heads, (num_tokens + kQ - 1) / kQ + num_entries);

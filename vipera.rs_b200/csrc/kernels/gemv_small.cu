@@ -8,7 +8,10 @@
 //     anyway; it normalises the few rows itself while it stages them in shared memory
 //     (rounded to bfloat16 there, as the separate norm kernel would store them);
 //   * behind: bias, the residual addition, SwiGLU, or (for the q/k/v product) the rotary
-//     encoding and the write of keys and values into their cache pages.
+//     encoding and the write of keys and values into their cache pages;
+//   * behind the residual addition, where the caller asks: the RMSNorm of the rows just
+//     completed, for the part that runs next.  The block that finishes last (a counter in
+//     device memory tells it) normalises the few rows, so the norm needs no kernel of its own.
 // The reference's decode path is likewise one weight read for all rows of the batch
 // (crates/vipera-backend-cpu/src/model.rs:1005-1025) with norm and activation fused into
 // the activation preparation of the next product (crates/vipera-backend-cpu/src/quant.rs:578-603,
@@ -53,6 +56,12 @@ struct GemvParams {
   const int* token_entry;
   const int* block_table;
   int table_width, page_size, write_cache;
+  // RESIDUAL, optional: RMSNorm of the finished rows of `resid`, written by the block that ends last
+  const float* post_norm_weight;  // [N] or null
+  float post_eps;
+  void* post_out;               // [T, N] in post_dtype
+  int post_dtype;
+  int* counter;                 // device word, 0 before the launch and again after it
 };
 
 constexpr int kGemvMaxShared = 200 * 1024;
@@ -157,14 +166,21 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
   const int step_begin = warp * steps_per_warp;
   const int step_end = min(steps_total, step_begin + steps_per_warp);
 
-  // the first weights are on their way before this kernel waits for the kernels ahead of it
+  // The weights do not depend on the kernels ahead of this one: the warp's first kHeld steps of
+  // its share of K (all of it where K is small) are asked for before the wait and are in
+  // registers when the activations arrive.
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  uint4 first_lo = zero, first_hi = zero;
-  if (step_begin < step_end) {
-    const int k = step_begin * 32 + tq * 8;
-    if (k < p.K) {
-      if (has_lo) first_lo = __ldg(reinterpret_cast<const uint4*>(w_lo + k));
-      if (has_hi) first_hi = __ldg(reinterpret_cast<const uint4*>(w_hi + k));
+  constexpr int kHeld = NT <= 2 ? 8 : (NT == 4 ? 6 : 4);
+  uint4 held_lo[kHeld], held_hi[kHeld];
+#pragma unroll
+  for (int u = 0; u < kHeld; ++u) {
+    const int step = step_begin + u;
+    const int k = step * 32 + tq * 8;
+    held_lo[u] = zero;
+    held_hi[u] = zero;
+    if (step < step_end && k < p.K) {
+      if (has_lo) held_lo[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + k));
+      if (has_hi) held_hi[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + k));
     }
   }
   pdl_wait();
@@ -216,13 +232,15 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
     has_hi = row_hi < p.N;
     w_lo = p.weight + static_cast<size_t>(has_lo ? row_lo : 0) * p.K;
     w_hi = p.weight + static_cast<size_t>(has_hi ? row_hi : 0) * p.K;
-    first_lo = zero;
-    first_hi = zero;
-    if (step_begin < step_end) {
-      const int k = step_begin * 32 + tq * 8;
-      if (k < p.K) {
-        if (has_lo) first_lo = __ldg(reinterpret_cast<const uint4*>(w_lo + k));
-        if (has_hi) first_hi = __ldg(reinterpret_cast<const uint4*>(w_hi + k));
+#pragma unroll
+    for (int u = 0; u < kHeld; ++u) {
+      const int step = step_begin + u;
+      const int k = step * 32 + tq * 8;
+      held_lo[u] = zero;
+      held_hi[u] = zero;
+      if (step < step_end && k < p.K) {
+        if (has_lo) held_lo[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + k));
+        if (has_hi) held_hi[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + k));
       }
     }
   }
@@ -233,8 +251,24 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
 
+  // the held steps first ...
+#pragma unroll
+  for (int u = 0; u < kHeld; ++u) {
+    const int step = step_begin + u;
+    const int k = step * 32 + tq * 8;
+    if (step >= step_end) continue;   // the same for every lane of the warp
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      // a lane past the end of K (its weights are zeros) must not read past the row either
+      const uint4 a = k < p.K
+          ? *reinterpret_cast<const uint4*>(shared + static_cast<size_t>(n * 8 + g) * act_stride + k * 2) : zero;
+      mma_16816(acc[n], held_lo[u].x, held_hi[u].x, held_lo[u].y, held_hi[u].y, a.x, a.y);
+      mma_16816(acc[n], held_lo[u].z, held_hi[u].z, held_lo[u].w, held_hi[u].w, a.z, a.w);
+    }
+  }
+  // ... then the rest of the warp's share, four steps in flight at a time
   constexpr int kUnroll = 4;
-  for (int step0 = step_begin; step0 < step_end; step0 += kUnroll) {
+  for (int step0 = step_begin + kHeld; step0 < step_end; step0 += kUnroll) {
     uint4 lo[kUnroll], hi[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
@@ -242,10 +276,7 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
       const int k = step * 32 + tq * 8;
       lo[u] = zero;
       hi[u] = zero;
-      if (step == step_begin) {
-        lo[u] = first_lo;
-        hi[u] = first_hi;
-      } else if (step < step_end && k < p.K) {
+      if (step < step_end && k < p.K) {
         if (has_lo) lo[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + k));
         if (has_hi) hi[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + k));
       }
@@ -257,7 +288,6 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
       if (step >= step_end) continue;   // the same for every lane of the warp
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
-        // a lane past the end of K (its weights are zeros) must not read past the row either
         const uint4 a = k < p.K
             ? *reinterpret_cast<const uint4*>(shared + static_cast<size_t>(n * 8 + g) * act_stride + k * 2) : zero;
         mma_16816(acc[n], lo[u].x, hi[u].x, lo[u].y, hi[u].y, a.x, a.y);
@@ -293,6 +323,42 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
     if (out_lo < p.N) finish(p, out_lo, out_hi, t, v_lo, v_hi);
   }
   __syncthreads();  // the partials are read; the next tile may overwrite them
+  }
+
+  if (p.post_norm_weight) {
+    // Which block ends last?  Each makes its additions visible, then takes a ticket.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(p.counter, 1) == static_cast<int>(gridDim.x) - 1 ? 1 : 0;
+    __syncthreads();
+    if (is_last) {
+      __threadfence();
+      const int chunks4 = p.N >> 2;   // N is a multiple of 4 here (the launcher sees to it)
+      for (int t = warp; t < p.T; t += warps) {
+        const float* x = p.resid + static_cast<size_t>(t) * p.N;
+        float squares = 0.0f;
+        for (int c = lane; c < chunks4; c += 32) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(x) + c);
+          squares += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        squares = warp_sum(squares);
+        const float inverse = 1.0f / sqrtf(squares / static_cast<float>(p.N) + p.post_eps);
+        for (int c = lane; c < chunks4; c += 32) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(x) + c);
+          const float4 w = *(reinterpret_cast<const float4*>(p.post_norm_weight) + c);
+          const float r0 = v.x * inverse * w.x, r1 = v.y * inverse * w.y, r2 = v.z * inverse * w.z, r3 = v.w * inverse * w.w;
+          if (p.post_dtype == VIPERA_BF16) {
+            __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(p.post_out) + static_cast<size_t>(t) * p.N) + 2 * c;
+            dst[0] = __floats2bfloat162_rn(r0, r1);
+            dst[1] = __floats2bfloat162_rn(r2, r3);
+          } else {
+            reinterpret_cast<float4*>(static_cast<float*>(p.post_out) + static_cast<size_t>(t) * p.N)[c] = make_float4(r0, r1, r2, r3);
+          }
+        }
+      }
+      if (threadIdx.x == 0) *p.counter = 0;  // as the next launch expects it
+    }
   }
 }
 
@@ -369,10 +435,14 @@ VIPERA_API int vipera_gemv_small(const GemvParams* params, void* stream) {
     tiles = (p.N + 15) / 16;
   } else if (p.epilogue == GEMV_RESIDUAL) {
     if (!p.resid) return VIPERA_BAD_ARGUMENT;
+    if (p.post_norm_weight && (!p.post_out || !p.counter || (p.N % 4) != 0 ||
+                               (p.post_dtype != VIPERA_F32 && p.post_dtype != VIPERA_BF16)))
+      return VIPERA_BAD_ARGUMENT;
     tiles = (p.N + 15) / 16;
   } else {
     return VIPERA_BAD_ARGUMENT;
   }
+  if (p.post_norm_weight && p.epilogue != GEMV_RESIDUAL) return VIPERA_BAD_ARGUMENT;
   const int warps = gemv_warps(p.K);
   const size_t shared = gemv_shared_bytes(p.T, p.K, warps);
   cudaStream_t s = static_cast<cudaStream_t>(stream);

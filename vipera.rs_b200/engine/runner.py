@@ -88,6 +88,7 @@ class ModelRunner:
         self._step_graphs = {}
         self.graph_replays = 0   # steps that replayed a captured graph ...
         self.eager_steps = 0     # ... and steps launched kernel by kernel
+        self.graph_captures = 0  # graphs captured (a buffer that grows makes the graphs before it stale)
         self._page_sizes = [self.manager.group(g)[0] for g in range(self.manager.num_groups)]
 
     # ------------------------------------------------------------------------------
@@ -176,7 +177,7 @@ class ModelRunner:
             block_tables=block_tables, logit_rows=part(7) if rows.size else None, num_logit_rows=int(rows.size),
             host_counts=[int(c) for c in counts], host_pos0=[int(p) for p in pos0],
             max_count=int(counts.max()), max_kv_len=max_len, all_single=bool((counts == 1).all()),
-            dtype=self.model.dtype, workspace=self.workspace,
+            any_single=bool((counts == 1).any()), dtype=self.model.dtype, workspace=self.workspace,
             logits_all_rows=bool(rows.size == total and np.array_equal(rows, np.arange(total))))
 
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
@@ -220,14 +221,17 @@ class ModelRunner:
         longest = int(max(first + count for first, count in zip(step.pos0, step.counts)))
         widths = tuple(_round_up_pow2(max(-(-longest // page_size), -(-bucket // page_size)))
                        for page_size in self._page_sizes)
-        key = (bucket, entry_bucket, row_bucket, widths)
+        # whether the split-key attention runs beside the flash kernel is part of the class: some
+        # entry (the padding entry included) brings exactly one token
+        any_single = 1 in step.counts or bucket - total == 1
+        key = (bucket, entry_bucket, row_bucket, widths, any_single)
         graph = self._step_graphs.get(key)
         if graph is not None and graph.stale():
             graph = None
         if graph is None:
             if len(self._step_graphs) >= self.max_kept_graphs:
                 self._step_graphs.pop(next(iter(self._step_graphs)))
-            graph = self._step_graphs[key] = _StepGraph(self, bucket, entry_bucket, row_bucket, widths)
+            graph = self._step_graphs[key] = _StepGraph(self, bucket, entry_bucket, row_bucket, widths, any_single)
         return graph
 
     # ------------------------------------------------------------------------------
@@ -359,8 +363,8 @@ class _DecodeGraph:
             state_slots=self._part(5), fresh=self._part(6), block_tables=tables, logit_rows=self._part(7),
             num_logit_rows=b, host_counts=[1] * b, host_pos0=[0] * b, max_count=1,
             max_kv_len=min(w * runner.manager.group(g)[0] for g, w in enumerate(self.widths)) if self.widths else 0,
-            all_single=True, dtype=runner.model.dtype, workspace=runner.workspace, logits_all_rows=True,
-            extras={"graph": True})
+            all_single=True, any_single=True, dtype=runner.model.dtype, workspace=runner.workspace,
+            logits_all_rows=True, extras={"graph": True})
 
     def capture(self) -> None:
         """Capture the step whose inputs `fill` has just put on their way."""
@@ -380,6 +384,7 @@ class _DecodeGraph:
         ops.launches = before
         self.graph = graph
         self.generations = (runner.workspace.generation, ops.buffer_generation)
+        runner.graph_captures += 1
 
     def replay(self, entries: int) -> torch.Tensor:
         from ..kernels import ops
@@ -396,9 +401,10 @@ class _StepGraph:
     only the group's scratch page (a page no request ever holds), so what they compute lands
     nowhere; entries beyond that bring no tokens; spare wanted rows repeat the first."""
 
-    def __init__(self, runner: ModelRunner, tokens: int, entries: int, rows: int, widths):
+    def __init__(self, runner: ModelRunner, tokens: int, entries: int, rows: int, widths, any_single: bool):
         self.runner = runner
         self.tokens, self.entries, self.rows = int(tokens), int(entries), int(rows)
+        self.any_single = bool(any_single)
         self.widths = [int(w) for w in widths]
         t, e = self.tokens, self.entries
         self.sizes = [t, t, t, e + 1, e, e, e, max(self.rows, 1)] + [e * w for w in self.widths]
@@ -474,7 +480,7 @@ class _StepGraph:
             block_tables=tables, logit_rows=self._part(7) if self.rows else None, num_logit_rows=self.rows,
             host_counts=[], host_pos0=[], max_count=t,
             max_kv_len=min(w * runner._page_sizes[g] for g, w in enumerate(self.widths)) if self.widths else 0,
-            all_single=False, dtype=runner.model.dtype, workspace=runner.workspace,
+            all_single=False, any_single=self.any_single, dtype=runner.model.dtype, workspace=runner.workspace,
             logits_all_rows=False, extras={"graph": True})
 
     def run(self, step: StepInput) -> Optional[torch.Tensor]:
@@ -496,6 +502,7 @@ class _StepGraph:
             ops.launches = before
             self.graph = graph
             self.generations = (runner.workspace.generation, ops.buffer_generation)
+            runner.graph_captures += 1
         self.graph.replay()
         ops.launches += self.kernels
         if self.logits is None:

@@ -374,10 +374,13 @@ def _tc_buffers(device, scratch_bytes: int):
     buffer that also receives the sampler's token ids and row states, so that one copy to the
     host brings all three."""
     global buffer_generation
-    state = _tc_state.setdefault(str(device), {"scratch": None, "status": None, "words": None})
+    state = _tc_state.setdefault(str(device), {"scratch": None, "status": None, "words": None, "counters": None})
     if state["status"] is None:
         state["words"] = torch.zeros(_WORDS_HEAD + 2 * SAMPLER_MAX_ROWS, dtype=torch.int32, device=device)
         state["status"] = state["words"][:1]
+        # tickets by which the blocks of a kernel find out which of them ends last; every kernel
+        # that uses one leaves it at zero
+        state["counters"] = torch.zeros(4096, dtype=torch.int32, device=device)
     if scratch_bytes and (state["scratch"] is None or state["scratch"].numel() * 4 < scratch_bytes):
         state["scratch"] = torch.empty(max(scratch_bytes // 4, 8 << 20), dtype=torch.float32, device=device)
         buffer_generation += 1
@@ -528,10 +531,11 @@ TC_ATTENTION_HEAD_DIM = 128
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
                       entry_starts: torch.Tensor, entry_pos0: torch.Tensor, block_table: torch.Tensor,
                       num_entries: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                      window: int = 0) -> None:
+                      window: int = 0, skip_single: bool = False) -> None:
     """Flash-style attention of a step whose entries bring any number of tokens (bfloat16,
     head sizes 64 and 128).  Head size 128 runs on tcgen05 with accumulators in tensor memory
-    (VIPERA_ATTENTION_TC=0 keeps it on the mma.sync kernel, which also serves head size 64)."""
+    (VIPERA_ATTENTION_TC=0 keeps it on the mma.sync kernel, which also serves head size 64).
+    ``skip_single`` leaves entries of one token out: attention_decode with ``entry_starts`` runs them."""
     if head_dim not in MMA_HEAD_DIMS:
         raise UnsupportedError(f"attention_prefill: head size {head_dim} (built: 64, 128)")
     count = q.shape[0]
@@ -545,13 +549,14 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
     sizes = (block_table.shape[1], k_pool.shape[1], num_entries, count, num_heads, num_kv_heads, head_dim,
              float(scale), int(window or 0))
     kinds = [_c_void] * 7 + [_c_int] * 7 + [_c_float, _c_int]
+    skip = 1 if skip_single else 0
     if head_dim == TC_ATTENTION_HEAD_DIM and os.environ.get("VIPERA_ATTENTION_TC", "1") != "0":
-        fn = _function("attention_tc", "vipera_attention_prefill_tc", kinds + [_c_int, _c_void, _c_void])
-        _check(fn(*pointers, *sizes, k_pool.shape[0], kernel_status_word(q.device).data_ptr(), _stream()),
+        fn = _function("attention_tc", "vipera_attention_prefill_tc", kinds + [_c_int, _c_int, _c_void, _c_void])
+        _check(fn(*pointers, *sizes, k_pool.shape[0], skip, kernel_status_word(q.device).data_ptr(), _stream()),
                "attention_prefill_tc")
         return
-    fn = _function("attention_mma", "vipera_attention_prefill", kinds + [_c_void])
-    _check(fn(*pointers, *sizes, _stream()), "attention_prefill")
+    fn = _function("attention_mma", "vipera_attention_prefill", kinds + [_c_int, _c_void])
+    _check(fn(*pointers, *sizes, skip, _stream()), "attention_prefill")
 
 
 def decode_splits(num_entries: int, num_kv_heads: int, max_keys: int, sm_count: int):
@@ -569,26 +574,33 @@ def decode_splits(num_entries: int, num_kv_heads: int, max_keys: int, sm_count: 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
                      positions: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int,
                      head_dim: int, scale: float, window: int, chunk: int, num_splits: int,
-                     scratch: torch.Tensor) -> None:
-    """Split-key attention of a step in which every entry brings one token (bfloat16, head
-    sizes 64 and 128); the partial results of the splits are combined by a second kernel."""
+                     scratch: torch.Tensor, entry_starts: Optional[torch.Tensor] = None) -> None:
+    """Split-key attention of the entries that bring one token (bfloat16, head sizes 64 and
+    128); the partial results of the splits are combined by a second kernel.  Without
+    ``entry_starts`` every entry brings one token (q and out are [entries, heads * d], positions
+    one per entry).  With ``entry_starts`` [entries + 1] the step has portions too: q and out
+    are [tokens, heads * d], ``positions`` holds each entry's first position, and entries of
+    more than one token are skipped (attention_prefill with ``skip_single`` runs them)."""
     fn = _function("attention_mma", "vipera_attention_decode",
                    [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
-                    _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, ctypes.c_size_t, _c_void])
+                    _c_int, _c_float, _c_int, _c_int, _c_int, _c_void, ctypes.c_size_t, _c_void, _c_void])
     if head_dim not in MMA_HEAD_DIMS:
         raise UnsupportedError(f"attention_decode: head size {head_dim} (built: 64, 128)")
-    count = q.shape[0]
+    count = block_table.shape[0]
     if q.shape[1] != num_heads * head_dim or out.shape != q.shape:
-        raise InvalidArgumentError("attention_decode: q and out must be [entries, heads * d]")
+        raise InvalidArgumentError("attention_decode: q and out must be [rows, heads * d]")
     if k_pool.shape[2:] != (num_kv_heads, head_dim) or v_pool.shape != k_pool.shape:
         raise InvalidArgumentError("attention_decode: cache pools must be [pages, page_size, kv_heads, d]")
-    if block_table.shape[0] != count or positions.numel() != count:
+    if positions.numel() != count or (entry_starts is None and q.shape[0] != count):
         raise InvalidArgumentError("attention_decode: one position and one block table row per entry")
+    if entry_starts is not None and entry_starts.numel() != count + 1:
+        raise InvalidArgumentError("attention_decode: entry_starts must hold one more item than there are entries")
     _check(fn(_gpu(q, "q", torch.bfloat16), _gpu(out, "out", torch.bfloat16), _gpu(k_pool, "k_pool", torch.bfloat16),
               _gpu(v_pool, "v_pool", torch.bfloat16), _gpu(positions, "positions", torch.int32),
               _gpu(block_table, "block_table", torch.int32), block_table.shape[1], k_pool.shape[1], count,
               num_heads, num_kv_heads, head_dim, float(scale), int(window or 0), int(chunk), int(num_splits),
-              _gpu(scratch, "scratch", torch.float32), scratch.numel(), _stream()), "attention_decode", kernels=2)
+              _gpu(scratch, "scratch", torch.float32), scratch.numel(), _opt(entry_starts, "entry_starts", torch.int32),
+              _stream()), "attention_decode", kernels=2)
 
 
 def attention_decode_scratch_floats(num_entries: int, num_heads: int, head_dim: int, num_splits: int) -> int:
@@ -620,6 +632,8 @@ class _GemvParams(ctypes.Structure):
         ("positions", _c_void), ("cos_table", _c_void), ("sin_table", _c_void), ("q_out", _c_void),
         ("k_pool", _c_void), ("v_pool", _c_void), ("token_entry", _c_void), ("block_table", _c_void),
         ("table_width", _c_int), ("page_size", _c_int), ("write_cache", _c_int),
+        ("post_norm_weight", _c_void), ("post_eps", _c_float), ("post_out", _c_void), ("post_dtype", _c_int),
+        ("counter", _c_void),
     ]
 
 
@@ -629,11 +643,14 @@ _gemv_checked = False
 def gemv_small(w: torch.Tensor, *, a: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None,
                norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, rows: Optional[torch.Tensor] = None,
                tokens: Optional[int] = None, epilogue: int = GEMV_STORE, bias: Optional[torch.Tensor] = None,
-               out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None, rope: Optional[dict] = None) -> None:
+               out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None, rope: Optional[dict] = None,
+               post_norm: Optional[tuple] = None) -> None:
     """w[N, K] (bfloat16) times at most 32 tokens.  The input is either ``a`` (bfloat16 [T, K])
     or the float32 residual stream ``x`` with an RMSNorm (``norm_weight``, ``eps``, optional
     ``rows`` choosing which rows of x are the tokens) computed on the way.  ``rope`` holds
-    the arguments of the rotary/cache ending (see GQAttention)."""
+    the arguments of the rotary/cache ending (see GQAttention).  ``post_norm`` = (weight, eps,
+    out) with the residual ending: the RMSNorm of the finished rows of ``resid`` goes to ``out``
+    [T, N], written by the block that ends last."""
     global _gemv_checked
     fn = _function("gemv_small", "vipera_gemv_small", [ctypes.POINTER(_GemvParams), _c_void])
     if not _gemv_checked:
@@ -682,6 +699,14 @@ def gemv_small(w: torch.Tensor, *, a: Optional[torch.Tensor] = None, x: Optional
         p.out = _opt(out, "out")
         p.out_dtype = dtype_code(out.dtype) if out is not None else F32
         p.resid = _opt(resid, "resid", torch.float32)
+        if post_norm is not None:
+            weight, post_eps, post_out = post_norm
+            if epilogue != GEMV_RESIDUAL or weight.numel() != n or tuple(post_out.shape) != (t, n):
+                raise InvalidArgumentError("gemv_small: a norm behind the product needs the residual ending, a "
+                                           "weight of N values and an output of [T, N]")
+            p.post_norm_weight, p.post_eps = _gpu(weight, "post_norm weight", torch.float32), float(post_eps)
+            p.post_out, p.post_dtype = _gpu(post_out, "post_norm out"), dtype_code(post_out.dtype)
+            p.counter = _tc_buffers(w.device, 0)["counters"].data_ptr()
     _check(fn(ctypes.byref(p), _stream()), "gemv_small")
 
 

@@ -122,7 +122,7 @@ class GQAttention(Mixer):
                                epilogue=ops.GEMV_ROPE_CACHE, bias=self.qkv.bias, rope=rope)
             mixed = ws.get("attention.out", (count, heads * d), ctx.dtype)
             self._attend(ctx, q, mixed, cache, table)
-            self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
+            self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual, norm_after=ctx.norm_after)
             return
         if (ctx.dtype == torch.bfloat16 and style in (ops.ROPE_NONE, ops.ROPE_NEOX)
                 and self.qkv.tensor_core
@@ -136,7 +136,7 @@ class GQAttention(Mixer):
                              page_size=cache.page_size, write_cache=writes_cache)
             mixed = ws.get("attention.out", (count, heads * d), ctx.dtype)
             self._attend(ctx, q, mixed, cache, table)
-            self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
+            self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual, norm_after=ctx.norm_after)
             return
         qkv = ws.get("attention.qkv", (count, (heads + 2 * kv_heads) * d), torch.float32)
         self.qkv(ctx, h, epilogue=ops.EPI_STORE, out=qkv)
@@ -155,7 +155,7 @@ class GQAttention(Mixer):
                        page_size=cache.page_size, write_cache=writes_cache)
         mixed = ws.get("attention.out", (count, heads * d), ctx.dtype)
         self._attend(ctx, q, mixed, cache, table)
-        self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
+        self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual, norm_after=ctx.norm_after)
 
     def _attend(self, ctx, q, mixed, cache, table):
         """Choose the attention kernel: on the bfloat16 path with a head size the tensor-core
@@ -174,10 +174,23 @@ class GQAttention(Mixer):
                                      num_heads=heads, num_kv_heads=kv_heads, head_dim=d, scale=self.scale,
                                      window=window, chunk=chunk, num_splits=splits, scratch=scratch)
             else:
+                # portions through the flash kernel; the single tokens beside them (the running
+                # decodes of a mixed step) through the split-key kernel, which streams their
+                # history once per KV head instead of once per head and tile of 128 queries
                 ops.attention_prefill(q, mixed, cache.k, cache.v, entry_starts=ctx.entry_starts,
                                       entry_pos0=ctx.entry_pos0, block_table=table, num_entries=ctx.num_entries,
                                       num_heads=heads, num_kv_heads=kv_heads, head_dim=d, scale=self.scale,
-                                      window=window)
+                                      window=window, skip_single=ctx.any_single)
+                if ctx.any_single:
+                    chunk, splits = ops.decode_splits(ctx.num_entries, kv_heads, max(ctx.max_kv_len, 1),
+                                                      ops.sm_count(q.device))
+                    scratch = ctx.workspace.get(
+                        "attention.partials",
+                        (ops.attention_decode_scratch_floats(ctx.num_entries, heads, d, splits),), torch.float32)
+                    ops.attention_decode(q, mixed, cache.k, cache.v, positions=ctx.entry_pos0, block_table=table,
+                                         num_heads=heads, num_kv_heads=kv_heads, head_dim=d, scale=self.scale,
+                                         window=window, chunk=chunk, num_splits=splits, scratch=scratch,
+                                         entry_starts=ctx.entry_starts)
             return
         ops.attention(q, mixed, cache.k, cache.v, token_seq=ctx.token_entry, positions=ctx.positions,
                       block_table=table, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
