@@ -43,16 +43,6 @@
 
 enum { ATTENTION_TC_WAIT_EXPIRED = 3 };
 
-#ifdef VIPERA_ATTN_TIMING
-#include <cstdio>
-#define ATT_T(var) const long long var = clock64()
-#define ATT_ADD(acc, a, b) acc += (b) - (a)
-#define ATT_EVENT(kind, j) do { if (blockIdx.y == 1 && blockIdx.x == 0 && (j) < 16) bars->trace[kind][j] = clock64(); } while (0)
-#else
-#define ATT_T(var)
-#define ATT_ADD(acc, a, b)
-#define ATT_EVENT(kind, j)
-#endif
 
 namespace {
 
@@ -227,9 +217,6 @@ struct Barriers {
   uint64_t p_full[2], pv_done[2];  // per softmax group
   uint32_t tmem_base;
   int abort_flag;
-#ifdef VIPERA_ATTN_TIMING
-  long long trace[10][16];  // [event][tile]: when things happened in one block
-#endif
 };
 
 template <bool TMA_KV>
@@ -318,18 +305,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     uint8_t* p_tile = p_tiles + group * kTileBytes;
     const int group_tiles = (num_tiles - group + 1) / 2;  // tiles group, group + 2, ...
     float row_max = -INFINITY, row_sum = 0.0f;
-#ifdef VIPERA_ATTN_TIMING
-    long long w_s = 0, w_pv = 0, c_p1 = 0, c_rs = 0, c_p2 = 0;
-#endif
     for (int i = 0; i < group_tiles; ++i) {
       const int j = 2 * i + group;
       const int key0 = (first_tile + j) * kKeys;
-      ATT_T(t0);
       mbar_wait(&bars->s_full[group], static_cast<uint32_t>(i) & 1u, abort_flag, p.status);
       tcgen05_fence_after();
-      ATT_T(t1);
-      ATT_ADD(w_s, t0, t1);
-      if (quarter == 0 && lane == 0) ATT_EVENT(2, j);
       // does any row of this block need a mask in this tile?
       const bool edge = key0 + kKeys - 1 > pos0 || (p.window > 0 && key0 < pos0 + tokens_here - p.window + 1) || tokens_here < kQ;
       // first pass over the row's 128 scores: the largest visible one
@@ -369,14 +349,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       row_max = new_max;
       row_sum *= alpha;
       // the group's output accumulator and P tile are free once the product of its tile before is done
-      ATT_T(t2);
-      ATT_ADD(c_p1, t1, t2);
-      if (quarter == 0 && lane == 0) ATT_EVENT(3, j);
       if (i > 0) mbar_wait(&bars->pv_done[group], static_cast<uint32_t>(i - 1) & 1u, abort_flag, p.status);
       tcgen05_fence_after();
-      ATT_T(t3);
-      ATT_ADD(w_pv, t2, t3);
-      if (quarter == 0 && lane == 0) ATT_EVENT(4, j);
       if (i > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
         for (int c = 0; c < kD; c += 32) {
@@ -389,8 +363,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         tmem_store_wait();
       }
       // second pass: p = 2^(s * scale * log2 e - max), summed in 32-bit, rounded to bfloat16 into the P tile
-      ATT_T(t4);
-      ATT_ADD(c_rs, t3, t4);
       float tile_sum = 0.0f, tile_sum_b = 0.0f;
       const float shift = row_max == -INFINITY ? 0.0f : row_max;  // a row without visible keys: 2^(-inf) = 0 everywhere
 #pragma unroll 1
@@ -403,7 +375,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
           // the scores are in registers: the accumulator is free for the group's next tile
           tcgen05_fence_before();
           mbar_arrive(&bars->s_empty[group]);
-          if (quarter == 0 && lane == 0) ATT_EVENT(9, j);
         }
         if (edge) {
 #pragma unroll
@@ -432,15 +403,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       tcgen05_fence_before();
       fence_async_shared();
       mbar_arrive(&bars->p_full[group]);
-      ATT_T(t5);
-      ATT_ADD(c_p2, t4, t5);
-      if (quarter == 0 && lane == 0) ATT_EVENT(5, j);
     }
-#ifdef VIPERA_ATTN_TIMING
-    if (blockIdx.y == 1 && blockIdx.x == 0 && lane == 0 && quarter == 0 && group_tiles > 0)
-      printf("softmax group %d: tiles %d wait_s %lld pass1 %lld wait_pv %lld rescale %lld pass2 %lld (cycles per tile)\n", group,
-             group_tiles, w_s / group_tiles, c_p1 / group_tiles, w_pv / group_tiles, c_rs / group_tiles, c_p2 / group_tiles);
-#endif
     // ---------------- ending: join the two groups' folds, out = O / sum ----------------
     if (num_tiles > 0) {
       // A group's last product must be done before its P tile carries the group's max and sum
@@ -512,7 +475,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       auto issue_scores = [&](int i) {   // the group's tile i
         mbar_wait(&bars->k_full[g], static_cast<uint32_t>(i) & 1u, abort_flag, p.status);
         if (i > 0) mbar_wait(&bars->s_empty[g], static_cast<uint32_t>(i - 1) & 1u, abort_flag, p.status);
-        ATT_EVENT(0, 2 * i + g);
         tcgen05_fence_after();
 #pragma unroll
         for (int ks = 0; ks < kD / 16; ++ks) {
@@ -535,7 +497,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         const bool zeroed_rows = key0 < first_key || key0 + kKeys > end_key;  // then a loader warp hands the tile over (as the cp.async path always does)
         mbar_wait(&bars->p_full[g], static_cast<uint32_t>(i) & 1u, abort_flag, p.status);
         mbar_wait((zeroed_rows || !TMA_KV) ? &bars->v_full[g] : &bars->v_landed[g], static_cast<uint32_t>(i) & 1u, abort_flag, p.status);
-        ATT_EVENT(1, 2 * i + g);
         tcgen05_fence_after();
 #pragma unroll
         for (int ks = 0; ks < kKeys / 16; ++ks) {
@@ -623,7 +584,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
             if (values) issue_boxes(j, page, &v_map, &v_run_map, v_tiles + stream_group * kTileBytes, &bars->v_landed[stream_group]);
             else issue_boxes(j, page, &k_map, &k_run_map, k_tiles + stream_group * kTileBytes, &bars->k_full[stream_group]);
           }
-          if (lane == 0) ATT_EVENT(values ? 7 : 6, j);
         };
         if (stream_tiles > 0) issue_tile(0);
         cp_async_wait<0>();
@@ -649,7 +609,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
             fence_async_shared();
           }
           mbar_arrive(&bars->v_full[stream_group]);
-          if (lane == 0) ATT_EVENT(8, 2 * i + stream_group);
         }
       } else {
       // A tile is copied in 16 passes of 8 rows: 16 consecutive threads copy the 16 chunks of
@@ -679,28 +638,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         }
         cp_async_commit();
       };
-#ifdef VIPERA_ATTN_TIMING
-      long long l_ke = 0, l_ve = 0, l_copy = 0, l_land = 0;
-#endif
       auto issue_keys = [&](int j) {    // waits until the scores of tile j - 2 have read the buffer
         const int buffer = j & 1;
-        ATT_T(c0);
         if (j >= 2) mbar_wait(&bars->k_empty[buffer], static_cast<uint32_t>((j >> 1) - 1) & 1u, abort_flag, p.status);
-        ATT_T(c1);
         copy_tile(j, p.k_pool, smem_u32(k_tiles + buffer * kTileBytes));
-        ATT_T(c2);
-        ATT_ADD(l_ke, c0, c1);
-        ATT_ADD(l_copy, c1, c2);
       };
       auto issue_values = [&](int j) {  // waits until the output product of tile j - 2 has read the buffer
         const int buffer = j & 1;
-        ATT_T(c0);
         if (j >= 2) mbar_wait(&bars->v_empty[buffer], static_cast<uint32_t>((j >> 1) - 1) & 1u, abort_flag, p.status);
-        ATT_T(c1);
         copy_tile(j, p.v_pool, smem_u32(v_tiles + buffer * kTileBytes));
-        ATT_T(c2);
-        ATT_ADD(l_ve, c0, c1);
-        ATT_ADD(l_copy, c1, c2);
       };
       auto wait_pending = [&](int groups) {  // until at most `groups` of this thread's copy groups are in flight
         if (groups <= 0) cp_async_wait<0>();
@@ -722,37 +668,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         const int buffer = j & 1;
         // groups committed after K_j so far: V_j, K_j+1 (and V_1 in pass 0)
         const int after_keys = j == 0 ? (num_tiles > 1 ? 3 : 1) : (j + 1 < num_tiles ? 2 : 1);
-        ATT_T(d0);
         wait_pending(after_keys);
         fence_async_shared();
         mbar_arrive(&bars->k_full[buffer]);
         wait_pending(after_keys - 1);
         fence_async_shared();
         mbar_arrive(&bars->v_full[buffer]);
-        ATT_T(d1);
-        ATT_ADD(l_land, d0, d1);
         if (j >= 1 && j + 1 < num_tiles) issue_values(j + 1);
         if (j + 2 < num_tiles) issue_keys(j + 2);
       }
-#ifdef VIPERA_ATTN_TIMING
-      if (blockIdx.y == 1 && blockIdx.x == 0 && t == 0)
-        printf("loader: wait k_empty %lld v_empty %lld issue %lld landing %lld (cycles per tile)\n", l_ke / num_tiles,
-               l_ve / num_tiles, l_copy / num_tiles, l_land / num_tiles);
-#endif
       }
     }
   }
   __syncthreads();
-#ifdef VIPERA_ATTN_TIMING
-  if (blockIdx.y == 1 && blockIdx.x == 0 && threadIdx.x == 0 && num_tiles > 0) {
-    const long long base = bars->trace[6][0];
-    printf("tile: K issued, S issued, S seen, pass 1 done, P.V seen done, S taken, P handed, V issued, V handed, P.V issued\n");
-    for (int j = 0; j < min(num_tiles, 16); ++j)
-      printf("%2d: %6lld %6lld %6lld %6lld %6lld %6lld %6lld %6lld %6lld %6lld\n", j, bars->trace[6][j] - base, bars->trace[0][j] - base,
-             bars->trace[2][j] - base, bars->trace[3][j] - base, bars->trace[4][j] - base, bars->trace[9][j] - base,
-             bars->trace[5][j] - base, bars->trace[7][j] - base, bars->trace[8][j] - base, bars->trace[1][j] - base);
-  }
-#endif
   if (warp == kMmaWarp) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));

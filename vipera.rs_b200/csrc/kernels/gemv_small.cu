@@ -8,10 +8,7 @@
 //     anyway; it normalises the few rows itself while it stages them in shared memory
 //     (rounded to bfloat16 there, as the separate norm kernel would store them);
 //   * behind: bias, the residual addition, SwiGLU, or (for the q/k/v product) the rotary
-//     encoding and the write of keys and values into their cache pages;
-//   * behind the residual addition, where the caller asks: the RMSNorm of the rows just
-//     completed, for the part that runs next.  The block that finishes last (a counter in
-//     device memory tells it) normalises the few rows, so the norm needs no kernel of its own.
+//     encoding and the write of keys and values into their cache pages.
 // The reference's decode path is likewise one weight read for all rows of the batch
 // (crates/vipera-backend-cpu/src/model.rs:1005-1025) with norm and activation fused into
 // the activation preparation of the next product (crates/vipera-backend-cpu/src/quant.rs:578-603,
@@ -56,12 +53,6 @@ struct GemvParams {
   const int* token_entry;
   const int* block_table;
   int table_width, page_size, write_cache;
-  // RESIDUAL, optional: RMSNorm of the finished rows of `resid`, written by the block that ends last
-  const float* post_norm_weight;  // [N] or null
-  float post_eps;
-  void* post_out;               // [T, N] in post_dtype
-  int post_dtype;
-  int* counter;                 // device word, 0 before the launch and again after it
 };
 
 constexpr int kGemvMaxShared = 200 * 1024;
@@ -324,42 +315,6 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
   }
   __syncthreads();  // the partials are read; the next tile may overwrite them
   }
-
-  if (p.post_norm_weight) {
-    // Which block ends last?  Each makes its additions visible, then takes a ticket.
-    __shared__ int is_last;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) is_last = atomicAdd(p.counter, 1) == static_cast<int>(gridDim.x) - 1 ? 1 : 0;
-    __syncthreads();
-    if (is_last) {
-      __threadfence();
-      const int chunks4 = p.N >> 2;   // N is a multiple of 4 here (the launcher sees to it)
-      for (int t = warp; t < p.T; t += warps) {
-        const float* x = p.resid + static_cast<size_t>(t) * p.N;
-        float squares = 0.0f;
-        for (int c = lane; c < chunks4; c += 32) {
-          const float4 v = __ldcg(reinterpret_cast<const float4*>(x) + c);
-          squares += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        }
-        squares = warp_sum(squares);
-        const float inverse = 1.0f / sqrtf(squares / static_cast<float>(p.N) + p.post_eps);
-        for (int c = lane; c < chunks4; c += 32) {
-          const float4 v = __ldcg(reinterpret_cast<const float4*>(x) + c);
-          const float4 w = *(reinterpret_cast<const float4*>(p.post_norm_weight) + c);
-          const float r0 = v.x * inverse * w.x, r1 = v.y * inverse * w.y, r2 = v.z * inverse * w.z, r3 = v.w * inverse * w.w;
-          if (p.post_dtype == VIPERA_BF16) {
-            __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(p.post_out) + static_cast<size_t>(t) * p.N) + 2 * c;
-            dst[0] = __floats2bfloat162_rn(r0, r1);
-            dst[1] = __floats2bfloat162_rn(r2, r3);
-          } else {
-            reinterpret_cast<float4*>(static_cast<float*>(p.post_out) + static_cast<size_t>(t) * p.N)[c] = make_float4(r0, r1, r2, r3);
-          }
-        }
-      }
-      if (threadIdx.x == 0) *p.counter = 0;  // as the next launch expects it
-    }
-  }
 }
 
 template <int NT, bool NORM>
@@ -435,14 +390,10 @@ VIPERA_API int vipera_gemv_small(const GemvParams* params, void* stream) {
     tiles = (p.N + 15) / 16;
   } else if (p.epilogue == GEMV_RESIDUAL) {
     if (!p.resid) return VIPERA_BAD_ARGUMENT;
-    if (p.post_norm_weight && (!p.post_out || !p.counter || (p.N % 4) != 0 ||
-                               (p.post_dtype != VIPERA_F32 && p.post_dtype != VIPERA_BF16)))
-      return VIPERA_BAD_ARGUMENT;
     tiles = (p.N + 15) / 16;
   } else {
     return VIPERA_BAD_ARGUMENT;
   }
-  if (p.post_norm_weight && p.epilogue != GEMV_RESIDUAL) return VIPERA_BAD_ARGUMENT;
   const int warps = gemv_warps(p.K);
   const size_t shared = gemv_shared_bytes(p.T, p.K, warps);
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -15,7 +15,9 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
+import gc
 import os
+import weakref
 
 import numpy as np
 import torch
@@ -47,6 +49,24 @@ def _round_up_pow2(value: int, least: int = 8) -> int:
 # Token counts a captured step is padded to.  Steps under a token budget are mostly full, so the
 # steps that matter hit a bucket exactly; in between at most a third of a step is padding.
 _TOKEN_BUCKETS = (8, 16, 32, 64, 96, 128, 192, 256, 384, 512, 768, 1024, 1536, 2048, 3072, 4096, 6144, 8192)
+
+
+def _capture(forward):
+    """Capture `forward()` (kernel launches on the current stream) in a CUDA graph; returns the
+    graph and what `forward` returned.  The collector is held off meanwhile: it may run in any
+    thread at any allocation, and an object it finalises there (an old graph, a pool) can make
+    a CUDA call that is not allowed while a stream is capturing, which spoils the capture.  For
+    the same reason only this thread's calls count as part of the capture."""
+    graph = torch.cuda.CUDAGraph()
+    collecting = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            result = forward()
+    finally:
+        if collecting:
+            gc.enable()
+    return graph, result
 
 
 def _token_bucket(tokens: int) -> Optional[int]:
@@ -286,7 +306,7 @@ class _DecodeGraph:
     stores the same values twice."""
 
     def __init__(self, runner: ModelRunner, bucket: int, widths):
-        self.runner = runner
+        self._runner = weakref.ref(runner)   # the runner owns its graphs, not the other way round
         self.bucket = bucket
         self.widths = [int(w) for w in widths]
         b = bucket
@@ -308,6 +328,10 @@ class _DecodeGraph:
         self.logits = None
         self.generations = None
         self._plain = {}  # per entry count: the constant arrays of a step launched ahead
+
+    @property
+    def runner(self) -> "ModelRunner":
+        return self._runner()
 
     def stale(self) -> bool:
         from ..kernels import ops
@@ -376,13 +400,10 @@ class _DecodeGraph:
         # own keys and values are written here and again, identically, by the replay.
         runner.forward(ctx)
         torch.cuda.current_stream().synchronize()
-        graph = torch.cuda.CUDAGraph()
         before = ops.launches
-        with torch.cuda.graph(graph):
-            self.logits = runner.forward(ctx)
+        self.graph, self.logits = _capture(lambda: runner.forward(ctx))
         self.kernels = ops.launches - before
         ops.launches = before
-        self.graph = graph
         self.generations = (runner.workspace.generation, ops.buffer_generation)
         runner.graph_captures += 1
 
@@ -402,7 +423,7 @@ class _StepGraph:
     nowhere; entries beyond that bring no tokens; spare wanted rows repeat the first."""
 
     def __init__(self, runner: ModelRunner, tokens: int, entries: int, rows: int, widths, any_single: bool):
-        self.runner = runner
+        self._runner = weakref.ref(runner)   # the runner owns its graphs, not the other way round
         self.tokens, self.entries, self.rows = int(tokens), int(entries), int(rows)
         self.any_single = bool(any_single)
         self.widths = [int(w) for w in widths]
@@ -418,6 +439,10 @@ class _StepGraph:
         self.logits = None
         self.generations = None
         self.kernels = 0
+
+    @property
+    def runner(self) -> "ModelRunner":
+        return self._runner()
 
     def stale(self) -> bool:
         from ..kernels import ops
@@ -494,13 +519,10 @@ class _StepGraph:
             # and values of the step are written here and again, identically, by the replay.
             runner.forward(ctx)
             torch.cuda.current_stream().synchronize()
-            graph = torch.cuda.CUDAGraph()
             before = ops.launches
-            with torch.cuda.graph(graph):
-                self.logits = runner.forward(ctx)
+            self.graph, self.logits = _capture(lambda: runner.forward(ctx))
             self.kernels = ops.launches - before
             ops.launches = before
-            self.graph = graph
             self.generations = (runner.workspace.generation, ops.buffer_generation)
             runner.graph_captures += 1
         self.graph.replay()

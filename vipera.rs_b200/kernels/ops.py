@@ -374,13 +374,10 @@ def _tc_buffers(device, scratch_bytes: int):
     buffer that also receives the sampler's token ids and row states, so that one copy to the
     host brings all three."""
     global buffer_generation
-    state = _tc_state.setdefault(str(device), {"scratch": None, "status": None, "words": None, "counters": None})
+    state = _tc_state.setdefault(str(device), {"scratch": None, "status": None, "words": None})
     if state["status"] is None:
         state["words"] = torch.zeros(_WORDS_HEAD + 2 * SAMPLER_MAX_ROWS, dtype=torch.int32, device=device)
         state["status"] = state["words"][:1]
-        # tickets by which the blocks of a kernel find out which of them ends last; every kernel
-        # that uses one leaves it at zero
-        state["counters"] = torch.zeros(4096, dtype=torch.int32, device=device)
     if scratch_bytes and (state["scratch"] is None or state["scratch"].numel() * 4 < scratch_bytes):
         state["scratch"] = torch.empty(max(scratch_bytes // 4, 8 << 20), dtype=torch.float32, device=device)
         buffer_generation += 1
@@ -632,8 +629,6 @@ class _GemvParams(ctypes.Structure):
         ("positions", _c_void), ("cos_table", _c_void), ("sin_table", _c_void), ("q_out", _c_void),
         ("k_pool", _c_void), ("v_pool", _c_void), ("token_entry", _c_void), ("block_table", _c_void),
         ("table_width", _c_int), ("page_size", _c_int), ("write_cache", _c_int),
-        ("post_norm_weight", _c_void), ("post_eps", _c_float), ("post_out", _c_void), ("post_dtype", _c_int),
-        ("counter", _c_void),
     ]
 
 
@@ -643,14 +638,11 @@ _gemv_checked = False
 def gemv_small(w: torch.Tensor, *, a: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None,
                norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, rows: Optional[torch.Tensor] = None,
                tokens: Optional[int] = None, epilogue: int = GEMV_STORE, bias: Optional[torch.Tensor] = None,
-               out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None, rope: Optional[dict] = None,
-               post_norm: Optional[tuple] = None) -> None:
+               out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None, rope: Optional[dict] = None) -> None:
     """w[N, K] (bfloat16) times at most 32 tokens.  The input is either ``a`` (bfloat16 [T, K])
     or the float32 residual stream ``x`` with an RMSNorm (``norm_weight``, ``eps``, optional
     ``rows`` choosing which rows of x are the tokens) computed on the way.  ``rope`` holds
-    the arguments of the rotary/cache ending (see GQAttention).  ``post_norm`` = (weight, eps,
-    out) with the residual ending: the RMSNorm of the finished rows of ``resid`` goes to ``out``
-    [T, N], written by the block that ends last."""
+    the arguments of the rotary/cache ending (see GQAttention)."""
     global _gemv_checked
     fn = _function("gemv_small", "vipera_gemv_small", [ctypes.POINTER(_GemvParams), _c_void])
     if not _gemv_checked:
@@ -699,14 +691,6 @@ def gemv_small(w: torch.Tensor, *, a: Optional[torch.Tensor] = None, x: Optional
         p.out = _opt(out, "out")
         p.out_dtype = dtype_code(out.dtype) if out is not None else F32
         p.resid = _opt(resid, "resid", torch.float32)
-        if post_norm is not None:
-            weight, post_eps, post_out = post_norm
-            if epilogue != GEMV_RESIDUAL or weight.numel() != n or tuple(post_out.shape) != (t, n):
-                raise InvalidArgumentError("gemv_small: a norm behind the product needs the residual ending, a "
-                                           "weight of N values and an output of [T, N]")
-            p.post_norm_weight, p.post_eps = _gpu(weight, "post_norm weight", torch.float32), float(post_eps)
-            p.post_out, p.post_dtype = _gpu(post_out, "post_norm out"), dtype_code(post_out.dtype)
-            p.counter = _tc_buffers(w.device, 0)["counters"].data_ptr()
     _check(fn(ctypes.byref(p), _stream()), "gemv_small")
 
 

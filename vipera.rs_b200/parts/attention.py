@@ -122,7 +122,7 @@ class GQAttention(Mixer):
                                epilogue=ops.GEMV_ROPE_CACHE, bias=self.qkv.bias, rope=rope)
             mixed = ws.get("attention.out", (count, heads * d), ctx.dtype)
             self._attend(ctx, q, mixed, cache, table)
-            self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual, norm_after=ctx.norm_after)
+            self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
             return
         if (ctx.dtype == torch.bfloat16 and style in (ops.ROPE_NONE, ops.ROPE_NEOX)
                 and self.qkv.tensor_core
@@ -136,7 +136,7 @@ class GQAttention(Mixer):
                              page_size=cache.page_size, write_cache=writes_cache)
             mixed = ws.get("attention.out", (count, heads * d), ctx.dtype)
             self._attend(ctx, q, mixed, cache, table)
-            self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual, norm_after=ctx.norm_after)
+            self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
             return
         qkv = ws.get("attention.qkv", (count, (heads + 2 * kv_heads) * d), torch.float32)
         self.qkv(ctx, h, epilogue=ops.EPI_STORE, out=qkv)
@@ -155,7 +155,7 @@ class GQAttention(Mixer):
                        page_size=cache.page_size, write_cache=writes_cache)
         mixed = ws.get("attention.out", (count, heads * d), ctx.dtype)
         self._attend(ctx, q, mixed, cache, table)
-        self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual, norm_after=ctx.norm_after)
+        self.out(ctx, mixed, epilogue=ops.EPI_RESIDUAL, resid=residual)
 
     def _attend(self, ctx, q, mixed, cache, table):
         """Choose the attention kernel: on the bfloat16 path with a head size the tensor-core

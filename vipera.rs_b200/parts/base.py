@@ -132,10 +132,6 @@ class StepContext:
     workspace: Workspace
     logits_all_rows: bool = False  # the wanted rows are all the step's tokens, in order
     extras: Dict[str, Any] = field(default_factory=dict)
-    # A hint from the arrangement to the part it runs: the normalised input (a NormedInput) of
-    # the part that reads the residual stream next.  A part whose last product can compute that
-    # norm in its ending does so and fills it in; any other part ignores the hint.
-    norm_after: Any = None
 
 
 class Part:
@@ -199,10 +195,5 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    def fuses_norm(self, tokens: int) -> bool:
-        """Whether the part computes the norm of its input in front of its first product itself
-        (given a NormedInput) in a step of `tokens` tokens."""
-        return False
-
     def forward(self, ctx: StepContext, h: torch.Tensor, residual: torch.Tensor) -> None:
         raise NotImplementedError

@@ -97,16 +97,9 @@ class PreNormBlock(Block):
 
     def forward(self, ctx, residual, cache, writes_cache):
         h = NormedInput(ctx, self.mixer_norm, residual)
-        after = NormedInput(ctx, self.ffn_norm, residual)
-        # The mixer may compute the feed-forward's norm in the ending of its last product, unless
-        # the feed-forward computes it in front of its first product itself.
-        fuses = getattr(self.ffn, "fuses_norm", None)
-        ctx.norm_after = None if (fuses is not None and fuses(ctx.num_tokens)) else after
-        try:
-            self.mixer.forward(ctx, self._input(self.mixer, h), residual, cache, writes_cache)
-        finally:
-            ctx.norm_after = None
-        self.ffn.forward(ctx, self._input(self.ffn, after), residual)
+        self.mixer.forward(ctx, self._input(self.mixer, h), residual, cache, writes_cache)
+        h = NormedInput(ctx, self.ffn_norm, residual)
+        self.ffn.forward(ctx, self._input(self.ffn, h), residual)
 
 
 BLOCKS.register("prenorm", PreNormBlock)

@@ -100,30 +100,18 @@ class Linear:
         return known
 
     def __call__(self, ctx, a, *, epilogue: int = ops.EPI_STORE,
-                 out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None,
-                 norm_after: Optional[NormedInput] = None) -> None:
-        """``a`` is a tensor [tokens, K] in the run dtype, or a NormedInput.  ``norm_after``
-        (with the residual ending): the normalised input of the part that reads ``resid`` next;
-        where this product's kernel can compute it in its ending it does, and fills it in."""
+                 out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None) -> None:
+        """``a`` is a tensor [tokens, K] in the run dtype, or a NormedInput."""
         bias = self.bias if epilogue == ops.EPI_STORE else None
         lazy = a if isinstance(a, NormedInput) else None
         tokens = lazy.num_rows if lazy is not None else a.shape[0]
-        post_norm = None
-        if (norm_after is not None and epilogue == ops.EPI_RESIDUAL and self.takes_small(tokens)
-                and norm_after.fusable and norm_after.rows is None and norm_after._tensor is None
-                and norm_after.residual is resid and self.out_features % 4 == 0):
-            target = ctx.workspace.get(norm_after.name, (tokens, self.out_features), ctx.dtype)
-            post_norm = (norm_after.norm.weight, norm_after.norm.eps, target)
         if self.takes_small(tokens):
             if lazy is not None and lazy.fusable and lazy._tensor is None:
                 ops.gemv_small(self.weight, x=lazy.residual, norm_weight=lazy.norm.weight, eps=lazy.norm.eps,
-                               rows=lazy.rows, tokens=tokens, epilogue=epilogue, bias=bias, out=out, resid=resid,
-                               post_norm=post_norm)
+                               rows=lazy.rows, tokens=tokens, epilogue=epilogue, bias=bias, out=out, resid=resid)
             else:
                 ops.gemv_small(self.weight, a=lazy.tensor() if lazy is not None else a, epilogue=epilogue,
-                               bias=bias, out=out, resid=resid, post_norm=post_norm)
-            if post_norm is not None:
-                norm_after._tensor = post_norm[2]
+                               bias=bias, out=out, resid=resid)
             return
         if lazy is not None:
             a = lazy.tensor()

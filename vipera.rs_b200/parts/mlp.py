@@ -53,10 +53,6 @@ class SwiGLU(FeedForward):
     def kernel_families(self):
         return tuple(dict.fromkeys(self.gate_up.kernel_families() + self.down.kernel_families()))
 
-    def fuses_norm(self, tokens: int) -> bool:
-        # the small-token kernel computes the norm in front of the gate and up product itself
-        return self.gate_up.takes_small(tokens)
-
     def forward(self, ctx, h, residual):
         act = ctx.workspace.get("swiglu.act", (ctx.num_tokens, self.inter), ctx.dtype)
         self.gate_up(ctx, h, epilogue=ops.EPI_SWIGLU, out=act)
