@@ -164,7 +164,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   static_assert(16 * (D + 4) * 4 <= kWarpTile, "a warp's partial must fit in its tiles");
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_launch_dependents();
-  pdl_wait();
+  // What follows up to pdl_wait() reads only what the host wrote before the step began (the
+  // step's description: starts, positions, block tables) and keys and values of earlier steps.
   const int entry = blockIdx.x, kv_head = blockIdx.y, split = blockIdx.z;
   // Token i is entry i in a step of single tokens.  In a step with portions (`entry_starts`
   // given) the entry's token is where its tokens start, and entries that bring more than one
@@ -189,11 +190,26 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const uint32_t k_tile = smem_addr(warp_bytes);
   const uint32_t v_tile = k_tile + kKeys * D * 2;
 
+  // The step's own key and value (at `position`) are written by the kernel ahead of this one;
+  // every other row is from earlier steps.  A warp whose first block of keys does not hold
+  // `position` asks for it now, before the wait: the block table and the cache are then read
+  // while the kernel ahead still runs, and only the queries remain to be fetched after it.
+  bool asked_early = false;
+  {
+    const int key0 = begin + warp * kKeys;
+    if (key0 < end && !(position >= key0 && position < key0 + kKeys)) {
+      load_kv_rows32<D>(k_tile, v_tile, k_pool, v_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0,
+                        first_visible, end, lane);
+      asked_early = true;
+    }
+  }
+  pdl_wait();
+
   for (int m_tile = 0; m_tile * 16 < group; ++m_tile) {
     __syncthreads();
     // this warp's first block of keys goes on its way before anything else
     int key0 = begin + warp * kKeys;
-    if (key0 < end) {
+    if (key0 < end && !(asked_early && m_tile == 0)) {
       load_kv_rows32<D>(k_tile, v_tile, k_pool, v_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0,
                         first_visible, end, lane);
     }
@@ -311,7 +327,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
   __shared__ float maxima[128];
   __shared__ float sums[128];
   pdl_launch_dependents();
-  pdl_wait();
+  // the step's description (written by the host before the step) is read before the wait
   const size_t row = static_cast<size_t>(blockIdx.x) * num_heads + blockIdx.y;
   size_t out_row = row;
   if (entry_starts) {   // a step with portions: only entries of one token, written at their token's row
@@ -323,6 +339,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
   const float* values = partial_out + row * slices * D + threadIdx.x;
   // only the splits that hold visible keys were written by the decode kernel
   const int position = positions[blockIdx.x];
+  pdl_wait();
   const int first_visible = window > 0 ? max(0, position - window + 1) : 0;
   const int first = (first_visible / 32 * 32) / chunk;
   const int last = min(slices - 1, position / chunk);
@@ -382,7 +399,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, const __nv_
   static_assert(16 * kRow * 4 <= kWarpTile, "a warp's partial must fit in its tiles");
   extern __shared__ __align__(128) uint8_t smem[];
   pdl_launch_dependents();
-  pdl_wait();
+  // up to pdl_wait(): only what the host wrote before the step, and keys and values of earlier steps
   const int entry = blockIdx.x, kv_head = blockIdx.y;
   const int rank = static_cast<int>(cluster_rank());
   const int group = num_heads / num_kv_heads;   // at most 16 (the launcher sees to it)
@@ -404,7 +421,14 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, const __nv_
   const uint32_t q_tile = smem_addr(q_bytes);
   const uint32_t tiles = smem_addr(warp_bytes);
 
-  // queries of the group, and this warp's first block of keys
+  // This warp's first block of keys goes on its way before the wait unless it holds the step's own
+  // key (the kernel ahead writes that one); then the queries of the group, which that kernel wrote.
+  int key0 = begin + warp * kKeys;
+  const bool early = key0 < end && !(position >= key0 && position < key0 + kKeys);
+  if (early)
+    load_kv_rows32<D>(tiles, tiles + kKeys * D * 2, k_pool, v_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0,
+                      first_visible, end, lane);
+  pdl_wait();
   {
     constexpr int kChunks = D / 8;
     for (int index = threadIdx.x; index < 16 * kChunks; index += 128) {
@@ -414,8 +438,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, const __nv_
       cp_async_16(q_tile + tile_offset<D>(row, c), src, valid);
     }
   }
-  int key0 = begin + warp * kKeys;
-  if (key0 < end)
+  if (key0 < end && !early)
     load_kv_rows32<D>(tiles, tiles + kKeys * D * 2, k_pool, v_pool, table, page_size, page_shift, num_kv_heads, kv_head, key0,
                       first_visible, end, lane);
   cp_async_commit();

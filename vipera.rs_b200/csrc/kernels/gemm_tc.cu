@@ -665,7 +665,7 @@ splitk_finish_kernel(const GemmParams p) {
   const float value = total(n0);
   const size_t at = static_cast<size_t>(t) * N + o;
   if (p.epilogue == EPI_RESIDUAL) {
-    p.resid[at] += value;
+    atomicAdd(p.resid + at, value);   // one addition per element: no need to read the old value back
   } else {
     const float biased = value + (p.bias ? p.bias[o] : 0.0f);
     if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(biased);

@@ -81,41 +81,40 @@ __device__ __forceinline__ void tile_rows(const GemvParams& p, int tile, int g, 
   }
 }
 
-// One (row pair, token) result, finished and stored.
-__device__ __forceinline__ void finish(const GemvParams& p, int row_lo, int row_hi, int t, float v_lo, float v_hi) {
+// What the ending of one (row pair, token) result needs besides the two sums, fetched ahead of
+// the products: bias values, the rotation's cosine and sine, where the result goes.  Everything
+// read here was written before the step began (biases, tables, the step's positions and block
+// tables), so it may be fetched before the kernel waits for the kernels ahead of it; the ending
+// itself then touches memory only to store (or to add, without reading back).
+struct Ending {
+  float bias_lo, bias_hi, cosine, sine;
+  void* dst;        // STORE, SWIGLU: the output element; RESIDUAL: the stream's element of row_lo; ROPE: the head's row
+  int active;       // 0: nothing to write (a value that is not cached)
+  int rotate;
+};
+
+__device__ __forceinline__ Ending prepare_ending(const GemvParams& p, int row_lo, int row_hi, int t) {
+  Ending e;
+  e.bias_lo = e.bias_hi = 0.0f;
+  e.cosine = 1.0f;
+  e.sine = 0.0f;
+  e.dst = nullptr;
+  e.active = 1;
+  e.rotate = 0;
   const bool has_hi = row_hi < p.N;
-  if (p.epilogue == GEMV_RESIDUAL) {
-    p.resid[static_cast<size_t>(t) * p.N + row_lo] += v_lo;
-    if (has_hi) p.resid[static_cast<size_t>(t) * p.N + row_hi] += v_hi;
-  } else if (p.epilogue == GEMV_SWIGLU) {
-    const int feature = (row_lo >> 5) * 16 + (row_lo & 15);
-    const float value = v_hi * (v_lo / (1.0f + __expf(-v_lo)));
-    const size_t at = static_cast<size_t>(t) * (p.N >> 1) + feature;
-    if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
-    else static_cast<float*>(p.out)[at] = value;
-  } else if (p.epilogue == GEMV_STORE) {
-    if (p.bias) { v_lo += p.bias[row_lo]; if (has_hi) v_hi += p.bias[row_hi]; }
-    const size_t at = static_cast<size_t>(t) * p.N;
-    if (p.out_dtype == VIPERA_BF16) {
-      static_cast<__nv_bfloat16*>(p.out)[at + row_lo] = __float2bfloat16_rn(v_lo);
-      if (has_hi) static_cast<__nv_bfloat16*>(p.out)[at + row_hi] = __float2bfloat16_rn(v_hi);
-    } else {
-      static_cast<float*>(p.out)[at + row_lo] = v_lo;
-      if (has_hi) static_cast<float*>(p.out)[at + row_hi] = v_hi;
-    }
-  } else {  // GEMV_ROPE_CACHE
-    if (p.bias) { v_lo += p.bias[row_lo]; v_hi += p.bias[row_hi]; }
+  if (p.epilogue == GEMV_STORE) {
+    if (p.bias) { e.bias_lo = p.bias[row_lo]; if (has_hi) e.bias_hi = p.bias[row_hi]; }
+  } else if (p.epilogue == GEMV_ROPE_CACHE) {
+    if (p.bias) { e.bias_lo = p.bias[row_lo]; e.bias_hi = p.bias[row_hi]; }
     const int d = p.head_dim, half = d >> 1;
     const int head = row_lo / d, i = row_lo % d;
     const int position = p.positions[t];
     const bool is_q = head < p.num_heads;
     const bool is_v = head >= p.num_heads + p.num_kv_heads;
     if (!is_v && p.rope_style == ROPE_NEOX) {
-      const float c = p.cos_table[static_cast<size_t>(position) * half + i];
-      const float s = p.sin_table[static_cast<size_t>(position) * half + i];
-      const float lo = v_lo * c - v_hi * s, hi = v_lo * s + v_hi * c;
-      v_lo = lo;
-      v_hi = hi;
+      e.cosine = p.cos_table[static_cast<size_t>(position) * half + i];
+      e.sine = p.sin_table[static_cast<size_t>(position) * half + i];
+      e.rotate = 1;
     }
     __nv_bfloat16* dst = nullptr;
     if (is_q) {
@@ -128,9 +127,50 @@ __device__ __forceinline__ void finish(const GemvParams& p, int row_lo, int row_
         dst = pool + ((static_cast<size_t>(page) * p.page_size + position % p.page_size) * p.num_kv_heads + kv_head) * d;
       }
     }
-    if (dst) {
-      dst[i] = __float2bfloat16_rn(v_lo);
-      dst[i + half] = __float2bfloat16_rn(v_hi);
+    e.dst = dst ? dst + i : nullptr;
+    e.active = dst != nullptr;
+  }
+  return e;
+}
+
+// One (row pair, token) result, finished and stored.
+__device__ __forceinline__ void finish(const GemvParams& p, const Ending& e, int row_lo, int row_hi, int t, float v_lo,
+                                       float v_hi) {
+  const bool has_hi = row_hi < p.N;
+  if (p.epilogue == GEMV_RESIDUAL) {
+    // every element of the stream gets one addition from one thread: an addition that does not
+    // read the old value back gives the same sum and spares the ending a memory round trip
+    atomicAdd(p.resid + static_cast<size_t>(t) * p.N + row_lo, v_lo);
+    if (has_hi) atomicAdd(p.resid + static_cast<size_t>(t) * p.N + row_hi, v_hi);
+  } else if (p.epilogue == GEMV_SWIGLU) {
+    const int feature = (row_lo >> 5) * 16 + (row_lo & 15);
+    const float value = v_hi * (v_lo / (1.0f + __expf(-v_lo)));
+    const size_t at = static_cast<size_t>(t) * (p.N >> 1) + feature;
+    if (p.out_dtype == VIPERA_BF16) static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(value);
+    else static_cast<float*>(p.out)[at] = value;
+  } else if (p.epilogue == GEMV_STORE) {
+    v_lo += e.bias_lo;
+    v_hi += e.bias_hi;
+    const size_t at = static_cast<size_t>(t) * p.N;
+    if (p.out_dtype == VIPERA_BF16) {
+      static_cast<__nv_bfloat16*>(p.out)[at + row_lo] = __float2bfloat16_rn(v_lo);
+      if (has_hi) static_cast<__nv_bfloat16*>(p.out)[at + row_hi] = __float2bfloat16_rn(v_hi);
+    } else {
+      static_cast<float*>(p.out)[at + row_lo] = v_lo;
+      if (has_hi) static_cast<float*>(p.out)[at + row_hi] = v_hi;
+    }
+  } else {  // GEMV_ROPE_CACHE
+    v_lo += e.bias_lo;
+    v_hi += e.bias_hi;
+    if (e.rotate) {
+      const float lo = v_lo * e.cosine - v_hi * e.sine, hi = v_lo * e.sine + v_hi * e.cosine;
+      v_lo = lo;
+      v_hi = hi;
+    }
+    if (e.active) {
+      __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(e.dst);
+      dst[0] = __float2bfloat16_rn(v_lo);
+      dst[p.head_dim >> 1] = __float2bfloat16_rn(v_hi);
     }
   }
 }
@@ -161,7 +201,9 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
   // its share of K (all of it where K is small) are asked for before the wait and are in
   // registers when the activations arrive.
   const uint4 zero = make_uint4(0, 0, 0, 0);
-  constexpr int kHeld = NT <= 2 ? 8 : (NT == 4 ? 6 : 4);
+  // (six steps are a warp's whole share at an inner size of 1536; eight were measured slower, the
+  // kernel then spills, and so were five and four, which leave loads for after the wait)
+  constexpr int kHeld = NT <= 2 ? 6 : 4;
   uint4 held_lo[kHeld], held_hi[kHeld];
 #pragma unroll
   for (int u = 0; u < kHeld; ++u) {
@@ -173,6 +215,17 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
       if (has_lo) held_lo[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + k));
       if (has_hi) held_hi[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + k));
     }
+  }
+  // A thread's own ending (where the block's threads cover the tile's (token, row pair) items
+  // one each) is prepared ahead too.
+  const bool one_item = p.T * 8 <= static_cast<int>(blockDim.x);
+  const int my_t = threadIdx.x >> 3, my_r = threadIdx.x & 7;
+  Ending my_ending;
+  my_ending.active = 0;
+  if (one_item && my_t < p.T) {
+    int out_lo, out_hi;
+    tile_rows(p, tile, my_r, &out_lo, &out_hi);
+    if (out_lo < p.N) my_ending = prepare_ending(p, out_lo, out_hi, my_t);
   }
   pdl_wait();
 
@@ -233,6 +286,11 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
         if (has_lo) held_lo[u] = __ldg(reinterpret_cast<const uint4*>(w_lo + k));
         if (has_hi) held_hi[u] = __ldg(reinterpret_cast<const uint4*>(w_hi + k));
       }
+    }
+    if (one_item && my_t < p.T) {
+      int out_lo, out_hi;
+      tile_rows(p, tile, my_r, &out_lo, &out_hi);
+      if (out_lo < p.N) my_ending = prepare_ending(p, out_lo, out_hi, my_t);
     }
   }
   // ---- the products ----
@@ -311,7 +369,10 @@ gemv_small_kernel(const GemvParams p, int num_tiles) {
     }
     int out_lo, out_hi;
     tile_rows(p, tile, r, &out_lo, &out_hi);
-    if (out_lo < p.N) finish(p, out_lo, out_hi, t, v_lo, v_hi);
+    if (out_lo < p.N) {
+      if (one_item) finish(p, my_ending, out_lo, out_hi, t, v_lo, v_hi);
+      else finish(p, prepare_ending(p, out_lo, out_hi, t), out_lo, out_hi, t, v_lo, v_hi);
+    }
   }
   __syncthreads();  // the partials are read; the next tile may overwrite them
   }

@@ -53,14 +53,24 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                const int* __restrict__ rows, TO* __restrict__ out, int hidden, float eps) {
   __shared__ float scratch[32];
   pdl_launch_dependents();
-  pdl_wait();
   const int r = blockIdx.x;
+  const bool fits = hidden <= kNormThreads * kNormRegs;
+  // The norm's weights depend on no kernel ahead of this one: they are in registers before the
+  // wait, so that the second pass does not pay a memory round trip for them.
+  float gain[kNormRegs];
+  if (fits) {
+#pragma unroll
+    for (int j = 0; j < kNormRegs; ++j) {
+      const int i = threadIdx.x + j * kNormThreads;
+      gain[j] = i < hidden ? weight[i] : 0.0f;
+    }
+  }
+  pdl_wait();
   const int src_row = rows ? rows[r] : r;
   const float* src = x + static_cast<size_t>(src_row) * hidden;
   TO* dst = out + static_cast<size_t>(r) * hidden;
   float kept[kNormRegs];
   float sum = 0.0f;
-  const bool fits = hidden <= kNormThreads * kNormRegs;
   if (fits) {
 #pragma unroll
     for (int j = 0; j < kNormRegs; ++j) {
@@ -80,7 +90,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 #pragma unroll
     for (int j = 0; j < kNormRegs; ++j) {
       const int i = threadIdx.x + j * kNormThreads;
-      if (i < hidden) dst[i] = from_float<TO>(kept[j] * inverse * weight[i]);
+      if (i < hidden) dst[i] = from_float<TO>(kept[j] * inverse * gain[j]);
     }
   } else {
     for (int i = threadIdx.x; i < hidden; i += kNormThreads)
