@@ -106,3 +106,21 @@ def temperature(logits, temperature, top_k, top_p, min_p, uniform):
         if target < running:
             return token
     return weights[-1][0]
+
+
+def logprobs(logits, token, temperature=0.0, top_n=0):
+    """lib.rs:302-378: over every finite logit, x = logit / temperature (1 for greedy),
+    logprob = x - max - ln(sum exp(x - max)); the token's, and the top_n ids with theirs, best
+    first, ties to the lowest id.  (Penalties, where a request has them, are applied to the logits
+    first, as in `penalised`.)"""
+    t = temperature if temperature > 0.0 else 1.0
+    scaled = [(i, f32(v / t)) for i, v in enumerate(logits) if math.isfinite(v)]
+    peak = max(x for _, x in scaled)
+    mass = 0.0
+    for _, x in scaled:
+        mass = f32(mass + f32(math.exp(f32(x - peak))))
+    log_mass = f32(math.log(mass))
+    of = lambda x: f32(f32(x - peak) - log_mass)  # noqa: E731
+    chosen = of(f32(logits[token] / t))
+    top = sorted(scaled, key=lambda item: (-item[1], item[0]))[:top_n]
+    return chosen, [(i, of(x)) for i, x in top]

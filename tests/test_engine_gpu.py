@@ -273,3 +273,35 @@ def test_counters_and_the_per_step_profile_lines(monkeypatch, capfd):
     assert len(logs) == 2 and all(log["event"] == "generation" and log["finish"] == "length" for log in logs)
     assert {log["prompt_tokens"] for log in logs} == {20, 9}
     assert all(set(log["stage_micros"]) == {"allocate", "compute", "sample", "complete"} for log in logs)
+
+
+def test_logprobs_of_the_drawn_tokens_and_the_most_likely_ones():
+    """A request that asks for log-probabilities gets, for every generated token, its log-probability
+    and the n most likely tokens with theirs, as the plain restatement of the reference's
+    formula gives them on the plain logits; a request beside it that did not ask gets none, and
+    its tokens are what it gets alone."""
+    import plain_sampler
+    from vipera_rs_b200 import SamplingParams
+
+    folder, engine = _engine("A", "float32", page_size=16, ctx=128, max_num_seqs=3)
+    vocab = helpers.CONFIGS["A"]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, 70 + n) for n in (11, 30, 6)]
+    params = [SamplingParams(max_new_tokens=7, logprobs=4),
+              SamplingParams(max_new_tokens=9),
+              SamplingParams(max_new_tokens=6, temperature=0.7, seed=3, logprobs=0)]
+    results = engine.generate(prompts, params)
+    assert results[1].logprobs is None and results[1].top_logprobs is None
+    assert results[1].tokens == engine.generate([prompts[1]], params[1])[0].tokens
+    for prompt, asked, result in ((prompts[0], params[0], results[0]), (prompts[2], params[2], results[2])):
+        assert len(result.logprobs) == len(result.tokens) == len(result.top_logprobs)
+        logits = helpers.plain_logits(folder, list(prompt) + result.tokens[:-1])
+        for index, token in enumerate(result.tokens):
+            row = [plain_sampler.f32(float(v)) for v in logits[len(prompt) - 1 + index]]
+            want, want_top = plain_sampler.logprobs(row, token, asked.temperature, asked.logprobs)
+            assert abs(result.logprobs[index] - want) < 2e-4, (index, result.logprobs[index], want)
+            got_top = result.top_logprobs[index]
+            assert [i for i, _ in got_top] == [i for i, _ in want_top]
+            assert all(abs(a - b) < 2e-4 for (_, a), (_, b) in zip(got_top, want_top))
+        if asked.temperature == 0.0:   # the greedy token is the most likely one
+            assert all(top[0][0] == token for top, token in zip(result.top_logprobs, result.tokens))
+    assert engine.pools.manager.audit() == ""

@@ -490,3 +490,53 @@ def test_toy_position_encoding_runs_unfused(dtype):
         _commit(pools, entries)
         done += count
     assert _rel(got, want) < LIMIT[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_the_interleaved_rotary_encoding_is_a_registered_kind(dtype):
+    """Rotary positions with the other pairing (values 2i and 2i + 1 turn together): a registered
+    position encoding the fused endings do not know, so the attention part runs it through the
+    rotation kernel behind the q/k/v product; in portions and token by token against the plain
+    rotation of those pairs."""
+    _pkg()
+    from vipera_rs_b200.config import MIXERS, POSITION_ENCODINGS, PartSpec
+
+    assert "rope_interleaved" in POSITION_ENCODINGS
+    hidden, heads, kv_heads, d, n, theta = 64, 2, 1, 32, 45, 10000.0
+    tensors = _attention_tensors(hidden, heads, kv_heads, d, True, seed=13)
+    params = {"hidden_size": hidden, "num_heads": heads, "num_kv_heads": kv_heads, "head_dim": d, "qkv_bias": True,
+              "window": None, "softmax_scale": 1 / math.sqrt(d),
+              "position": PartSpec("rope_interleaved", {"head_dim": d, "theta": theta, "max_positions": 128})}
+    mixer = MIXERS.find("gqa_attention")(params, "a", tensors, dtype, DEV)
+    torch.manual_seed(3)
+    h = torch.randn(n, hidden).to(dtype)
+    round_to = torch.bfloat16 if dtype == torch.bfloat16 else None
+    rounded = lambda v: v if round_to is None else v.to(round_to).to(v.dtype)  # noqa: E731
+    hd = h.double()
+    project = lambda name: hd @ rounded(tensors[f"a.{name}_proj.weight"].double()).T + tensors[f"a.{name}_proj.bias"].double()  # noqa: E731
+    sin, cos = plain.rope_angles(range(n), d, theta)
+
+    def turn(x):   # pairs (2i, 2i + 1) by the angle of index i
+        even, odd = x[..., 0::2], x[..., 1::2]
+        s, c = sin.double()[:, None, :], cos.double()[:, None, :]
+        out = torch.empty_like(x)
+        out[..., 0::2] = even * c - odd * s
+        out[..., 1::2] = even * s + odd * c
+        return out
+
+    q = rounded(turn(project("q").view(n, heads, d)))
+    k = rounded(turn(project("k").view(n, kv_heads, d)))
+    v = rounded(project("v").view(n, kv_heads, d))
+    want = rounded(plain.attention(q, k, v).reshape(n, heads * d)) @ rounded(tensors["a.o_proj.weight"].double()).T
+    pools, runner = _context(dtype, {0: mixer.cache_request()}, [])
+    got = torch.zeros(n, hidden, dtype=torch.float64)
+    done = 0
+    for count in (17, 2, 1, 1, 24):
+        entries = [(0, done, count, 1 if done == 0 else 0)]
+        ctx = _step(pools, runner, entries)
+        residual = torch.zeros(count, hidden, device=DEV)
+        mixer.forward(ctx, h[done:done + count].to(DEV), residual, pools.views[0], True)
+        got[done:done + count] = residual.double().cpu()
+        _commit(pools, entries)
+        done += count
+    assert _rel(got, want) < LIMIT[dtype]

@@ -395,6 +395,98 @@ VIPERA_API int vipera_sample(const float* logits, int rows, int vocab, const flo
   return vipera_launch_status();
 }
 
+// ---------------------------------------------------------------------------------------
+// Log-probabilities of drawn tokens (crates/vipera-sampler/src/lib.rs:319-378): over every
+// finite logit (penalties already applied), x = logit / temperature (1 where the row is drawn
+// greedily), logprob(id) = x_id - max - ln(sum exp(x - max)); the drawn token's, and the top_n
+// most likely ids with theirs, best first, ties to the lowest id.  One block per asked row.
+// ---------------------------------------------------------------------------------------
+constexpr int kLogprobThreads = 256;
+
+__global__ void __launch_bounds__(kLogprobThreads)
+logprob_kernel(const float* __restrict__ logits, int vocab, const int* __restrict__ rows, const int* __restrict__ tokens,
+               const float* __restrict__ temperature, int top_n, float* __restrict__ chosen, int* __restrict__ top_ids,
+               float* __restrict__ top_values) {
+  __shared__ float scratch[32];
+  __shared__ float best_value[kLogprobThreads];
+  __shared__ int best_id[kLogprobThreads];
+  const int item = blockIdx.x;
+  const float* row = logits + static_cast<size_t>(rows[item]) * vocab;
+  const float t = temperature[item] > 0.0f ? temperature[item] : 1.0f;
+  float peak = -INFINITY;
+  for (int i = threadIdx.x; i < vocab; i += kLogprobThreads) {
+    const float v = row[i];
+    if (finite(v)) peak = fmaxf(peak, v / t);
+  }
+  peak = block_max(peak, scratch);
+  float mass = 0.0f;
+  for (int i = threadIdx.x; i < vocab; i += kLogprobThreads) {
+    const float v = row[i];
+    if (finite(v)) mass += expf(v / t - peak);
+  }
+  mass = block_sum(mass, scratch);
+  const float log_mass = logf(mass);
+  if (threadIdx.x == 0) {
+    const float v = row[tokens[item]];
+    chosen[item] = finite(peak) && finite(v) ? v / t - peak - log_mass : -INFINITY;
+  }
+  // the top_n: each round takes the best (value, then lowest id) that comes after the one before
+  float last_value = INFINITY;
+  int last_id = -1;
+  for (int k = 0; k < top_n; ++k) {
+    float mine = -INFINITY;
+    int mine_id = -1;
+    for (int i = threadIdx.x; i < vocab; i += kLogprobThreads) {
+      const float v = row[i];
+      if (!finite(v)) continue;
+      const float x = v / t;
+      const bool after = x < last_value || (x == last_value && i > last_id);
+      if (after && (x > mine || mine_id < 0)) {   // ids rise within a thread, so the first of equals stays
+        mine = x;
+        mine_id = i;
+      }
+    }
+    best_value[threadIdx.x] = mine;
+    best_id[threadIdx.x] = mine_id;
+    __syncthreads();
+    for (int stride = kLogprobThreads / 2; stride > 0; stride >>= 1) {
+      if (threadIdx.x < stride) {
+        const float a = best_value[threadIdx.x], b = best_value[threadIdx.x + stride];
+        const int ia = best_id[threadIdx.x], ib = best_id[threadIdx.x + stride];
+        const bool take_b = ib >= 0 && (ia < 0 || b > a || (b == a && ib < ia));
+        if (take_b) {
+          best_value[threadIdx.x] = b;
+          best_id[threadIdx.x] = ib;
+        }
+      }
+      __syncthreads();
+    }
+    last_value = best_value[0];
+    last_id = best_id[0];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      top_ids[static_cast<size_t>(item) * top_n + k] = last_id;
+      top_values[static_cast<size_t>(item) * top_n + k] = last_id >= 0 ? last_value - peak - log_mass : -INFINITY;
+    }
+    if (last_id < 0) last_value = -INFINITY;   // nothing left: the remaining places stay empty
+  }
+}
+
+// chosen[i] = log-probability of tokens[i] in row rows[i] of `logits` at temperature[i]; with
+// top_n > 0 also the top_n most likely ids of that row and their log-probabilities (-1 and
+// -inf where the row has fewer finite logits).
+VIPERA_API int vipera_logprobs(const float* logits, int vocab, int count, const int* rows, const int* tokens,
+                               const float* temperature, int top_n, float* chosen, int* top_ids, float* top_values,
+                               void* stream) {
+  if (count <= 0) return VIPERA_OK;
+  if (vocab <= 0 || top_n < 0) return VIPERA_BAD_SHAPE;
+  if (!logits || !rows || !tokens || !temperature || !chosen || (top_n > 0 && (!top_ids || !top_values)))
+    return VIPERA_BAD_ARGUMENT;
+  logprob_kernel<<<count, kLogprobThreads, 0, static_cast<cudaStream_t>(stream)>>>(logits, vocab, rows, tokens, temperature,
+                                                                                   top_n, chosen, top_ids, top_values);
+  return vipera_launch_status();
+}
+
 VIPERA_API const char* vipera_sampling_status_text(int status) { return vipera_status_text(status); }
 
 // ---------------------------------------------------------------------------------------

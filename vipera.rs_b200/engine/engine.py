@@ -43,6 +43,11 @@ class Generation:
     # reservation, compute = building and launching the step, sample = drawing and waiting for
     # the tokens, complete = bookkeeping after the step.  A step's time counts for each of its requests.
     stage_micros: Dict[str, int] = field(default_factory=dict)
+    # Where the request asked for them (``SamplingParams.logprobs``): the log-probability of every
+    # generated token under the distribution it was drawn from, and the most likely tokens there
+    # with theirs, best first (crates/vipera-sampler/src/lib.rs:302-378).
+    logprobs: Optional[List[float]] = None
+    top_logprobs: Optional[List[List[tuple]]] = None
 
     def to_json(self) -> str:
         """One line in the shape of the reference's request log (pipeline.rs:234-271)."""
@@ -162,6 +167,7 @@ class Engine:
         self.totals = {"steps": 0, "tokens": 0, "entries": 0, "graph_steps": 0, "steps_with_portions": 0,
                        "stage_micros": {"allocate": 0, "compute": 0, "sample": 0, "complete": 0}}
         self._request_micros: Dict[int, Dict[str, int]] = {}
+        self._logprobs: Dict[int, tuple] = {}   # request -> (top n, temperature, logprobs so far, top lists so far)
         # VIPERA_PROFILE_STEP=1: a line per step on stderr (what ran, how, the host's time by stage),
         # and a line per finished request in the shape of the reference's request log.
         self.profile_steps = os.environ.get("VIPERA_PROFILE_STEP", "0") not in ("", "0")
@@ -184,7 +190,11 @@ class Engine:
         vocab = self.model.spec.vocab_size
         if any(t < 0 or t >= vocab for t in prompt):
             raise InvalidArgumentError(f"prompt holds a token id outside the vocabulary of {vocab}")
+        if params.logprobs is not None and not 0 <= int(params.logprobs) <= 64:
+            raise InvalidArgumentError("logprobs must be between 0 and 64 (the number of most likely tokens reported)")
         self.scheduler.add(int(request_id), prompt, params.to_native(self.default_eos))
+        if params.logprobs is not None:
+            self._logprobs[int(request_id)] = (int(params.logprobs), float(params.temperature), [], [])
         return int(request_id)
 
     def cancel(self, request_id: int) -> None:
@@ -227,6 +237,8 @@ class Engine:
                         self._ahead = self._launch_ahead(plan)
                     # also reads the kernels' status word
                     sampled = self.sampler.collect(drawn, logits, plan, logits_intact=self._ahead is None)
+                    if self._logprobs:
+                        self._record_logprobs(plan, logits, sampled)
                 else:
                     sampled = []
                     torch.cuda.current_stream().synchronize()
@@ -297,6 +309,8 @@ class Engine:
         again, or that belong to requests that ended."""
         if not self.scheduler.plan_ahead(plan, ops.SAMPLER_MAX_TOP_K):
             return None
+        if self._logprobs and any(int(r) in self._logprobs for r in plan.row_requests):
+            return None   # the log-probabilities are read from this step's logits after its tokens
         requests = plan.requests
         positions = plan.starts + 1
         count = len(requests)
@@ -307,6 +321,25 @@ class Engine:
         rows = None if plan.all_greedy else _RowsAhead(plan, self.scheduler.peek_uniforms(plan))
         return _Ahead(requests, positions, logits, self.sampler.launch(logits, rows), rows)
 
+    def _record_logprobs(self, plan, logits: torch.Tensor, sampled) -> None:
+        """For the rows of requests that asked: the log-probability of the token just drawn and
+        the most likely tokens, computed on the device from the step's logits (penalties are
+        already applied to them)."""
+        wanted = [(row, int(request)) for row, request in enumerate(plan.row_requests) if int(request) in self._logprobs]
+        if not wanted:
+            return
+        top_n = max(self._logprobs[request][0] for _, request in wanted)
+        device = logits.device
+        rows = torch.tensor([row for row, _ in wanted], dtype=torch.int32, device=device)
+        tokens = torch.tensor([int(sampled[row]) for row, _ in wanted], dtype=torch.int32, device=device)
+        temperature = torch.tensor([self._logprobs[request][1] for _, request in wanted], dtype=torch.float32, device=device)
+        chosen, top_ids, top_values = ops.logprobs(logits, rows, tokens, temperature, top_n)
+        chosen, top_ids, top_values = chosen.tolist(), top_ids.tolist(), top_values.tolist()
+        for index, (_, request) in enumerate(wanted):
+            count, _, values, tops = self._logprobs[request]
+            values.append(chosen[index])
+            tops.append([(int(i), float(v)) for i, v in zip(top_ids[index][:count], top_values[index][:count]) if i >= 0])
+
     def _collect(self, report: StepReport, outcome: dict) -> None:
         report.tokens.extend((int(r), int(t)) for r, t in outcome["tokens"])
         for item in outcome["finished"]:
@@ -315,6 +348,9 @@ class Engine:
                 prompt_tokens=int(item["prompt_tokens"]), processed_tokens=int(item["processed_tokens"]),
                 preemptions=int(item["preemptions"]), reused_tokens=int(item["reused_tokens"]),
                 stage_micros=self._request_micros.pop(int(item["request"]), {}))
+            asked = self._logprobs.pop(generation.request, None)
+            if asked is not None:
+                generation.logprobs, generation.top_logprobs = asked[2][:len(generation.tokens)], asked[3][:len(generation.tokens)]
             report.finished.append(generation)
             self.generations += 1
             if self.profile_steps:

@@ -90,6 +90,7 @@ class KernelProfile:
         "attention": "attention", "attention_prefill": "attention", "attention_prefill_tc": "attention",
         "attention_decode": "attention",
         "argmax": "sample", "sample": "sample", "apply_penalties": "sample", "feed_tokens": "sample",
+        "logprobs": "sample",
     }
     ORDER = ("proj", "attention", "norm", "rope_kv", "embed", "sample", "other")
 
@@ -342,6 +343,22 @@ def sample(logits: torch.Tensor, *, temperature: torch.Tensor, top_k: torch.Tens
               _gpu(top_p, "top_p", torch.float32), _gpu(min_p, "min_p", torch.float32),
               _gpu(uniform, "uniform", torch.float64), _gpu(tokens, "tokens", torch.int32),
               _gpu(status, "status", torch.int32), _stream()), "sample")
+
+
+def logprobs(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor, temperature: torch.Tensor, top_n: int):
+    """Log-probabilities of ``tokens[i]`` in row ``rows[i]`` of ``logits`` at ``temperature[i]``
+    (0: as 1), and the ``top_n`` most likely ids of each row with theirs.  Returns device tensors
+    (chosen [n], top ids [n, top_n], top values [n, top_n])."""
+    fn = _function("sampling", "vipera_logprobs",
+                   [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void])
+    count = rows.numel()
+    chosen = torch.empty(count, dtype=torch.float32, device=logits.device)
+    top_ids = torch.empty((count, max(top_n, 1)), dtype=torch.int32, device=logits.device)
+    top_values = torch.empty((count, max(top_n, 1)), dtype=torch.float32, device=logits.device)
+    _check(fn(_gpu(logits, "logits", torch.float32), logits.shape[1], count, _gpu(rows, "rows", torch.int32),
+              _gpu(tokens, "tokens", torch.int32), _gpu(temperature, "temperature", torch.float32), int(top_n),
+              chosen.data_ptr(), top_ids.data_ptr(), top_values.data_ptr(), _stream()), "logprobs")
+    return chosen, top_ids[:, :top_n], top_values[:, :top_n]
 
 
 def apply_penalties(logits: torch.Tensor, *, entry_row, entry_id, entry_count, entry_bias,

@@ -1,5 +1,5 @@
 """Parts a decoder is put together from.  Importing this package registers the built-in
-kinds: ``rmsnorm``; ``rope_neox`` and ``none``; ``gqa_attention``; ``swiglu``; ``prenorm``."""
+kinds: ``rmsnorm``; ``rope_neox``, ``rope_interleaved`` and ``none``; ``gqa_attention``; ``swiglu``; ``prenorm``."""
 from . import attention, block, mlp, norm, rotary  # noqa: F401  (registration)
 from .base import (
     FeedForward,

@@ -78,6 +78,13 @@ class RopeNeox(PositionEncoding):
         return self._tables.pair
 
 
+class RopeInterleaved(RopeNeox):
+    """The same angles with the other pairing: values ``(2i, 2i + 1)`` turn together.  No fused
+    ending knows it; the rotation kernel behind the q/k/v product does (so it runs unfused)."""
+
+    style = ops.ROPE_INTERLEAVED
+
+
 class NoPositions(PositionEncoding):
     """Leaves q and k as they are."""
 
@@ -88,4 +95,5 @@ class NoPositions(PositionEncoding):
 
 
 POSITION_ENCODINGS.register("rope_neox", RopeNeox)
+POSITION_ENCODINGS.register("rope_interleaved", RopeInterleaved)
 POSITION_ENCODINGS.register("none", NoPositions)

@@ -21,6 +21,10 @@ class SamplingParams:
     seed: int = 0
     eos_ids: Optional[Sequence[int]] = None  # None: the model configuration's end tokens
     recent_window: int = 128           # tokens the penalties look back over
+    # None: no log-probabilities.  n >= 0: every generated token comes with its log-probability
+    # under the distribution it was drawn from (penalties and temperature applied, no cut), and
+    # with the n most likely tokens and theirs (crates/vipera-sampler/src/lib.rs:302-378).
+    logprobs: Optional[int] = None
 
     def to_native(self, default_eos: Sequence[int] = ()) -> dict:
         return {
