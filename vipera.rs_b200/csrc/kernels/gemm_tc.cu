@@ -148,6 +148,18 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, float* v) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_load_32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_load_16(uint32_t taddr, float* v) {
   uint32_t r[16];
   asm volatile(
@@ -408,65 +420,91 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const int tx = tile % p.tiles_x, ty = tile / p.tiles_x;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
-      mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status);
-      tcgen05_fence_after();
       const int row_in_tile = warp * 32 + lane;
       const int row = tx * kTileX + row_in_tile;
+      // The q/k/v ending's inputs that the host wrote before the step (the token's position, its
+      // cache page, the biases of the tile's columns) are fetched while the products still run;
+      // after them only the rows of the cosine and sine tables are read from memory.
+      int rope_position = 0, rope_page = -1;
+      float* tile_bias = reinterpret_cast<float*>(staging) + (local & 1) * BN;   // two buffers: a warp may be one tile ahead
+      if (!SWAP && BN >= 128 && p.epilogue == EPI_ROPE_CACHE) {
+        if (row < p.tokens) {
+          rope_position = p.positions[row];
+          if (p.write_cache)
+            rope_page = p.block_table[static_cast<size_t>(p.token_entry[row]) * p.table_width + rope_position / p.page_size];
+        }
+        for (int c = row_in_tile; c < BN; c += 128) {
+          const int n = ty * BN + c;
+          tile_bias[c] = (p.bias && n < p.features) ? p.bias[n] : 0.0f;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status);
+      tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(acc * BN);
       if (p.splits == 1) {
         if (!SWAP && BN >= 128 && p.epilogue == EPI_ROPE_CACHE) {
           // The q/k/v product's ending: thread = token; a head's d columns are read as pairs of
-          // 32-column chunks (i, i + d/2), the halves of the rotary pairs.
+          // 32-column chunks (i, i + d/2), the halves of the rotary pairs.  A chunk of the token's
+          // cosines and sines serves every head of the tile, and the next chunk is asked for
+          // before this one is used.
           const int d = p.head_dim, half = d >> 1;
           const int t = row;
           const bool live = t < p.tokens;
-          const int position = live ? p.positions[t] : 0;
-          const float* cos_row = p.cos_table + static_cast<size_t>(position) * half;
-          const float* sin_row = p.sin_table + static_cast<size_t>(position) * half;
+          const int position = rope_position;
+          const bool rotate = p.rope_style == GEMM_ROPE_NEOX;
+          const float4* cos_row = reinterpret_cast<const float4*>(p.cos_table + static_cast<size_t>(position) * half);
+          const float4* sin_row = reinterpret_cast<const float4*>(p.sin_table + static_cast<size_t>(position) * half);
+          float4 cs[8], sn[8];
+          if (rotate && live) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { cs[i] = cos_row[i]; sn[i] = sin_row[i]; }
+          }
 #pragma unroll 1
-          for (int hc = 0; hc < BN; hc += d) {
-            const int n0 = ty * BN + hc;
-            if (n0 >= p.features) break;
-            const int head = n0 / d;
-            const bool is_q = head < p.num_heads;
-            const bool is_v = head >= p.num_heads + p.num_kv_heads;
-            __nv_bfloat16* dst = nullptr;
-            if (live) {
-              if (is_q) {
-                dst = p.q_out + (static_cast<size_t>(t) * p.num_heads + head) * d;
-              } else if (p.write_cache) {
-                const int page = p.block_table[static_cast<size_t>(p.token_entry[t]) * p.table_width + position / p.page_size];
-                if (page >= 0) {
-                  const int kv_head = is_v ? head - p.num_heads - p.num_kv_heads : head - p.num_heads;
-                  dst = (is_v ? p.v_pool : p.k_pool) +
-                        ((static_cast<size_t>(page) * p.page_size + position % p.page_size) * p.num_kv_heads + kv_head) * d;
-                }
-              }
+          for (int i0 = 0; i0 < half; i0 += 32) {
+            float4 cs_next[8], sn_next[8];
+            if (rotate && live && i0 + 32 < half) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) { cs_next[i] = cos_row[(i0 + 32) / 4 + i]; sn_next[i] = sin_row[(i0 + 32) / 4 + i]; }
             }
 #pragma unroll 1
-            for (int i0 = 0; i0 < half; i0 += 32) {
-              float lo[32], hi[32];
-              tmem_load_32(taddr + hc + i0, lo);
-              tmem_load_32(taddr + hc + half + i0, hi);
-              if (dst == nullptr) continue;
-              if (p.bias) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                  lo[i] += p.bias[n0 + i0 + i];
-                  hi[i] += p.bias[n0 + half + i0 + i];
+            for (int hc = 0; hc < BN; hc += d) {
+              const int n0 = ty * BN + hc;
+              if (n0 >= p.features) break;
+              const int head = n0 / d;
+              const bool is_q = head < p.num_heads;
+              const bool is_v = head >= p.num_heads + p.num_kv_heads;
+              __nv_bfloat16* dst = nullptr;
+              if (live) {
+                if (is_q) {
+                  dst = p.q_out + (static_cast<size_t>(t) * p.num_heads + head) * d;
+                } else if (rope_page >= 0) {
+                  const int kv_head = is_v ? head - p.num_heads - p.num_kv_heads : head - p.num_heads;
+                  dst = (is_v ? p.v_pool : p.k_pool) +
+                        ((static_cast<size_t>(rope_page) * p.page_size + position % p.page_size) * p.num_kv_heads + kv_head) * d;
                 }
               }
-              if (!is_v && p.rope_style == GEMM_ROPE_NEOX) {
+              uint32_t lo_bits[32], hi_bits[32];
+              tmem_load_32_nowait(taddr + hc + i0, lo_bits);
+              tmem_load_32_nowait(taddr + hc + half + i0, hi_bits);
+              tmem_load_wait();
+              if (dst == nullptr) continue;
+              float lo[32], hi[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                lo[i] = __uint_as_float(lo_bits[i]) + tile_bias[hc + i0 + i];
+                hi[i] = __uint_as_float(hi_bits[i]) + tile_bias[hc + half + i0 + i];
+              }
+              if (!is_v && rotate) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 4) {
-                  const float4 c4 = *reinterpret_cast<const float4*>(cos_row + i0 + i);
-                  const float4 s4 = *reinterpret_cast<const float4*>(sin_row + i0 + i);
-                  const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+                  const float4 c4 = cs[i >> 2], s4 = sn[i >> 2];
+                  const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
                   for (int u = 0; u < 4; ++u) {
-                    const float a = lo[i + u], b = hi[i + u];
-                    lo[i + u] = a * cs[u] - b * sn[u];
-                    hi[i + u] = a * sn[u] + b * cs[u];
+                    const float x = lo[i + u], y = hi[i + u];
+                    lo[i + u] = x * cv[u] - y * sv[u];
+                    hi[i + u] = x * sv[u] + y * cv[u];
                   }
                 }
               }
@@ -480,6 +518,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 *reinterpret_cast<uint4*>(dst + i0 + i) = packed_lo;
                 *reinterpret_cast<uint4*>(dst + half + i0 + i) = packed_hi;
               }
+            }
+            if (rotate && live && i0 + 32 < half) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) { cs[i] = cs_next[i]; sn[i] = sn_next[i]; }
             }
           }
         } else if (!SWAP && BN >= 128 && p.tma_ending) {
