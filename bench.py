@@ -17,7 +17,11 @@ requests, each with 2,048 tokens of history, and reports on ONE JSON line:
              of the bfloat16 tensor-core peak that its flops amount to
   roofline   bytes the decode step has to read (every weight once, the cache of the live
              requests) over its time, against the measured HBM copy bandwidth
-  points     decode tokens per second at batch 1 and batch 64
+  points     decode tokens per second at batch 1 and batch 64; prefill tokens per second for prompts
+             of 128 and 512 tokens; milliseconds of a step of 8 decode tokens beside a 64-token portion
+  mixed_7b   the Qwen2.5-7B shape under a mixed continuous batch through ``Engine.step()``
+  shape_32b  the Qwen2.5-32B shape: decode at batch 1, 8 and the largest batch that fits, one prefill,
+             and what the memory plan says about a batch of 64
 
 Peaks come from MEASURED_PEAKS.json beside this file when it exists, else from the
 figures measured earlier on the same pool (6.65 TB/s, 1.59 PFLOP/s).  Data are synthetic:
@@ -219,6 +223,58 @@ class DecodeHarness:
     def close(self):
         for r in self.requests:
             self.manager.close(r)
+
+
+def measure_mixed_step(model, decodes, history, portion, repeats, warmup, page_size=16):
+    """One step that carries `decodes` single tokens (each with `history` tokens behind it) and
+    one prompt portion of `portion` tokens, as continuous batching makes them: milliseconds,
+    median of `repeats`, device time of the step function and the device's greedy draw."""
+    import numpy as np
+    import torch
+
+    from vipera_rs_b200.cache import CachePools
+    from vipera_rs_b200.engine import ModelRunner, StepInput
+    from vipera_rs_b200.kernels import ops
+
+    per_request = -(-(history + warmup + repeats + 2) // page_size)
+    pools = CachePools(model.cache_requests, page_size=page_size,
+                       num_pages=decodes * per_request + -(-portion // page_size) + 1, num_state_slots=decodes + 1,
+                       dtype=model.dtype, device=model.device)
+    for pool in pools.pool_tensors:
+        pool.normal_(0.0, 0.5)
+    runner = ModelRunner(model, pools, max_model_len=model.spec.max_position_embeddings)
+    manager = pools.manager
+    for r in range(decodes):
+        manager.open(r)
+        manager.reserve(r, history)
+        manager.commit(r, history)
+    rng = np.random.default_rng(3)
+    drawn = torch.empty(decodes + 1, dtype=torch.int32, device=model.device)
+    times = []
+    for index in range(warmup + repeats):
+        position = history + index
+        for r in range(decodes):
+            manager.reserve(r, position + 1)
+        manager.open(decodes)
+        manager.reserve(decodes, portion)
+        tokens = rng.integers(0, model.spec.vocab_size, size=decodes + portion, dtype=np.int32)
+        step = StepInput(requests=list(range(decodes + 1)), tokens=tokens, counts=[1] * decodes + [portion],
+                         pos0=[position] * decodes + [0], fresh=[0] * decodes + [1],
+                         logit_rows=np.asarray(list(range(decodes)) + [decodes + portion - 1], dtype=np.int32))
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        logits = runner.run(step)
+        ops.argmax(logits, drawn)
+        stop.record()
+        torch.cuda.synchronize()
+        for r in range(decodes):
+            manager.commit(r, position + 1)
+        manager.close(decodes)
+        if index >= warmup:
+            times.append(start.elapsed_time(stop))
+    times.sort()
+    return times[len(times) // 2]
 
 
 def measure_prefill(model, tokens, repeats, warmup, page_size=16):
@@ -511,6 +567,13 @@ def main():
             points[f"decode_b{batch}"] = round(batch * 1000.0 / ms, 1)
             del other
             release_memory()
+        # steps as continuous batching makes them: short prompts whole, and a portion beside decodes
+        for tokens in (128, 512):
+            ms = measure_prefill(model, tokens, repeats=5, warmup=3, page_size=args.page_size)
+            points[f"prefill_{tokens}"] = round(tokens * 1000.0 / ms, 1)
+        points["step_8_decodes_and_64_token_portion_ms"] = round(
+            measure_mixed_step(model, 8, args.history, 64, repeats=9, warmup=4, page_size=args.page_size), 4)
+        release_memory()
 
     prefill_tokens = args.prefill_tokens
     prefill_ms = measure_prefill(model, prefill_tokens, repeats=5, warmup=3, page_size=args.page_size)
