@@ -43,7 +43,7 @@ def test_greedy_generation_tiny_a(dtype):
     stats = engine.stats()
     # only the pages kept for requests that begin the same way are still in use
     assert stats["kv_used_pages"] == stats["kv_kept_pages"] == 6 and stats["sequences"] == 0
-    assert engine.pools.manager.audit() == ""
+    assert engine.pools.audit() == ""
 
 
 def test_batched_equals_alone_and_seed_replays():
@@ -63,7 +63,7 @@ def test_batched_equals_alone_and_seed_replays():
     assert again.tokens == together[0].tokens
     other = engine.generate(prompts[:1], SamplingParams(max_new_tokens=24, temperature=0.8, seed=4321))[0]
     assert other.tokens != together[0].tokens
-    assert engine.pools.manager.audit() == ""
+    assert engine.pools.audit() == ""
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -81,7 +81,7 @@ def test_few_pages_preempt_and_recompute(dtype):
     for prompt, result in zip(prompts, results):
         assert len(result.tokens) == 40
         _check_greedy(folder, prompt, result.tokens, dtype)
-    assert engine.pools.manager.audit() == ""
+    assert engine.pools.audit() == ""
     assert engine.stats()["kv_used_pages"] == engine.stats()["kv_kept_pages"]   # nothing but pages kept for reuse
     assert sum(r.reused_tokens for r in results if r.preemptions) > 0             # who was put back found its pages
 
@@ -128,7 +128,7 @@ def test_temperature_sampling_is_the_plain_samplers_on_the_plain_logits():
             row = [plain_sampler.f32(float(v)) for v in logits[len(prompt) - 1 + index]]
             want = plain_sampler.temperature(row, 0.8, 40, 0.95, 0.05, rng.next_f64())
             assert token == want, f"prompt of {len(prompt)}: token {index} is {token}, the plain sampler draws {want}"
-    assert engine.pools.manager.audit() == ""
+    assert engine.pools.audit() == ""
 
 
 def test_sampling_options_through_the_entry_point():
@@ -230,7 +230,7 @@ def test_steps_launched_ahead_change_no_token(dtype):
     drawn_plain = plain_engine.generate(prompts, sampling)
     assert [g.tokens for g in drawn_ahead] == [g.tokens for g in drawn_plain]
     assert ahead_engine.steps_ahead > before
-    assert ahead_engine.pools.manager.audit() == "" and plain_engine.pools.manager.audit() == ""
+    assert ahead_engine.pools.audit() == "" and plain_engine.pools.audit() == ""
     stats = ahead_engine.stats()
     assert stats["sequences"] == 0 and stats["kv_used_pages"] == stats["kv_kept_pages"]
 
@@ -304,4 +304,4 @@ def test_logprobs_of_the_drawn_tokens_and_the_most_likely_ones():
             assert all(abs(a - b) < 2e-4 for (_, a), (_, b) in zip(got_top, want_top))
         if asked.temperature == 0.0:   # the greedy token is the most likely one
             assert all(top[0][0] == token for top, token in zip(result.top_logprobs, result.tokens))
-    assert engine.pools.manager.audit() == ""
+    assert engine.pools.audit() == ""

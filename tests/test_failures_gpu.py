@@ -59,7 +59,7 @@ def test_a_failing_step_ends_only_its_own_requests(kind):
     assert set(finished) == {ids[2]}                      # the request that waited was untouched ...
     assert finished[ids[2]].finish == "length" and len(finished[ids[2]].tokens) == 6
     _check_greedy(folder, prompts[2], finished[ids[2]].tokens, "float32")   # ... and its tokens are right
-    assert engine.pools.manager.audit() == "" and engine.stats()["sequences"] == 0
+    assert engine.pools.audit() == "" and engine.stats()["sequences"] == 0
     assert engine.stats()["running"] == 0 and engine.stats()["waiting"] == 0
     # the engine goes on serving
     again = engine.generate([prompts[0]], SamplingParams(max_new_tokens=4))[0]
@@ -82,7 +82,7 @@ def test_a_refused_prompt_leaves_no_request_behind():
     result = engine.generate([good], SamplingParams(max_new_tokens=4))[0]
     assert len(result.tokens) == 4
     assert engine.stats()["steps"] - steps_before <= 5    # nothing left over was run first
-    assert engine.pools.manager.audit() == ""
+    assert engine.pools.audit() == ""
 
 
 def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
@@ -140,6 +140,6 @@ def test_a_wait_that_runs_out_under_the_engine_fails_that_step_only():
         engine.step()
     engine.runner.run = real_run
     assert engine.failed == 1 and not engine.has_work()
-    assert engine.pools.manager.audit() == ""
+    assert engine.pools.audit() == ""
     result = engine.generate([prompt], SamplingParams(max_new_tokens=5))[0]
     _check_greedy(folder, prompt, result.tokens, "bfloat16")

@@ -319,7 +319,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
         for index, token in enumerate(result.tokens):
             row = logits[len(prompt) - 1 + index]
             assert row.max() - row[token] <= 1e-4 * np.abs(row).max()
-    assert engine.pools.manager.audit() == "" and engine.stats()["sequences"] == 0
+    assert engine.pools.audit() == "" and engine.stats()["sequences"] == 0
 
 
 def _plain_toy_routed(folder, tokens):
@@ -540,3 +540,22 @@ def test_the_interleaved_rotary_encoding_is_a_registered_kind(dtype):
         _commit(pools, entries)
         done += count
     assert _rel(got, want) < LIMIT[dtype]
+
+
+def test_guard_regions_beside_the_pools_show_a_stray_write():
+    """Every pool lies between two guard regions; the audit the tests end with reads them."""
+    _pkg()
+    from vipera_rs_b200.parts import PagedKV
+
+    pools, _ = _context(torch.bfloat16, {0: PagedKV(2, 64, None), 1: PagedKV(1, 128, 40)}, [])
+    assert len(pools.pool_tensors) == 2 and pools.audit() == "" and pools.guards_intact()
+    pools.poison()
+    assert pools.audit() == ""                      # filling every page touches no guard
+    pools.pool_tensors[1].view(-1)[-1:].fill_(3.0)  # the last value of a pool is still the pool's
+    assert pools.audit() == ""
+    end = pools._guards[3]
+    saved = end[:1].clone()
+    end[:1].fill_(3.0)                              # one value past the end of the second pool
+    assert "guard" in pools.audit()
+    end[:1].copy_(saved)
+    assert pools.audit() == ""

@@ -66,7 +66,7 @@ def test_many_requests_decode_at_once(count, dtype):
     _check_all_greedy(folder, prompts, results, dtype, 14)
     stats = engine.stats()
     assert stats["entries_per_step"] > count / 2 and stats["graph_steps"] >= 10
-    assert engine.pools.manager.audit() == ""
+    assert engine.pools.audit() == ""
 
 
 def test_forty_requests_on_the_benchmarks_layer_sizes():
@@ -81,7 +81,7 @@ def test_forty_requests_on_the_benchmarks_layer_sizes():
     engine = Engine(folder, dtype="bfloat16", page_size=16, ctx=48, max_num_seqs=40, max_tokens_per_step=1024)
     results = engine.generate(prompts, SamplingParams(max_new_tokens=6))
     _check_all_greedy(folder, prompts, results, "bfloat16", 6)
-    assert engine.pools.manager.audit() == ""
+    assert engine.pools.audit() == ""
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

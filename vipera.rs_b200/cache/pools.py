@@ -24,6 +24,9 @@ from ..errors import InvalidArgumentError
 from ..parts.base import FixedState, PagedKV, PagedKVView, StateView
 
 
+GUARD_WORD = 0x5A5A   # fits 16 bits: the guard regions are viewed as integers of the element's width
+
+
 @dataclass
 class CacheGroup:
     num_kv_heads: int
@@ -81,9 +84,21 @@ class CachePools:
         # One page beyond those the manager hands out, per group: the scratch page.  No request
         # ever holds it; tokens that pad a captured step to its size class write there.
         self.scratch_pages: List[int] = list(self.num_pages)
+        # Each pool lies between two guard regions of one page each, filled with a fixed word that
+        # no kernel ever writes: `guards_intact()` (the tests call it after they ran) shows a write
+        # that went past either end of a pool.
+        self._guards: List[torch.Tensor] = []
         for index, (group, pages) in enumerate(zip(self.groups, self.num_pages)):
-            pool = torch.zeros((len(group.slots), 2, pages + 1, self.page_size, group.num_kv_heads, group.head_dim),
-                               dtype=dtype, device=device)
+            shape = (len(group.slots), 2, pages + 1, self.page_size, group.num_kv_heads, group.head_dim)
+            count = 1
+            for extent in shape:
+                count *= extent
+            guard = self.page_size * group.num_kv_heads * group.head_dim
+            storage = torch.zeros(count + 2 * guard, dtype=dtype, device=device)
+            storage[:guard].view(torch.int16 if storage.element_size() == 2 else torch.int32).fill_(GUARD_WORD)
+            storage[guard + count:].view(torch.int16 if storage.element_size() == 2 else torch.int32).fill_(GUARD_WORD)
+            self._guards.extend([storage[:guard], storage[guard + count:]])
+            pool = storage[guard:guard + count].view(shape)
             self.pool_tensors.append(pool)
             for position, slot in enumerate(group.slots):
                 self.views[slot] = PagedKVView(index, pool[position, 0], pool[position, 1], self.page_size,
@@ -91,6 +106,22 @@ class CachePools:
         for slot, request in self.states.items():
             data = torch.zeros((int(num_state_slots), *request.shape), dtype=request.dtype, device=device)
             self.views[slot] = StateView(data)
+
+    def guards_intact(self) -> bool:
+        """Whether the guard regions in front of and behind every pool still hold their word."""
+        for guard in self._guards:
+            words = guard.view(torch.int16 if guard.element_size() == 2 else torch.int32)
+            if not bool((words == GUARD_WORD).all()):
+                return False
+        return True
+
+    def audit(self) -> str:
+        """"" when the manager's books are sound (no page lost, held twice or freed twice) and
+        the guard regions are intact; else what is wrong."""
+        problem = self.manager.audit()
+        if not problem and not self.guards_intact():
+            problem = "a guard region beside a cache pool was written"
+        return problem
 
     def bytes(self) -> int:
         total = sum(p.numel() * p.element_size() for p in self.pool_tensors)
