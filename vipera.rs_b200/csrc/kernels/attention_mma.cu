@@ -343,7 +343,16 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
   const int first_visible = window > 0 ? max(0, position - window + 1) : 0;
   const int first = (first_visible / 32 * 32) / chunk;
   const int last = min(slices - 1, position / chunk);
-  // all (max, sum) pairs at once, then the weights of the splits (at most 128 splits)
+  // Everything is asked for at once: this thread's column of every split's partial output (up to
+  // kHeld of them stay in registers) beside all (max, sum) pairs, so that the combine costs one
+  // trip to memory and not one per few splits; then the weights of the splits (at most 128 splits).
+  constexpr int kHeld = 32;
+  const int count = last - first + 1;
+  float held[kHeld];
+  if (count <= kHeld) {
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) held[i] = i < count ? values[static_cast<size_t>(first + i) * D] : 0.0f;
+  }
   float mine = -INFINITY;
   for (int s = first + threadIdx.x; s <= last; s += D) {
     maxima[s] = ml[2 * s];
@@ -352,12 +361,24 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial_ml, c
   __syncthreads();
   for (int s = first; s <= last; ++s) mine = fmaxf(mine, maxima[s]);
   float total = 0.0f, value = 0.0f;
+  if (count <= kHeld) {
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) {
+      if (i < count) {
+        const float m = maxima[first + i];
+        const float w = m == -INFINITY ? 0.0f : exp2f(m - mine);  // a split that saw no key
+        total += sums[first + i] * w;
+        value += held[i] * w;
+      }
+    }
+  } else {
 #pragma unroll 8
-  for (int s = first; s <= last; ++s) {
-    const float m = maxima[s];
-    const float w = m == -INFINITY ? 0.0f : exp2f(m - mine);  // a split that saw no key
-    total += sums[s] * w;
-    value += values[static_cast<size_t>(s) * D] * w;
+    for (int s = first; s <= last; ++s) {
+      const float m = maxima[s];
+      const float w = m == -INFINITY ? 0.0f : exp2f(m - mine);
+      total += sums[s] * w;
+      value += values[static_cast<size_t>(s) * D] * w;
+    }
   }
   out[out_row * D + threadIdx.x] = __float2bfloat16_rn(value / total);
 }

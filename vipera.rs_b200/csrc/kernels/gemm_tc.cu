@@ -684,17 +684,18 @@ splitk_finish_kernel(const GemmParams p) {
     const size_t tile = static_cast<size_t>(ty) * p.tiles_x + tx;
     const float* src = p.scratch + ((tile * p.splits) * BN + col) * kTileX + row;
     const size_t step = static_cast<size_t>(BN) * kTileX;
+    // sixteen loads in flight at a time (a decode step's products have at most about that many
+    // splits, so the sum costs one trip to L2, not one per few splits); the additions stay in the
+    // order of the splits
     float sum = 0.0f;
-    int s = 0;
-    for (; s + 4 <= p.splits; s += 4) {
-      const float a = __ldcg(src + (s + 0) * step), b = __ldcg(src + (s + 1) * step);
-      const float c = __ldcg(src + (s + 2) * step), d = __ldcg(src + (s + 3) * step);
-      sum += a;
-      sum += b;
-      sum += c;
-      sum += d;
+    for (int s0 = 0; s0 < p.splits; s0 += 16) {
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = s0 + i < p.splits ? __ldcg(src + (s0 + i) * step) : 0.0f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (s0 + i < p.splits) sum += v[i];
     }
-    for (; s < p.splits; ++s) sum += __ldcg(src + s * step);
     return sum;
   };
   if (swiglu) {
