@@ -126,6 +126,59 @@ def test_gemm_tc_repeats_exactly():
     assert _rel(alone, outs[0][3:4]) < 1e-5
 
 
+EVEN_SHAPES = [(300, 672, 1096), (260, 1003 // 4 * 4, 4000), (1100, 1536, 520), (2048, 1536, 8960), (513, 260, 3000),
+               (192, 128, 2048)]
+
+
+@pytest.mark.parametrize("m,n,k", EVEN_SHAPES)
+@pytest.mark.parametrize("epilogue", [0, 1])
+def test_gemm_tc_even_shares(m, n, k, epilogue):
+    """The product with one equal share of all k-blocks per block (a tile's partial sums pass from
+    block to block): forced wherever the ending allows it, checked to be the form that ran, twice
+    for the same bits, and with the flags down again afterwards (a second product follows)."""
+    ops = _ops()
+    before = ops.gemm_tc_even_shares(2)
+    try:
+        plan = ops.gemm_tc_plan(m, n, k, epilogue, True)
+        assert plan["even_shares"] and not plan["swapped"] and plan["blocks"] >= 2, plan
+        torch.manual_seed(m + n + k)
+        a = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+        w = (torch.randn(n, k, device=DEV) * 0.1).bfloat16()
+        bias = torch.randn(n, device=DEV)
+        resid0 = torch.randn(m, n, device=DEV)
+        outs = []
+        for _ in range(3):
+            if epilogue == 0:
+                out = torch.full((m, n), float("nan"), device=DEV)
+                ops.gemm_tc(a, w, epilogue=0, bias=bias, out=out)
+            else:
+                out = resid0.clone()
+                ops.gemm_tc(a, w, epilogue=1, resid=out)
+            outs.append(out)
+        torch.cuda.synchronize()
+        ops.check_kernel_status(a.device)
+        want = _gemm_reference(a, w, epilogue, bias, resid0)
+        assert _rel(outs[0], want) < 2e-5
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    finally:
+        ops.gemm_tc_even_shares(before)
+
+
+def test_gemm_tc_takes_even_shares_where_whole_tiles_leave_a_wave_half_empty():
+    ops = _ops()
+    before = ops.gemm_tc_even_shares(1)
+    try:
+        # 2,048 tokens through a [1536, 8960] matrix: 96 tiles of 256 columns or 128 of 192 on 148 SMs
+        plan = ops.gemm_tc_plan(2048, 1536, 8960, 1, True)
+        if ops.sm_count(torch.device(DEV)) == 148:
+            assert plan["even_shares"] and plan["tile"] == 256 and plan["blocks"] == 148, plan
+        # the same sizes where the ending cannot take partial sums
+        assert not ops.gemm_tc_plan(2048, 1536, 8960, 1, False)["even_shares"]
+    finally:
+        ops.gemm_tc_even_shares(before)
+    assert not ops.gemm_tc_plan(2048, 1536, 8960, 1, True)["even_shares"] or before != 0
+
+
 # ---------------------------------------------------------------------------------------
 def _paged_case(entries, heads, kv_heads, d, page, dtype, seed, window=0, lengths=None, counts=None, shuffle=True):
     """Random q and a paged cache whose pages are handed out in a shuffled order (or, with

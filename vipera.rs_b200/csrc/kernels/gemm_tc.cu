@@ -22,10 +22,19 @@
 // records an error code, stops waiting anywhere, drains and frees its tensor memory, and
 // the launcher's caller finds the code in the status word.
 //
+// Even shares (tokens on the 128-row side, endings through TMA): where whole tiles would leave
+// SMs idle in the last wave, the run of all k-blocks of all tiles is cut into one equal share
+// per block instead.  A block whose share starts inside a tile writes that tile's partial sums
+// to a slot of its own and raises a flag; the block whose share holds the tile's first k-block
+// adds the partial sums of the blocks behind it, in their order, before the ending.  A tile's
+// later parts are the first work of their blocks and its first part is the last work of its
+// block, so the flags are long up when they are looked at; the wait is bounded all the same.
+//
 // Endings (as in gemm_simt.cu): STORE (+bias) as float32 or bfloat16, RESIDUAL (add into
 // the 32-bit residual stream), SWIGLU over gate and up rows interleaved in groups of 16.
 #include <cuda.h>
 
+#include <algorithm>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -52,8 +61,10 @@ struct GemmParams {
   void* out;
   float* resid;
   int tma_ending;    // 1: the ending goes through shared memory and TMA stores (map_out)
-  float* scratch;    // split partials: [item][BN][128] floats
+  float* scratch;    // split partials: [item][BN][128] floats; even shares: [block][BN][128]
   int* status;       // device word: 0, or an error code
+  int even_shares;   // 1: every block takes an equal share of all k-blocks of all tiles
+  int* share_flags;  // even shares: [blocks], 0 between launches
   // EPI_ROPE_CACHE: the columns are the q, k and v heads of a step's tokens; the ending adds the
   // bias, turns the rotary pairs of q and k, and writes q to q_out and k and v into their pages
   int num_heads, num_kv_heads, head_dim, rope_style, write_cache;
@@ -290,6 +301,54 @@ __device__ __forceinline__ void finish_chunk(const GemmParams& p, const float* v
   }
 }
 
+// The work of one block, piece by piece: whole tiles or splits of tiles dealt round robin, or
+// (even shares) the pieces of its run of k-blocks.  All three roles of a block walk it alike.
+constexpr int kShareSnap = 2;   // a share boundary this close to a tile's edge moves onto it
+__device__ __forceinline__ long share_begin(const GemmParams& p, int block, int blocks) {
+  const long all = static_cast<long>(p.tiles_x) * p.tiles_y * p.num_k_blocks;
+  if (block >= blocks) return all;
+  long at = all * block / blocks;
+  const int inside = static_cast<int>(at % p.num_k_blocks);
+  if (inside <= kShareSnap) at -= inside;
+  else if (p.num_k_blocks - inside <= kShareSnap) at += p.num_k_blocks - inside;
+  return at;
+}
+struct Piece {
+  int tile, kb_begin, kb_end;
+  int slot;      // where a partial sum of this piece goes in the scratch
+};
+struct WorkLoop {
+  const GemmParams& p;
+  int item;
+  long at, end;
+  __device__ __forceinline__ explicit WorkLoop(const GemmParams& params) : p(params), item(blockIdx.x), at(0), end(0) {
+    if (p.even_shares) {
+      at = share_begin(p, blockIdx.x, gridDim.x);
+      end = share_begin(p, blockIdx.x + 1, gridDim.x);
+    }
+  }
+  __device__ __forceinline__ bool next(Piece& piece) {
+    if (p.even_shares) {
+      if (at >= end) return false;
+      piece.tile = static_cast<int>(at / p.num_k_blocks);
+      piece.kb_begin = static_cast<int>(at % p.num_k_blocks);
+      const long left = end - at;
+      piece.kb_end = left < p.num_k_blocks - piece.kb_begin ? piece.kb_begin + static_cast<int>(left) : p.num_k_blocks;
+      piece.slot = blockIdx.x;
+      at += piece.kb_end - piece.kb_begin;
+      return true;
+    }
+    if (item >= p.tiles_x * p.tiles_y * p.splits) return false;
+    const int split = item % p.splits;
+    piece.tile = item / p.splits;
+    piece.kb_begin = split * p.k_blocks_per_split;
+    piece.kb_end = min(p.num_k_blocks, piece.kb_begin + p.k_blocks_per_split);
+    piece.slot = item;
+    item += gridDim.x;
+    return true;
+  }
+};
+
 template <int BN, bool SWAP>
 __global__ void __launch_bounds__(kThreads, (BN >= 128 || VIPERA_SMALL_BUDGET > 110 ? 1 : 2))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
@@ -327,22 +386,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_items = p.tiles_x * p.tiles_y * p.splits;
-
   if (warp == 4) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       // The weight operand depends on no earlier kernel: its tiles for the first stages are
       // on their way before this kernel waits for the kernels ahead of it.
       int prefetched = 0;
-      if (static_cast<int>(blockIdx.x) < total_items) {
-        const int item = blockIdx.x;
-        const int split = item % p.splits;
-        const int tile = item / p.splits;
-        const int tx = tile % p.tiles_x, ty = tile / p.tiles_x;
-        const int kb_begin = split * p.k_blocks_per_split;
-        const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
-        prefetched = min(kStages, kb_end - kb_begin);
+      Piece first;
+      if (WorkLoop(p).next(first)) {
+        const int tx = first.tile % p.tiles_x, ty = first.tile / p.tiles_x;
+        const int kb_begin = first.kb_begin;
+        prefetched = min(kStages, first.kb_end - first.kb_begin);
         for (int i = 0; i < prefetched; ++i) {
           uint8_t* x_tile = tiles + i * Config::kStageBytes;
           uint8_t* y_tile = x_tile + kTileX * kBlockK * 2;
@@ -354,13 +408,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       pdl_wait();
       int stage = 0, issued = 0;
       uint32_t phase = 0;
-      for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-        const int split = item % p.splits;
-        const int tile = item / p.splits;
-        const int tx = tile % p.tiles_x, ty = tile / p.tiles_x;
-        const int kb_begin = split * p.k_blocks_per_split;
-        const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
-        for (int kb = kb_begin; kb < kb_end; ++kb, ++issued) {
+      WorkLoop work(p);
+      Piece piece;
+      while (work.next(piece)) {
+        const int tx = piece.tile % p.tiles_x, ty = piece.tile / p.tiles_x;
+        for (int kb = piece.kb_begin; kb < piece.kb_end; ++kb, ++issued) {
           uint8_t* x_tile = tiles + stage * Config::kStageBytes;
           uint8_t* y_tile = x_tile + kTileX * kBlockK * 2;
           if (issued < prefetched) {
@@ -383,10 +435,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
-      for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++local) {
-        const int split = item % p.splits;
-        const int kb_begin = split * p.k_blocks_per_split;
-        const int kb_end = min(p.num_k_blocks, kb_begin + p.k_blocks_per_split);
+      WorkLoop work(p);
+      Piece piece;
+      for (; work.next(piece); ++local) {
+        const int kb_begin = piece.kb_begin, kb_end = piece.kb_end;
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
         mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status);
@@ -415,10 +467,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // ---------------- epilogue warps 0..3 ----------------
     pdl_wait();  // outputs, the residual stream, and the scratch belong to earlier kernels until now
     int local = 0;
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++local) {
-      const int tile = item / p.splits;
+    WorkLoop work(p);
+    Piece piece;
+    for (; work.next(piece); ++local) {
+      const int tile = piece.tile;
       const int tx = tile % p.tiles_x, ty = tile / p.tiles_x;
       const int acc = local & 1;
+      // Even shares: a piece that starts inside a tile is a partial sum for another block; the
+      // piece with the tile's first k-block that does not reach its last one waits for the blocks
+      // behind this one whose shares start inside the same tile.
+      const bool whole = piece.kb_begin == 0 && piece.kb_end == p.num_k_blocks;
+      const bool partial = p.splits > 1 || (p.even_shares && piece.kb_begin > 0);
+      int helpers = 0;
+      if (p.even_shares && !whole && !partial) {
+        const long tile_end = static_cast<long>(tile + 1) * p.num_k_blocks;
+        while (share_begin(p, blockIdx.x + 1 + helpers, gridDim.x) < tile_end) ++helpers;
+      }
       const uint32_t acc_phase = (local >> 1) & 1u;
       const int row_in_tile = warp * 32 + lane;
       const int row = tx * kTileX + row_in_tile;
@@ -442,7 +506,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status);
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(acc * BN);
-      if (p.splits == 1) {
+      if (helpers > 0) {
+        if (warp == 0 && lane == 0) {
+          for (int h = 0; h < helpers; ++h) {
+            int* flag = p.share_flags + blockIdx.x + 1 + h;
+            uint32_t spin = 0;
+            int up = 0;
+            for (; spin < kWaitLimit; ++spin) {
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(up) : "l"(flag) : "memory");
+              if (up != 0) break;
+              if ((spin & 1023u) == 1023u && *abort_flag) break;
+              __nanosleep(64);
+            }
+            if (up == 0 && !*abort_flag) {
+              *abort_flag = 1;
+              atomicExch(p.status, GEMM_TC_WAIT_EXPIRED);
+            }
+            *flag = 0;   // down again for the next launch; its slot is not written again in this one
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      if (!partial) {
         if (!SWAP && BN >= 128 && p.epilogue == EPI_ROPE_CACHE) {
           // The q/k/v product's ending: thread = token; a head's d columns are read as pairs of
           // 32-column chunks (i, i + d/2), the halves of the rotary pairs.  A chunk of the token's
@@ -579,6 +664,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               uint8_t* buffer = mine + use * 4096;
               float v[32];
               tmem_load_32(taddr + c, v);
+              for (int h = 0; h < helpers; ++h) {
+                const float* part = p.scratch + (static_cast<size_t>(blockIdx.x + 1 + h) * BN + c) * kTileX + row_in_tile;
+                float more[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) more[i] = __ldcg(part + i * kTileX);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] += more[i];
+              }
               if (p.epilogue == EPI_STORE && p.bias) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
@@ -620,8 +713,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
       } else {
-        // split partial: scratch[item][column][row_in_tile]
-        float* part = p.scratch + static_cast<size_t>(item) * BN * kTileX;
+        // partial sums: scratch[slot][column][row_in_tile]
+        float* part = p.scratch + static_cast<size_t>(piece.slot) * BN * kTileX;
         if (BN >= 32) {
 #pragma unroll 1
           for (int c = 0; c < BN; c += 32) {
@@ -639,6 +732,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (p.even_shares) {
+          // the flag goes up when all four warps' partial sums can be seen by the other blocks
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (warp == 0 && lane == 0) {
+            int* flag = p.share_flags + piece.slot;
+            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(1) : "memory");
+          }
+        }
       }
     }
   }
@@ -715,6 +817,11 @@ splitk_finish_kernel(const GemmParams p) {
     else static_cast<float*>(p.out)[at] = biased;
   }
 }
+
+// Even shares: one flag per block, up while that block's partial sum waits to be taken.  All
+// are 0 between launches (the taker lowers them); products run one after another on a stream.
+constexpr int kMostShares = 1024;
+__device__ int share_flags_store[kMostShares];
 
 // ---------------------------------------------------------------------------------------
 // host side
@@ -809,6 +916,8 @@ static int make_out_map(CUtensorMap* map, void* base, int rows, int cols, bool b
 
 struct GemmPlan {
   bool swap;
+  bool even_shares;   // one equal share of all k-blocks per block instead of whole tiles
+  int blocks;         // even shares: the grid
   int bn;
   int tiles_x, tiles_y, splits, k_blocks_per_split, num_k_blocks;
   size_t scratch_floats;
@@ -825,7 +934,20 @@ static int sm_count() {
   return count;
 }
 
-static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE) {
+// 0: never; 1: where the estimate favours them; 2: wherever the ending allows them (tests).
+// Off unless asked for: blocks with even shares drift apart along K, and tiles read by several
+// blocks at different times cost more lookups in L2 than tiles read in step (2,048 tokens through
+// a [1536, 8960] matrix: 68 us against 65 with whole tiles of 192 columns; ahead only from about
+// 4,096 tokens on: 110 us against 124).
+static int& even_shares_mode() {
+  static int mode = std::getenv("VIPERA_GEMM_EVEN_SHARES") ? std::atoi(std::getenv("VIPERA_GEMM_EVEN_SHARES")) : 0;
+  return mode;
+}
+constexpr int kShareLeast = 8;      // even shares: k-blocks a block must get at least
+constexpr double kShareCost = 4.0;  // what a block's partial sum costs (written, read back, added), in k-blocks of its time
+
+// `even_ok`: the ending can take partial sums of other blocks (the TMA ending of STORE and RESIDUAL).
+static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE, bool even_ok = false) {
   GemmPlan plan{};
   plan.num_k_blocks = (K + kBlockK - 1) / kBlockK;
   // Tokens go on the 128-row side from 192 tokens on.  A matrix wide enough to give half
@@ -852,6 +974,25 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
       efficiency *= bn == 256 ? 1.0 : bn == 192 ? 0.95 : 0.85;  // narrower tiles run below the wide tile's rate
       if (efficiency > best) { best = efficiency; plan.bn = bn; }
     }
+    // Against that, even shares of all k-blocks with the widest tile: no idle SMs in a last
+    // wave, but every block pays for one partial sum.
+    const int even_mode = even_shares_mode();
+    if (even_ok && even_mode > 0 && N >= 128) {
+      const int bn = N >= 256 ? 256 : 128;
+      const long tiles = static_cast<long>(plan.tiles_x) * ((N + bn - 1) / bn);
+      const long all = tiles * plan.num_k_blocks;
+      const int blocks = static_cast<int>(std::min<long>(sms, all / kShareLeast));
+      if (blocks >= 2 && tiles % blocks != 0) {
+        double efficiency = static_cast<double>(plan.tiles_x) * N / (static_cast<double>(tiles) * bn);
+        efficiency *= static_cast<double>(all) / (static_cast<double>(all) + kShareCost * blocks);
+        efficiency *= (bn == 256 ? 1.0 : 0.85) * static_cast<double>(blocks) / sms;
+        if (efficiency > best + 0.03 || even_mode > 1) {
+          plan.even_shares = true;
+          plan.blocks = blocks;
+          plan.bn = bn;
+        }
+      }
+    }
     plan.tiles_y = (N + plan.bn - 1) / plan.bn;
     plan.splits = 1;
     plan.k_blocks_per_split = plan.num_k_blocks;
@@ -860,7 +1001,7 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
     // form does: its tiles of 128 features x 256 tokens are cut along K until every SM has one.
     // (The q/k/v ending exists in this form only.)
     static const bool narrow_swaps = std::getenv("VIPERA_GEMM_NARROW_NONSWAP") == nullptr;
-    if (narrow_swaps && epilogue != EPI_ROPE_CACHE && 4 * plan.tiles_x * plan.tiles_y < 3 * sms) plan.swap = true;
+    if (narrow_swaps && !plan.even_shares && epilogue != EPI_ROPE_CACHE && 4 * plan.tiles_x * plan.tiles_y < 3 * sms) plan.swap = true;
   }
   if (plan.swap) {
     plan.bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
@@ -875,6 +1016,7 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
   }
   plan.scratch_floats = plan.splits > 1
       ? static_cast<size_t>(plan.tiles_x) * plan.tiles_y * plan.splits * plan.bn * kTileX : 0;
+  if (plan.even_shares) plan.scratch_floats = static_cast<size_t>(plan.blocks) * plan.bn * kTileX;
   return plan;
 }
 
@@ -882,7 +1024,25 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
 // it runs without splits).
 VIPERA_API int vipera_gemm_tc_workspace(int T, int N, int K, size_t* scratch_bytes) {
   const GemmPlan plan = make_plan(T, N, K, sm_count());
-  *scratch_bytes = plan.scratch_floats * sizeof(float);
+  const GemmPlan even = make_plan(T, N, K, sm_count(), EPI_RESIDUAL, true);
+  *scratch_bytes = std::max(plan.scratch_floats, even.scratch_floats) * sizeof(float);
+  return VIPERA_OK;
+}
+
+VIPERA_API int vipera_gemm_tc_even_shares(int mode) {
+  const int before = even_shares_mode();
+  if (mode >= 0) even_shares_mode() = mode;
+  return before;
+}
+
+// The form a product of these sizes takes: {swapped, tile width, splits, even shares, blocks}.
+VIPERA_API int vipera_gemm_tc_plan(int T, int N, int K, int epilogue, int even_ok, int* form) {
+  const GemmPlan plan = make_plan(T, N, K, sm_count(), epilogue, even_ok != 0);
+  form[0] = plan.swap ? 1 : 0;
+  form[1] = plan.bn;
+  form[2] = plan.splits;
+  form[3] = plan.even_shares ? 1 : 0;
+  form[4] = plan.even_shares ? plan.blocks : std::min(sm_count(), plan.tiles_x * plan.tiles_y * plan.splits);
   return VIPERA_OK;
 }
 
@@ -897,7 +1057,7 @@ static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, co
     configured = true;
   }
   int status = vipera_launch(gemm_tc_kernel<BN, SWAP>, grid, kThreads, Config::kSmemBytes, s, map_x, map_y, map_out, p);
-  if (status != VIPERA_OK || p.splits == 1) return status;
+  if (status != VIPERA_OK || p.splits == 1) return status;   // (even shares run with splits == 1)
   const long outputs = static_cast<long>(p.tokens) * (p.epilogue == EPI_SWIGLU ? p.features / 2 : p.features);
   return vipera_launch(splitk_finish_kernel<BN>, dim3(static_cast<unsigned>((outputs + 255) / 256)), dim3(256), 0, s, p);
 }
@@ -917,8 +1077,13 @@ static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilo
     return VIPERA_BAD_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return VIPERA_BAD_ARGUMENT;
   const int sms = sm_count();
-  const GemmPlan plan = make_plan(T, N, K, sms, epilogue);
-  if (plan.splits > 1) {
+  // what the TMA ending of STORE and RESIDUAL needs (the only ending that takes other blocks' partial sums)
+  const bool direct_store = std::getenv("VIPERA_GEMM_DIRECT_STORE") != nullptr;
+  const bool even_ok = !direct_store && N % 4 == 0 && scratch != nullptr &&
+      ((epilogue == EPI_STORE && out_dtype == VIPERA_F32 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) ||
+       (epilogue == EPI_RESIDUAL && (reinterpret_cast<uintptr_t>(resid) & 15) == 0));
+  const GemmPlan plan = make_plan(T, N, K, sms, epilogue, even_ok);
+  if (plan.splits > 1 || plan.even_shares) {
     if (!scratch || scratch_bytes < plan.scratch_floats * sizeof(float)) return VIPERA_BAD_ARGUMENT;
   }
   CUtensorMap map_x, map_y;
@@ -947,13 +1112,20 @@ static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilo
   p.scratch = scratch;
   p.status = status;
   const int items = plan.tiles_x * plan.tiles_y * plan.splits;
-  const int grid = items < sms ? items : sms;
+  const int grid = plan.even_shares ? plan.blocks : items < sms ? items : sms;
+  p.even_shares = plan.even_shares ? 1 : 0;
+  if (plan.even_shares) {
+    if (plan.blocks > kMostShares) return VIPERA_BAD_ARGUMENT;
+    void* flags = nullptr;
+    if (cudaGetSymbolAddress(&flags, share_flags_store) != cudaSuccess) return VIPERA_BAD_ARGUMENT;
+    p.share_flags = static_cast<int*>(flags);
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // The ending goes through TMA stores where the output's rows are whole multiples of 16
   // bytes: float32 [T, N] for STORE and RESIDUAL, bfloat16 [T, N / 2] for SWIGLU.
   CUtensorMap map_out = map_x;  // a valid map where the ending does not use one
   p.tma_ending = 0;
-  if (!plan.swap && std::getenv("VIPERA_GEMM_DIRECT_STORE") == nullptr) {
+  if (!plan.swap && !direct_store) {
     if (epilogue == EPI_SWIGLU && out_dtype == VIPERA_BF16 && (N / 2) % 8 == 0 &&
         (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
       if ((r = make_out_map(&map_out, out, T, N / 2, true)) != VIPERA_OK) return r;
@@ -1068,6 +1240,15 @@ VIPERA_API int vipera_gemm_tc_wait_probe(int* status, int limit, void* stream) {
   if (!status || limit < 1 || limit > (1 << 16)) return VIPERA_BAD_ARGUMENT;
   wait_probe_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(status, static_cast<uint32_t>(limit));
   return vipera_launch_status();
+}
+
+// After a kernel reported a wait that ran out, flags of partial sums nobody took may still be
+// up: this lowers them all (on the stream, after the work already there).
+VIPERA_API int vipera_gemm_tc_reset(void* stream) {
+  void* flags = nullptr;
+  if (cudaGetSymbolAddress(&flags, share_flags_store) != cudaSuccess) return VIPERA_BAD_ARGUMENT;
+  return cudaMemsetAsync(flags, 0, sizeof(int) * kMostShares, static_cast<cudaStream_t>(stream)) == cudaSuccess
+      ? VIPERA_OK : VIPERA_BAD_ARGUMENT;
 }
 
 VIPERA_API const char* vipera_gemm_tc_status_text(int status) { return vipera_status_text(status); }

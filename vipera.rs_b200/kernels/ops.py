@@ -414,6 +414,7 @@ def raise_on_kernel_status(device, code: int) -> None:
     """`code` is the status word as just read: non-zero means a bounded wait ran out."""
     if code:
         _tc_buffers(device, 0)["status"].zero_()
+        _function("gemm_tc", "vipera_gemm_tc_reset", [_c_void])(_stream())
         raise InternalError(f"a tensor-core kernel gave up waiting (code {code}); the step's results are invalid")
 
 
@@ -431,6 +432,45 @@ def gemm_tc_workspace(m: int, n: int, k: int):
             _workspace_sizes.clear()
         size = _workspace_sizes[(m, n, k)] = scratch.value
     return size
+
+
+def _even_ok(n: int, epilogue: int, out) -> bool:
+    return n % 4 == 0 and (epilogue == EPI_RESIDUAL or
+                           (epilogue == EPI_STORE and out is not None and out.dtype == torch.float32))
+
+
+_plans = {}
+
+
+def gemm_tc_plan(m: int, n: int, k: int, epilogue: int = EPI_STORE, even_ok: bool = False):
+    """The form the tensor-core product takes for these sizes: a dict with `swapped`, `tile`,
+    `splits`, `even_shares` (equal shares of all k-blocks per block instead of whole tiles) and
+    `blocks`.  `even_ok`: the ending is one that can take other blocks' partial sums (float32
+    output or the residual stream, rows a multiple of 16 bytes)."""
+    key = (int(m), int(n), int(k), int(epilogue), bool(even_ok), _even_shares_mode[0])
+    plan = _plans.get(key)
+    if plan is None:
+        fn = _function("gemm_tc", "vipera_gemm_tc_plan", [_c_int] * 5 + [ctypes.POINTER(_c_int)])
+        form = (_c_int * 5)()
+        _check(fn(key[0], key[1], key[2], key[3], int(key[4]), form), "gemm_tc_plan", kernels=0)
+        if len(_plans) > 65536:
+            _plans.clear()
+        plan = _plans[key] = {"swapped": bool(form[0]), "tile": form[1], "splits": form[2],
+                              "even_shares": bool(form[3]), "blocks": form[4]}
+    return plan
+
+
+_even_shares_mode = [None]
+
+
+def gemm_tc_even_shares(mode: int) -> int:
+    """Sets when the product takes even shares (0 never, 1 where its estimate favours them, 2
+    wherever the ending allows) and returns the mode before; -1 only asks."""
+    before = _function("gemm_tc", "vipera_gemm_tc_even_shares", [_c_int])(int(mode))
+    if mode >= 0:
+        _even_shares_mode[0] = int(mode)
+        _workspace_sizes.clear()
+    return before
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE,
@@ -455,7 +495,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_STORE,
               dtype_code(out.dtype) if out is not None else F32, _opt(resid, "resid", torch.float32),
               None if scratch is None else scratch.data_ptr(),
               0 if scratch is None else scratch.numel() * 4,
-              state["status"].data_ptr(), _stream()), "gemm_tc", kernels=2 if scratch_bytes else 1)
+              state["status"].data_ptr(), _stream()), "gemm_tc",
+           kernels=2 if scratch_bytes and gemm_tc_plan(m, n, k, epilogue, _even_ok(n, epilogue, out))["splits"] > 1 else 1)
 
 
 class _GemmRope(ctypes.Structure):
