@@ -164,6 +164,54 @@ def test_gemm_tc_even_shares(m, n, k, epilogue):
         ops.gemm_tc_even_shares(before)
 
 
+PAIR_SHAPES = [(256, 256, 128), (300, 704, 520), (777, 1536, 1536), (1000, 4096, 512), (2048, 1536, 2240), (193, 384, 200)]
+
+
+@pytest.mark.parametrize("m,n,k", PAIR_SHAPES)
+@pytest.mark.parametrize("epilogue", [0, 1, 2])
+def test_gemm_tc_pairs(m, n, k, epilogue):
+    """The product on pairs of blocks (clusters of two; each block holds its own 128 tokens and half
+    of the tile's weight rows, one block issues for both): forced wherever the form allows it, and
+    checked to be the form that ran."""
+    ops = _ops()
+    before = ops.gemm_tc_pairs(2)
+    try:
+        plan = ops.gemm_tc_plan(m, n, k, epilogue, epilogue != 2)
+        assert plan["pairs"] and not plan["swapped"], plan
+        torch.manual_seed(m + n + k)
+        a = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+        w = (torch.randn(n, k, device=DEV) * 0.1).bfloat16()
+        bias = torch.randn(n, device=DEV)
+        resid0 = torch.randn(m, n, device=DEV)
+        if epilogue == 0:
+            out = torch.full((m, n), float("nan"), device=DEV)
+            ops.gemm_tc(a, w, epilogue=0, bias=bias, out=out)
+        elif epilogue == 1:
+            out = resid0.clone()
+            ops.gemm_tc(a, w, epilogue=1, resid=out)
+        else:
+            out = torch.full((m, n // 2), float("nan"), device=DEV, dtype=torch.bfloat16)
+            ops.gemm_tc(a, w, epilogue=2, out=out)
+        torch.cuda.synchronize()
+        ops.check_kernel_status(a.device)
+        assert _rel(out, _gemm_reference(a, w, epilogue, bias, resid0)) < (5e-3 if epilogue == 2 else 2e-5)
+    finally:
+        ops.gemm_tc_pairs(before)
+
+
+def test_gemm_tc_takes_pairs_for_long_portions():
+    ops = _ops()
+    if ops.sm_count(torch.device(DEV)) != 148 or ops.gemm_tc_pairs(-1) != 1:
+        pytest.skip("the rule is stated for 148 SMs and the default mode")
+    assert ops.gemm_tc_plan(2048, 17920, 1536, 2, False) == {
+        "swapped": False, "tile": 256, "splits": 1, "even_shares": False, "blocks": 148, "pairs": True}
+    assert ops.gemm_tc_plan(2048, 1536, 8960, 1, True)["pairs"]
+    # one wave over a short K, and few tokens, stay with blocks alone
+    assert not ops.gemm_tc_plan(2048, 1536, 1536, 1, True)["pairs"]
+    assert not ops.gemm_tc_plan(64, 17920, 1536, 2, False)["pairs"]
+    assert not ops.gemm_tc_plan(8, 17920, 1536, 2, False)["pairs"]
+
+
 def test_gemm_tc_takes_even_shares_where_whole_tiles_leave_a_wave_half_empty():
     ops = _ops()
     before = ops.gemm_tc_even_shares(1)
@@ -685,11 +733,14 @@ def test_gemv_small_rope_cache():
 
 @pytest.mark.parametrize("heads,kv_heads,d", [(3, 1, 128), (6, 2, 64), (12, 2, 128)])
 @pytest.mark.parametrize("style_name", ["neox", "none"])
-def test_gemm_tc_rope_cache(heads, kv_heads, d, style_name):
+@pytest.mark.parametrize("pairs", [0, 2])
+def test_gemm_tc_rope_cache(heads, kv_heads, d, style_name, pairs, request):
     """The q/k/v product of many tokens on the tensor cores with its ending: bias, rotation of
     the q and k pairs, q to its buffer, k and v to their pages; two entries, one of them at the
-    end of a longer history, pages in shuffled order."""
+    end of a longer history, pages in shuffled order.  With blocks alone, and on pairs of blocks."""
     ops = _ops()
+    before = ops.gemm_tc_pairs(pairs)
+    request.addfinalizer(lambda: ops.gemm_tc_pairs(before))
     page, hidden = 16, 320
     counts, firsts = [200, 131], [0, 77]
     tokens = sum(counts)

@@ -15,10 +15,20 @@
 // (crates/vipera-backend-gpu/src/q4k_matvec_q8_batch.cu:40-116); this kernel is that idea on
 // tcgen05.
 //
-// Roles inside a block of 192 threads: warps 0-3 read accumulators from tensor memory and
-// write the ending; one thread of warp 4 issues TMA loads; one thread of warp 5 issues
-// tcgen05.mma.  Two accumulators alternate, so that the ending of one tile overlaps the
-// products of the next.  Every wait on an mbarrier is bounded: when it runs out the block
+// Roles inside a block: warps 0-3 read accumulators from tensor memory and write the ending; one
+// thread of warp 4 issues TMA loads (wide tiles: one thread of warp 6 too, the two taking turns at
+// the k-blocks); warp 5 issues tcgen05.mma through an elected lane.  Two accumulators alternate,
+// so that the ending of one tile overlaps the products of the next.  What bounds the loop over K
+// is instruction latency in these single threads, not bytes: a wait on a barrier and an arrival
+// cost about 100 clocks each, a TMA instruction 60 to 90, and a k-block of a 128 x 256 tile is
+// only 512 clocks of tensor-core work.  Hence the second loading warp, the look ahead at the next
+// stage's barrier while this stage's products are issued, and the uniform operands.
+//
+// Pairs (many tokens): two blocks of a cluster share tiles of 256 tokens (cta_group::2).  Each
+// loads its own 128 tokens and half of the tile's weight rows; the first block's warp issues
+// products that read both blocks' shared memory and write both blocks' tensor memory; each block
+// writes the ending of its own 128 tokens.  A third fewer bytes per flop pass through each SM's
+// shared memory, and six stages fit where four did.  Every wait on an mbarrier is bounded: when it runs out the block
 // records an error code, stops waiting anywhere, drains and frees its tensor memory, and
 // the launcher's caller finds the code in the status word.
 //
@@ -48,6 +58,11 @@ enum { GEMM_TC_WAIT_EXPIRED = 1 };
 constexpr int kBlockK = 64;        // bf16 elements per k-block: one 128-byte swizzle row
 constexpr int kTileX = 128;        // rows on the 128-row side of the instruction
 constexpr int kThreads = 192;
+// Wide tiles have a second loading warp: the two take turns at the k-blocks.  Waiting for a
+// stage, announcing its bytes and handing two boxes to TMA are some 600 clocks of instruction
+// latency in one thread, more than the 512 the tensor core needs for the stage.
+constexpr int kThreadsWide = 224;
+template <int BN> constexpr int threads_for() { return BN >= 128 ? kThreadsWide : kThreads; }
 constexpr uint32_t kWaitLimit = 1u << 22;
 
 struct GemmParams {
@@ -101,6 +116,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return done != 0;
 }
+// whether the phase has completed, without waiting
+__device__ __forceinline__ uint32_t mbar_peek(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done;
+}
 // Bounded wait.  When the limit runs out, or another thread's wait already did, the caller
 // goes on as if the barrier had completed: every role then runs to its end without waiting,
 // so the block drains; what it writes is marked invalid by the status word.
@@ -136,12 +159,64 @@ __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bu
 __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Issued by a whole warp that walks the loop together: every lane holds the same operands (so they
+// can live in the warp's uniform registers, which is where the instruction wants them) and one
+// elected lane issues.  A single lane in a diverged branch pays for moving each operand there:
+// about 77 clocks an instruction, measured, against 35 this way and 96 that the instruction runs.
 __device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tcgen05_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_elect(uint64_t* bar) {
+  asm volatile(
+      "{\n .reg .pred leader;\n elect.sync _|leader, 0xffffffff;\n"
+      " @leader tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n"
+      ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p, leader;\n elect.sync _|leader, 0xffffffff;\n setp.ne.b32 p, %4, 0;\n"
+      " @leader tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// ---- the forms for a pair of blocks (a cluster of two, cta_group::2) ----
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+// the address, in the cluster's window, of the same shared-memory location in the block of `rank`
+__device__ __forceinline__ uint32_t in_block(uint32_t saddr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(saddr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// a load into this block's shared memory whose bytes count on a barrier of the pair's first block
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile(
+      "{\n .reg .pred leader;\n elect.sync _|leader, 0xffffffff;\n"
+      " @leader tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n"
+      ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p, leader;\n elect.sync _|leader, 0xffffffff;\n setp.ne.b32 p, %4, 0;\n"
+      " @leader tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tmem_load_32(uint32_t taddr, float* v) {
@@ -207,18 +282,22 @@ __device__ __forceinline__ float silu_mul(float gate, float up) { return up * __
 #ifndef VIPERA_SMALL_BUDGET
 #define VIPERA_SMALL_BUDGET 100
 #endif
-template <int BN>
+// PAIR: two blocks of a cluster work on one tile of 256 rows (cta_group::2); each holds its own
+// 128 rows of the one operand and half of the BN rows of the other.
+template <int BN, bool PAIR = false>
 struct TileConfig {
-  static constexpr int kStageBytes = (kTileX + BN) * kBlockK * 2;
+  static constexpr int kRowsY = PAIR ? BN / 2 : BN;   // rows of the second operand in this block's stage
+  static constexpr int kStageBytes = (kTileX + kRowsY) * kBlockK * 2;
   // Wide tiles take all the shared memory of an SM; narrow ones (few tokens) take less
   // than half, so that two blocks share an SM and the next product's block can set up and
   // prefetch weights while this one finishes.
   static constexpr int kStagingBytes = BN >= 128 ? 4 * 2 * 4096 : 0;  // 2 buffers of 32 rows x 128 B per epilogue warp
-  static constexpr int kBudget = BN >= 128 ? 196 * 1024 - kStagingBytes + 32 * 1024 : VIPERA_SMALL_BUDGET * 1024;
+  static constexpr int kBudget = BN >= 128 ? 193 * 1024 : VIPERA_SMALL_BUDGET * 1024;   // for the stages
   static constexpr int kStages = kBudget / kStageBytes;
   // two accumulators; tensor memory is handed out in powers of two of at least 32 columns
   static constexpr int kTmemCols = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+  static_assert(kSmemBytes <= 227 * 1024, "more shared memory than a block can have");
 };
 
 // ---------------------------------------------------------------------------------------
@@ -317,18 +396,24 @@ struct Piece {
   int tile, kb_begin, kb_end;
   int slot;      // where a partial sum of this piece goes in the scratch
 };
+// EVEN: whether this form of the kernel can be given even shares at all (the others keep the
+// code out: the few-token forms are bound by the latency of their first instructions)
+template <bool EVEN>
 struct WorkLoop {
   const GemmParams& p;
   int item;
   long at, end;
-  __device__ __forceinline__ explicit WorkLoop(const GemmParams& params) : p(params), item(blockIdx.x), at(0), end(0) {
-    if (p.even_shares) {
+  int stride;
+  // `pair`: the two blocks of a cluster walk the same tiles
+  __device__ __forceinline__ explicit WorkLoop(const GemmParams& params, bool pair = false)
+      : p(params), item(pair ? blockIdx.x >> 1 : blockIdx.x), at(0), end(0), stride(pair ? gridDim.x >> 1 : gridDim.x) {
+    if (EVEN && p.even_shares) {
       at = share_begin(p, blockIdx.x, gridDim.x);
       end = share_begin(p, blockIdx.x + 1, gridDim.x);
     }
   }
   __device__ __forceinline__ bool next(Piece& piece) {
-    if (p.even_shares) {
+    if (EVEN && p.even_shares) {
       if (at >= end) return false;
       piece.tile = static_cast<int>(at / p.num_k_blocks);
       piece.kb_begin = static_cast<int>(at % p.num_k_blocks);
@@ -344,19 +429,25 @@ struct WorkLoop {
     piece.kb_begin = split * p.k_blocks_per_split;
     piece.kb_end = min(p.num_k_blocks, piece.kb_begin + p.k_blocks_per_split);
     piece.slot = item;
-    item += gridDim.x;
+    item += stride;
     return true;
   }
 };
 
-template <int BN, bool SWAP>
-__global__ void __launch_bounds__(kThreads, (BN >= 128 || VIPERA_SMALL_BUDGET > 110 ? 1 : 2))
+template <int BN, bool SWAP, bool PAIR = false, bool EVEN = false>
+__global__ void __launch_bounds__(threads_for<BN>(), (BN >= 128 || VIPERA_SMALL_BUDGET > 110 ? 1 : 2))
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
-  using Config = TileConfig<BN>;
+  static_assert(!PAIR || (!SWAP && BN >= 128), "pairs of blocks: tokens on the 128-row side, wide tiles");
+  using Config = TileConfig<BN, PAIR>;
   constexpr int kStages = Config::kStages;
+  // a pair's instruction covers 256 rows: 128 in each block's tensor memory
   constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                              (static_cast<uint32_t>(kTileX >> 4) << 24);
+                              (static_cast<uint32_t>((PAIR ? 2 * kTileX : kTileX) >> 4) << 24);
+  const uint32_t rank = PAIR ? cluster_rank() : 0u;   // 0: the block that issues the pair's products
+  constexpr bool kWide = BN >= 128;                   // the forms for many tokens
+  constexpr bool kEven = EVEN;                        // the form that runs with even shares, an instance of its own
+  static_assert(!EVEN || (!SWAP && BN >= 128 && !PAIR), "even shares: tokens on the 128-row side, wide tiles, blocks alone");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* tiles = smem;
@@ -373,33 +464,54 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    // a pair's accumulator is free when the epilogue warps of both blocks have read their halves
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], PAIR ? 8 : 4); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Config::kTmemCols));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    if (PAIR) {
+      // the same warp of both blocks: the columns are handed out in both blocks' tensor memory
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Config::kTmemCols));
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(Config::kTmemCols));
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
   }
   tcgen05_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();   // the other block's barriers exist before anything arrives at them
+  else __syncthreads();
   tcgen05_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);   // the same in every lane, and known to be
 
-  if (warp == 4) {
-    // ---------------- TMA producer ----------------
+  constexpr int kProducers = BN >= 128 ? 2 : 1;
+  if (warp == 4 || (kProducers == 2 && warp == 6)) {
+    // ---------------- TMA producers: warp 4, and warp 6 for every other k-block of wide tiles ----------------
+    const int mine = warp == 4 ? 0 : 1;
     if (lane == 0) {
       // The weight operand depends on no earlier kernel: its tiles for the first stages are
       // on their way before this kernel waits for the kernels ahead of it.
+      // A pair: both blocks load their own rows into their own shared memory; all four loads of
+      // a stage count on the first block's barrier, which expects the bytes of both blocks.
       int prefetched = 0;
+      const uint32_t pair_full = PAIR ? in_block(smem_u32(&full[0]), 0) : 0u;   // + 8 * stage
+      const int y_row = PAIR ? static_cast<int>(rank) * (BN / 2) : 0;           // this block's rows inside the tile's BN
       Piece first;
-      if (WorkLoop(p).next(first)) {
-        const int tx = first.tile % p.tiles_x, ty = first.tile / p.tiles_x;
+      if (WorkLoop<kEven>(p, PAIR).next(first)) {
+        const int tx = PAIR ? 2 * (first.tile % p.tiles_x) + static_cast<int>(rank) : first.tile % p.tiles_x;
+        const int ty = first.tile / p.tiles_x;
         const int kb_begin = first.kb_begin;
         prefetched = min(kStages, first.kb_end - first.kb_begin);
         for (int i = 0; i < prefetched; ++i) {
+          if (i % kProducers != mine) continue;
           uint8_t* x_tile = tiles + i * Config::kStageBytes;
           uint8_t* y_tile = x_tile + kTileX * kBlockK * 2;
+          if (PAIR) {
+            if (rank == 0) mbar_expect_tx(&full[i], 2 * Config::kStageBytes);
+            tma_load_2d_pair(y_tile, &map_y, pair_full + 8 * i, (kb_begin + i) * kBlockK, ty * BN + y_row);
+            continue;
+          }
           mbar_expect_tx(&full[i], Config::kStageBytes);
           if (SWAP) tma_load_2d(x_tile, &map_x, &full[i], (kb_begin + i) * kBlockK, tx * kTileX);
           else tma_load_2d(y_tile, &map_y, &full[i], (kb_begin + i) * kBlockK, ty * BN);
@@ -408,14 +520,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       pdl_wait();
       int stage = 0, issued = 0;
       uint32_t phase = 0;
-      WorkLoop work(p);
+      WorkLoop<kEven> work(p, PAIR);
       Piece piece;
       while (work.next(piece)) {
-        const int tx = piece.tile % p.tiles_x, ty = piece.tile / p.tiles_x;
+        const int tx = PAIR ? 2 * (piece.tile % p.tiles_x) + static_cast<int>(rank) : piece.tile % p.tiles_x;
+        const int ty = piece.tile / p.tiles_x;
         for (int kb = piece.kb_begin; kb < piece.kb_end; ++kb, ++issued) {
+          if (issued % kProducers != mine) {
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           uint8_t* x_tile = tiles + stage * Config::kStageBytes;
           uint8_t* y_tile = x_tile + kTileX * kBlockK * 2;
-          if (issued < prefetched) {
+          if (PAIR) {
+            if (issued < prefetched) {
+              tma_load_2d_pair(x_tile, &map_x, pair_full + 8 * stage, kb * kBlockK, tx * kTileX);
+            } else {
+              mbar_wait(&empty[stage], phase ^ 1u, abort_flag, p.status);
+              if (rank == 0) mbar_expect_tx(&full[stage], 2 * Config::kStageBytes);
+              tma_load_2d_pair(x_tile, &map_x, pair_full + 8 * stage, kb * kBlockK, tx * kTileX);
+              tma_load_2d_pair(y_tile, &map_y, pair_full + 8 * stage, kb * kBlockK, ty * BN + y_row);
+            }
+          } else if (issued < prefetched) {
             // the weight half of this stage is already in flight: add the activation half
             if (SWAP) tma_load_2d(y_tile, &map_y, &full[stage], kb * kBlockK, ty * BN);
             else tma_load_2d(x_tile, &map_x, &full[stage], kb * kBlockK, tx * kTileX);
@@ -431,21 +557,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
   } else if (warp == 5) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    // Wide tiles: the whole warp walks the loop (see tcgen05_mma_bf16_elect); of a pair, the first
+    // block's warp issues for both.  Narrow tiles (few tokens) wait for their weights, not for the
+    // issue, and keep the shortest code: one lane.
+    if (rank == 0 && (kWide || lane == 0)) {
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
-      WorkLoop work(p);
+      bool arrived = false;
+      uint32_t arrived_next = 0;
+      const uint32_t other_empty = PAIR ? in_block(smem_u32(&empty[0]), 1) : 0u;
+      const uint32_t other_acc_full = PAIR ? in_block(smem_u32(&acc_full[0]), 1) : 0u;
+      WorkLoop<kEven> work(p, PAIR);
       Piece piece;
       for (; work.next(piece); ++local) {
         const int kb_begin = piece.kb_begin, kb_end = piece.kb_end;
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
-        mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status);
+        if (kWide) {
+          if (lane == 0) mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status);
+          __syncwarp();
+        } else {
+          mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_flag, p.status);
+        }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          mbar_wait(&full[stage], phase, abort_flag, p.status);
+          // `arrived`: the look ahead of the k-block before already saw this stage full
+          if (kWide) {
+            if (!arrived && lane == 0) mbar_wait(&full[stage], phase, abort_flag, p.status);   // one lane polls, the warp follows
+            __syncwarp();
+          } else {
+            mbar_wait(&full[stage], phase, abort_flag, p.status);
+          }
+          if (kWide) {
+            // a look at the next stage, asked now and read after this stage's products are issued:
+            // the barrier's answer takes about 100 clocks, which the issue then hides
+            const int next = stage + 1 == kStages ? 0 : stage + 1;
+            arrived_next = mbar_peek(&full[next], next == 0 ? phase ^ 1u : phase);
+          }
           tcgen05_fence_after();
           const uint32_t x_addr = smem_u32(tiles + stage * Config::kStageBytes);
           const uint32_t y_addr = x_addr + kTileX * kBlockK * 2;
@@ -454,32 +604,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < kBlockK / 16; ++k) {
             // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in the address field
-            tcgen05_mma_bf16(d_tmem, x_desc + static_cast<uint64_t>(2 * k), y_desc + static_cast<uint64_t>(2 * k),
-                             kIdesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+            if (PAIR)
+              tcgen05_mma_bf16_pair(d_tmem, x_desc + static_cast<uint64_t>(2 * k), y_desc + static_cast<uint64_t>(2 * k),
+                                    kIdesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+            else if (kWide)
+              tcgen05_mma_bf16_elect(d_tmem, x_desc + static_cast<uint64_t>(2 * k), y_desc + static_cast<uint64_t>(2 * k),
+                                     kIdesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+            else
+              tcgen05_mma_bf16(d_tmem, x_desc + static_cast<uint64_t>(2 * k), y_desc + static_cast<uint64_t>(2 * k),
+                               kIdesc, (kb > kb_begin || k > 0) ? 1u : 0u);
           }
-          tcgen05_commit(&empty[stage]);  // the stage is free once these products have read it
+          // the stage is free once these products have read it (in both blocks of a pair)
+          if (PAIR) {
+            tcgen05_commit_pair(smem_u32(&empty[stage]));
+            tcgen05_commit_pair(other_empty + 8 * stage);
+          } else if (kWide) {
+            tcgen05_commit_elect(&empty[stage]);
+          } else {
+            tcgen05_commit(&empty[stage]);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          if (kWide) arrived = __shfl_sync(0xffffffffu, arrived_next, 0) != 0;
         }
-        tcgen05_commit(&acc_full[acc]);
+        if (PAIR) {
+          tcgen05_commit_pair(smem_u32(&acc_full[acc]));
+          tcgen05_commit_pair(other_acc_full + 8 * acc);
+        } else if (kWide) {
+          tcgen05_commit_elect(&acc_full[acc]);
+        } else {
+          tcgen05_commit(&acc_full[acc]);
+        }
       }
     }
   } else {
     // ---------------- epilogue warps 0..3 ----------------
     pdl_wait();  // outputs, the residual stream, and the scratch belong to earlier kernels until now
     int local = 0;
-    WorkLoop work(p);
+    WorkLoop<kEven> work(p, PAIR);
     Piece piece;
+    const uint32_t pair_acc_empty = PAIR ? in_block(smem_u32(&acc_empty[0]), 0) : 0u;
     for (; work.next(piece); ++local) {
       const int tile = piece.tile;
-      const int tx = tile % p.tiles_x, ty = tile / p.tiles_x;
+      const int tx = PAIR ? 2 * (tile % p.tiles_x) + static_cast<int>(rank) : tile % p.tiles_x;
+      const int ty = tile / p.tiles_x;
       const int acc = local & 1;
       // Even shares: a piece that starts inside a tile is a partial sum for another block; the
       // piece with the tile's first k-block that does not reach its last one waits for the blocks
       // behind this one whose shares start inside the same tile.
       const bool whole = piece.kb_begin == 0 && piece.kb_end == p.num_k_blocks;
-      const bool partial = p.splits > 1 || (p.even_shares && piece.kb_begin > 0);
+      const bool partial = p.splits > 1 || (kEven && p.even_shares && piece.kb_begin > 0);
       int helpers = 0;
-      if (p.even_shares && !whole && !partial) {
+      if (kEven && p.even_shares && !whole && !partial) {
         const long tile_end = static_cast<long>(tile + 1) * p.num_k_blocks;
         while (share_begin(p, blockIdx.x + 1 + helpers, gridDim.x) < tile_end) ++helpers;
       }
@@ -503,10 +678,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
-      mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status);
+      if (kWide) {
+        if (lane == 0) mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status);   // one lane of a warp polls
+        __syncwarp();
+      } else {
+        mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status);
+      }
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(acc * BN);
-      if (helpers > 0) {
+      if (kEven && helpers > 0) {
         if (warp == 0 && lane == 0) {
           for (int h = 0; h < helpers; ++h) {
             int* flag = p.share_flags + blockIdx.x + 1 + h;
@@ -635,11 +815,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 uint32_t packed[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
-#ifdef GEMM_DEBUG_NO_MATH
-                  packed[i] = pack_bf16x2(v[2 * i] + v[16 + 2 * i], v[2 * i + 1] + v[16 + 2 * i + 1]);
-#else
                   packed[i] = pack_bf16x2(silu_mul(v[2 * i], v[16 + 2 * i]), silu_mul(v[2 * i + 1], v[16 + 2 * i + 1]));
-#endif
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                   const int chunk = (q4 * 2 + h) ^ (lane & 7);
@@ -649,12 +825,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               }
               fence_async_shared();
               __syncwarp();
-#ifndef GEMM_DEBUG_NO_STORE
               if (lane == 0) {
                 tma_store_2d(&map_out, buffer, (ty * BN + c) >> 1, row0);
                 tma_store_commit();
               }
-#endif
               use ^= 1;
             }
           } else {
@@ -664,7 +838,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
               uint8_t* buffer = mine + use * 4096;
               float v[32];
               tmem_load_32(taddr + c, v);
-              for (int h = 0; h < helpers; ++h) {
+              for (int h = 0; kEven && h < helpers; ++h) {
                 const float* part = p.scratch + (static_cast<size_t>(blockIdx.x + 1 + h) * BN + c) * kTileX + row_in_tile;
                 float more[32];
 #pragma unroll
@@ -711,7 +885,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         tcgen05_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_cluster(pair_acc_empty + 8 * acc);
+          else mbar_arrive(&acc_empty[acc]);
+        }
       } else {
         // partial sums: scratch[slot][column][row_in_tile]
         float* part = p.scratch + static_cast<size_t>(piece.slot) * BN * kTileX;
@@ -732,7 +909,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
-        if (p.even_shares) {
+        if (kEven && p.even_shares) {
           // the flag goes up when all four warps' partial sums can be seen by the other blocks
           __threadfence();
           asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -750,7 +927,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
   // ---------------- teardown ----------------
   tcgen05_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();   // neither block leaves while the other may still read its shared memory
+  else __syncthreads();
   if (*abort_flag && threadIdx.x == 0) {
     // Loads this block issued may still be landing in its shared memory: give them time.
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
@@ -758,7 +936,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   __syncthreads();
   if (warp == 0) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Config::kTmemCols));
+    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Config::kTmemCols));
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Config::kTmemCols));
   }
 }
 
@@ -916,6 +1095,7 @@ static int make_out_map(CUtensorMap* map, void* base, int rows, int cols, bool b
 
 struct GemmPlan {
   bool swap;
+  bool pair;          // tiles of 256 tokens by pairs of blocks (clusters of two)
   bool even_shares;   // one equal share of all k-blocks per block instead of whole tiles
   int blocks;         // even shares: the grid
   int bn;
@@ -941,6 +1121,11 @@ static int sm_count() {
 // 4,096 tokens on: 110 us against 124).
 static int& even_shares_mode() {
   static int mode = std::getenv("VIPERA_GEMM_EVEN_SHARES") ? std::atoi(std::getenv("VIPERA_GEMM_EVEN_SHARES")) : 0;
+  return mode;
+}
+// 0: never; 1: where the estimate favours them; 2: wherever the form allows them
+static int& pair_mode() {
+  static int mode = std::getenv("VIPERA_GEMM_PAIR") ? std::atoi(std::getenv("VIPERA_GEMM_PAIR")) : 1;
   return mode;
 }
 constexpr int kShareLeast = 8;      // even shares: k-blocks a block must get at least
@@ -993,6 +1178,36 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
         }
       }
     }
+    // Pairs of blocks on tiles of 256 tokens: each block reads its own 128 tokens and half of the
+    // tile's weight rows, a third less per flop than a block alone, which is what holds the
+    // tensor cores up.  Clusters of two fill half as many slots as there are SMs.
+    const int pairs_mode = pair_mode();
+    if (!plan.even_shares && pairs_mode > 0 && T > kTileX) {
+      static const int forced_bn = std::getenv("VIPERA_GEMM_PAIR_BN") ? std::atoi(std::getenv("VIPERA_GEMM_PAIR_BN")) : 0;
+      const int clusters = sms / 2;
+      const int rows2 = (T + 2 * kTileX - 1) / (2 * kTileX);
+      double best_pair = -1.0;
+      int bn_pair = 0;
+      for (int bn : candidates) {
+        if (N < bn) continue;
+        if (bn == 192 && (epilogue == EPI_SWIGLU || epilogue == EPI_ROPE_CACHE)) continue;
+        if (forced_bn && bn != forced_bn) continue;
+        const long items = static_cast<long>(rows2) * ((N + bn - 1) / bn);
+        const long waves = (items + clusters - 1) / clusters;
+        // one wave over a short K is all set-up and ending, and a pair has more of both
+        if (waves < 2 && plan.num_k_blocks < 48 && pairs_mode < 2) continue;
+        double efficiency = static_cast<double>(T) * N / (static_cast<double>(waves) * clusters * 2 * kTileX * bn);
+        efficiency *= bn == 256 ? 1.15 : bn == 192 ? 1.1 : 0.9;   // measured against blocks alone
+        if (efficiency > best_pair) { best_pair = efficiency; bn_pair = bn; }
+      }
+      // `best` counts whole 128-row tiles; put it on the same footing (tokens, not tiles)
+      const double best_alone = best * T / (static_cast<double>(plan.tiles_x) * kTileX);
+      if (bn_pair && (best_pair > best_alone || pairs_mode > 1)) {
+        plan.pair = true;
+        plan.bn = bn_pair;
+        plan.tiles_x = rows2;
+      }
+    }
     plan.tiles_y = (N + plan.bn - 1) / plan.bn;
     plan.splits = 1;
     plan.k_blocks_per_split = plan.num_k_blocks;
@@ -1001,7 +1216,12 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
     // form does: its tiles of 128 features x 256 tokens are cut along K until every SM has one.
     // (The q/k/v ending exists in this form only.)
     static const bool narrow_swaps = std::getenv("VIPERA_GEMM_NARROW_NONSWAP") == nullptr;
-    if (narrow_swaps && !plan.even_shares && epilogue != EPI_ROPE_CACHE && 4 * plan.tiles_x * plan.tiles_y < 3 * sms) plan.swap = true;
+    const int tiles_alone = (plan.pair ? 2 : 1) * plan.tiles_x * plan.tiles_y;
+    const bool forced = (plan.pair && pair_mode() > 1);   // tests ask for pairs on small sizes too
+    if (narrow_swaps && !plan.even_shares && !forced && epilogue != EPI_ROPE_CACHE && 4 * tiles_alone < 3 * sms) {
+      plan.swap = true;
+      plan.pair = false;
+    }
   }
   if (plan.swap) {
     plan.bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
@@ -1035,7 +1255,13 @@ VIPERA_API int vipera_gemm_tc_even_shares(int mode) {
   return before;
 }
 
-// The form a product of these sizes takes: {swapped, tile width, splits, even shares, blocks}.
+VIPERA_API int vipera_gemm_tc_pairs(int mode) {
+  const int before = pair_mode();
+  if (mode >= 0) pair_mode() = mode;
+  return before;
+}
+
+// The form a product of these sizes takes: {swapped, tile width, splits, even shares, blocks, pairs}.
 VIPERA_API int vipera_gemm_tc_plan(int T, int N, int K, int epilogue, int even_ok, int* form) {
   const GemmPlan plan = make_plan(T, N, K, sm_count(), epilogue, even_ok != 0);
   form[0] = plan.swap ? 1 : 0;
@@ -1043,23 +1269,62 @@ VIPERA_API int vipera_gemm_tc_plan(int T, int N, int K, int epilogue, int even_o
   form[2] = plan.splits;
   form[3] = plan.even_shares ? 1 : 0;
   form[4] = plan.even_shares ? plan.blocks : std::min(sm_count(), plan.tiles_x * plan.tiles_y * plan.splits);
+  if (plan.pair) form[4] = 2 * std::min(sm_count() / 2, plan.tiles_x * plan.tiles_y);
+  form[5] = plan.pair ? 1 : 0;
   return VIPERA_OK;
 }
 
-template <int BN, bool SWAP>
+template <int BN, bool SWAP, bool EVEN = false>
 static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, const CUtensorMap& map_out,
                           const GemmParams& p, int grid, cudaStream_t s) {
   using Config = TileConfig<BN>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, Config::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP, false, EVEN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Config::kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  int status = vipera_launch(gemm_tc_kernel<BN, SWAP>, grid, kThreads, Config::kSmemBytes, s, map_x, map_y, map_out, p);
+  int status = vipera_launch(gemm_tc_kernel<BN, SWAP, false, EVEN>, grid, threads_for<BN>(), Config::kSmemBytes, s, map_x, map_y, map_out, p);
   if (status != VIPERA_OK || p.splits == 1) return status;   // (even shares run with splits == 1)
   const long outputs = static_cast<long>(p.tokens) * (p.epilogue == EPI_SWIGLU ? p.features / 2 : p.features);
   return vipera_launch(splitk_finish_kernel<BN>, dim3(static_cast<unsigned>((outputs + 255) / 256)), dim3(256), 0, s, p);
+}
+
+// Pairs of blocks: clusters of two, as many as fit on the device at once (a persistent loop).
+template <int BN>
+static int launch_pairs(const CUtensorMap& map_x, const CUtensorMap& map_y, const CUtensorMap& map_out,
+                        const GemmParams& p, int items, cudaStream_t s) {
+  using Config = TileConfig<BN, true>;
+  auto kernel = gemm_tc_kernel<BN, false, true>;
+  cudaLaunchConfig_t config = {};
+  config.blockDim = dim3(threads_for<BN>());
+  config.dynamicSmemBytes = Config::kSmemBytes;
+  config.stream = s;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = 2;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = vipera_pdl_enabled() ? 1 : 0;
+  config.attrs = attributes;
+  static int clusters = 0;
+  if (clusters == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Config::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    config.gridDim = dim3(2 * (sm_count() / 2));
+    config.numAttrs = 1;
+    int fit = 0;
+    if (cudaOccupancyMaxActiveClusters(&fit, kernel, &config) != cudaSuccess || fit <= 0) {
+      cudaGetLastError();
+      fit = sm_count() / 2;
+    }
+    clusters = std::min(fit, sm_count() / 2);
+  }
+  config.numAttrs = 2;
+  config.gridDim = dim3(2 * std::min(items, clusters));
+  cudaError_t error = cudaLaunchKernelEx(&config, kernel, map_x, map_y, map_out, p);
+  return error == cudaSuccess ? VIPERA_OK : static_cast<int>(error);
 }
 
 // A is [T, K] bfloat16, W is [N, K] bfloat16, both row-major and contiguous with K a
@@ -1093,7 +1358,7 @@ static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilo
     if ((r = make_map(&map_y, A, T, K, plan.bn)) != VIPERA_OK) return r;
   } else {
     if ((r = make_map(&map_x, A, T, K, kTileX)) != VIPERA_OK) return r;
-    if ((r = make_map(&map_y, W, N, K, plan.bn)) != VIPERA_OK) return r;
+    if ((r = make_map(&map_y, W, N, K, plan.pair ? plan.bn / 2 : plan.bn)) != VIPERA_OK) return r;
   }
   GemmParams p{};
   if (rope) p = *rope;
@@ -1138,6 +1403,15 @@ static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilo
       if ((r = make_out_map(&map_out, resid, T, N, false)) != VIPERA_OK) return r;
       p.tma_ending = 1;
     }
+  }
+  if (plan.pair) {
+    if (plan.bn == 256) return launch_pairs<256>(map_x, map_y, map_out, p, items, s);
+    if (plan.bn == 192) return launch_pairs<192>(map_x, map_y, map_out, p, items, s);
+    return launch_pairs<128>(map_x, map_y, map_out, p, items, s);
+  }
+  if (plan.even_shares) {
+    if (plan.bn == 256) return launch_variant<256, false, true>(map_x, map_y, map_out, p, grid, s);
+    return launch_variant<128, false, true>(map_x, map_y, map_out, p, grid, s);
   }
   if (!plan.swap) {
     if (plan.bn == 256) return launch_variant<256, false>(map_x, map_y, map_out, p, grid, s);

@@ -451,12 +451,12 @@ def gemm_tc_plan(m: int, n: int, k: int, epilogue: int = EPI_STORE, even_ok: boo
     plan = _plans.get(key)
     if plan is None:
         fn = _function("gemm_tc", "vipera_gemm_tc_plan", [_c_int] * 5 + [ctypes.POINTER(_c_int)])
-        form = (_c_int * 5)()
+        form = (_c_int * 6)()
         _check(fn(key[0], key[1], key[2], key[3], int(key[4]), form), "gemm_tc_plan", kernels=0)
         if len(_plans) > 65536:
             _plans.clear()
         plan = _plans[key] = {"swapped": bool(form[0]), "tile": form[1], "splits": form[2],
-                              "even_shares": bool(form[3]), "blocks": form[4]}
+                              "even_shares": bool(form[3]), "blocks": form[4], "pairs": bool(form[5])}
     return plan
 
 
@@ -468,7 +468,18 @@ def gemm_tc_even_shares(mode: int) -> int:
     wherever the ending allows) and returns the mode before; -1 only asks."""
     before = _function("gemm_tc", "vipera_gemm_tc_even_shares", [_c_int])(int(mode))
     if mode >= 0:
-        _even_shares_mode[0] = int(mode)
+        _even_shares_mode[0] = (_even_shares_mode[0], "even", int(mode))
+        _workspace_sizes.clear()
+    return before
+
+
+def gemm_tc_pairs(mode: int) -> int:
+    """Sets when the product runs on pairs of blocks that share tiles of 256 tokens (0 never, 1
+    where its estimate favours them, 2 wherever the form allows) and returns the mode before; -1
+    only asks."""
+    before = _function("gemm_tc", "vipera_gemm_tc_pairs", [_c_int])(int(mode))
+    if mode >= 0:
+        _even_shares_mode[0] = (_even_shares_mode[0], "pairs", int(mode))   # a new key for the kept plans
         _workspace_sizes.clear()
     return before
 
