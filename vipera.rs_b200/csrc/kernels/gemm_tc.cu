@@ -485,7 +485,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   tcgen05_fence_after();
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);   // the same in every lane, and known to be
 
-  constexpr int kProducers = BN >= 128 ? 2 : 1;
+  constexpr int kProducers = BN >= 128 ? 2 : 1;   // (narrow tiles: a second loading warp was measured and changes nothing)
   if (warp == 4 || (kProducers == 2 && warp == 6)) {
     // ---------------- TMA producers: warp 4, and warp 6 for every other k-block of wide tiles ----------------
     const int mine = warp == 4 ? 0 : 1;
