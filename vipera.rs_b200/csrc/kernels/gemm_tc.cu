@@ -1128,6 +1128,36 @@ static int& pair_mode() {
   static int mode = std::getenv("VIPERA_GEMM_PAIR") ? std::atoi(std::getenv("VIPERA_GEMM_PAIR")) : 1;
   return mode;
 }
+// How many pairs of blocks of this tile width the device runs at once (0: clusters of two with
+// this much shared memory cannot be launched here, and the product stays with blocks alone).
+template <int BN>
+static int pair_clusters() {
+  static int clusters = -1;
+  if (clusters < 0) {
+    using Config = TileConfig<BN, true>;
+    auto kernel = gemm_tc_kernel<BN, false, true>;
+    clusters = 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Config::kSmemBytes) == cudaSuccess) {
+      cudaLaunchConfig_t config = {};
+      config.blockDim = dim3(threads_for<BN>());
+      config.dynamicSmemBytes = Config::kSmemBytes;
+      config.gridDim = dim3(2 * (sm_count() / 2));
+      cudaLaunchAttribute attribute[1];
+      attribute[0].id = cudaLaunchAttributeClusterDimension;
+      attribute[0].val.clusterDim.x = 2;
+      attribute[0].val.clusterDim.y = 1;
+      attribute[0].val.clusterDim.z = 1;
+      config.attrs = attribute;
+      config.numAttrs = 1;
+      int fit = 0;
+      if (cudaOccupancyMaxActiveClusters(&fit, kernel, &config) == cudaSuccess && fit > 0) clusters = std::min(fit, sm_count() / 2);
+    }
+    cudaGetLastError();   // a refusal above is an answer, not an error of the caller's
+  }
+  return clusters;
+}
+static int pair_clusters_for(int bn) { return bn == 256 ? pair_clusters<256>() : bn == 192 ? pair_clusters<192>() : pair_clusters<128>(); }
+
 constexpr int kShareLeast = 8;      // even shares: k-blocks a block must get at least
 constexpr double kShareCost = 4.0;  // what a block's partial sum costs (written, read back, added), in k-blocks of its time
 
@@ -1184,7 +1214,6 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
     const int pairs_mode = pair_mode();
     if (!plan.even_shares && pairs_mode > 0 && T > kTileX) {
       static const int forced_bn = std::getenv("VIPERA_GEMM_PAIR_BN") ? std::atoi(std::getenv("VIPERA_GEMM_PAIR_BN")) : 0;
-      const int clusters = sms / 2;
       const int rows2 = (T + 2 * kTileX - 1) / (2 * kTileX);
       double best_pair = -1.0;
       int bn_pair = 0;
@@ -1192,6 +1221,8 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
         if (N < bn) continue;
         if (bn == 192 && (epilogue == EPI_SWIGLU || epilogue == EPI_ROPE_CACHE)) continue;
         if (forced_bn && bn != forced_bn) continue;
+        const int clusters = pair_clusters_for(bn);
+        if (clusters <= 0) continue;
         const long items = static_cast<long>(rows2) * ((N + bn - 1) / bn);
         const long waves = (items + clusters - 1) / clusters;
         // one wave over a short K is all set-up and ending, and a pair has more of both
@@ -1269,7 +1300,7 @@ VIPERA_API int vipera_gemm_tc_plan(int T, int N, int K, int epilogue, int even_o
   form[2] = plan.splits;
   form[3] = plan.even_shares ? 1 : 0;
   form[4] = plan.even_shares ? plan.blocks : std::min(sm_count(), plan.tiles_x * plan.tiles_y * plan.splits);
-  if (plan.pair) form[4] = 2 * std::min(sm_count() / 2, plan.tiles_x * plan.tiles_y);
+  if (plan.pair) form[4] = 2 * std::min(pair_clusters_for(plan.bn), plan.tiles_x * plan.tiles_y);
   form[5] = plan.pair ? 1 : 0;
   return VIPERA_OK;
 }
@@ -1308,19 +1339,8 @@ static int launch_pairs(const CUtensorMap& map_x, const CUtensorMap& map_y, cons
   attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attributes[1].val.programmaticStreamSerializationAllowed = vipera_pdl_enabled() ? 1 : 0;
   config.attrs = attributes;
-  static int clusters = 0;
-  if (clusters == 0) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Config::kSmemBytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    config.gridDim = dim3(2 * (sm_count() / 2));
-    config.numAttrs = 1;
-    int fit = 0;
-    if (cudaOccupancyMaxActiveClusters(&fit, kernel, &config) != cudaSuccess || fit <= 0) {
-      cudaGetLastError();
-      fit = sm_count() / 2;
-    }
-    clusters = std::min(fit, sm_count() / 2);
-  }
+  const int clusters = pair_clusters<BN>();
+  if (clusters <= 0) return VIPERA_BAD_ARGUMENT;   // (the plan does not choose pairs then)
   config.numAttrs = 2;
   config.gridDim = dim3(2 * std::min(items, clusters));
   cudaError_t error = cudaLaunchKernelEx(&config, kernel, map_x, map_y, map_out, p);
