@@ -215,7 +215,27 @@ def runtime_module():
     return module
 
 
+def _drop_stale(keep: Iterable[str]) -> None:
+    """Remove libraries in the build folder that no current source and flags lead to (every change
+    of a source file leaves one behind).  A library another process has loaded stays usable: the
+    file's name goes, not its contents."""
+    keep = {os.path.abspath(path) for path in keep}
+    out_dir = build_dir()
+    for name in os.listdir(out_dir):
+        path = os.path.abspath(os.path.join(out_dir, name))
+        try:
+            if name.startswith("libvipera_") and name.endswith(".so") and path not in keep:
+                os.remove(path)
+            elif name.startswith("runtime-") and os.path.isdir(path) and path not in keep:
+                shutil.rmtree(path, ignore_errors=True)
+        except OSError:
+            pass
+
+
 def build_all() -> None:
-    """Compile everything: the host runtime and every kernel family."""
-    runtime_module()
-    build_kernels(all_kernel_names())
+    """Compile everything: the host runtime and every kernel family; then clear the build folder
+    of what earlier sources left behind."""
+    module = runtime_module()
+    names = all_kernel_names()
+    build_kernels(names)
+    _drop_stale([kernel_library_path(name) for name in names] + [os.path.dirname(module.__file__)])
