@@ -1250,8 +1250,17 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
     const int tiles_alone = (plan.pair ? 2 : 1) * plan.tiles_x * plan.tiles_y;
     const bool forced = (plan.pair && pair_mode() > 1);   // tests ask for pairs on small sizes too
     if (narrow_swaps && !plan.even_shares && !forced && epilogue != EPI_ROPE_CACHE && 4 * tiles_alone < 3 * sms) {
-      plan.swap = true;
-      plan.pair = false;
+      // ... where cutting K gives it more blocks than this form has tiles (a [5120, 5120] matrix under
+      // 512 tokens has 80 tiles either way, and K is not cut at all: 163 us swapped, 52 like this)
+      const int bn_other = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+      const int tiles_other = ((N + kTileX - 1) / kTileX) * ((T + bn_other - 1) / bn_other);
+      const int want = std::max(1, std::min(sms / tiles_other, plan.num_k_blocks));
+      const int per_split = (plan.num_k_blocks + want - 1) / want;
+      const int splits_other = (plan.num_k_blocks + per_split - 1) / per_split;
+      if (4 * tiles_other * splits_other > 5 * tiles_alone) {
+        plan.swap = true;
+        plan.pair = false;
+      }
     }
   }
   if (plan.swap) {
