@@ -209,6 +209,57 @@ __device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr) {
   return desc;
 }
 
+// One block's work: a tile of 128 queries of an entry (entry < 0: none).
+struct Job {
+  int entry, tile;
+  int token0, tokens_here, pos0;   // the tile's first token in the step, how many it has, the first one's position
+};
+// Blocks are numbered from the back, and the heads run along x (the index that changes fastest
+// as blocks are handed out), so that the tiles with the longest history, of every head, start
+// first.  The step's entries are the host's, written before the step: they may be read before
+// the kernel waits for the one ahead.
+// A warp looks at 32 entries at a time, a lane each (one trip to memory for all of them).
+__device__ __forceinline__ Job find_job(const Params& p, int from_the_back, int lane) {
+  Job job{-1, 0, 0, 0, 0};
+  int remaining = from_the_back;
+  for (int e0 = 0; e0 < p.num_entries; e0 += 32) {
+    const int e = e0 + lane;
+    int start = 0, next = 0, first_position = 0;
+    if (e < p.num_entries) {
+      start = p.entry_starts[e];
+      next = p.entry_starts[e + 1];
+      first_position = p.entry_pos0[e];
+    }
+    const int count = next - start;
+    // entries of one token are left to the split-key kernel where the caller says so
+    const int tiles = (count <= 0 || (p.skip_single && count == 1)) ? 0 : (count + kQ - 1) / kQ;
+    // tiles of the lanes before this one, and of all 32
+    int before = tiles;
+#pragma unroll
+    for (int step = 1; step < 32; step <<= 1) {
+      const int other = __shfl_up_sync(0xffffffffu, before, step);
+      if (lane >= step) before += other;
+    }
+    const int all = __shfl_sync(0xffffffffu, before, 31);
+    before -= tiles;
+    const bool mine = remaining >= before && remaining < before + tiles;
+    const unsigned found = __ballot_sync(0xffffffffu, mine);
+    if (found) {
+      const int owner = __ffs(found) - 1;
+      const int tile = remaining - __shfl_sync(0xffffffffu, before, owner);
+      const int owner_start = __shfl_sync(0xffffffffu, start, owner), owner_next = __shfl_sync(0xffffffffu, next, owner);
+      job.entry = e0 + owner;
+      job.tile = tile;
+      job.token0 = owner_start + tile * kQ;
+      job.tokens_here = min(kQ, owner_next - job.token0);
+      job.pos0 = __shfl_sync(0xffffffffu, first_position, owner) + tile * kQ;
+      break;
+    }
+    remaining -= all;
+  }
+  return job;
+}
+
 struct Barriers {
   uint64_t q_full;
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
@@ -217,6 +268,7 @@ struct Barriers {
   uint64_t p_full[2], pv_done[2];  // per softmax group
   uint32_t tmem_base;
   int abort_flag;
+  Job job;
 };
 
 template <bool TMA_KV>
@@ -235,6 +287,36 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
+  // One thread finds the block's tile and hands it to the others through shared memory (each
+  // role reading the entry arrays for itself was three dependent trips to memory after the
+  // wait); a block without a tile leaves before it sets anything up.
+  if (warp == 0) {
+    const Job found = find_job(p, static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y), lane);
+    if (lane == 0) bars->job = found;
+  }
+  __syncthreads();
+  const Job job = bars->job;
+  if (job.entry < 0) return;
+  const int entry = job.entry;
+  const int head = blockIdx.x;
+  const int kv_head = head / (p.num_heads / p.num_kv_heads);
+  const int token0 = job.token0, tokens_here = job.tokens_here;
+  const int pos0 = job.pos0;                                  // position of the tile's first query
+  const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int end_key = pos0 + tokens_here;                     // one past the last visible key
+  const int first_tile = first_key / kKeys;
+  const int num_tiles = (end_key + kKeys - 1) / kKeys - first_tile;
+
+  // The pages of a loading warp's first tile are asked for now (the block table is the host's),
+  // so that the answer travels while the barriers and the tensor memory are set up.
+  int early_page = -1;
+  if (TMA_KV && warp >= kFirstLoaderWarp) {
+    const int stream_group = (warp - kFirstLoaderWarp) >> 1;
+    const int rows_per_box = min(p.page_size, kKeys);
+    const int key = (first_tile + stream_group) * kKeys + lane * rows_per_box;
+    if (stream_group < num_tiles && lane < kKeys / rows_per_box && key + rows_per_box > first_key && key < end_key)
+      early_page = p.block_table[static_cast<size_t>(entry) * p.table_width + key / p.page_size];
+  }
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, kLoaderThreads);
     for (int i = 0; i < 2; ++i) {
@@ -259,40 +341,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
-  pdl_wait();
-
-  // Which (entry, tile of that entry) is this block?  Blocks are numbered from the back, and
-  // the heads run along x (the index that changes fastest as blocks are handed out), so that
-  // the tiles with the longest history, of every head, start first.
-  int entry = -1, tile_in_entry = 0;
-  {
-    int remaining = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);
-    for (int e = 0; e < p.num_entries; ++e) {
-      const int count = p.entry_starts[e + 1] - p.entry_starts[e];
-      // entries of one token are left to the split-key kernel where the caller says so
-      const int tiles = (p.skip_single && count == 1) ? 0 : (count + kQ - 1) / kQ;
-      if (remaining < tiles) { entry = e; tile_in_entry = remaining; break; }
-      remaining -= tiles;
-    }
-  }
-  int num_tiles = 0, first_tile = 0, token0 = 0, tokens_here = 0, pos0 = 0, first_key = 0, end_key = 0;
-  const int head = blockIdx.x;
-  const int kv_head = head / (p.num_heads / p.num_kv_heads);
-  if (entry >= 0) {
-    token0 = p.entry_starts[entry] + tile_in_entry * kQ;
-    tokens_here = min(kQ, p.entry_starts[entry + 1] - token0);
-    pos0 = p.entry_pos0[entry] + tile_in_entry * kQ;  // position of the tile's first query
-    first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-    end_key = pos0 + tokens_here;                     // one past the last visible key
-    first_tile = first_key / kKeys;
-    num_tiles = (end_key + kKeys - 1) / kKeys - first_tile;
-  }
+  // (Each role waits for the kernels ahead where it first needs what they wrote: the loaders
+  // after they have looked up their first pages, the softmax warps at once; the issuing warps
+  // touch shared and tensor memory only.)
 
   if (warp < kSoftmaxWarps) {
     // ---------------- softmax and ending: thread = query row, group = every other key tile ----------------
     // Warps w and w + 4 share the rows 32 (w % 4) .. + 31 (a warp reaches only its quarter of
     // the tensor memory's lanes); they belong to different groups and so work on different key
     // tiles, independently, and fill each other's waits.
+    pdl_wait();   // the output belongs to earlier kernels until now
     const int quarter = warp & 3, group = warp >> 2;
     const int row = quarter * 32 + lane;
     const int position = pos0 + row;
@@ -427,28 +485,42 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       const bool own_has_tiles = group_tiles > 0;
       // each group writes half of the row's columns
       const int col0 = group * kHalfCols;
-      __nv_bfloat16* dst = p.out + (static_cast<size_t>(token0 + row) * p.num_heads + head) * kD + col0;
+      // The tile leaves through shared memory (the query tile's space: every product that read
+      // it is done once both groups' last output products are), so that a warp's store covers two
+      // whole rows of the output.  A thread writing its own row straight to memory makes 32 lines
+      // per store instruction; the block's eight warps then queue for 5,000 clocks.
+      uint8_t* staged = q_tile;
 #pragma unroll 1
       for (int c = 0; c < kHalfCols; c += 32) {
         uint32_t v[32], w[32];
         if (own_has_tiles) tmem_load_32_nowait(o_addr + col0 + c, v);
         if (other_has_tiles) tmem_load_32_nowait(other_o + col0 + c, w);
         tmem_load_wait();
-        if (row < tokens_here && !*abort_flag) {
-          float joined[32];
+        float joined[32];
 #pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            joined[k] = own_has_tiles ? __uint_as_float(v[k]) * own_factor : 0.0f;
-            if (other_has_tiles) joined[k] = fmaf(__uint_as_float(w[k]), other_factor, joined[k]);
-          }
+        for (int k = 0; k < 32; ++k) {
+          joined[k] = own_has_tiles ? __uint_as_float(v[k]) * own_factor : 0.0f;
+          if (other_has_tiles) joined[k] = fmaf(__uint_as_float(w[k]), other_factor, joined[k]);
+        }
 #pragma unroll
-          for (int k = 0; k < 32; k += 8) {
-            uint4 packed;
-            __nv_bfloat162* halves = reinterpret_cast<__nv_bfloat162*>(&packed);
+        for (int k = 0; k < 32; k += 8) {
+          uint4 packed;
+          __nv_bfloat162* halves = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-            for (int h = 0; h < 4; ++h) halves[h] = __floats2bfloat162_rn(joined[k + 2 * h], joined[k + 2 * h + 1]);
-            *reinterpret_cast<uint4*>(dst + c + k) = packed;
-          }
+          for (int h = 0; h < 4; ++h) halves[h] = __floats2bfloat162_rn(joined[k + 2 * h], joined[k + 2 * h + 1]);
+          *reinterpret_cast<uint4*>(staged + tile_offset(row, (col0 + c + k) >> 3)) = packed;
+        }
+      }
+      asm volatile("bar.sync 6, 256;" ::: "memory");
+      if (!*abort_flag) {
+        __nv_bfloat16* out_tile = p.out + (static_cast<size_t>(token0) * p.num_heads + head) * kD;
+        const size_t row_pitch = static_cast<size_t>(p.num_heads) * kD;
+#pragma unroll
+        for (int pass = 0; pass < kQ * 16 / (kSoftmaxWarps * 32); ++pass) {
+          const int id = pass * (kSoftmaxWarps * 32) + static_cast<int>(threadIdx.x);   // 16 neighbours copy one row
+          const int r = id >> 4, chunk = id & 15;
+          if (r < tokens_here)
+            *reinterpret_cast<uint4*>(out_tile + r * row_pitch + chunk * 8) = *reinterpret_cast<const uint4*>(staged + tile_offset(r, chunk));
         }
       }
     }
@@ -516,13 +588,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     const int t = threadIdx.x - kFirstLoaderWarp * 32;  // 0..127
     if (num_tiles > 0) {
       const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
-      for (int index = t; index < kQ * 16; index += kLoaderThreads) {
-        const int row = index >> 4, chunk = index & 15;
-        const bool valid = row < tokens_here;
-        const __nv_bfloat16* src = p.q + (static_cast<size_t>(token0 + (valid ? row : 0)) * p.num_heads + head) * kD + chunk * 8;
-        cp_async_16(smem_u32(q_tile) + tile_offset(row, chunk), src, valid);
-      }
-      cp_async_commit();
+      auto load_queries = [&]() {
+        for (int index = t; index < kQ * 16; index += kLoaderThreads) {
+          const int row = index >> 4, chunk = index & 15;
+          const bool valid = row < tokens_here;
+          const __nv_bfloat16* src = p.q + (static_cast<size_t>(token0 + (valid ? row : 0)) * p.num_heads + head) * kD + chunk * 8;
+          cp_async_16(smem_u32(q_tile) + tile_offset(row, chunk), src, valid);
+        }
+        cp_async_commit();
+      };
       if constexpr (TMA_KV) {
         // ---- keys and values by TMA: the first loader warp issues one box per page and half ----
         const int rows_per_box = min(p.page_size, kKeys);
@@ -573,7 +647,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         const int stream_group = loader_warp >> 1;
         const bool values = (loader_warp & 1) != 0;
         const int stream_tiles = (num_tiles - stream_group + 1) / 2;
-        int pages = stream_tiles > 0 ? look_up(stream_group) : -1;
+        // (the block table is the host's: the first look-up does not wait for the kernels ahead)
+        int pages = early_page;   // = look_up(stream_group), asked for before the set-up
+        pdl_wait();
+        load_queries();
         auto issue_tile = [&](int i) {   // the group's tile i
           const int j = 2 * i + stream_group;
           const int page = pages;
@@ -611,6 +688,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
           mbar_arrive(&bars->v_full[stream_group]);
         }
       } else {
+      pdl_wait();
+      load_queries();
       // A tile is copied in 16 passes of 8 rows: 16 consecutive threads copy the 16 chunks of
       // one cache row, so that global reads are whole 256-byte rows.  Where a page holds a power
       // of two of keys, page and slot come from a shift and a mask.
