@@ -107,6 +107,37 @@ def test_gemm(m, n, k, epilogue, kind):
     assert _rel(out, want) < limit
 
 
+@pytest.mark.parametrize("m,n,k", [(512, 1536, 8960), (1024, 1536, 2048), (600, 1000, 1024)])
+@pytest.mark.parametrize("epilogue", [0, 1, 2])
+def test_gemm_tc_split_sums_of_portions(m, n, k, epilogue):
+    """A few hundred tokens through a narrow matrix: K is cut, and the kernel that adds the partial
+    sums takes four outputs to a thread once there are enough of them."""
+    ops = _ops()
+    if epilogue == 2:
+        n = (n + 31) // 32 * 32
+    plan = ops.gemm_tc_plan(m, n, k, epilogue, epilogue != 2)
+    assert plan["swapped"] and plan["splits"] > 1, plan
+    torch.manual_seed(m + n + k)
+    a = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * 0.1).bfloat16()
+    bias = torch.randn(n, device=DEV)
+    resid0 = torch.randn(m, n, device=DEV)
+    for out_dtype in ([torch.float32, torch.bfloat16] if epilogue == 0 else [None]):
+        if epilogue == 0:
+            out = torch.full((m, n), float("nan"), device=DEV, dtype=out_dtype)
+            ops.gemm_tc(a, w, epilogue=0, bias=bias, out=out)
+        elif epilogue == 1:
+            out = resid0.clone()
+            ops.gemm_tc(a, w, epilogue=1, resid=out)
+        else:
+            out = torch.full((m, n // 2), float("nan"), device=DEV, dtype=torch.bfloat16)
+            ops.gemm_tc(a, w, epilogue=2, out=out)
+        torch.cuda.synchronize()
+        ops.check_kernel_status(a.device)
+        want = _gemm_reference(a, w, epilogue, bias, resid0)
+        assert _rel(out, want) < (5e-3 if out.dtype == torch.bfloat16 else 2e-5)
+
+
 def test_gemm_tc_repeats_exactly():
     """Split sums are added in a fixed order: the same product twice gives the same bits."""
     ops = _ops()
