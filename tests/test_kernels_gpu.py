@@ -765,15 +765,20 @@ def test_gemv_small_rope_cache():
 @pytest.mark.parametrize("heads,kv_heads,d", [(3, 1, 128), (6, 2, 64), (12, 2, 128)])
 @pytest.mark.parametrize("style_name", ["neox", "none"])
 @pytest.mark.parametrize("pairs", [0, 2])
-def test_gemm_tc_rope_cache(heads, kv_heads, d, style_name, pairs, request):
-    """The q/k/v product of many tokens on the tensor cores with its ending: bias, rotation of
-    the q and k pairs, q to its buffer, k and v to their pages; two entries, one of them at the
-    end of a longer history, pages in shuffled order.  With blocks alone, and on pairs of blocks."""
+@pytest.mark.parametrize("counts", [[200, 131], [40, 25], [100, 77]])
+def test_gemm_tc_rope_cache(heads, kv_heads, d, style_name, pairs, counts, request):
+    """The q/k/v product on the tensor cores with its ending: bias, rotation of the q and k pairs,
+    q to its buffer, k and v to their pages; two entries, one of them at the end of a longer
+    history, pages in shuffled order.  Many tokens (the ending inside the product kernel, with
+    blocks alone and on pairs of blocks) and fewer than 192 (K cut, the ending in the kernel
+    that adds the partial sums)."""
     ops = _ops()
+    if sum(counts) < 192 and pairs:
+        pytest.skip("pairs of blocks are for many tokens")
     before = ops.gemm_tc_pairs(pairs)
     request.addfinalizer(lambda: ops.gemm_tc_pairs(before))
     page, hidden = 16, 320
-    counts, firsts = [200, 131], [0, 77]
+    firsts = [0, 77]
     tokens = sum(counts)
     style = ops.ROPE_NEOX if style_name == "neox" else ops.ROPE_NONE
     torch.manual_seed(heads * 7 + d)

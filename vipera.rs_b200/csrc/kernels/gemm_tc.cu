@@ -1059,6 +1059,86 @@ splitk_finish4_kernel(const GemmParams p) {
   }
 }
 
+// The split sums of a q/k/v product of a few dozen to a few hundred tokens, with that product's
+// ending: a thread adds up, for one token and one head, four neighbouring values of the head's
+// first half and the four they are paired with in the second half, adds the biases, turns the
+// pairs by the token's position and writes q to its buffer, k and v into their cache pages.  (The
+// same sums, formulas and roundings as the split-sum kernel followed by the rotation kernel, in
+// one launch instead of two.)
+template <int BN>
+__global__ void __launch_bounds__(256)
+splitk_finish_rope_kernel(const GemmParams p) {
+  pdl_launch_dependents();
+  const int d = p.head_dim, half = d >> 1;
+  const int quads = half >> 2;                          // per head
+  const int all_heads = p.num_heads + 2 * p.num_kv_heads;
+  const long id = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const bool mine = id < static_cast<long>(p.tokens) * all_heads * quads;
+  const int t = mine ? static_cast<int>(id / (all_heads * quads)) : 0;
+  const int within = mine ? static_cast<int>(id % (all_heads * quads)) : 0;
+  const int head = within / quads, i = (within % quads) * 4;
+  // what the host wrote before the step is read before the wait
+  const int position = p.positions[t];
+  const bool is_q = head < p.num_heads;
+  const bool is_v = head >= p.num_heads + p.num_kv_heads;
+  __nv_bfloat16* dst = nullptr;
+  if (is_q) {
+    dst = p.q_out + (static_cast<size_t>(t) * p.num_heads + head) * d;
+  } else if (p.write_cache) {
+    const int page = p.block_table[static_cast<size_t>(p.token_entry[t]) * p.table_width + position / p.page_size];
+    if (page >= 0) {
+      const int kv_head = is_v ? head - p.num_heads - p.num_kv_heads : head - p.num_heads;
+      dst = (is_v ? p.v_pool : p.k_pool) +
+            ((static_cast<size_t>(page) * p.page_size + position % p.page_size) * p.num_kv_heads + kv_head) * d;
+    }
+  }
+  const bool rotate = !is_v && p.rope_style == GEMM_ROPE_NEOX;
+  float4 c4 = make_float4(1.0f, 1.0f, 1.0f, 1.0f), s4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  if (rotate) {
+    c4 = *reinterpret_cast<const float4*>(p.cos_table + static_cast<size_t>(position) * half + i);
+    s4 = *reinterpret_cast<const float4*>(p.sin_table + static_cast<size_t>(position) * half + i);
+  }
+  const int n_lo = head * d + i, n_hi = n_lo + half;
+  float4 b_lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), b_hi = b_lo;
+  if (p.bias) {
+    b_lo = *reinterpret_cast<const float4*>(p.bias + n_lo);
+    b_hi = *reinterpret_cast<const float4*>(p.bias + n_hi);
+  }
+  pdl_wait();
+  if (!mine || dst == nullptr) return;
+  const int ty = t / BN, col = t % BN;
+  auto total = [&](int n) {
+    const int tx = n / kTileX, row = n % kTileX;
+    const size_t tile = static_cast<size_t>(ty) * p.tiles_x + tx;
+    const float4* src = reinterpret_cast<const float4*>(p.scratch + ((tile * p.splits) * BN + col) * kTileX + row);
+    const size_t step = static_cast<size_t>(BN) * kTileX / 4;
+    float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int s0 = 0; s0 < p.splits; s0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = s0 + k < p.splits ? __ldcg(src + (s0 + k) * step) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (s0 + k < p.splits) { sum.x += v[k].x; sum.y += v[k].y; sum.z += v[k].z; sum.w += v[k].w; }
+      }
+    }
+    return sum;
+  };
+  float4 lo = total(n_lo), hi = total(n_hi);
+  lo = make_float4(lo.x + b_lo.x, lo.y + b_lo.y, lo.z + b_lo.z, lo.w + b_lo.w);
+  hi = make_float4(hi.x + b_hi.x, hi.y + b_hi.y, hi.z + b_hi.z, hi.w + b_hi.w);
+  if (rotate) {
+    const float4 a = lo, b = hi;
+    lo = make_float4(a.x * c4.x - b.x * s4.x, a.y * c4.y - b.y * s4.y, a.z * c4.z - b.z * s4.z, a.w * c4.w - b.w * s4.w);
+    hi = make_float4(a.x * s4.x + b.x * c4.x, a.y * s4.y + b.y * c4.y, a.z * s4.z + b.z * c4.z, a.w * s4.w + b.w * c4.w);
+  }
+  uint2 packed_lo, packed_hi;
+  packed_lo.x = pack_bf16x2(lo.x, lo.y); packed_lo.y = pack_bf16x2(lo.z, lo.w);
+  packed_hi.x = pack_bf16x2(hi.x, hi.y); packed_hi.y = pack_bf16x2(hi.z, hi.w);
+  *reinterpret_cast<uint2*>(dst + i) = packed_lo;
+  *reinterpret_cast<uint2*>(dst + half + i) = packed_hi;
+}
+
 // Even shares: one flag per block, up while that block's partial sum waits to be taken.  All
 // are 0 between launches (the taker lowers them); products run one after another on a stream.
 constexpr int kMostShares = 1024;
@@ -1388,6 +1468,10 @@ static int launch_variant(const CUtensorMap& map_x, const CUtensorMap& map_y, co
   }
   int status = vipera_launch(gemm_tc_kernel<BN, SWAP, false, EVEN>, grid, threads_for<BN>(), Config::kSmemBytes, s, map_x, map_y, map_out, p);
   if (status != VIPERA_OK || p.splits == 1) return status;   // (even shares run with splits == 1)
+  if (p.epilogue == EPI_ROPE_CACHE) {
+    const long threads = static_cast<long>(p.tokens) * (p.num_heads + 2 * p.num_kv_heads) * (p.head_dim / 8);
+    return vipera_launch(splitk_finish_rope_kernel<BN>, dim3(static_cast<unsigned>((threads + 255) / 256)), dim3(256), 0, s, p);
+  }
   const int width = p.epilogue == EPI_SWIGLU ? p.features / 2 : p.features;
   const long outputs = static_cast<long>(p.tokens) * width;
   // portions: four outputs to a thread where rows and pointers allow 16-byte accesses
@@ -1549,19 +1633,25 @@ struct GemmRope {
 
 VIPERA_API int vipera_gemm_tc_rope_size() { return static_cast<int>(sizeof(GemmRope)); }
 
-// Whether vipera_gemm_tc_rope takes these sizes: enough tokens for tiles with the tokens on
-// the 128-row side, heads of 64 or 128 values, whole heads in every 128-column step.
+// Whether vipera_gemm_tc_rope takes these sizes: heads of 64 or 128 values, whole heads in every
+// 128-column step, and either enough tokens for tiles with the tokens on the 128-row side or a
+// product whose K is cut.
 VIPERA_API int vipera_gemm_tc_rope_takes(int T, int N, int K, int head_dim) {
-  if (T < 128 + 64 || K <= 0 || K % 8 || N <= 0) return 0;
+  if (T <= 0 || K <= 0 || K % 8 || N <= 0) return 0;
   if (head_dim != 64 && head_dim != 128) return 0;
-  return N % head_dim == 0 ? 1 : 0;
+  if (N % head_dim) return 0;
+  if (T >= 128 + 64) return 1;
+  // fewer tokens: the form with the tokens on the other side, whose split sums' kernel has this
+  // ending; where K is not cut there is no such kernel
+  const GemmPlan plan = make_plan(T, N, K, sm_count(), EPI_ROPE_CACHE);
+  return plan.swap && plan.splits > 1 ? 1 : 0;
 }
 
 // The q/k/v product of a step with its ending: out = A . W^T + bias, rotary pairs of the q and k
 // heads turned by the tokens' positions, q written to q_out [T, heads * d] and k, v into their
 // cache pages (rope_style 0: no rotation).  N = (heads + 2 * kv_heads) * d.
 VIPERA_API int vipera_gemm_tc_rope(const void* A, const void* W, int T, int N, int K, const float* bias,
-                                   const GemmRope* rope, int* status, void* stream) {
+                                   const GemmRope* rope, float* scratch, size_t scratch_bytes, int* status, void* stream) {
   if (!rope || !vipera_gemm_tc_rope_takes(T, N, K, rope->head_dim)) return VIPERA_BAD_SHAPE;
   if (N != (rope->num_heads + 2 * rope->num_kv_heads) * rope->head_dim) return VIPERA_BAD_SHAPE;
   if (!rope->positions || !rope->q_out) return VIPERA_BAD_ARGUMENT;
@@ -1585,7 +1675,7 @@ VIPERA_API int vipera_gemm_tc_rope(const void* A, const void* W, int T, int N, i
   p.head_dim = rope->head_dim;
   p.rope_style = rope->rope_style;
   p.write_cache = rope->write_cache;
-  return run_gemm(A, W, T, N, K, EPI_ROPE_CACHE, bias, nullptr, VIPERA_BF16, nullptr, nullptr, 0, status, stream, &p);
+  return run_gemm(A, W, T, N, K, EPI_ROPE_CACHE, bias, nullptr, VIPERA_BF16, nullptr, scratch, scratch_bytes, status, stream, &p);
 }
 
 // ---------------------------------------------------------------------------------------

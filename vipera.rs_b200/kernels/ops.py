@@ -540,12 +540,14 @@ def gemm_tc_rope(a: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tenso
                  v_pool: torch.Tensor, token_entry: torch.Tensor, block_table: torch.Tensor, page_size: int,
                  write_cache: bool) -> None:
     """The q/k/v product of a step on the tensor cores with bias, rotation of q and k and the
-    write of keys and values into their pages as its ending (bfloat16, at least 192 tokens)."""
+    write of keys and values into their pages as its ending (bfloat16; from 192 tokens on in the
+    product kernel itself, below that in the kernel that adds the partial sums of the cut K)."""
     size = _function("gemm_tc", "vipera_gemm_tc_rope_size", [])()
     if size != ctypes.sizeof(_GemmRope):
         raise InternalError("the q/k/v ending's structure differs from its Python mirror")
     fn = _function("gemm_tc", "vipera_gemm_tc_rope",
-                   [_c_void, _c_void, _c_int, _c_int, _c_int, _c_void, ctypes.POINTER(_GemmRope), _c_void, _c_void])
+                   [_c_void, _c_void, _c_int, _c_int, _c_int, _c_void, ctypes.POINTER(_GemmRope), _c_void,
+                    ctypes.c_size_t, _c_void, _c_void])
     m, k = a.shape
     n = w.shape[0]
     if w.shape[1] != k or n != (num_heads + 2 * num_kv_heads) * head_dim:
@@ -566,9 +568,14 @@ def gemm_tc_rope(a: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tenso
     r.table_width, r.page_size = int(block_table.shape[1]), int(page_size)
     r.num_heads, r.num_kv_heads, r.head_dim = int(num_heads), int(num_kv_heads), int(head_dim)
     r.rope_style, r.write_cache = int(style), 1 if write_cache else 0
-    state = _tc_buffers(a.device, 0)
+    # (fewer than 192 tokens: K is cut, and the kernel that adds the partial sums has the ending)
+    scratch_bytes = gemm_tc_workspace(m, n, k)
+    state = _tc_buffers(a.device, scratch_bytes)
+    scratch = state["scratch"]
     _check(fn(_gpu(a, "a", torch.bfloat16), _gpu(w, "w", torch.bfloat16), m, n, k, _opt(bias, "bias", torch.float32),
-              ctypes.byref(r), state["status"].data_ptr(), _stream()), "gemm_tc_rope")
+              ctypes.byref(r), None if scratch is None else scratch.data_ptr(),
+              0 if scratch is None else scratch.numel() * 4, state["status"].data_ptr(), _stream()), "gemm_tc_rope",
+           kernels=2 if m < 192 else 1)
 
 
 def wait_probe(device, limit: int = 4096) -> None:
