@@ -73,3 +73,22 @@ def test_the_benchmarks_layer_sizes_match_plain(dtype):
     tolerance = 1e-4 if dtype == "float32" else 1e-2
     worst = helpers.compare(outputs, builder, reference, tolerance, f"1.5B layer sizes {dtype}")
     print(f"1.5B layer sizes, {dtype}: worst relative error {worst:.3e}")
+
+
+def test_a_long_portion_at_the_benchmarks_layer_sizes_matches_plain():
+    """A prompt of 1,700 tokens in one step and a few decode steps behind it, bfloat16: at this
+    length the feed-forward products run on pairs of blocks (tiles of 256 tokens), the q/k/v
+    product ends inside the product kernel and the attention of portions walks fourteen key
+    tiles; the tiny models never get there."""
+    folder = _folder()
+    vocab = CONFIG["vocab_size"]
+    tokens = helpers.random_tokens(vocab, 1704, 11)
+    builder = TraceBuilder()
+    builder.step([("p", tokens[:1700], [0, 127, 128, 1023, 1699])])
+    for position in range(1700, 1704):
+        builder.step([("p", tokens[position:position + 1], [0])], end=["p"] if position == 1703 else [])
+    outputs = helpers.run_trace(folder, "bfloat16", builder.steps, max_tokens=1728, page_size=16, timeout=1200)
+    config, weights = plain.read_config(folder), plain.read_weights(folder)
+    reference = {"p": plain.forward(config, weights, tokens, dtype=torch.float64, round_to=torch.bfloat16).numpy()}
+    worst = helpers.compare(outputs, builder, reference, 1e-2, "1.5B layer sizes, long portion")
+    print(f"1.5B layer sizes, 1,700-token portion: worst relative error {worst:.3e}")
