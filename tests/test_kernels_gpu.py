@@ -107,7 +107,7 @@ def test_gemm(m, n, k, epilogue, kind):
     assert _rel(out, want) < limit
 
 
-@pytest.mark.parametrize("m,n,k", [(512, 1536, 8960), (1024, 1536, 2048), (600, 1000, 1024)])
+@pytest.mark.parametrize("m,n,k", [(512, 1536, 8960), (1024, 1536, 8960), (600, 1000, 6144)])
 @pytest.mark.parametrize("epilogue", [0, 1, 2])
 def test_gemm_tc_split_sums_of_portions(m, n, k, epilogue):
     """A few hundred tokens through a narrow matrix: K is cut, and the kernel that adds the partial

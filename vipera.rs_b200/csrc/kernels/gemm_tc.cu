@@ -1386,20 +1386,27 @@ static GemmPlan make_plan(int T, int N, int K, int sms, int epilogue = EPI_STORE
     plan.k_blocks_per_split = plan.num_k_blocks;
     // A narrow matrix under a portion of a few hundred tokens has tiles for a fraction of the
     // SMs only (1,536 columns, 512 tokens: 32 tiles), and this form does not cut K.  The other
-    // form does: its tiles of 128 features x 256 tokens are cut along K until every SM has one.
-    // (The q/k/v ending exists in this form only.)
+    // form does: its tiles of 128 features x 256 tokens are cut along K until every SM has one,
+    // at the price of a second kernel that adds the partial sums.  Which is quicker is estimated
+    // where this form is a single wave (microseconds: 5 for a block's start and ending, 0.3 for a
+    // k-block, 6 for the second kernel and 1 more per 1.5 MB of partial sums; fitted to
+    // [1536, 1536], [1536, 8960], [3584, 3584] and [3584, 18944] under 192 to 1,792 tokens).
+    // (The q/k/v ending inside the product kernel exists in this form only.)
     static const bool narrow_swaps = std::getenv("VIPERA_GEMM_NARROW_NONSWAP") == nullptr;
-    const int tiles_alone = (plan.pair ? 2 : 1) * plan.tiles_x * plan.tiles_y;
     const bool forced = (plan.pair && pair_mode() > 1);   // tests ask for pairs on small sizes too
-    if (narrow_swaps && !plan.even_shares && !forced && epilogue != EPI_ROPE_CACHE && 4 * tiles_alone < 3 * sms) {
-      // ... where cutting K gives it more blocks than this form has tiles (a [5120, 5120] matrix under
-      // 512 tokens has 80 tiles either way, and K is not cut at all: 163 us swapped, 52 like this)
+    const int at_once = plan.pair ? std::max(1, pair_clusters_for(plan.bn)) : sms;
+    if (narrow_swaps && !plan.even_shares && !forced && epilogue != EPI_ROPE_CACHE && plan.tiles_x * plan.tiles_y <= at_once) {
+      const double this_form = 5.0 + plan.num_k_blocks * 0.3;
       const int bn_other = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
       const int tiles_other = ((N + kTileX - 1) / kTileX) * ((T + bn_other - 1) / bn_other);
       const int want = std::max(1, std::min(sms / tiles_other, plan.num_k_blocks));
       const int per_split = (plan.num_k_blocks + want - 1) / want;
       const int splits_other = (plan.num_k_blocks + per_split - 1) / per_split;
-      if (4 * tiles_other * splits_other > 5 * tiles_alone) {
+      const int waves_other = (tiles_other * splits_other + sms - 1) / sms;
+      // the second kernel: its launch and one trip to memory, and the partial sums it has to read
+      const double second = splits_other > 1 ? 6.0 + static_cast<double>(T) * N * splits_other * 4.0 / 1.5e6 : 0.0;
+      const double other_form = 5.0 + waves_other * per_split * 0.3 + second;
+      if (other_form + 5.0 < this_form) {   // (a margin: the estimate is coarse)
         plan.swap = true;
         plan.pair = false;
       }
