@@ -1596,9 +1596,14 @@ static int run_gemm(const void* A, const void* W, int T, int N, int K, int epilo
     }
   }
   if (plan.pair) {
-    if (plan.bn == 256) return launch_pairs<256>(map_x, map_y, map_out, p, items, s);
-    if (plan.bn == 192) return launch_pairs<192>(map_x, map_y, map_out, p, items, s);
-    return launch_pairs<128>(map_x, map_y, map_out, p, items, s);
+    const int launched = plan.bn == 256 ? launch_pairs<256>(map_x, map_y, map_out, p, items, s)
+                       : plan.bn == 192 ? launch_pairs<192>(map_x, map_y, map_out, p, items, s)
+                                        : launch_pairs<128>(map_x, map_y, map_out, p, items, s);
+    if (launched == VIPERA_OK) return launched;
+    // The device refused the clusters (nothing has run): from now on blocks alone, this product too.
+    cudaGetLastError();
+    pair_mode() = 0;
+    return run_gemm(A, W, T, N, K, epilogue, bias, out, out_dtype, resid, scratch, scratch_bytes, status, stream, rope);
   }
   if (plan.even_shares) {
     if (plan.bn == 256) return launch_variant<256, false, true>(map_x, map_y, map_out, p, grid, s);
