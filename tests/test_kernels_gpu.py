@@ -138,6 +138,47 @@ def test_gemm_tc_split_sums_of_portions(m, n, k, epilogue):
         assert _rel(out, want) < (5e-3 if out.dtype == torch.bfloat16 else 2e-5)
 
 
+def _random_gemm_shapes(count, seed):
+    g = torch.Generator().manual_seed(seed)
+    pick = lambda low, high: int(torch.randint(low, high + 1, (1,), generator=g))  # noqa: E731
+    shapes = []
+    for _ in range(count):
+        # token counts around every switch of form: 16/32/64/128 (tile widths), 33 and 192 (which
+        # side the tokens go), a few hundred (K cut or not), a few thousand (pairs of blocks)
+        m = pick(1, 40) if pick(0, 3) == 0 else pick(41, 300) if pick(0, 2) == 0 else pick(301, 2600)
+        n = 8 * pick(1, 64) if pick(0, 2) == 0 else 32 * pick(16, 160)
+        k = 8 * pick(1, 40) if pick(0, 2) == 0 else 64 * pick(4, 40) + 8 * pick(0, 7)
+        shapes.append((m, n, k, pick(0, 2)))
+    return shapes
+
+
+@pytest.mark.parametrize("m,n,k,epilogue", _random_gemm_shapes(48, 20240607))
+def test_gemm_tc_shapes_drawn_at_random(m, n, k, epilogue):
+    """The tensor-core product over shapes drawn at random (a fixed seed) around every switch of
+    its form, each ending: whatever form the plan picks must give the product."""
+    ops = _ops()
+    if epilogue == 2:
+        n = (n + 31) // 32 * 32
+    torch.manual_seed(m * 31 + n * 7 + k)
+    a = (torch.randn(m, k, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(n, k, device=DEV) * 0.1).bfloat16()
+    bias = torch.randn(n, device=DEV)
+    resid0 = torch.randn(m, n, device=DEV)
+    if epilogue == 0:
+        out = torch.full((m, n), float("nan"), device=DEV)
+        ops.gemm_tc(a, w, epilogue=0, bias=bias, out=out)
+    elif epilogue == 1:
+        out = resid0.clone()
+        ops.gemm_tc(a, w, epilogue=1, resid=out)
+    else:
+        out = torch.full((m, n // 2), float("nan"), device=DEV, dtype=torch.bfloat16)
+        ops.gemm_tc(a, w, epilogue=2, out=out)
+    torch.cuda.synchronize()
+    ops.check_kernel_status(a.device)
+    plan = ops.gemm_tc_plan(m, n, k, epilogue, epilogue != 2 and n % 4 == 0)
+    assert _rel(out, _gemm_reference(a, w, epilogue, bias, resid0)) < (5e-3 if epilogue == 2 else 2e-5), plan
+
+
 def test_gemm_tc_repeats_exactly():
     """Split sums are added in a fixed order: the same product twice gives the same bits."""
     ops = _ops()
