@@ -475,6 +475,16 @@ def test_attention_portions(heads, kv_heads, d, page, dtype, window):
                               num_entries=entries, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
                               scale=scale, window=window)
         assert _rel(out2.float().cpu().view(total, heads, d), want) < limit
+        # the mma.sync kernel that the switch leaves these head sizes to
+        os.environ["VIPERA_ATTENTION_TC"] = "0"
+        try:
+            out_mma = torch.full_like(qd, float("nan"))
+            ops.attention_prefill(qd, out_mma, kp, vp, entry_starts=starts, entry_pos0=pos0, block_table=tb,
+                                  num_entries=entries, num_heads=heads, num_kv_heads=kv_heads, head_dim=d,
+                                  scale=scale, window=window)
+        finally:
+            os.environ.pop("VIPERA_ATTENTION_TC", None)
+        assert _rel(out_mma.float().cpu().view(total, heads, d), want) < limit
         # the two kernels of a mixed step together: the flash kernel leaves entries of one token
         # out, the split-key kernel runs those and only those, at the rows of their tokens
         out3 = torch.full_like(qd, float("nan"))
@@ -498,19 +508,19 @@ def test_attention_portions(heads, kv_heads, d, page, dtype, window):
 @pytest.mark.parametrize("page", [8, 16, 24, 64, 128, 256])
 @pytest.mark.parametrize("window", [0, 300])
 @pytest.mark.parametrize("shuffle", [True, False])
-def test_attention_prefill_tensor_memory(page, window, shuffle):
-    """The tcgen05 kernel (head size 128) on portions that span several tiles of 128 queries and
+@pytest.mark.parametrize("heads,kv_heads,d", [(6, 2, 128), (5, 1, 64)])
+def test_attention_prefill_tensor_memory(page, window, shuffle, heads, kv_heads, d):
+    """The tcgen05 kernel (head sizes 128 and 64) on portions that span several tiles of 128 queries and
     of 128 keys: whole prompts, a portion at the end of a longer history, two tokens, one
     token; pages from 8 to 256 keys (TMA boxes per page; 24 goes the cp.async way), handed out
     in shuffled order or one after another (runs of pages are then fetched as one box), pages a
     window has passed given back and filled with NaN, and once with TMA switched off."""
     ops = _ops()
-    heads, kv_heads, d = 6, 2, 128
     lengths = [700, 333, 130, 1]
     counts = [700, 200, 2, 1]
     entries = len(lengths)
     lengths, counts, table, k_pool, v_pool, keys, values, q = _paged_case(
-        entries, heads, kv_heads, d, page, torch.bfloat16, seed=page + window, lengths=lengths, counts=counts,
+        entries, heads, kv_heads, d, page, torch.bfloat16, seed=page + window + d, lengths=lengths, counts=counts,
         shuffle=shuffle)
     scale = 1.0 / math.sqrt(d)
     want = _attention_reference(q, keys, values, lengths, counts, heads, kv_heads, scale, window)
@@ -537,11 +547,12 @@ def test_attention_prefill_tensor_memory(page, window, shuffle):
         assert _rel(out.float().cpu().view(total, heads, d), want) < 1e-2, (page, window, no_tma)
 
 
-def test_attention_prefill_tensor_memory_finds_one_far_key():
+@pytest.mark.parametrize("d", [128, 64])
+def test_attention_prefill_tensor_memory_finds_one_far_key(d):
     """One key far back, in a tile of its own, scaled so that its score stands out: every
     query of a long portion must return that key's value."""
     ops = _ops()
-    heads, kv_heads, d, page, n = 2, 1, 128, 16, 900
+    heads, kv_heads, page, n = 2, 1, 16, 900
     for far in (0, 127, 128, 511, 640):
         lengths, counts, table, k_pool, v_pool, keys, values, q = _paged_case(
             1, heads, kv_heads, d, page, torch.bfloat16, seed=far + 5, lengths=[n], counts=[200])

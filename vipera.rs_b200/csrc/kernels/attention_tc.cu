@@ -1,15 +1,15 @@
 // bfloat16 attention of prompt portions over the paged cache on the fifth-generation tensor
-// cores (tcgen05, accumulators in tensor memory), head size 128.
+// cores (tcgen05, accumulators in tensor memory), head sizes 64 and 128.
 //
 // One block serves 128 queries of one entry and one query head and walks the visible keys
 // 128 at a time, in the flash form of the reference's online fold
 // (crates/vipera-backend-cpu/src/model.rs:2752-2857; definition model.rs:1804-1859):
 //
-//   scores  S = Q . K^T        tcgen05.mma, 128 x 128 x 128, into tensor memory
+//   scores  S = Q . K^T        tcgen05.mma, 128 x 128 x d, into tensor memory
 //   softmax                    one query row per thread: running max and sum in 32-bit,
 //                              p = 2^(s * scale * log2 e - max), rounded to bfloat16 into
 //                              shared memory
-//   output  O += P . V         tcgen05.mma, 128 x 128 x 128, accumulated in tensor memory;
+//   output  O += P . V         tcgen05.mma, 128 x d x 128, accumulated in tensor memory;
 //                              when a row's max grows, its accumulator is scaled first
 //
 // The key tiles are dealt to two softmax groups of four warps, even tiles to one and odd tiles
@@ -46,14 +46,12 @@ enum { ATTENTION_TC_WAIT_EXPIRED = 3 };
 
 namespace {
 
-constexpr int kD = 128;                 // head size
 constexpr int kQ = 128;                 // queries per block
 constexpr int kKeys = 128;              // keys per tile
-constexpr int kTileBytes = 128 * 256;   // a [128][128] bfloat16 tile: two halves of [128 rows][128 bytes]
+constexpr int kTileBytes = 128 * 256;   // a [128][128] bfloat16 tile: two halves of [128 rows][128 bytes]; head size 64 fills one
 constexpr int kHalfBytes = 128 * 128;
 constexpr int kSoftmaxWarps = 8, kLoaderWarps = 4;   // two softmax groups of four warps
 constexpr int kGroupThreads = 128;
-constexpr int kHalfCols = 64;            // output columns of a row one thread writes in the ending
 constexpr int kMmaWarp = kSoftmaxWarps;           // and the next one: an MMA issuer per softmax group
 constexpr int kFirstLoaderWarp = kSoftmaxWarps + 2;
 constexpr int kThreads = (kSoftmaxWarps + 2 + kLoaderWarps) * 32;
@@ -65,9 +63,9 @@ constexpr float kMaxSlack = 8.0f;       // in powers of two
 constexpr uint32_t kColsS0 = 0, kColsS1 = 128, kColsO0 = 256, kColsO1 = 384, kTmemCols = 512;
 
 struct Params {
-  const __nv_bfloat16* q;      // [tokens, heads, 128]
-  __nv_bfloat16* out;          // [tokens, heads, 128]
-  const __nv_bfloat16* k_pool; // [pages, page_size, kv_heads, 128]
+  const __nv_bfloat16* q;      // [tokens, heads, d]
+  __nv_bfloat16* out;          // [tokens, heads, d]
+  const __nv_bfloat16* k_pool; // [pages, page_size, kv_heads, d]
   const __nv_bfloat16* v_pool;
   const int* entry_starts;     // [entries + 1]
   const int* entry_pos0;       // [entries]
@@ -180,8 +178,9 @@ __device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t (&r
 }
 __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// A tile in shared memory: two halves (columns 0-63 and 64-127) of [128 rows][128 bytes], the
-// 16-byte chunks of a row XOR-swizzled by the row (the 128-byte swizzle of the tensor cores).
+// A tile in shared memory: halves (columns 0-63 and, where there are more, 64-127) of
+// [128 rows][128 bytes], the 16-byte chunks of a row XOR-swizzled by the row (the 128-byte
+// swizzle of the tensor cores).
 __device__ __forceinline__ uint32_t tile_offset(int row, int chunk /* 0..15 */) {
   return static_cast<uint32_t>((chunk >> 3) * kHalfBytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
@@ -271,7 +270,7 @@ struct Barriers {
   Job job;
 };
 
-template <bool TMA_KV>
+template <int D, bool TMA_KV>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                             const __grid_constant__ CUtensorMap k_run_map, const __grid_constant__ CUtensorMap v_run_map,
@@ -285,6 +284,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
   Barriers* bars = reinterpret_cast<Barriers*>(smem + 7 * kTileBytes);
   volatile int* abort_flag = &bars->abort_flag;
 
+  static_assert(D == 64 || D == 128, "whole halves of 64 values");
+  constexpr int kHalves = D / 64;      // halves of a query, key or value tile
+  constexpr int kChunks = D / 8;       // 16-byte chunks of a row
+  constexpr int kHalfCols = D / 2;     // output columns of a row one thread writes in the ending
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
   // One thread finds the block's tile and hands it to the others through shared memory (each
@@ -411,7 +414,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       tcgen05_fence_after();
       if (i > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
-        for (int c = 0; c < kD; c += 32) {
+        for (int c = 0; c < D; c += 32) {
           uint32_t v[32];
           tmem_load_32(o_addr + c, v);
 #pragma unroll
@@ -513,12 +516,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       }
       asm volatile("bar.sync 6, 256;" ::: "memory");
       if (!*abort_flag) {
-        __nv_bfloat16* out_tile = p.out + (static_cast<size_t>(token0) * p.num_heads + head) * kD;
-        const size_t row_pitch = static_cast<size_t>(p.num_heads) * kD;
+        __nv_bfloat16* out_tile = p.out + (static_cast<size_t>(token0) * p.num_heads + head) * D;
+        const size_t row_pitch = static_cast<size_t>(p.num_heads) * D;
 #pragma unroll
-        for (int pass = 0; pass < kQ * 16 / (kSoftmaxWarps * 32); ++pass) {
-          const int id = pass * (kSoftmaxWarps * 32) + static_cast<int>(threadIdx.x);   // 16 neighbours copy one row
-          const int r = id >> 4, chunk = id & 15;
+        for (int pass = 0; pass < kQ * kChunks / (kSoftmaxWarps * 32); ++pass) {
+          const int id = pass * (kSoftmaxWarps * 32) + static_cast<int>(threadIdx.x);   // neighbours copy one row
+          const int r = id / kChunks, chunk = id % kChunks;
           if (r < tokens_here)
             *reinterpret_cast<uint4*>(out_tile + r * row_pitch + chunk * 8) = *reinterpret_cast<const uint4*>(staged + tile_offset(r, chunk));
         }
@@ -530,9 +533,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     const int g = warp - kMmaWarp;
     const int group_tiles = (num_tiles - g + 1) / 2;
     if (lane == 0 && group_tiles > 0) {
-      // instruction descriptors: bf16 x bf16 -> f32, M = 128, N = 128; B K-major for the scores, MN-major for the output
-      constexpr uint32_t kIdescS = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kKeys >> 3) << 17) | (static_cast<uint32_t>(kQ >> 4) << 24);
-      constexpr uint32_t kIdescO = kIdescS | (1u << 16);
+      // instruction descriptors: bf16 x bf16 -> f32, M = 128; N = 128 keys and B K-major for the
+      // scores, N = d and B MN-major for the output
+      constexpr uint32_t kIdescCommon = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kQ >> 4) << 24);
+      constexpr uint32_t kIdescS = kIdescCommon | (static_cast<uint32_t>(kKeys >> 3) << 17);
+      constexpr uint32_t kIdescO = kIdescCommon | (static_cast<uint32_t>(D >> 3) << 17) | (1u << 16);
       const uint32_t q_addr = smem_u32(q_tile);
       // Tile j belongs to softmax group j & 1 and is that group's tile number j >> 1; its keys
       // and values lie in buffer j & 1 as well.  The two groups drift against one another, so
@@ -549,7 +554,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
         if (i > 0) mbar_wait(&bars->s_empty[g], static_cast<uint32_t>(i - 1) & 1u, abort_flag, p.status);
         tcgen05_fence_after();
 #pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks) {
+        for (int ks = 0; ks < D / 16; ++ks) {
           // 16 values further along the row: 32 bytes inside a half, the other half after 4 steps
           const uint32_t offset = static_cast<uint32_t>((ks >> 2) * kHalfBytes + (ks & 3) * 32);
           tcgen05_mma_bf16(s_tmem, desc_k_major(q_addr + offset), desc_k_major(k_addr + offset), kIdescS, ks > 0 ? 1u : 0u);
@@ -589,10 +594,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
     if (num_tiles > 0) {
       const int* table = p.block_table + static_cast<size_t>(entry) * p.table_width;
       auto load_queries = [&]() {
-        for (int index = t; index < kQ * 16; index += kLoaderThreads) {
-          const int row = index >> 4, chunk = index & 15;
+        for (int index = t; index < kQ * kChunks; index += kLoaderThreads) {
+          const int row = index / kChunks, chunk = index % kChunks;
           const bool valid = row < tokens_here;
-          const __nv_bfloat16* src = p.q + (static_cast<size_t>(token0 + (valid ? row : 0)) * p.num_heads + head) * kD + chunk * 8;
+          const __nv_bfloat16* src = p.q + (static_cast<size_t>(token0 + (valid ? row : 0)) * p.num_heads + head) * D + chunk * 8;
           cp_async_16(smem_u32(q_tile) + tile_offset(row, chunk), src, valid);
         }
         cp_async_commit();
@@ -623,19 +628,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
             // the wanted boxes must be the first ones, one after another
             if (page0 >= 0 && __all_sync(0xffffffffu, in_run) && (wanted & (wanted + 1u)) == 0u) {
               if (lane == 0) {
-                mbar_expect_tx(landed, static_cast<uint32_t>(kKeys * 256));
-                tma_load_run(tile, run_map, landed, 0, kv_head, page0 * p.page_size);
-                tma_load_run(tile + kHalfBytes, run_map, landed, 64, kv_head, page0 * p.page_size);
+                mbar_expect_tx(landed, static_cast<uint32_t>(kKeys * D * 2));
+#pragma unroll
+                for (int h = 0; h < kHalves; ++h) tma_load_run(tile + h * kHalfBytes, run_map, landed, 64 * h, kv_head, page0 * p.page_size);
               }
               return;
             }
           }
-          if (lane == 0) mbar_expect_tx(landed, static_cast<uint32_t>(__popc(fetched) * rows_per_box * 256));
+          if (lane == 0) mbar_expect_tx(landed, static_cast<uint32_t>(__popc(fetched) * rows_per_box * D * 2));
           __syncwarp();
           if (page >= 0) {
             uint8_t* dst = tile + lane * rows_per_box * 128;
-            tma_load_box(dst, map, landed, 0, kv_head, key % p.page_size, page);
-            tma_load_box(dst + kHalfBytes, map, landed, 64, kv_head, key % p.page_size, page);
+#pragma unroll
+            for (int h = 0; h < kHalves; ++h) tma_load_box(dst + h * kHalfBytes, map, landed, 64 * h, kv_head, key % p.page_size, page);
           }
         };
         // Four streams with waits of their own, a loader warp each: the keys and the values of
@@ -680,7 +685,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
               const int key = key0 + r;
               if (key < first_key || key >= end_key) {
 #pragma unroll
-                for (int chunk = 0; chunk < 16; ++chunk) *reinterpret_cast<uint4*>(tile + tile_offset(r, chunk)) = make_uint4(0, 0, 0, 0);
+                for (int chunk = 0; chunk < kChunks; ++chunk) *reinterpret_cast<uint4*>(tile + tile_offset(r, chunk)) = make_uint4(0, 0, 0, 0);
               }
             }
             fence_async_shared();
@@ -690,30 +695,31 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map, const __g
       } else {
       pdl_wait();
       load_queries();
-      // A tile is copied in 16 passes of 8 rows: 16 consecutive threads copy the 16 chunks of
-      // one cache row, so that global reads are whole 256-byte rows.  Where a page holds a power
+      // A tile is copied in passes of 8 rows (16 with head size 64): consecutive threads copy the
+      // chunks of one cache row, so that global reads are whole rows.  Where a page holds a power
       // of two of keys, page and slot come from a shift and a mask.
+      constexpr int kRowsPerPass = kLoaderThreads / kChunks, kPasses = kKeys / kRowsPerPass;
       const int page_shift = (p.page_size & (p.page_size - 1)) == 0 ? 31 - __clz(p.page_size) : -1;
-      const long long row_stride = static_cast<long long>(p.num_kv_heads) * kD;
+      const long long row_stride = static_cast<long long>(p.num_kv_heads) * D;
       auto copy_tile = [&](int j, const __nv_bfloat16* pool, uint32_t dst) {
-        const int key_base = (first_tile + j) * kKeys + (t >> 4);
-        const int chunk = t & 15;
-        const __nv_bfloat16* base = pool + static_cast<long long>(kv_head) * kD + chunk * 8;
+        const int key_base = (first_tile + j) * kKeys + t / kChunks;
+        const int chunk = t % kChunks;
+        const __nv_bfloat16* base = pool + static_cast<long long>(kv_head) * D + chunk * 8;
         // the block table first (independent reads), then the copies
-        int pages[16];
+        int pages[kPasses];
 #pragma unroll
-        for (int pass = 0; pass < 16; ++pass) {
-          const int key = key_base + pass * 8;
+        for (int pass = 0; pass < kPasses; ++pass) {
+          const int key = key_base + pass * kRowsPerPass;
           pages[pass] = -1;
           if (key >= first_key && key < end_key) pages[pass] = table[page_shift >= 0 ? key >> page_shift : key / p.page_size];
         }
 #pragma unroll
-        for (int pass = 0; pass < 16; ++pass) {
-          const int key = key_base + pass * 8;
+        for (int pass = 0; pass < kPasses; ++pass) {
+          const int key = key_base + pass * kRowsPerPass;
           const int slot = page_shift >= 0 ? key & (p.page_size - 1) : key % p.page_size;
           const bool valid = pages[pass] >= 0;
           const long long at = valid ? (static_cast<long long>(pages[pass]) * p.page_size + slot) * row_stride : 0;
-          cp_async_16(dst + tile_offset(pass * 8 + (t >> 4), chunk), base + at, valid);
+          cp_async_16(dst + tile_offset(pass * kRowsPerPass + t / kChunks, chunk), base + at, valid);
         }
         cp_async_commit();
       };
@@ -792,16 +798,17 @@ bool tma_takes_page(int page_size) {
   return page_size % 8 == 0 && (kKeys % page_size == 0 || page_size % kKeys == 0);
 }
 
-// A cache pool [pages, page_size, kv_heads, 128] as TMA reads it: boxes of one page's rows
+// A cache pool [pages, page_size, kv_heads, d] as TMA reads it: boxes of one page's rows
 // (at most 128) of one KV head and 64 values, 128-byte swizzle.  Maps are kept by pool.
 // `run`: the same pool as rows that follow one another whatever page they are in,
-// [pages * page_size, kv_heads, 128], in boxes of 128 rows.
+// [pages * page_size, kv_heads, d], in boxes of 128 rows.
 // The map is copied out under the lock: the table may be emptied by a later call.
-bool pool_map(const void* pool, int pages, int page_size, int kv_heads, bool run, CUtensorMap* out) {
-  static std::map<std::tuple<const void*, int, int, int, bool>, CUtensorMap> kept;
+bool pool_map(const void* pool, int pages, int page_size, int kv_heads, int head_dim, bool run, CUtensorMap* out) {
+  static std::map<std::tuple<const void*, int, int, int, int, bool>, CUtensorMap> kept;
   static std::mutex guard;
   std::lock_guard<std::mutex> lock(guard);
-  const auto key = std::make_tuple(pool, pages, page_size, kv_heads, run);
+  const auto key = std::make_tuple(pool, pages, page_size, kv_heads, head_dim, run);
+  const cuuint64_t d = static_cast<cuuint64_t>(head_dim);
   auto found = kept.find(key);
   if (found != kept.end()) {
     *out = found->second;
@@ -811,9 +818,9 @@ bool pool_map(const void* pool, int pages, int page_size, int kv_heads, bool run
   if (!encode || (reinterpret_cast<uintptr_t>(pool) & 15)) return false;
   CUtensorMap map;
   if (run) {
-    cuuint64_t dims[3] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(kv_heads),
+    cuuint64_t dims[3] = {d, static_cast<cuuint64_t>(kv_heads),
                           static_cast<cuuint64_t>(pages) * page_size};
-    cuuint64_t strides[2] = {static_cast<cuuint64_t>(kD) * 2, static_cast<cuuint64_t>(kv_heads) * kD * 2};
+    cuuint64_t strides[2] = {d * 2, static_cast<cuuint64_t>(kv_heads) * d * 2};
     cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(kKeys)};
     cuuint32_t elem[3] = {1, 1, 1};
     CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(pool), dims, strides, box, elem,
@@ -825,10 +832,10 @@ bool pool_map(const void* pool, int pages, int page_size, int kv_heads, bool run
     *out = map;
     return true;
   }
-  cuuint64_t dims[4] = {static_cast<cuuint64_t>(kD), static_cast<cuuint64_t>(kv_heads), static_cast<cuuint64_t>(page_size),
+  cuuint64_t dims[4] = {d, static_cast<cuuint64_t>(kv_heads), static_cast<cuuint64_t>(page_size),
                         static_cast<cuuint64_t>(pages)};
-  cuuint64_t strides[3] = {static_cast<cuuint64_t>(kD) * 2, static_cast<cuuint64_t>(kv_heads) * kD * 2,
-                           static_cast<cuuint64_t>(page_size) * kv_heads * kD * 2};
+  cuuint64_t strides[3] = {d * 2, static_cast<cuuint64_t>(kv_heads) * d * 2,
+                           static_cast<cuuint64_t>(page_size) * kv_heads * d * 2};
   cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(page_size < kKeys ? page_size : kKeys), 1};
   cuuint32_t elem[4] = {1, 1, 1, 1};
   CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(pool), dims, strides, box, elem,
@@ -841,22 +848,22 @@ bool pool_map(const void* pool, int pages, int page_size, int kv_heads, bool run
   return true;
 }
 
-template <bool TMA_KV>
+template <int D, bool TMA_KV>
 int launch_attention(const CUtensorMap& k_map, const CUtensorMap& v_map, const CUtensorMap& k_run_map,
                      const CUtensorMap& v_run_map, const Params& p, dim3 grid, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<TMA_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<D, TMA_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  return vipera_launch(attention_prefill_tc_kernel<TMA_KV>, grid, dim3(kThreads), kSmemBytes, stream, k_map, v_map, k_run_map,
+  return vipera_launch(attention_prefill_tc_kernel<D, TMA_KV>, grid, dim3(kThreads), kSmemBytes, stream, k_map, v_map, k_run_map,
                        v_run_map, p);
 }
 
 }  // namespace
 
-// Attention of a step with portions of any length, head size 128 (see attention_mma.cu for the
+// Attention of a step with portions of any length, head size 64 or 128 (see attention_mma.cu for the
 // meaning of the arguments; `num_pages` is the pools' first extent).  `status` is a device word
 // that must be 0 before the launch; it is non-zero afterwards when a bounded wait inside the
 // kernel ran out.
@@ -866,7 +873,7 @@ VIPERA_API int vipera_attention_prefill_tc(const void* q, void* out, const void*
                                            int num_heads, int num_kv_heads, int head_dim, float scale, int window,
                                            int num_pages, int skip_single, int* status, void* stream) {
   if (num_tokens <= 0 || num_entries <= 0) return VIPERA_OK;
-  if (head_dim != kD || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || num_pages <= 0)
+  if ((head_dim != 64 && head_dim != 128) || num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads || page_size <= 0 || num_pages <= 0)
     return VIPERA_BAD_SHAPE;
   if (!status) return VIPERA_BAD_ARGUMENT;
   Params p{};
@@ -891,14 +898,16 @@ VIPERA_API int vipera_attention_prefill_tc(const void* q, void* out, const void*
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (tma_takes_page(page_size) && std::getenv("VIPERA_ATTENTION_NO_TMA") == nullptr) {
     CUtensorMap k_map, v_map, k_run, v_run;
-    if (pool_map(k_pool, num_pages, page_size, num_kv_heads, false, &k_map) &&
-        pool_map(v_pool, num_pages, page_size, num_kv_heads, false, &v_map) &&
-        pool_map(k_pool, num_pages, page_size, num_kv_heads, true, &k_run) &&
-        pool_map(v_pool, num_pages, page_size, num_kv_heads, true, &v_run))
-      return launch_attention<true>(k_map, v_map, k_run, v_run, p, grid, s);
+    if (pool_map(k_pool, num_pages, page_size, num_kv_heads, head_dim, false, &k_map) &&
+        pool_map(v_pool, num_pages, page_size, num_kv_heads, head_dim, false, &v_map) &&
+        pool_map(k_pool, num_pages, page_size, num_kv_heads, head_dim, true, &k_run) &&
+        pool_map(v_pool, num_pages, page_size, num_kv_heads, head_dim, true, &v_run))
+      return head_dim == 64 ? launch_attention<64, true>(k_map, v_map, k_run, v_run, p, grid, s)
+                            : launch_attention<128, true>(k_map, v_map, k_run, v_run, p, grid, s);
   }
   CUtensorMap none{};
-  return launch_attention<false>(none, none, none, none, p, grid, s);
+  return head_dim == 64 ? launch_attention<64, false>(none, none, none, none, p, grid, s)
+                        : launch_attention<128, false>(none, none, none, none, p, grid, s);
 }
 
 VIPERA_API const char* vipera_attention_tc_status_text(int status) { return vipera_status_text(status); }

@@ -598,7 +598,7 @@ def check_kernel_status(device) -> None:
 # bfloat16 attention on the tensor cores
 # ----------------------------------------------------------------------------------------
 MMA_HEAD_DIMS = (64, 128)
-TC_ATTENTION_HEAD_DIM = 128
+TC_ATTENTION_HEAD_DIMS = (64, 128)
 
 
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
@@ -606,8 +606,8 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
                       num_entries: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                       window: int = 0, skip_single: bool = False) -> None:
     """Flash-style attention of a step whose entries bring any number of tokens (bfloat16,
-    head sizes 64 and 128).  Head size 128 runs on tcgen05 with accumulators in tensor memory
-    (VIPERA_ATTENTION_TC=0 keeps it on the mma.sync kernel, which also serves head size 64).
+    head sizes 64 and 128), on tcgen05 with accumulators in tensor memory
+    (VIPERA_ATTENTION_TC=0 keeps it on the mma.sync kernel).
     ``skip_single`` leaves entries of one token out: attention_decode with ``entry_starts`` runs them."""
     if head_dim not in MMA_HEAD_DIMS:
         raise UnsupportedError(f"attention_prefill: head size {head_dim} (built: 64, 128)")
@@ -623,7 +623,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
              float(scale), int(window or 0))
     kinds = [_c_void] * 7 + [_c_int] * 7 + [_c_float, _c_int]
     skip = 1 if skip_single else 0
-    if head_dim == TC_ATTENTION_HEAD_DIM and os.environ.get("VIPERA_ATTENTION_TC", "1") != "0":
+    if head_dim in TC_ATTENTION_HEAD_DIMS and os.environ.get("VIPERA_ATTENTION_TC", "1") != "0":
         fn = _function("attention_tc", "vipera_attention_prefill_tc", kinds + [_c_int, _c_int, _c_void, _c_void])
         _check(fn(*pointers, *sizes, k_pool.shape[0], skip, kernel_status_word(q.device).data_ptr(), _stream()),
                "attention_prefill_tc")

@@ -75,12 +75,12 @@ class GQAttention(Mixer):
         self.position = POSITION_ENCODINGS.find(position.kind)(position.params, prefix, tensors, dtype, device)
 
     def kernel_families(self):
-        # the tensor-core attention kernels serve bfloat16 with head sizes 64 and 128 (the tcgen05
-        # one 128 only); everything else runs through the general kernel
+        # the tensor-core attention kernels serve bfloat16 with head sizes 64 and 128; everything
+        # else runs through the general kernel
         own = ["rope_cache", "attention"]
         if self.dtype == torch.bfloat16 and self.head_dim in (64, 128):
             own.append("attention_mma")
-            if self.head_dim == ops.TC_ATTENTION_HEAD_DIM:
+            if self.head_dim in ops.TC_ATTENTION_HEAD_DIMS:
                 own.append("attention_tc")
         return tuple(dict.fromkeys(tuple(own) + self.qkv.kernel_families() + self.out.kernel_families()
                                    + self.position.kernel_families()))
