@@ -45,6 +45,12 @@ QWEN25_1P5B = {
     "max_position_embeddings": 32768, "use_sliding_window": False, "sliding_window": 32768,
     "max_window_layers": 21,
 }
+QWEN25_0P5B = {   # head size 64
+    "architectures": ["Qwen2ForCausalLM"], "num_hidden_layers": 24, "hidden_size": 896,
+    "num_attention_heads": 14, "num_key_value_heads": 2, "intermediate_size": 4864, "vocab_size": 151936,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+    "max_position_embeddings": 32768, "use_sliding_window": False,
+}
 QWEN25_7B = {
     "architectures": ["Qwen2ForCausalLM"], "num_hidden_layers": 28, "hidden_size": 3584,
     "num_attention_heads": 28, "num_key_value_heads": 4, "intermediate_size": 18944, "vocab_size": 152064,
@@ -57,8 +63,8 @@ QWEN25_32B = {
     "rope_theta": 1000000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
     "max_position_embeddings": 32768, "use_sliding_window": False,
 }
-SHAPES = {"1.5b": ("Qwen2.5-1.5B shape", QWEN25_1P5B), "7b": ("Qwen2.5-7B shape", QWEN25_7B),
-          "32b": ("Qwen2.5-32B shape", QWEN25_32B)}
+SHAPES = {"0.5b": ("Qwen2.5-0.5B shape", QWEN25_0P5B), "1.5b": ("Qwen2.5-1.5B shape", QWEN25_1P5B),
+          "7b": ("Qwen2.5-7B shape", QWEN25_7B), "32b": ("Qwen2.5-32B shape", QWEN25_32B)}
 FULL_LAYERS = 28
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
