@@ -1,0 +1,36 @@
+"""Host-side rules of the kernels' wrappers that need no device: how a decode step's keys are
+cut for the split-key attention (vipera.rs_b200/kernels/ops.py, decode_splits).  A cut that does
+not cover the longest history would leave keys out without any error, so the properties are
+checked over every size a step can have."""
+import random
+
+import vipera_rs_b200  # noqa: F401
+from vipera_rs_b200.kernels import ops
+
+
+def _check(entries, kv_heads, keys, sms):
+    chunk, splits = ops.decode_splits(entries, kv_heads, keys, sms)
+    assert chunk >= 128 and chunk % 128 == 0, (entries, kv_heads, keys, sms, chunk)
+    assert 1 <= splits <= 64, (entries, kv_heads, keys, sms, splits)        # the combine kernel holds at most 128
+    assert chunk * splits >= keys, (entries, kv_heads, keys, sms, chunk, splits)
+    assert chunk * (splits - 1) < keys, "no split without keys for the longest history"
+    return chunk, splits
+
+
+def test_the_cut_of_a_decode_steps_keys_covers_every_history():
+    for keys in list(range(1, 700)) + [2047, 2048, 2049, 4096, 8191, 8192, 32768, 131072, 1000003]:
+        for entries, kv_heads in ((1, 1), (1, 2), (8, 2), (64, 2), (48, 8), (256, 8), (1000, 1)):
+            _check(entries, kv_heads, keys, 148)
+    drawn = random.Random(20240611)
+    for _ in range(5000):
+        _check(drawn.randint(1, 512), drawn.choice([1, 2, 3, 4, 8, 16]), drawn.randint(1, 300000),
+               drawn.choice([1, 8, 108, 132, 148, 160]))
+
+
+def test_short_histories_of_few_entries_are_cut_into_tiles_of_128_keys():
+    """Every block then asks for all its keys at once, before it waits for the kernel ahead."""
+    for entries in (1, 2, 8):
+        assert ops.decode_splits(entries, 2, 2048, 148) == (128, 16)
+    # many entries: fewer and longer splits, never more than sixteen blocks an SM
+    chunk, splits = ops.decode_splits(64, 2, 8192, 148)
+    assert chunk > 128 and 64 * 2 * splits <= 16 * 148
