@@ -13,7 +13,9 @@ def _check(entries, kv_heads, keys, sms):
     assert chunk >= 128 and chunk % 128 == 0, (entries, kv_heads, keys, sms, chunk)
     assert 1 <= splits <= 64, (entries, kv_heads, keys, sms, splits)        # the combine kernel holds at most 128
     assert chunk * splits >= keys, (entries, kv_heads, keys, sms, chunk, splits)
-    assert chunk * (splits - 1) < keys, "no split without keys for the longest history"
+    # splits past the longest history are allowed (their blocks leave at once), but never more
+    # than the next power of two of keys would need
+    assert chunk * (splits - 1) < 2 * max(keys, 128), (entries, kv_heads, keys, sms, chunk, splits)
     return chunk, splits
 
 
@@ -31,6 +33,8 @@ def test_short_histories_of_few_entries_are_cut_into_tiles_of_128_keys():
     """Every block then asks for all its keys at once, before it waits for the kernel ahead."""
     for entries in (1, 2, 8):
         assert ops.decode_splits(entries, 2, 2048, 148) == (128, 16)
-    # many entries: fewer and longer splits, never more than sixteen blocks an SM
+    assert ops.decode_splits(8, 2, 8192, 148) == (128, 64)
+    assert ops.decode_splits(8, 2, 9216, 148) == (256, 64)     # as for 16,384 keys
+    # many entries with long histories: fewer and longer splits, whole waves of three blocks an SM
     chunk, splits = ops.decode_splits(64, 2, 8192, 148)
-    assert chunk > 128 and 64 * 2 * splits <= 16 * 148
+    assert chunk > 128 and 64 * 2 * splits <= 2 * 3 * 148

@@ -46,6 +46,17 @@ def _round_up_pow2(value: int, least: int = 8) -> int:
     return out
 
 
+def _width_bucket(pages: int) -> int:
+    """The width a decode graph's block tables are rounded up to: a power of two up to 128
+    pages, eighths of an octave beyond (the cut of the keys for the split-key attention is
+    chosen for the graph's width, so a width far above the longest history cuts badly)."""
+    width = _round_up_pow2(pages)
+    if width <= 128:
+        return width
+    step = width // 16
+    return -(-pages // step) * step
+
+
 # Token counts a captured step is padded to.  Steps under a token budget are mostly full, so the
 # steps that matter hit a bucket exactly; in between at most a third of a step is padding.
 _TOKEN_BUCKETS = (8, 16, 32, 64, 96, 128, 192, 256, 384, 512, 768, 1024, 1536, 2048, 3072, 4096, 6144, 8192)
@@ -265,7 +276,7 @@ class ModelRunner:
         last = int(max(step.pos0))
         widths = []
         for g, page_size in enumerate(self._page_sizes):
-            widths.append(_round_up_pow2((last + page_size) // page_size))
+            widths.append(_width_bucket((last + page_size) // page_size))
         key = (bucket, tuple(widths))
         graph = self._graphs.get(key)
         if graph is not None and graph.stale():
@@ -291,7 +302,7 @@ class ModelRunner:
             return None
         bucket = _round_up_pow2(entries, 1)
         last = int(pos0.max())
-        widths = tuple(_round_up_pow2((last + page_size) // page_size) for page_size in self._page_sizes)
+        widths = tuple(_width_bucket((last + page_size) // page_size) for page_size in self._page_sizes)
         graph = self._graphs.get((bucket, widths))
         if graph is None or graph.stale():
             return None

@@ -8,6 +8,7 @@ compiler or a kernel that reports an error raises.
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 from typing import Optional
 
@@ -632,16 +633,61 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, 
     _check(fn(*pointers, *sizes, skip, _stream()), "attention_prefill")
 
 
+# The split-key kernel's blocks that an SM holds at once (its launch bounds and shared memory).
+DECODE_BLOCKS_PER_SM = 3
+# The cut by whole waves serves steps whose longest history is above DECODE_SHORT_HISTORY keys and
+# whose histories hold at least DECODE_LONG_WORK rows of keys per layer (entries x KV heads x keys):
+# launches of some 30 microseconds and more.
+DECODE_SHORT_HISTORY = 4096
+DECODE_LONG_WORK = 1 << 18
+
+
+@functools.lru_cache(maxsize=4096)
 def decode_splits(num_entries: int, num_kv_heads: int, max_keys: int, sm_count: int):
-    """How a decode step's keys are cut: (keys per split, splits).  A split is 128 keys (32
-    for each of a block's four warps), so that every block asks for all its keys at once and
-    the whole cache of the step is in flight together; only when that would make more than
-    64 splits, or more than sixteen blocks per SM, do splits grow."""
-    blocks = max(1, num_entries * num_kv_heads)
-    most = max(1, min(64, (16 * sm_count) // blocks))
-    chunk = max(128, -(-max_keys // most))
-    chunk = -(-chunk // 128) * 128
-    return chunk, max(1, -(-max_keys // chunk))
+    """How a decode step's keys are cut: (keys per split, splits).  A block is an (entry, KV
+    head, split) and folds its split 128 keys at a time, 32 for each of its four warps.
+
+    Short launches: a split is 128 keys, so that every block asks for all its keys at once,
+    before it waits for the kernel ahead, and the whole cache of the step is in flight together;
+    only when that would make more than 64 splits, or more than sixteen blocks per SM, do splits
+    grow.  Long histories of many entries: the kernel runs for tens of microseconds and what
+    counts is that its blocks fill whole waves (the GPU holds three blocks an SM at once; 512 blocks take as long
+    as 888, measured), so the cut is the one a small model of the launch's time likes best: per
+    wave a fixed cost and a cost per 128 keys, which is the memory's when the wave is full and a
+    block's own latency when it is not; the constants are fitted to launches timed at batch 1 to
+    64 and 8,192 to 32,768 keys."""
+    base = max(1, num_entries * num_kv_heads)
+    if max_keys <= DECODE_SHORT_HISTORY or base * max_keys < DECODE_LONG_WORK:
+        # For the next power of two of keys, the splits past the longest history included (their
+        # blocks leave at once): with a power of two of splits every row's (max, sum) pairs start
+        # on whole sectors of the scratch, and the step is 0.1 ms faster at batch 8 and 8,192 keys
+        # than with the 36 splits that hold keys.
+        bound = 128
+        while bound < max_keys:
+            bound *= 2
+        most = max(1, min(64, (16 * sm_count) // base))
+        chunk = max(128, -(-bound // most))
+        chunk = -(-chunk // 128) * 128
+        return chunk, max(1, -(-bound // chunk))
+    slots = DECODE_BLOCKS_PER_SM * max(1, sm_count)
+    fixed, per_tile_full, per_tile_alone, combine, per_split = 2.7, 3.7, 2.75, 3.0, 0.02   # microseconds
+    best = None
+    seen = set()
+    for wanted in range(1, 65):
+        chunk = -(-(-(-max_keys // wanted)) // 128) * 128
+        if chunk in seen:
+            continue
+        seen.add(chunk)
+        splits = max(1, -(-max_keys // chunk))
+        tiles = chunk / 128
+        full, rest = divmod(base * splits, slots)
+        time = full * (fixed + tiles * per_tile_full)
+        if rest:
+            time += fixed + tiles * max(per_tile_full * rest / slots, per_tile_alone)
+        time += combine + per_split * splits
+        if best is None or time < best[0] - 1e-9:
+            best = (time, chunk, splits)
+    return best[1], best[2]
 
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, *,
