@@ -285,6 +285,9 @@ class ModelRunner:
             graph = _DecodeGraph(self, bucket, widths)
             if graph.fill(step) < 0:
                 return None
+            self._graphs.pop(key, None)
+            if len(self._graphs) >= self.max_kept_graphs:   # the oldest goes (widths come in eighths of an octave)
+                self._graphs.pop(next(iter(self._graphs)))
             self._graphs[key] = graph
             graph.capture()
         elif graph.fill(step) < 0:
