@@ -38,3 +38,19 @@ def test_short_histories_of_few_entries_are_cut_into_tiles_of_128_keys():
     # many entries with long histories: fewer and longer splits, whole waves of three blocks an SM
     chunk, splits = ops.decode_splits(64, 2, 8192, 148)
     assert chunk > 128 and 64 * 2 * splits <= 2 * 3 * 148
+
+
+def test_the_width_classes_of_decode_graphs_hold_the_table_and_little_more():
+    """vipera.rs_b200/engine/runner.py, _width_bucket: a class is never narrower than the table,
+    never shrinks as the table grows, and above 128 pages is at most an eighth of its octave
+    wider than the table."""
+    from vipera_rs_b200.engine.runner import _width_bucket
+
+    before = 0
+    for pages in range(1, 70000):
+        width = _width_bucket(pages)
+        assert width >= pages and width >= before
+        if pages > 128:
+            assert width - pages < max(16, pages // 8 + 1), (pages, width)
+        before = width
+    assert [_width_bucket(p) for p in (1, 8, 9, 128, 129, 133, 517, 2049)] == [8, 8, 16, 128, 144, 144, 576, 2304]
